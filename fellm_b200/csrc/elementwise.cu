@@ -1,0 +1,99 @@
+// Embedding gather, RMSNorm, SiLU-gate, row gather.
+//
+// FeLLM counterparts (plugins/cuda_kernels/src/oxide_kernels.rs): embedding_bf16_rows (3140),
+// rmsnorm_group (165), silu_gate (67).  The residual stream is float32 in both engine dtypes;
+// norms read it and write the engine's activation dtype.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                                  float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+  int row = blockIdx.x;
+  int tok = tokens[row];
+  float* o = out + (size_t)row * d;
+  if (tok < 0 || tok >= vocab) {          // never read outside the table: record and write zeros
+    if (threadIdx.x == 0 && status) atomicExch(status, 1);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const TW* src = table + (size_t)tok * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f(src[i]);
+}
+
+FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_is_bf16, float* out,
+                               int rows, int d, int vocab, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!tokens || !table || !out) return FELLM_ERR_ARG;
+  int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
+  if (table_is_bf16)
+    embed_rows_kernel<bf16><<<rows, threads, 0, stream>>>(tokens, (const bf16*)table, out, d, vocab, status);
+  else
+    embed_rows_kernel<float><<<rows, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab, status);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w, product order (x*scale)*w, all in float32.
+// One block per output row; the reduction order depends on d and the block size only, so a row's
+// result does not depend on which other rows are in the batch.
+template <typename TO, int THREADS>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+  __shared__ float partial[THREADS / 32];
+  __shared__ float scale_s;
+  int orow = blockIdx.x;
+  int irow = rows ? rows[orow] : orow;
+  const float* xr = x + (size_t)irow * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += THREADS) { float v = xr[i]; ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < THREADS / 32; ++i) t += partial[i];
+    scale_s = 1.0f / sqrtf(t / (float)d + eps);
+  }
+  __syncthreads();
+  float scale = scale_s;
+  TO* o = out + (size_t)orow * d;
+  for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_f<TO>((xr[i] * scale) * w[i]);
+}
+
+FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_is_bf16,
+                            const int* rows, int n_out_rows, int d, float eps, cudaStream_t stream) {
+  if (n_out_rows <= 0) return 0;
+  if (!x || !w || !out) return FELLM_ERR_ARG;
+  if (d >= 512) {
+    if (out_is_bf16) rmsnorm_kernel<bf16, 256><<<n_out_rows, 256, 0, stream>>>(x, w, (bf16*)out, rows, d, eps);
+    else rmsnorm_kernel<float, 256><<<n_out_rows, 256, 0, stream>>>(x, w, (float*)out, rows, d, eps);
+  } else {
+    if (out_is_bf16) rmsnorm_kernel<bf16, 64><<<n_out_rows, 64, 0, stream>>>(x, w, (bf16*)out, rows, d, eps);
+    else rmsnorm_kernel<float, 64><<<n_out_rows, 64, 0, stream>>>(x, w, (float*)out, rows, d, eps);
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- SiLU gate
+// in [T, 2F]: gate in columns [0,F), up in [F,2F); out [T,F] = gate/(1+exp(-gate)) * up.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int F) {
+  size_t n = (size_t)rows * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t r = i / F; int c = (int)(i - r * F);
+    float g = to_f(gu[r * 2 * F + c]);
+    float u = to_f(gu[r * 2 * F + F + c]);
+    out[i] = from_f<T>((g / (1.0f + expf(-g))) * u);
+  }
+}
+
+FELLM_API int fellm_silu_mul(const void* gu, void* out, int is_bf16, int rows, int F, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  size_t n = (size_t)rows * F;
+  int blocks = (int)((n + 255) / 256); if (blocks > 148 * 16) blocks = 148 * 16;
+  if (is_bf16) silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, F);
+  else silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, rows, F);
+  return launch_status();
+}

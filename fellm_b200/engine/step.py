@@ -1,0 +1,178 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+FeLLM's `Engine::step_batch(sequences, conv_states, rows: [BatchToken{sequence, token, position,
+compute_logits}])` takes one entry per token row and, for the hybrid model, at most one row per
+sequence (crates/fellm-runtime/src/engine.rs:461-470,1805-1818,2801-2996;
+crates/fellm-runtime/src/scheduler.rs:423-427).  Here an item is a request with n >= 1 next
+tokens: a portion of its prompt, cut anywhere, or one decoded token; all items of a step run as
+one batch.  Positions are absolute and continue the request's length in the cache
+(engine.rs:2848-2873: position = RoPE position = cache row; visible length = position + 1).
+
+Per step, the host fills ONE pinned int32 buffer with every index array the kernels need and
+copies it once; the logits come back for the wanted rows only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..config.errors import CacheError, FellmError, KernelError
+
+
+@dataclass
+class StepItem:
+    """`want`: indices into `tokens` whose logits are asked for (may be empty)."""
+    req: object
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+class StepContext:
+    """Who is in the batch and where: device int32 arrays, all views of one buffer.
+
+    tokens[T], positions[T] (absolute), row_item[T] (index of the row's item), row_slot[T] (its
+    request's slot: the row of block tables and state arrays), item_start[n_items+1] (row offsets),
+    item_slot[n_items], item_len[n_items] (request length after this step), logit_rows[W].
+    """
+    __slots__ = ("tokens", "positions", "row_item", "row_slot", "item_start", "item_slot", "item_len",
+                 "logit_rows", "n_rows", "n_items", "n_logit_rows", "all_single", "max_item_rows",
+                 "max_len", "status", "host")
+
+
+class StepBuffers:
+    """Pinned host staging and its device twin, sized for the largest step."""
+
+    def __init__(self, max_rows: int, max_items: int, device):
+        self.max_rows, self.max_items = max_rows, max_items
+        self.capacity = 5 * max_rows + 3 * max_items + 16
+        self.on_gpu = torch.cuda.is_available() and str(device).startswith("cuda")
+        # The copy engine reads a pinned buffer when the copy runs, not when it is queued: a ring
+        # of staging buffers, each guarded by an event, keeps a later step from overwriting what an
+        # earlier, still queued copy has yet to read.
+        self.ring = [torch.zeros(self.capacity, dtype=torch.int32, pin_memory=self.on_gpu) for _ in range(4)]
+        self.ring_np = [b.numpy() for b in self.ring]
+        self.ring_events = [torch.cuda.Event() if self.on_gpu else None for _ in self.ring]
+        self.ring_used = [False] * len(self.ring)
+        self.ring_next = 0
+        self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def fill(self, tokens, positions, row_item, row_slot, item_start, item_slot, item_len, logit_rows,
+             max_item_rows, max_len) -> StepContext:
+        T, n, W = len(tokens), len(item_slot), len(logit_rows)
+        if T > self.max_rows or n > self.max_items:
+            raise FellmError(f"a step of {T} rows / {n} items exceeds the engine's buffers "
+                             f"({self.max_rows} rows / {self.max_items} items)")
+        ctx = StepContext()
+        off = 0
+        k = self.ring_next
+        self.ring_next = (k + 1) % len(self.ring)
+        if self.on_gpu and self.ring_used[k]:
+            self.ring_events[k].synchronize()
+        h, d = self.ring_np[k], self.dev
+
+        def put(name, arr, count):
+            nonlocal off
+            h[off:off + count] = arr
+            setattr(ctx, name, d[off:off + count])
+            off += count
+        put("tokens", tokens, T)
+        put("positions", positions, T)
+        put("row_item", row_item, T)
+        put("row_slot", row_slot, T)
+        put("item_start", item_start, n + 1)
+        put("item_slot", item_slot, n)
+        put("item_len", item_len, n)
+        put("logit_rows", logit_rows, W)
+        d[:off].copy_(self.ring[k][:off], non_blocking=True)
+        if self.on_gpu:
+            self.ring_events[k].record()
+            self.ring_used[k] = True
+        ctx.n_rows, ctx.n_items, ctx.n_logit_rows = T, n, W
+        ctx.all_single = (T == n)
+        ctx.max_item_rows, ctx.max_len = max_item_rows, max_len
+        ctx.status = self.status
+        ctx.host = None
+        return ctx
+
+
+class Stepper:
+    """Owns the model, the cache manager and the step buffers; `step()` is the step function."""
+
+    def __init__(self, model, cache, *, max_rows: int, max_items: int, device):
+        self.model, self.cache, self.device = model, cache, device
+        self.buffers = StepBuffers(max_rows, max_items, device)
+        self.vocab = model.spec.vocab_size
+        self.steps_run = 0
+        self.kernel_launch_hook = None
+
+    def step(self, items: List[StepItem]) -> torch.Tensor:
+        """Runs exactly the given tokens as one batch and returns float32 logits
+        [sum(len(want)), vocab] on the device, in the order of the items and of each `want`.
+        Nothing is changed when the step cannot be placed (unknown request, no pages)."""
+        if not items:
+            raise FellmError("a step needs at least one item")
+        cache = self.cache
+        seen = set()
+        for it in items:
+            if it.req in seen:
+                raise FellmError(f"request {it.req!r} appears twice in one step")
+            seen.add(it.req)
+            if not cache.has(it.req):
+                raise CacheError(f"unknown request {it.req!r}")
+            if len(it.tokens) < 1:
+                raise FellmError(f"request {it.req!r} brings no tokens")
+            for w in it.want:
+                if not 0 <= w < len(it.tokens):
+                    raise FellmError(f"request {it.req!r}: wanted place {w} is outside its {len(it.tokens)} tokens")
+        asks = [(it.req, len(it.tokens)) for it in items]
+        for req, n in asks:
+            if cache.length(req) + n > cache.n_ctx:
+                raise CacheError(f"request {req!r} would reach {cache.length(req) + n} tokens; "
+                                 f"the context holds {cache.n_ctx}")
+        if not cache.can_reserve(asks):
+            raise CacheError("out of cache pages for this step")
+
+        tok_parts, pos_parts, ri_parts, rs_parts, logit_rows = [], [], [], [], []
+        item_start, item_slot, item_len = [0], [], []
+        max_rows, max_len = 0, 0
+        for i, it in enumerate(items):
+            n = len(it.tokens)
+            t = np.asarray(it.tokens, dtype=np.int64)
+            if t.min() < 0 or t.max() >= self.vocab:
+                raise FellmError(f"request {it.req!r}: token id outside the vocabulary of {self.vocab}")
+            p0, slot = cache.length(it.req), cache.slot(it.req)
+            tok_parts.append(t)
+            pos_parts.append(np.arange(p0, p0 + n))
+            ri_parts.append(np.full(n, i))
+            rs_parts.append(np.full(n, slot))
+            base = item_start[-1]
+            logit_rows += [base + w for w in it.want]
+            item_start.append(base + n)
+            item_slot.append(slot)
+            item_len.append(p0 + n)
+            max_rows, max_len = max(max_rows, n), max(max_len, p0 + n)
+        for req, n in asks:
+            cache.reserve(req, n)
+        ctx = self.buffers.fill(np.concatenate(tok_parts), np.concatenate(pos_parts), np.concatenate(ri_parts),
+                                np.concatenate(rs_parts), item_start, item_slot, item_len, logit_rows,
+                                max_rows, max_len)
+        cache.flush()
+        logits = self.model.forward(ctx, cache.views(ctx.item_slot))
+        for req, n in asks:
+            cache.advance(req, n)
+        self.steps_run += 1
+        return logits
+
+    def check_status(self):
+        """Reads the device status word (synchronises).  Kernels set it instead of faulting:
+        1 = a token id outside the embedding table, 2 = a cache write with no page mapped."""
+        code = int(self.buffers.status.item())
+        if code:
+            self.buffers.status.zero_()
+            what = {1: "a token id outside the embedding table",
+                    2: "a cache write to a position with no page"}.get(code, f"code {code}")
+            raise KernelError(f"a kernel reported: {what}")

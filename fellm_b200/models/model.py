@@ -1,0 +1,110 @@
+"""A model assembled from a ModelSpec: embedding, blocks of (norm, mixer, norm, feed-forward),
+final norm and head, run in the order the spec's schedule gives.
+
+The forward pass here is the body of the step function: it runs exactly the rows of one
+StepContext, reads and writes the caches through the views it is given, and computes the final
+norm and the head only for the rows whose logits are wanted (FeLLM skips final_norm + lm_head for
+mid-prompt tokens the same way, crates/fellm-runtime/src/compiled.rs:425-434).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.errors import ConfigError
+from ..parts.base import ParamDecl, build_part
+from ..parts.spec import ModelSpec
+
+
+class Block:
+    """One layer's parts and their arrangement."""
+
+    def __init__(self, spec, dtype: str):
+        if spec.arrangement != "prenorm":
+            raise ConfigError(f"unknown block arrangement {spec.arrangement!r}")
+        self.spec = spec
+        self.norm1 = build_part("norm", spec.norm1, dtype)
+        self.mixer = build_part("mixer", spec.mixer, dtype)
+        self.norm2 = build_part("norm", spec.norm2, dtype)
+        self.ffn = build_part("feed_forward", spec.ffn, dtype)
+
+    def parts(self):
+        return [self.norm1, self.mixer, self.norm2, self.ffn]
+
+    def forward(self, x, ctx, cache, act_dtype, reads_only=False):
+        """x: float32 residual stream [T, d], updated in place:
+        x += mixer(norm1(x)); x += ffn(norm2(x))."""
+        self.mixer.forward(self.norm1.forward(x, act_dtype), ctx, cache, x, reads_only=reads_only)
+        self.ffn.forward(self.norm2.forward(x, act_dtype), ctx, x)
+        return x
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype: str):
+        self.spec, self.dtype = spec, dtype
+        self.act_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        self.embedding = build_part("embedding", spec.embedding, dtype)
+        self.blocks: List[Block] = [Block(ls, dtype) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, dtype)
+        self.head = build_part("head", spec.head, dtype)
+        self.schedule = list(spec.schedule)
+
+    # ---- parameters
+    def all_parts(self):
+        parts = [self.embedding]
+        for b in self.blocks:
+            parts += b.parts()
+        return parts + [self.final_norm, self.head]
+
+    def param_table(self) -> Dict[str, tuple]:
+        """{tensor name in the file: (part, local name, ParamDecl)} over all parts."""
+        table = {}
+        for part in self.all_parts():
+            for local, decl in part.param_decls().items():
+                name = part.spec.tensor_name(local)
+                if name in table:
+                    raise ConfigError(f"two parts claim the tensor {name}")
+                table[name] = (part, local, decl)
+        return table
+
+    def bind(self, tensors: Dict[str, torch.Tensor]):
+        """tensors: {file name: tensor already on the device, in its kept dtype}."""
+        per_part: Dict[int, dict] = {}
+        for name, (part, local, _) in self.param_table().items():
+            per_part.setdefault(id(part), {})[local] = tensors[name]
+        for part in self.all_parts():
+            if part is self.head and getattr(part, "tied", False):
+                continue
+            part.bind(per_part.get(id(part), {}))
+        if getattr(self.head, "tied", False):
+            self.head.bind({"weight": self.embedding.w["weight"]})
+
+    def kernel_modules(self):
+        mods = []
+        for part in self.all_parts():
+            mods += part.kernel_modules(self.dtype)
+        return mods
+
+    def cache_needs(self):
+        """Per schedule entry: the mixer's cache need, or None when the entry reads another's."""
+        return [None if run.cache_of is not None else self.blocks[run.layer].mixer.cache_need()
+                for run in self.schedule]
+
+    # ---- the step's body
+    def forward(self, ctx, caches) -> torch.Tensor:
+        """ctx: StepContext; caches[n]: the cache view of schedule entry n.  Returns float32
+        logits [len(ctx.logit_rows), vocab] (an empty tensor when none are wanted)."""
+        x = self.embedding.forward(ctx.tokens, ctx.status)
+        for n, run in enumerate(self.schedule):
+            src = n if run.cache_of is None else run.cache_of
+            self.blocks[run.layer].forward(x, ctx, caches[src], self.act_dtype,
+                                           reads_only=run.cache_of is not None)
+        if ctx.n_logit_rows == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
+        xf = self.final_norm.forward(x, self.act_dtype, rows=ctx.logit_rows)
+        return self.head.forward(xf)
+
+
+def build_model(spec: ModelSpec, dtype: str) -> Model:
+    return Model(spec, dtype)

@@ -1,0 +1,250 @@
+"""Python faces of the CUDA launchers in fellm_b200/csrc: they check devices, dtypes, shapes and
+the sizes a kernel takes, pass raw pointers and the current stream, and turn a launcher's return
+code into a KernelError.  There is no CPU path and no library fallback behind any of them.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .config.errors import KernelError
+from .csrc import jit
+
+_c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+_fns = {}
+
+
+def _fn(module: str, name: str, argtypes, defines=None):
+    key = (module, name, jit._defines_key(defines))
+    f = _fns.get(key)
+    if f is None:
+        lib = jit.load_module(module, defines)
+        try:
+            f = getattr(lib, name)
+        except AttributeError:
+            raise KernelError(f"kernel library {module} has no entry point {name}") from None
+        f.argtypes = list(argtypes)
+        f.restype = _c_int
+        _fns[key] = f
+    return f
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: a size the kernel does not take")
+    if code == -2:
+        raise KernelError(f"{what}: bad arguments (null pointer or mismatched dtypes)")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _dev(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("fellm_b200 kernels run on CUDA tensors only (there is no CPU path)")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _is_bf16(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise KernelError(f"dtype {t.dtype} is not one the kernels take (bfloat16 or float32)")
+
+
+def _i32(t, name):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ------------------------------------------------------------------------------ elementwise
+
+def embed_rows(tokens, table, out, status=None):
+    """out[t, :] = float32(table[tokens[t], :]).  A token outside the table writes zeros and sets
+    status to 1 (the host checks ids first; the kernel never reads out of bounds)."""
+    _dev(tokens, table, out)
+    _i32(tokens, "tokens")
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
+    assert table.shape[1] == d and tokens.numel() == T
+    f = _fn("elementwise", "fellm_embed_rows", [_c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_p(tokens), _p(table), _is_bf16(table), _p(out), T, d, table.shape[0], _p(status), _stream()),
+           "embed_rows")
+    return out
+
+
+def rmsnorm(x, w, eps: float, out_dtype, rows=None, out=None):
+    """x float32 [T, d], w float32 [d] -> [T or len(rows), d] in out_dtype."""
+    _dev(x, w, rows)
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and x.is_contiguous()
+    d = x.shape[-1]
+    assert w.numel() == d
+    n = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _i32(rows, "rows")
+    if out is None:
+        out = torch.empty((n, d), dtype=out_dtype, device=x.device)
+    f = _fn("elementwise", "fellm_rmsnorm", [_c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_f, _c_p])
+    _check(f(_p(x), _p(w), _p(out), _is_bf16(out), _p(rows), n, d, float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def silu_mul(gu, out=None):
+    """gu [T, 2F] (gate | up) -> [T, F] = silu(gate) * up."""
+    _dev(gu)
+    assert gu.is_contiguous() and gu.shape[1] % 2 == 0
+    T, F = gu.shape[0], gu.shape[1] // 2
+    if out is None:
+        out = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    f = _fn("elementwise", "fellm_silu_mul", [_c_p, _c_p, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(gu), _p(out), _is_bf16(gu), T, F, _stream()), "silu_mul")
+    return out
+
+
+# ------------------------------------------------------------------------------ matrix products
+
+def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
+    """out[M, N] = a[M, K] @ w[N, K]^T (+ bias[N]) with float32 FMA on CUDA cores; with
+    accumulate=True, out (float32) += that.  Any mix of bfloat16/float32 a and w."""
+    _dev(a, w, bias, out)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: a is [{M},{K}] but w is {list(w.shape)}")
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    if _is_bf16(out) and not _is_bf16(a):
+        raise KernelError("gemm_simt: float32 activations do not round down to a bfloat16 result")
+    f = _fn("gemm_simt", "fellm_gemm_simt",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_p])
+    _check(f(_p(a), _is_bf16(a), _p(w), _is_bf16(w), _p(bias), _p(out), _is_bf16(out), M, N, K,
+             a.stride(0), w.stride(0), out.stride(0), int(accumulate), _stream()), "gemm_simt")
+    return out
+
+
+# ------------------------------------------------------------------------------ short convolution
+
+MAX_CONV_TAPS = 8
+
+
+def shortconv(bcx, w, conv_bias, state, item_slot, item_start, row_item, n_items, all_single, out=None):
+    """bcx [T, 3d] (B | C | X), w float32 [d, Lc], state float32 [slots, Lc-1, d] (a view of one
+    layer's slots; slot stride may be larger than (Lc-1)*d).  Returns y [T, d] = C * conv(B*X) and
+    advances each item's state slot."""
+    _dev(bcx, w, conv_bias, state, item_slot, item_start, row_item)
+    T = bcx.shape[0]
+    d, Lc = w.shape
+    if not 2 <= Lc <= MAX_CONV_TAPS:
+        raise KernelError(f"shortconv: conv_L_cache {Lc} is outside the kernel's range 2..{MAX_CONV_TAPS}")
+    assert bcx.shape[1] == 3 * d and bcx.is_contiguous() and w.dtype == torch.float32 and w.is_contiguous()
+    assert state.dtype == torch.float32 and state.shape[1:] == (Lc - 1, d)
+    assert state.stride(1) == d and state.stride(2) == 1
+    for t, nm in ((item_slot, "item_slot"), (item_start, "item_start"), (row_item, "row_item")):
+        _i32(t, nm)
+    if out is None:
+        out = torch.empty((T, d), dtype=bcx.dtype, device=bcx.device)
+    f = _fn("shortconv", "fellm_shortconv",
+            [_c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_p])
+    _check(f(_p(bcx), _is_bf16(bcx), _p(w), _p(conv_bias), _p(state), state.stride(0), _p(item_slot),
+             _p(item_start), _p(row_item), _p(out), T, n_items, d, Lc, int(all_single), _stream()),
+           "shortconv")
+    return out
+
+
+# ------------------------------------------------------------------------------ attention
+
+PAIRINGS = {"adjacent": 0, "split_half": 1}
+
+
+def qk_rope_write(qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, pool, layer,
+                  page_tokens, H, G, hd, write_kv=True, status=None, q_out=None):
+    """qkv [T, (H+2G)*hd] -> q_out [T, H, hd] (per-head RMSNorm, rotary), and k (normed, rotated)
+    and v written to pool[page, layer, 0/1, g, slot, :].  q_w/k_w None: no QK norm; inv_freq None:
+    no rotation.  pool: [pages, layers, 2, G, page_tokens, hd]; block_table [slots, width] is indexed
+    by row_slot[t], the slot of the request row t belongs to."""
+    _dev(qkv, q_w, k_w, inv_freq, positions, row_slot, block_table, pool)
+    T = qkv.shape[0]
+    if hd % 2:
+        raise KernelError(f"attention: head_dim {hd} must be even")
+    assert qkv.is_contiguous() and qkv.shape[1] == (H + 2 * G) * hd
+    if write_kv:
+        assert pool.is_contiguous() and pool.dtype == qkv.dtype
+        assert pool.shape[2:] == (2, G, page_tokens, hd), (pool.shape, G, page_tokens, hd)
+        _i32(block_table, "block_table")
+    _i32(positions, "positions"), _i32(row_slot, "row_slot")
+    if q_out is None:
+        q_out = torch.empty((T, H, hd), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("qk_rope_write", "fellm_qk_rope_write",
+            [_c_p, _c_int, _c_p, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int,
+             _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+    _check(f(_p(qkv), _is_bf16(qkv), _p(q_w), _p(k_w), float(eps), _p(inv_freq), PAIRINGS[pairing],
+             _p(positions), _p(row_slot), _p(block_table) if write_kv else None,
+             block_table.shape[1] if write_kv else 0, _p(pool) if write_kv else None,
+             _is_bf16(pool) if write_kv else _is_bf16(qkv), layer, pool.shape[1] if write_kv else 1,
+             page_tokens, _p(q_out), T, H, G, hd, int(write_kv), _p(status), _stream()), "qk_rope_write")
+    return q_out
+
+
+def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale, window=None, out=None):
+    """q [T, H, hd]; pool [pages, layers, 2, G, page_tokens, hd].  Row t attends to the cache
+    positions 0..positions[t] (or the last `window` of them) of its item.  Returns [T, H*hd]."""
+    _dev(q, pool, block_table, positions, row_slot)
+    T, H, hd = q.shape
+    G, page_tokens = pool.shape[3], pool.shape[4]
+    if hd > 256:
+        raise KernelError(f"attention: head_dim {hd} is above the kernel's maximum 256")
+    if H % G:
+        raise KernelError(f"attention: {H} heads are not a multiple of {G} kv heads")
+    assert q.is_contiguous() and pool.is_contiguous() and pool.shape[5] == hd
+    _i32(block_table, "block_table"), _i32(positions, "positions"), _i32(row_slot, "row_slot")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    f = _fn("attention_simt", "fellm_paged_attention_simt",
+            [_c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_f, _c_int, _c_p])
+    _check(f(_p(q), _is_bf16(q), _p(pool), _is_bf16(pool), _p(block_table), block_table.shape[1],
+             _p(positions), _p(row_slot), _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
+             float(scale), int(window or 0), _stream()), "paged_attention_simt")
+    return out
+
+
+# ------------------------------------------------------------------------------ dispatch
+
+def has_fast_gemm() -> bool:
+    return False
+
+
+def fast_gemm_modules():
+    return []
+
+
+def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False):
+    raise KernelError("no tensor-core product is built in")
+
+
+def attention_modules(dtype: str, head_dim: int):
+    return [("attention_simt", None)]
+
+
+def paged_attention(q, cache, ctx, scale, window=None):
+    """Attention of the step's rows over their items' cache pages; picks the kernel."""
+    return paged_attention_simt(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
+                                scale, window)

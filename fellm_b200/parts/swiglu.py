@@ -1,0 +1,35 @@
+"""SwiGLU feed-forward: f = W_down (silu(W_gate h) * (W_up h)), silu(g) = g/(1+exp(-g))
+(crates/fellm-model/src/graph.rs:2260-2287; crates/backend-cpu/src/kernels/swiglu.rs:4-16)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import FeedForward, ParamDecl, register_part
+from .linear import linear, linear_modules
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, *, dtype: str, size: int, ff: int):
+        super().__init__()
+        self.size, self.ff = int(size), int(ff)
+        self.decls = {"gate.weight": ParamDecl((self.ff, self.size)),
+                      "up.weight": ParamDecl((self.ff, self.size)),
+                      "down.weight": ParamDecl((self.size, self.ff))}
+
+    def prepare(self):
+        # one product for gate and up: [2F, d], gate rows first
+        g, u = self.w.pop("gate.weight"), self.w.pop("up.weight")
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w["gate_up.weight"] = torch.cat([g, u], dim=0).contiguous()
+
+    def forward(self, hn, ctx, out):
+        gu = linear(hn, self.w["gate_up.weight"])
+        z = ops.silu_mul(gu)
+        linear(z, self.w["down.weight"], out=out, accumulate=True)
+        return out
+
+    def kernel_modules(self, dtype):
+        return linear_modules(dtype) + [("elementwise", None)]
