@@ -22,6 +22,9 @@ from ..csrc import jit
 from ..models.model import build_model
 from ..weights.loader import bind_tensors, load_into
 from ..weights.random_init import random_tensors
+from ..sampling.params import GenParams, GenStats
+from ..sampling.sampler import Sampler
+from .scheduler import Scheduler
 from .step import StepItem, Stepper
 
 
@@ -62,6 +65,9 @@ class Engine:
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
                                device=self.device)
+        self.sampler = Sampler(spec.vocab_size, options.max_requests, options.max_requests, self.device)
+        self._tok_host = torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True)
+        self._scheduler: Optional[Scheduler] = None
 
     # ---- constructors
     @classmethod
@@ -116,3 +122,87 @@ class Engine:
 
     def check_status(self):
         self.stepper.check_status()
+
+    # ---- what the scheduler drives (its `backend`)
+    def start_request(self, slot: int, prompt, params: GenParams):
+        self.sampler.start_request(slot, prompt, params)
+
+    def run(self, items: List[StepItem], sample_rows) -> List[int]:
+        """One step and one sampling launch; returns the sampled tokens on the host.  The tokens
+        and the kernels' status word come back in one synchronisation."""
+        logits = self.stepper.step(items)
+        n = len(sample_rows)
+        if n:
+            toks = self.sampler.sample(logits, sample_rows)
+            self._tok_host[:n].copy_(toks, non_blocking=True)
+        self._tok_host[-1:].copy_(self.stepper.buffers.status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        if int(self._tok_host[-1]):
+            self.stepper.check_status()
+        return self._tok_host[:n].tolist()
+
+    # ---- generation
+    def scheduler(self) -> Scheduler:
+        """The engine's scheduler (made on first use): enqueue_ids / poll_event / step."""
+        if self._scheduler is None:
+            self._scheduler = Scheduler(self, self.options.n_batch, self.options.n_ubatch)
+        return self._scheduler
+
+    def generate(self, ids, params: Optional[GenParams] = None) -> "TokenStream":
+        """Token ids in, an iterator of generated token ids out (FeLLM: Engine::generate ->
+        TokenStream, engine.rs:947,3343-3538; text and tokenizer are outside this engine)."""
+        return TokenStream(self, [list(ids)], params or GenParams())
+
+    def generate_batch(self, prompts, params: Optional[GenParams] = None):
+        """Runs several prompts together; returns (list of generated id lists, list of GenStats)."""
+        sched = self.scheduler()
+        params = params or GenParams()
+        plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        rids = [sched.enqueue_ids(p, q) for p, q in zip(prompts, plist)]
+        out = {r: [] for r in rids}
+        stats = {}
+        while len(stats) < len(rids):
+            ev = sched.poll_event()
+            if ev is None:
+                break
+            if ev.req not in out:
+                continue
+            if ev.kind == "token":
+                out[ev.req].append(ev.token)
+            elif ev.kind == "done":
+                stats[ev.req] = ev.stats
+            elif ev.kind == "error":
+                raise KernelError(f"request {ev.req} failed: {ev.message}")
+        return [out[r] for r in rids], [stats.get(r) for r in rids]
+
+
+class TokenStream:
+    """Iterator over one request's generated tokens; finish_stats() after the last one."""
+
+    def __init__(self, engine: Engine, prompts, params: GenParams):
+        self.engine, self.sched = engine, engine.scheduler()
+        self.rid = self.sched.enqueue_ids(prompts[0], params)
+        self.stats: Optional[GenStats] = None
+        self._done = False
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> int:
+        while not self._done:
+            ev = self.sched.poll_event()
+            if ev is None:
+                break
+            if ev.req != self.rid:
+                continue
+            if ev.kind == "token":
+                return ev.token
+            self.stats, self._done = ev.stats, True
+            if ev.kind == "error":
+                raise KernelError(f"generation failed: {ev.message}")
+        raise StopIteration
+
+    def finish_stats(self) -> GenStats:
+        for _ in self:
+            pass
+        return self.stats

@@ -248,3 +248,31 @@ def paged_attention(q, cache, ctx, scale, window=None):
     """Attention of the step's rows over their items' cache pages; picks the kernel."""
     return paged_attention_simt(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                                 scale, window)
+
+
+# ------------------------------------------------------------------------------ sampling
+
+def sample_params_size() -> int:
+    f = _fn("sampling", "fellm_sample_params_size", [])
+    return int(f())
+
+
+def sample(logits, params_dev, counts, bias_tok, bias_val, out_tokens, out_probs=None, update_counts=True):
+    """One block per row of float32 logits [B, V]; params_dev: B packed records (see
+    fellm_b200/sampling/sampler.py).  counts [slots, V] int32 or None."""
+    _dev(logits, params_dev, counts, bias_tok, bias_val, out_tokens, out_probs)
+    B, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and out_tokens.dtype == torch.int32
+    if counts is not None:
+        assert counts.dtype == torch.int32 and counts.shape[1] == V and counts.is_contiguous()
+    f = _fn("sampling", "fellm_sample", [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p])
+    _check(f(_p(logits), B, V, _p(params_dev), _p(counts), _p(bias_tok), _p(bias_val), _p(out_tokens),
+             _p(out_probs), int(update_counts), _stream()), "sample")
+    return out_tokens
+
+
+def count_tokens(counts, slots, tokens):
+    _dev(counts, slots, tokens)
+    _i32(slots, "slots"), _i32(tokens, "tokens")
+    f = _fn("sampling", "fellm_count_tokens", [_c_p, _c_int, _c_p, _c_p, _c_int, _c_p])
+    _check(f(_p(counts), counts.shape[1], _p(slots), _p(tokens), tokens.numel(), _stream()), "count_tokens")

@@ -1,0 +1,2 @@
+from .params import GenParams, GenStats
+from .sampler import Sampler

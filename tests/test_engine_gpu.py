@@ -1,0 +1,94 @@
+"""The engine in process: long decoding, the first tokens of a sequence, greedy generation
+through the entry point, and the scheduler with a pool so small that it must preempt."""
+import pytest
+import torch
+
+import plain_lfm2
+import tiny
+from fellm_b200.engine import GenParams, StepItem
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding(name, dtype):
+    n = 330                                               # many pages of 16, far keys, every page edge
+    eng = tiny.make_engine(name, dtype)
+    toks, want = tiny.tokens(name, n, 40), tiny.plain_logits(name, n, 40)
+    eng.add_request("d")
+    rows = [eng.step([StepItem("d", toks[:10], list(range(10)))])]
+    for t in range(10, n):
+        rows.append(eng.step([StepItem("d", [toks[t]], [0])]))
+    eng.check_status()
+    ok, err, tol = tiny.close(torch.cat(rows), want, dtype)
+    assert ok, (err, tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens(name, dtype):
+    """Positions 0, 1, 2 ...: shorter than the conv history, one key only."""
+    eng = tiny.make_engine(name, dtype)
+    toks, want = tiny.tokens(name, 6, 41), tiny.plain_logits(name, 6, 41)
+    eng.add_request("one")                                # one by one from the first token
+    rows = [eng.step([StepItem("one", [t], [0])]) for t in toks]
+    ok, err, tol = tiny.close(torch.cat(rows), want, dtype)
+    assert ok, (err, tol)
+    eng.add_request("single")                             # a prompt of one token, alone
+    lg = eng.step([StepItem("single", toks[:1], [0])])
+    ok, err, tol = tiny.close(lg, want[:1], dtype)
+    assert ok, (err, tol)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(name, dtype):
+    cfg, w = tiny.plain_model(name)
+    eng = tiny.make_engine(name, dtype, n_ubatch=8, n_batch=16)
+    for length, seed in ((7, 50), (16, 51), (33, 52)):
+        prompt = tiny.tokens(name, length, seed)
+        want = plain_lfm2.greedy(cfg, w, prompt, 8)
+        stream = eng.generate(prompt, GenParams.greedy(8))
+        got = list(stream)
+        if dtype == "bfloat16" and got != want:
+            # a near-tie may flip under bfloat16: the first difference must be one
+            i = next(k for k in range(8) if got[k] != want[k])
+            lg = plain_lfm2.forward(cfg, w, prompt + want[:i])[-1]
+            assert abs(float(lg[got[i]] - lg[want[i]])) < 0.05 * float(lg.abs().max()), (got, want)
+        else:
+            assert got == want
+        st = stream.finish_stats()
+        assert st.prompt_tokens == length and st.predicted_tokens == 8 and st.finish_reason == "length"
+    assert eng.cache.free_pages() == eng.cache.n_pages
+
+
+def test_scheduler_preempts_on_a_small_pool_and_tokens_stay():
+    name = "B"
+    prompts = [tiny.tokens(name, n, 60 + i) for i, n in enumerate((40, 33, 25, 47))]
+    roomy = tiny.make_engine(name, "float32", n_ubatch=16, n_batch=48)
+    alone = [roomy.generate_batch([p], GenParams.greedy(24))[0][0] for p in prompts]
+    small = tiny.make_engine(name, "float32", max_tokens=160, n_ubatch=16, n_batch=48)     # 10 pages of 16
+    got, stats = small.generate_batch(prompts, GenParams.greedy(24))
+    sched = small.scheduler()
+    assert sched.counters["preempted"] > 0 or sched.counters["shrunk"] > 0
+    assert got == alone
+    assert all(s.finish_reason == "length" and s.predicted_tokens == 24 for s in stats)
+    small.cache.audit()
+    assert small.cache.free_pages() == small.cache.n_pages
+
+
+def test_step_refuses_what_it_cannot_place():
+    from fellm_b200.config import CacheError, FellmError
+    eng = tiny.make_engine("A", "float32", max_tokens=32)
+    eng.add_request("a")
+    with pytest.raises(CacheError, match="unknown request"):
+        eng.step([StepItem("nobody", [1], [0])])
+    with pytest.raises(FellmError, match="outside the vocabulary"):
+        eng.step([StepItem("a", [256], [0])])
+    with pytest.raises(CacheError, match="out of cache pages"):
+        eng.step([StepItem("a", tiny.tokens("A", 40, 1), [])])
+    assert eng.cache.length("a") == 0 and eng.cache.free_pages() == 2
+    eng.cache.audit()

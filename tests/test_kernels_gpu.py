@@ -1,0 +1,255 @@
+"""Each kernel alone against its plain reference, at sizes other than the tiny models'."""
+import math
+
+import pytest
+import torch
+
+import plain_lfm2 as P
+from fellm_b200 import ops
+from fellm_b200.config import KernelError
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(table_dtype):
+    table = torch.randn(1001, 200, device=DEV).to(table_dtype)
+    toks = i32([0, 1000, 17, 17, 512])
+    out = torch.empty(5, 200, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed_rows(toks, table, out, status)
+    assert torch.equal(out, table[toks.long()].float()) and int(status) == 0
+    ops.embed_rows(i32([3, 1001, -1, 4, 5]), table, out, status)       # outside the table: zeros + status
+    assert int(status) == 1 and float(out[1].abs().sum()) == 0 and torch.equal(out[0], table[3].float())
+
+
+@pytest.mark.parametrize("d", [48, 200, 1000, 1536])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(d, out_dtype):
+    x = torch.randn(37, d, device=DEV) * 3
+    w = torch.rand(d, device=DEV) + 0.5
+    got = ops.rmsnorm(x, w, 1e-6, out_dtype)
+    want = P.rmsnorm(x.cpu(), w.cpu(), 1e-6)
+    assert torch.allclose(got.float().cpu(), want, **tol(out_dtype))
+    rows = i32([36, 0, 5])
+    got = ops.rmsnorm(x, w, 1e-6, out_dtype, rows=rows)
+    assert torch.allclose(got.float().cpu(), want[[36, 0, 5]], **tol(out_dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    gu = (torch.randn(19, 2 * 328, device=DEV) * 2).to(dtype)
+    got = ops.silu_mul(gu)
+    g, u = gu.float().cpu()[:, :328], gu.float().cpu()[:, 328:]
+    assert torch.allclose(got.float().cpu(), (g / (1 + torch.exp(-g))) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 100, 72), (7, 515, 144), (64, 64, 16), (130, 200, 333), (257, 96, 1000)])
+@pytest.mark.parametrize("a_dt,w_dt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                       (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)])
+def test_gemm_simt(M, N, K, a_dt, w_dt):
+    a = torch.randn(M, K, device=DEV).to(a_dt)
+    w = (torch.randn(N, K, device=DEV) * 0.1).to(w_dt)
+    bias = torch.randn(N, device=DEV)
+    want = a.double().cpu() @ w.double().cpu().T
+    got = ops.gemm_simt(a, w, out_dtype=torch.float32)
+    assert torch.allclose(got.double().cpu(), want, rtol=1e-5, atol=1e-5 * math.sqrt(K))
+    got = ops.gemm_simt(a, w, bias, out_dtype=torch.float32)
+    assert torch.allclose(got.double().cpu(), want + bias.double().cpu(), rtol=1e-5, atol=1e-5 * math.sqrt(K))
+    res = torch.randn(M, N, device=DEV)
+    out = res.clone()
+    ops.gemm_simt(a, w, out=out, accumulate=True)
+    assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-5, atol=1e-5 * math.sqrt(K))
+    if a_dt == torch.bfloat16:
+        got = ops.gemm_simt(a, w)
+        assert got.dtype == torch.bfloat16 and torch.allclose(got.double().cpu(), want, rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    a = torch.randn(70, 200, device=DEV)
+    w = torch.randn(150, 200, device=DEV)
+    full = ops.gemm_simt(a, w)
+    one = ops.gemm_simt(a[33:34].contiguous(), w)
+    assert torch.equal(full[33:34], one)
+
+
+def conv_reference(bcx, w, bias, state):
+    """One request: state [Lc-1, d] then the portion's rows; returns y and the new state."""
+    T, d = bcx.shape[0], w.shape[0]
+    lc = w.shape[1]
+    B, C, X = bcx[:, :d], bcx[:, d:2 * d], bcx[:, 2 * d:]
+    hist = torch.cat([state, B * X], dim=0)
+    y = torch.empty(T, d)
+    for t in range(T):
+        conv = hist[t + lc - 1] * w[:, lc - 1]
+        for j in range(lc - 1):
+            conv = conv + hist[t + j] * w[:, j]
+        if bias is not None:
+            conv = conv + bias
+        y[t] = C[t] * conv
+    return y, hist[-(lc - 1):].clone()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d,lc,use_bias", [(40, 2, False), (200, 3, True), (136, 5, False), (72, 8, True)])
+def test_shortconv_portions_and_state(dtype, d, lc, use_bias):
+    torch.manual_seed(d + lc)
+    lens = [1, lc - 1, 1, 40, 2, 9]                       # shorter than the history, equal to it, longer
+    slots = [5, 0, 3, 1, 6, 2]
+    T = sum(lens)
+    bcx = torch.randn(T, 3 * d, device=DEV).to(dtype)
+    w = torch.randn(d, lc, device=DEV)
+    bias = torch.randn(d, device=DEV) if use_bias else None
+    state = torch.randn(8, 2, lc - 1, d, device=DEV)      # [slots, layers, Lc-1, d]; layer 1 is ours
+    before = state.clone()
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    row_item = [i for i, n in enumerate(lens) for _ in range(n)]
+    y = ops.shortconv(bcx, w, bias, state[:, 1], i32(slots), i32(starts), i32(row_item), len(lens), False)
+    for i, n in enumerate(lens):
+        ref_y, ref_s = conv_reference(bcx[starts[i]:starts[i + 1]].float().cpu(), w.cpu(),
+                                      None if bias is None else bias.cpu(), before[slots[i], 1].cpu())
+        assert torch.allclose(y[starts[i]:starts[i + 1]].float().cpu(), ref_y, **tol(dtype)), (i, n)
+        assert torch.allclose(state[slots[i], 1].cpu(), ref_s, rtol=1e-6, atol=1e-6), (i, n)
+    assert torch.equal(state[:, 0], before[:, 0]) and torch.equal(state[7], before[7])     # nothing else touched
+    # portions one token at a time give bit-equal outputs and state (float32)
+    if dtype == torch.float32:
+        st2 = before.clone()
+        y2 = torch.empty_like(y)
+        for i, n in enumerate(lens):
+            for t in range(n):
+                r = starts[i] + t
+                y2[r:r + 1] = ops.shortconv(bcx[r:r + 1].contiguous(), w, bias, st2[:, 1], i32([slots[i]]),
+                                            i32([0, 1]), i32([0]), 1, True)
+        assert torch.equal(y2, y) and torch.equal(st2, state)
+
+
+def test_shortconv_refuses_too_many_taps():
+    with pytest.raises(KernelError, match="outside the kernel's range"):
+        ops.shortconv(torch.zeros(1, 48, device=DEV), torch.zeros(16, 9, device=DEV), None,
+                      torch.zeros(1, 8, 16, device=DEV), i32([0]), i32([0, 1]), i32([0]), 1, True)
+
+
+def build_cache(keys, values, page_tokens, pages_order, dtype, n_layers=2, layer=1):
+    """keys/values [C, G, hd] of one request -> pool and block table with the given physical pages."""
+    C, G, hd = keys.shape
+    n_pages = max(pages_order) + 2
+    pool = torch.randn(n_pages, n_layers, 2, G, page_tokens, hd, device=DEV).to(dtype)     # garbage elsewhere
+    table = torch.full((3, len(pages_order) + 2), -1, dtype=torch.int32, device=DEV)
+    for p in range(C):
+        page = pages_order[p // page_tokens]
+        pool[page, layer, 0, :, p % page_tokens] = keys[p].to(dtype)
+        pool[page, layer, 1, :, p % page_tokens] = values[p].to(dtype)
+    table[1, :len(pages_order)] = i32(pages_order)
+    return pool, table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,page_tokens,window", [(6, 3, 16, 8, None), (8, 1, 80, 16, None), (4, 4, 128, 64, None),
+                                                       (5, 5, 48, 16, 37), (16, 2, 256, 32, 100)])
+def test_paged_attention_simt(dtype, H, G, hd, page_tokens, window):
+    torch.manual_seed(H * hd)
+    C = 300
+    keys, values = torch.randn(C, G, hd), torch.randn(C, G, hd)
+    n_pg = -(-C // page_tokens)
+    order = list(reversed(range(3, 3 + n_pg)))            # pages far from logical order
+    pool, table = build_cache(keys, values, page_tokens, order, dtype)
+    q_pos = [0, 1, page_tokens - 1, page_tokens, 2 * page_tokens - 1, 150, 298, 299]
+    q = torch.randn(len(q_pos), H, hd)
+    got = ops.paged_attention_simt(q.to(DEV).to(dtype), pool, table, i32(q_pos), i32([1] * len(q_pos)), 1,
+                                   hd ** -0.5, window)
+    kc, vc = keys.to(dtype).float(), values.to(dtype).float()
+    want = P.paged_attention_rows(q.to(dtype).float(), kc, vc, torch.tensor(q_pos), scale=hd ** -0.5, window=window)
+    assert torch.allclose(got.float().cpu().reshape(-1, H, hd), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far", [0, 63, 64, 255, 256, 511])
+def test_attention_finds_one_far_key(dtype, far):
+    """Among 600 keys one is made to stand out (a page's last slot, the next page's first, the very
+    first key): the output must be that key's value."""
+    H, G, hd, pt, C = 4, 2, 64, 64, 600
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    q = torch.randn(1, H, hd) * 0.1
+    direction = torch.randn(hd)
+    direction = direction / direction.norm()
+    keys[far] = direction * 30.0
+    q[0] = direction * 30.0
+    pool, table = build_cache(keys, values, pt, list(range(1, 1 + -(-C // pt))), dtype)
+    got = ops.paged_attention_simt(q.to(DEV).to(dtype), pool, table, i32([C - 1]), i32([1]), 1, hd ** -0.5)
+    got = got.float().cpu().reshape(H, hd)
+    for h in range(H):
+        assert torch.allclose(got[h], values[far, h // 2].to(dtype).float(), atol=2e-2), (far, h)
+
+
+@pytest.mark.parametrize("window", [16, 17, 64])
+def test_attention_window_edge(window):
+    """The key just outside the window must not count, the one just inside must."""
+    H, G, hd, pt, C = 2, 1, 32, 16, 200
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    d = torch.randn(hd); d = d / d.norm()
+    q = (d * 30.0).repeat(1, H, 1)
+    pos = C - 1
+    for edge, inside in ((pos - window, False), (pos - window + 1, True)):
+        k2 = keys.clone(); k2[edge] = d * 30.0
+        pool, table = build_cache(k2, values, pt, list(range(1, 1 + -(-C // pt))), torch.float32)
+        got = ops.paged_attention_simt(q.to(DEV), pool, table, i32([pos]), i32([1]), 1, hd ** -0.5, window)
+        hit = torch.allclose(got.cpu().reshape(H, hd)[0], values[edge, 0], atol=1e-3)
+        assert hit == inside, (window, edge, inside)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,pairing,qk_norm,rope", [(4, 2, 16, "adjacent", True, True), (6, 1, 48, "split_half", True, True),
+                                                         (3, 3, 80, "adjacent", False, True), (8, 2, 128, "split_half", True, False),
+                                                         (2, 2, 256, "split_half", True, True)])
+def test_qk_rope_write(dtype, H, G, hd, pairing, qk_norm, rope):
+    torch.manual_seed(hd)
+    T, pt, eps, theta = 11, 8, 1e-6, 10000.0
+    qkv = torch.randn(T, (H + 2 * G) * hd).to(dtype)
+    positions = [0, 1, 7, 8, 9, 100, 3000, 15, 16, 23, 24]
+    slots = [0, 0, 0, 0, 0, 1, 1, 2, 2, 2, 2]
+    qw, kw = torch.rand(hd) + 0.5, torch.rand(hd) + 0.5
+    inv = P.rope_inv_freq(theta, hd)
+    table = torch.full((3, 400), -1, dtype=torch.int32)
+    nxt = 1
+    for p, s in zip(positions, slots):
+        if table[s, p // pt] < 0:
+            table[s, p // pt] = nxt; nxt += 1
+    pool = torch.zeros(nxt + 1, 3, 2, G, pt, hd, device=DEV, dtype=dtype)
+    q = ops.qk_rope_write(qkv.to(DEV), qw.to(DEV) if qk_norm else None, kw.to(DEV) if qk_norm else None, eps,
+                          inv.to(DEV) if rope else None, pairing, i32(positions), i32(slots), table.to(DEV), pool, 2,
+                          pt, H, G, hd)
+    x = qkv.float()
+    qr, kr, vr = x[:, :H * hd].reshape(T, H, hd), x[:, H * hd:(H + G) * hd].reshape(T, G, hd), x[:, (H + G) * hd:].reshape(T, G, hd)
+    if qk_norm:
+        qr, kr = P.rmsnorm(qr, qw, eps), P.rmsnorm(kr, kw, eps)
+    if rope:
+        pos_t = torch.tensor(positions)
+        qr, kr = P.rope_apply(qr, pos_t, inv, pairing), P.rope_apply(kr, pos_t, inv, pairing)
+    t = tol(dtype)
+    assert torch.allclose(q.float().cpu(), qr, **t)
+    for r, (p, s) in enumerate(zip(positions, slots)):
+        page = int(table[s, p // pt])
+        assert torch.allclose(pool[page, 2, 0, :, p % pt].float().cpu(), kr[r], **t), r
+        assert torch.allclose(pool[page, 2, 1, :, p % pt].float().cpu(), vr[r], **t), r
+    assert float(pool[:, :2].abs().sum()) == 0 and float(pool[0].abs().sum()) == 0      # other layers, other pages
+
+
+def test_qk_rope_write_flags_a_missing_page():
+    H, G, hd = 2, 1, 16
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pool = torch.zeros(2, 1, 2, G, 8, hd, device=DEV)
+    table = torch.full((1, 4), -1, dtype=torch.int32, device=DEV)
+    ops.qk_rope_write(torch.randn(1, 4 * hd, device=DEV), None, None, 1e-6, None, "adjacent", i32([3]), i32([0]),
+                      table, pool, 0, 8, H, G, hd, status=status)
+    assert int(status) == 2 and float(pool.abs().sum()) == 0

@@ -1,0 +1,170 @@
+"""The scheduler's decisions, without a GPU: a fake backend stands in for the model (it returns
+a token that is a function of the request's whole history, so a recomputed request must reproduce
+its tokens) over the real cache manager on CPU tensors."""
+import pytest
+import torch
+
+from fellm_b200.cache import CacheManager
+from fellm_b200.config import SchedulerError
+from fellm_b200.engine.scheduler import Request, Scheduler, plan_batch
+from fellm_b200.parts.base import FixedState, PagedKV
+from fellm_b200.sampling import GenParams
+
+
+class FakeBackend:
+    def __init__(self, page_tokens=4, max_tokens=64, max_requests=4, n_ctx=64):
+        self.cache = CacheManager([FixedState((2, 4)), PagedKV(1, 16, None)], page_tokens=page_tokens,
+                                  max_tokens=max_tokens, max_requests=max_requests, n_ctx=n_ctx,
+                                  dtype=torch.float32, device="cpu")
+        self.n_ctx = n_ctx
+        self.history = {}          # request -> every token run so far
+        self.batches = []
+
+    def start_request(self, slot, prompt, params):
+        pass
+
+    def run(self, items, sample_rows):
+        self.batches.append([(it.req, len(it.tokens), bool(it.want)) for it in items])
+        out = []
+        for it in items:
+            if self.cache.length(it.req) == 0:
+                self.history[it.req] = []
+            self.cache.reserve(it.req, len(it.tokens))
+            self.cache.advance(it.req, len(it.tokens))
+            self.history[it.req] += list(it.tokens)
+            if it.want:
+                h = self.history[it.req]
+                out.append((sum(h) * 31 + len(h) * 7) % 97 + 3)
+        self.cache.audit()
+        assert len(out) == len(sample_rows)
+        return out
+
+
+def run_all(sched, limit=10_000):
+    toks, done = {}, {}
+    for _ in range(limit):
+        ev = sched.poll_event()
+        if ev is None:
+            break
+        if ev.kind == "token":
+            toks.setdefault(ev.req, []).append(ev.token)
+        elif ev.kind == "done":
+            done[ev.req] = ev.stats
+        else:
+            raise AssertionError(ev)
+    return toks, done
+
+
+def G(n, **kw):
+    return GenParams.greedy(n, **kw)
+
+
+def test_plan_decode_first_then_prefill_by_age_under_budget():
+    # scheduler.rs:930-1004: decode-first, then chunked prefill, never above the budget
+    def req(i, prompt, fed, pending=None, prio=0):
+        r = Request(i, list(range(prompt)), G(8, priority=prio), prompt, fed=fed, pending=pending)
+        r.seq = i
+        return r
+    running = [req(0, 40, 0), req(1, 10, 10, pending=5), req(2, 30, 8), req(3, 6, 6, pending=9)]
+    plan = plan_batch(running, n_batch=24, n_ubatch=16)
+    assert [(p.req.id, p.n_tokens, p.decode) for p in plan] == [(1, 1, True), (3, 1, True), (0, 16, False), (2, 6, False)]
+    assert sum(p.n_tokens for p in plan) == 24
+    plan = plan_batch(running, n_batch=1, n_ubatch=16)
+    assert [(p.req.id, p.decode) for p in plan] == [(1, True)]
+    running[2].params.priority = 5
+    plan = plan_batch(running, n_batch=24, n_ubatch=16)
+    assert [p.req.id for p in plan] == [1, 3, 2, 0]
+
+
+def test_portions_and_mixed_batches():
+    b = FakeBackend()
+    s = Scheduler(b, n_batch=12, n_ubatch=8)
+    r0 = s.enqueue_ids(list(range(1, 20)), G(3))
+    evs = s.step()
+    assert b.batches[-1] == [(r0, 8, False)]
+    r1 = s.enqueue_ids([5, 6, 7], G(2))
+    evs += s.step()
+    assert b.batches[-1] == [(r0, 8, False), (r1, 3, True)]         # budget 12: 8 + 3
+    evs += s.step()
+    assert b.batches[-1] == [(r1, 1, True), (r0, 3, True)]          # decode first, then the last portion
+    toks, done = run_all(s)
+    done.update({e.req: e.stats for e in evs if e.kind == "done"})
+    assert set(done) == {r0, r1} and done[r0].finish_reason == "length"
+    assert done[r0].prompt_tokens == 19 and done[r0].predicted_tokens == 3
+    assert b.cache.free_pages() == b.cache.n_pages and b.cache.slots.free_count == 4
+
+
+def test_finish_reasons_and_release():
+    b = FakeBackend(n_ctx=16)
+    s = Scheduler(b, 64, 64)
+    a = s.enqueue_ids([1, 2, 3], G(50))                    # runs into the end of the context
+    toks, done = run_all(s)
+    assert done[a].finish_reason == "length" and 3 + len(toks[a]) == 16
+    first = (sum([1, 2, 3]) * 31 + 3 * 7) % 97 + 3
+    c = s.enqueue_ids([1, 2, 3], G(50, stop_token_ids=(first,)))
+    toks, done = run_all(s)
+    assert done[c].finish_reason == "stop" and toks[c] == [first]
+    assert b.cache.free_pages() == b.cache.n_pages
+
+
+def test_refused_at_enqueue():
+    b = FakeBackend(page_tokens=4, max_tokens=16, n_ctx=64)
+    s = Scheduler(b, 64, 64)
+    with pytest.raises(SchedulerError, match="cache pages by itself"):
+        s.enqueue_ids(list(range(10)), G(20))
+    with pytest.raises(SchedulerError, match="does not fit the context"):
+        s.enqueue_ids(list(range(64)), G(1))
+    with pytest.raises(SchedulerError, match="at least one"):
+        s.enqueue_ids([], G(1))
+
+
+def test_waits_for_a_slot_fifo():
+    b = FakeBackend(max_requests=2)
+    s = Scheduler(b, 64, 64)
+    ids = [s.enqueue_ids([1 + i, 2, 3], G(4)) for i in range(4)]
+    s.step()
+    assert [r.id for r in s.running] == ids[:2] and [r.id for r in s.waiting] == ids[2:]
+    toks, done = run_all(s)
+    assert set(done) == set(ids) and s.counters["admission_waits"] > 0
+
+
+def test_shrinks_portions_then_preempts_newest_and_tokens_do_not_change():
+    prompts = [[3 + i, 9, 4, 7, 1, 8] for i in range(3)]
+    alone = {}
+    for i, p in enumerate(prompts):                         # each request by itself, roomy pool
+        s = Scheduler(FakeBackend(max_tokens=64), 64, 64)
+        rid = s.enqueue_ids(p, G(14))
+        alone[i] = run_all(s)[0][rid]
+    b = FakeBackend(page_tokens=4, max_tokens=40, max_requests=4)   # 10 pages: 3 x 20 tokens do not fit
+    s = Scheduler(b, 64, 64)
+    ids = [s.enqueue_ids(p, G(14)) for p in prompts]
+    toks, done = run_all(s)
+    assert s.counters["preempted"] > 0
+    for i, rid in enumerate(ids):
+        assert toks[rid] == alone[i], f"request {i} changed under preemption"
+        assert done[rid].predicted_tokens == 14
+    assert b.cache.free_pages() == b.cache.n_pages
+
+
+def test_prefill_portion_shrinks_to_the_pages_left():
+    b = FakeBackend(page_tokens=4, max_tokens=24, max_requests=4)   # 6 pages
+    s = Scheduler(b, 64, 64)
+    r0 = s.enqueue_ids(list(range(1, 15)), G(2))            # 14 tokens -> 4 pages
+    evs = s.step()
+    r1 = s.enqueue_ids(list(range(1, 13)), G(2))            # wants 3 pages, 2 are free
+    evs += s.step()
+    assert (r1, 8, False) in b.batches[-1] and s.counters["shrunk"] == 1
+    toks, done = run_all(s)
+    done.update({e.req: e.stats for e in evs if e.kind == "done"})
+    assert set(done) == {r0, r1}
+
+
+def test_cancel():
+    b = FakeBackend()
+    s = Scheduler(b, 64, 64)
+    a = s.enqueue_ids([1, 2, 3], G(30))
+    w = s.enqueue_ids([4, 5], G(30))
+    s.step()
+    assert s.cancel(a) and s.cancel(w) and not s.cancel(99)
+    toks, done = run_all(s)
+    assert done[a].finish_reason == "cancelled" and b.cache.free_pages() == b.cache.n_pages
