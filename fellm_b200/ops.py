@@ -226,26 +226,143 @@ def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale
     return out
 
 
-# ------------------------------------------------------------------------------ dispatch
+# ------------------------------------------------------------------------------ tensor-core products
+
+_EPI_STORE, _EPI_ACC, _EPI_SWIGLU, _EPI_F32 = 0, 1, 2, 3
+SKINNY_MAX_ROWS = 64
+_GEMM_ARGS = [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
+
 
 def has_fast_gemm() -> bool:
-    return False
+    return True
 
 
 def fast_gemm_modules():
-    return []
+    return [("gemm_skinny", None), ("gemm_tiled", None)]
 
 
-def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False):
-    raise KernelError("no tensor-core product is built in")
+def fast_gemm_takes(x, w) -> bool:
+    """The tensor-core kernels read 16-byte vectors along K."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False):
+    """out = x[M,K] @ w[N,K]^T (+bias) on tensor cores, bfloat16 in, float32 sums.
+    accumulate: out (float32 [M,N]) += ; swiglu: w's rows are interleaved in blocks of 8 gate / 8 up
+    and out is bfloat16 [M, N/2] = silu(gate)*up; out_dtype float32: float32 store."""
+    _dev(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm: x is [{M},{K}] but w is {list(w.shape)}")
+    if not fast_gemm_takes(x, w):
+        raise KernelError(f"gemm_bf16: K={K} and the row strides must be multiples of 8 bfloat16 elements")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    if accumulate:
+        epi = _EPI_ACC
+        assert out is not None and out.dtype == torch.float32 and out.shape == (M, N)
+    elif swiglu:
+        epi = _EPI_SWIGLU
+        if N % 16:
+            raise KernelError(f"gemm_bf16: the gate/up matrix needs a multiple of 16 rows, got {N}")
+        if out is None:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
+    elif (out_dtype or (out.dtype if out is not None else x.dtype)) == torch.float32:
+        epi = _EPI_F32
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        epi = _EPI_STORE
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        assert out.dtype == torch.bfloat16
+    assert out.stride(1) == 1
+    if M == 0:
+        return out
+    mod, name = ("gemm_skinny", "fellm_gemm_skinny") if M <= SKINNY_MAX_ROWS else ("gemm_tiled", "fellm_gemm_tiled")
+    f = _fn(mod, name, _GEMM_ARGS)
+    _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()), name)
+    return out
+
+
+def interleave_gate_up(gate, up):
+    """[F,K] gate and up -> [2F,K] with rows in blocks of 16: 8 gate rows, then the 8 up rows of the
+    same features (what the SiLU(gate)*up epilogues expect).  F must be a multiple of 8."""
+    F, K = gate.shape
+    assert F % 8 == 0 and up.shape == gate.shape
+    return torch.stack([gate.reshape(F // 8, 8, K), up.reshape(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+# ------------------------------------------------------------------------------ attention dispatch
+
+_decode_scratch = {}
+
+
+def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_dim: int, max_splits: int):
+    """Scratch of the split-KV decode kernel: partial results of every (row, head, key range) and
+    one counter per (row, kv head).  Allocated before any CUDA graph is captured, grown never
+    during one."""
+    need = rows * heads * max_splits * (head_dim + 2)
+    cur = _decode_scratch.get(device)
+    if cur is None or cur[0].numel() < need or cur[1].numel() < rows * kv_heads:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("decode attention scratch must be reserved before graph capture")
+        scratch = torch.empty(max(need, cur[0].numel() if cur else 0), dtype=torch.float32, device=device)
+        counters = torch.zeros(max(rows * kv_heads, cur[1].numel() if cur else 0), dtype=torch.int32, device=device)
+        _decode_scratch[device] = (scratch, counters)
+    return _decode_scratch[device]
+
+
+DECODE_TARGET_CTAS = 148 * 4
+
+
+def decode_split(max_len: int, rows: int, kv_heads: int):
+    """(split_len, max_splits): key ranges of a multiple of 64 keys, enough of them to fill the
+    machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
+    while contexts grow."""
+    bucket = -(-max(max_len, 1) // 1024) * 1024
+    want = max(1, DECODE_TARGET_CTAS // max(rows * kv_heads, 1))
+    split_len = max(64, -(-(-(-bucket // want)) // 64) * 64)
+    return split_len, -(-bucket // split_len)
+
+
+def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, window, max_len, out=None):
+    """One query row per request (bfloat16): split-KV decode attention.  q [T, H, hd]."""
+    _dev(q, pool, block_table, positions, row_slot)
+    T, H, hd = q.shape
+    G, page_tokens = pool.shape[3], pool.shape[4]
+    if q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
+        raise KernelError("attention_decode takes bfloat16 queries and cache")
+    if hd % 8 or hd > 256:
+        raise KernelError(f"attention_decode: head_dim {hd} must be a multiple of 8, at most 256")
+    split_len, max_splits = decode_split(max_len, T, G)
+    scratch, counters = reserve_decode_scratch(q.device, T, H, G, hd, max_splits)
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    f = _fn("attention_decode", "fellm_attention_decode",
+            [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_f, _c_int, _c_int, _c_int, _c_p])
+    _check(f(_p(q), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(out),
+             _p(scratch), _p(counters), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
+             int(window or 0), split_len, max_splits, _stream()), "attention_decode")
+    return out
 
 
 def attention_modules(dtype: str, head_dim: int):
-    return [("attention_simt", None)]
+    mods = [("attention_simt", None)]
+    if dtype == "bfloat16":
+        mods.append(("attention_decode", None))
+    return mods
 
 
 def paged_attention(q, cache, ctx, scale, window=None):
     """Attention of the step's rows over their items' cache pages; picks the kernel."""
+    if q.dtype == torch.bfloat16 and ctx.all_single:
+        return attention_decode(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
+                                scale, window, ctx.max_len)
     return paged_attention_simt(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                                 scale, window)
 

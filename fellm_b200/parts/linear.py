@@ -15,7 +15,7 @@ from .. import ops
 def linear(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False):
     """x [T, K], w [N, K] -> [T, N].  accumulate=True adds into the float32 `out` (the residual
     stream) instead of storing."""
-    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ops.has_fast_gemm():
+    if ops.fast_gemm_takes(x, w):
         return ops.gemm_bf16(x, w, bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
     return ops.gemm_simt(x, w, bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
 

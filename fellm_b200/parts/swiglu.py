@@ -19,15 +19,23 @@ class SwiGLU(FeedForward):
                       "down.weight": ParamDecl((self.size, self.ff))}
 
     def prepare(self):
-        # one product for gate and up: [2F, d], gate rows first
+        """One product for gate and up.  On the tensor-core path the rows are interleaved in blocks
+        of 8 gate / 8 up so that the product's epilogue computes SiLU(gate)*up itself; otherwise
+        [2F, d] with the gate rows first, and a separate SiLU kernel."""
         g, u = self.w.pop("gate.weight"), self.w.pop("up.weight")
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.w["gate_up.weight"] = torch.cat([g, u], dim=0).contiguous()
+        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.ff % 8 == 0 and self.size % 8 == 0)
+        if self.fused:
+            self.w["gate_up.weight"] = ops.interleave_gate_up(g, u)
+        else:
+            self.w["gate_up.weight"] = torch.cat([g, u], dim=0).contiguous()
 
     def forward(self, hn, ctx, out):
-        gu = linear(hn, self.w["gate_up.weight"])
-        z = ops.silu_mul(gu)
+        if self.fused and ops.fast_gemm_takes(hn, self.w["gate_up.weight"]):
+            z = ops.gemm_bf16(hn, self.w["gate_up.weight"], swiglu=True)
+        else:
+            z = ops.silu_mul(linear(hn, self.w["gate_up.weight"]))
         linear(z, self.w["down.weight"], out=out, accumulate=True)
         return out
 

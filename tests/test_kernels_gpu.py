@@ -253,3 +253,116 @@ def test_qk_rope_write_flags_a_missing_page():
     ops.qk_rope_write(torch.randn(1, 4 * hd, device=DEV), None, None, 1e-6, None, "adjacent", i32([3]), i32([0]),
                       table, pool, 0, 8, H, G, hd, status=status)
     assert int(status) == 2 and float(pool.abs().sum()) == 0
+
+
+# ------------------------------------------------------------------ tensor-core kernels (bfloat16)
+
+def _gemm_case(M, N, K, seed=0):
+    g = torch.Generator().manual_seed(seed + M * 7 + N * 3 + K)
+    x = (torch.randn(M, K, generator=g)).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    return x, w, x.double() @ w.double().T
+
+
+# M <= 64 runs the weight-streaming kernel, larger M the tiled one
+GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (3, 515, 144), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
+               (64, 2048, 200), (5, 65536, 64), (65, 144, 144), (128, 515, 320), (300, 1000, 1000), (2048, 256, 136)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_bf16_store_acc_f32(M, N, K):
+    x, w, want = _gemm_case(M, N, K)
+    xd, wd = x.to(DEV), w.to(DEV)
+    bias = torch.randn(N, device=DEV)
+    tol_abs = 4e-3 * math.sqrt(K) * 0.05 * 4                  # bfloat16 products are exact; float32 sums
+    got = ops.gemm_bf16(xd, wd, out_dtype=torch.float32)
+    assert got.dtype == torch.float32 and torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4)
+    got = ops.gemm_bf16(xd, wd, bias, out_dtype=torch.float32)
+    assert torch.allclose(got.double().cpu(), want + bias.double().cpu(), rtol=1e-4, atol=1e-4)
+    got = ops.gemm_bf16(xd, wd)
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.double().cpu(), want, rtol=1e-2, atol=tol_abs)
+    res = torch.randn(M, N, device=DEV)
+    out = res.clone()
+    ops.gemm_bf16(xd, wd, out=out, accumulate=True)
+    assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+def test_gemm_bf16_swiglu_epilogue(M, F, K):
+    g = torch.Generator().manual_seed(F)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wg, wu = (torch.randn(F, K, generator=g) * 0.1).bfloat16(), (torch.randn(F, K, generator=g) * 0.1).bfloat16()
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = (gate / (1 + torch.exp(-gate))) * up
+    w = ops.interleave_gate_up(wg.to(DEV), wu.to(DEV))
+    assert w.shape == (2 * F, K) and torch.equal(w[0], wg[0].to(DEV)) and torch.equal(w[8], wu[0].to(DEV))
+    got = ops.gemm_bf16(x.to(DEV), w, swiglu=True)
+    assert got.shape == (M, F) and got.dtype == torch.bfloat16
+    assert torch.allclose(got.double().cpu(), want, rtol=1.2e-2, atol=2e-3)
+
+
+def test_gemm_bf16_refuses_unaligned_k():
+    x = torch.randn(4, 100, device=DEV).bfloat16()
+    w = torch.randn(32, 100, device=DEV).bfloat16()
+    assert not ops.fast_gemm_takes(x, w)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        ops.gemm_bf16(x, w)
+
+
+def test_gemm_skinny_same_bits_every_run():
+    x, w, _ = _gemm_case(8, 1024, 4608)
+    a = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    b = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert torch.equal(a, b)                                # the cluster reduces in rank order
+
+
+@pytest.mark.parametrize("H,G,hd,page_tokens,window", [(16, 8, 64, 64, None), (6, 1, 48, 16, None), (4, 4, 128, 32, None),
+                                                       (24, 8, 64, 64, None), (8, 1, 16, 16, 70), (5, 5, 80, 8, None),
+                                                       (2, 1, 256, 64, 300), (32, 8, 64, 16, None), (6, 1, 32, 64, None)])
+def test_attention_decode_split_kv(H, G, hd, page_tokens, window):
+    """Rows of different lengths, each its own request, pages out of order, key ranges that end
+    inside pages: against the plain attention."""
+    torch.manual_seed(H + hd)
+    lens = [1, 2, 63, 64, 65, 200, 777, 1500]
+    T = len(lens)
+    n_pg = [-(-n // page_tokens) for n in lens]
+    total = sum(n_pg)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(1)).tolist()
+    pool = torch.randn(total + 1, 2, 2, G, page_tokens, hd, device=DEV).bfloat16()
+    table = torch.full((T + 2, max(n_pg) + 1), -1, dtype=torch.int32)
+    keys, values, at = [], [], 0
+    for r, n in enumerate(lens):
+        k, v = torch.randn(n, G, hd).bfloat16(), torch.randn(n, G, hd).bfloat16()
+        keys.append(k); values.append(v)
+        for p in range(n_pg[r]):
+            page = perm[at] + 1; at += 1
+            table[r + 1, p] = page
+            lo, hi = p * page_tokens, min(n, (p + 1) * page_tokens)
+            pool[page, 1, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1).to(DEV)
+            pool[page, 1, 1, :, :hi - lo] = v[lo:hi].transpose(0, 1).to(DEV)
+    q = torch.randn(T, H, hd).bfloat16()
+    got = ops.attention_decode(q.to(DEV), pool, table.to(DEV), i32([n - 1 for n in lens]), i32(list(range(1, T + 1))),
+                               1, hd ** -0.5, window, max(lens))
+    got = got.float().cpu().reshape(T, H, hd)
+    for r, n in enumerate(lens):
+        want = P.paged_attention_rows(q[r:r + 1].float(), keys[r].float(), values[r].float(), torch.tensor([n - 1]),
+                                      scale=hd ** -0.5, window=window)
+        assert torch.allclose(got[r], want[0], rtol=2e-2, atol=2e-2), (r, n, (got[r] - want[0]).abs().max())
+    # the same rows in one launch and alone give the same bits when the key ranges are the same
+    again = ops.attention_decode(q.to(DEV), pool, table.to(DEV), i32([n - 1 for n in lens]), i32(list(range(1, T + 1))),
+                                 1, hd ** -0.5, window, max(lens))
+    assert torch.equal(again.float().cpu().reshape(T, H, hd), got)
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 1023, 1024, 2999])
+def test_attention_decode_finds_one_far_key(far):
+    H, G, hd, pt, C = 16, 8, 64, 64, 3000
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    d = torch.randn(hd); d = d / d.norm()
+    keys[far] = d * 30.0
+    q = (d * 30.0).repeat(1, H, 1)
+    pool, table = build_cache(keys, values, pt, list(range(1, 1 + -(-C // pt))), torch.bfloat16)
+    got = ops.attention_decode(q.to(DEV).bfloat16(), pool, table, i32([C - 1]), i32([1]), 1, hd ** -0.5, None, C)
+    got = got.float().cpu().reshape(H, hd)
+    for h in range(H):
+        assert torch.allclose(got[h], values[far, h // 2].bfloat16().float(), atol=2e-2), (far, h)

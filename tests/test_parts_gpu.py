@@ -26,8 +26,9 @@ def tdtype(d):
     return torch.float32 if d == "float32" else torch.bfloat16
 
 
-def tol(d):
-    return dict(rtol=3e-5, atol=3e-6) if d == "float32" else dict(rtol=3e-2, atol=3e-3)
+def near(got, want, dtype):
+    """The engine's own criterion (tests/tiny.py): largest error against the largest magnitude."""
+    return tiny.close(got, want, dtype)[0]
 
 
 def bound(category, spec, dtype, seed=0):
@@ -81,7 +82,7 @@ def test_rmsnorm_part(dtype):
     part, raw = bound("norm", PartSpec.make("rmsnorm", size=200, eps=1e-6), dtype)
     x = torch.randn(9, 200)
     got = part.forward(x.to(DEV), tdtype(dtype))
-    assert torch.allclose(got.float().cpu(), P.rmsnorm(x, raw["weight"], 1e-6), **tol(dtype))
+    assert near(got.float().cpu(), P.rmsnorm(x, raw["weight"], 1e-6), dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -92,7 +93,7 @@ def test_embedding_and_head_parts(dtype):
     head, hraw = bound("head", PartSpec.make("linear", vocab=301, size=72, tied=False), dtype)
     xf = torch.randn(3, 72).bfloat16().float()
     got = head.forward(xf.to(DEV, tdtype(dtype)))
-    assert got.dtype == torch.float32 and torch.allclose(got.cpu(), xf @ hraw["weight"].T, **tol(dtype))
+    assert got.dtype == torch.float32 and near(got.cpu(), xf @ hraw["weight"].T, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -103,7 +104,7 @@ def test_swiglu_part(dtype):
     res = out.clone().cpu()
     part.forward(hn.to(DEV, tdtype(dtype)), None, out)
     want = res + P.swiglu(hn, raw["gate.weight"], raw["up.weight"], raw["down.weight"])
-    assert torch.allclose(out.cpu(), want, **tol(dtype))
+    assert near(out.cpu(), want, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -123,7 +124,7 @@ def test_shortconv_part_whole_and_cut(dtype, taps, bias):
             ctx, view = h.ctx([(req, n)])
             part.forward(xn[at:at + n].to(DEV, tdtype(dtype)), ctx, view, out[at:at + n])
             at += n
-        assert torch.allclose(out.cpu(), want, **tol(dtype)), cuts
+        assert near(out.cpu(), want, dtype), cuts
         h.cache.release(req)
 
 
@@ -150,7 +151,7 @@ def test_attention_part_whole_and_cut(dtype, H, G, hd, pairing, window):
             ctx, view = h.ctx([(req, n)])
             part.forward(xn[at:at + n].to(DEV, tdtype(dtype)), ctx, view, out[at:at + n])
             at += n
-        assert torch.allclose(out.cpu(), want, **tol(dtype)), cuts
+        assert near(out.cpu(), want, dtype), cuts
         if window:
             g = h.cache.paged[0]
             assert g.first_page[h.cache.slot(req)] == (T - window + 1) // 8        # pages behind the window came back
