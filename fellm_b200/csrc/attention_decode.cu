@@ -12,6 +12,7 @@
 
 #define DEC_WARPS 4
 #define DEC_UNROLL 4
+#define DEC_MAX_PAGES 256            // pages of one CTA's key range kept in shared memory
 
 __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
   uint4 v;
@@ -39,18 +40,28 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(Decode
   __shared__ float sm_acc[DEC_WARPS][RR][LPK * 8];
   __shared__ float sm_ml[DEC_WARPS][RR][2];
   __shared__ int sm_last;
+  __shared__ int sm_pages[DEC_MAX_PAGES];
   const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gi = lane / LPK, li = lane % LPK, d0 = li * 8;
   const bool lane_on = d0 < a.hd;
+  // positions, slots and block tables are written by copies before the step's kernels, not by a
+  // kernel: they may be read before the wait
   const int pos = a.positions[t];
   const int kb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
   const int s_lo = kb / a.split_len, s_hi = pos / a.split_len;
+  pdl_launch_dependents();
   if (s < s_lo || s > s_hi) return;
   const int n_active = s_hi - s_lo + 1;
   const int k0 = max(kb, s * a.split_len), k1 = min(pos + 1, (s + 1) * a.split_len);
   const int R = a.H / a.G;
   const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
+  const int pg0 = k0 / a.page_tokens, n_pg = (k1 - 1) / a.page_tokens - pg0 + 1;
+  const bool pages_in_smem = n_pg <= DEC_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = threadIdx.x; i < n_pg; i += DEC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
+  pdl_wait();
+  __syncthreads();
   const size_t head_stride = (size_t)a.page_tokens * a.hd;          // one kv head's tile in a page
   const size_t v_off = (size_t)a.G * head_stride;
   const int SW = a.hd + 2;                                           // scratch record: acc[hd], m, l
@@ -77,23 +88,26 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(Decode
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[rr][i] = 0.f;
     }
-    // keys k0 + ((j*UNROLL + u)*WARPS + warp)*KPW + gi
-    for (int base = k0; base < k1; base += DEC_UNROLL * DEC_WARPS * KPW) {
-      uint4 kv[DEC_UNROLL], vv[DEC_UNROLL];
-      bool ok[DEC_UNROLL];
+    // keys base + (u*WARPS + warp)*KPW + gi; the loads of the next round are in flight while this
+    // round is computed
+    constexpr int STEP = DEC_UNROLL * DEC_WARPS * KPW;
+    auto load = [&](int base, uint4* kv, uint4* vv, bool* ok) {
 #pragma unroll
       for (int u = 0; u < DEC_UNROLL; ++u) {
         int kj = base + (u * DEC_WARPS + warp) * KPW + gi;
         ok[u] = kj < k1;
         kv[u] = make_uint4(0, 0, 0, 0); vv[u] = kv[u];
         if (ok[u] && lane_on) {
-          int page = bt[kj / a.page_tokens];
+          int lp = kj / a.page_tokens;
+          int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
           const bf16* kp = a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * head_stride
-                           + (size_t)(kj % a.page_tokens) * a.hd + d0;
+                           + (size_t)(kj - lp * a.page_tokens) * a.hd + d0;
           kv[u] = ldg_nc16(kp);
           vv[u] = ldg_nc16(kp + v_off);
         }
       }
+    };
+    auto compute = [&](const uint4* kv, const uint4* vv, const bool* ok) {
       float sc[RR][DEC_UNROLL];
 #pragma unroll
       for (int u = 0; u < DEC_UNROLL; ++u) {
@@ -129,6 +143,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(Decode
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[rr][i] = fmaf(p, vf[i], acc[rr][i]);
         }
+      }
+    };
+    {
+      uint4 kA[DEC_UNROLL], vA[DEC_UNROLL], kB[DEC_UNROLL], vB[DEC_UNROLL];
+      bool okA[DEC_UNROLL], okB[DEC_UNROLL];
+      int base = k0;
+      load(base, kA, vA, okA);
+      while (true) {
+        if (base + STEP < k1) load(base + STEP, kB, vB, okB);
+        compute(kA, vA, okA);
+        base += STEP;
+        if (base >= k1) break;
+        if (base + STEP < k1) load(base + STEP, kA, vA, okA);
+        compute(kB, vB, okB);
+        base += STEP;
+        if (base >= k1) break;
       }
     }
     // merge the key groups of the warp, then the warps
@@ -210,12 +240,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(Decode
 
 template <int LPK>
 static int launch_lpk(const DecodeArgs& a, int R, cudaStream_t stream) {
-  dim3 grid(a.max_splits, a.G, a.T);
-  if (R == 1) attention_decode_kernel<LPK, 1><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-  else if (R == 2) attention_decode_kernel<LPK, 2><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-  else if (R == 3) attention_decode_kernel<LPK, 3><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-  else attention_decode_kernel<LPK, 4><<<grid, DEC_WARPS * 32, 0, stream>>>(a);
-  return launch_status();
+  dim3 grid(a.max_splits, a.G, a.T), block(DEC_WARPS * 32, 1, 1);
+  if (R == 1) return launch_k(attention_decode_kernel<LPK, 1>, grid, block, 0, stream, 1, a);
+  if (R == 2) return launch_k(attention_decode_kernel<LPK, 2>, grid, block, 0, stream, 1, a);
+  if (R == 3) return launch_k(attention_decode_kernel<LPK, 3>, grid, block, 0, stream, 1, a);
+  return launch_k(attention_decode_kernel<LPK, 4>, grid, block, 0, stream, 1, a);
 }
 
 // scratch: float32 [T*H*max_splits*(hd+2)]; counters: int32 [T*G], zero before the first launch

@@ -29,6 +29,46 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- programmatic dependent launch: a kernel launched with launch_k() may start while its
+// predecessor in the stream is still running.  What does not depend on the predecessor (weight
+// prefetch, index set-up) goes before pdl_wait(); everything that reads or writes data another
+// kernel of the step touches goes after it.  pdl_wait() returns once the predecessor has completed
+// and its writes are visible; it is a no-op for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("FELLM_B200_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on == 1;
+}
+
+// Launches `kernel` with an optional cluster along x and, unless FELLM_B200_PDL=0, as a
+// programmatic dependent of the kernel before it.  Returns a cudaError_t as int.
+template <typename... KArgs, typename... Args>
+static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                    int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr; cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return (int)e;

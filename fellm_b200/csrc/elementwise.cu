@@ -9,6 +9,8 @@
 template <typename TW>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                   float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();                 // the residual buffer may still be read by the step before
   int row = blockIdx.x;
   int tok = tokens[row];
   float* o = out + (size_t)row * d;
@@ -27,10 +29,8 @@ FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_i
   if (!tokens || !table || !out) return FELLM_ERR_ARG;
   int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_is_bf16)
-    embed_rows_kernel<bf16><<<rows, threads, 0, stream>>>(tokens, (const bf16*)table, out, d, vocab, status);
-  else
-    embed_rows_kernel<float><<<rows, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab, status);
-  return launch_status();
+    return launch_k(embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
+  return launch_k(embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -42,6 +42,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
   __shared__ float partial[THREADS / 32];
   __shared__ float scale_s;
+  pdl_launch_dependents();
+  pdl_wait();
   int orow = blockIdx.x;
   int irow = rows ? rows[orow] : orow;
   const float* xr = x + (size_t)irow * d;
@@ -66,20 +68,21 @@ FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_i
                             const int* rows, int n_out_rows, int d, float eps, cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
   if (!x || !w || !out) return FELLM_ERR_ARG;
+  dim3 grid(n_out_rows);
   if (d >= 512) {
-    if (out_is_bf16) rmsnorm_kernel<bf16, 256><<<n_out_rows, 256, 0, stream>>>(x, w, (bf16*)out, rows, d, eps);
-    else rmsnorm_kernel<float, 256><<<n_out_rows, 256, 0, stream>>>(x, w, (float*)out, rows, d, eps);
-  } else {
-    if (out_is_bf16) rmsnorm_kernel<bf16, 64><<<n_out_rows, 64, 0, stream>>>(x, w, (bf16*)out, rows, d, eps);
-    else rmsnorm_kernel<float, 64><<<n_out_rows, 64, 0, stream>>>(x, w, (float*)out, rows, d, eps);
+    if (out_is_bf16) return launch_k(rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+    return launch_k(rmsnorm_kernel<float, 256>, grid, dim3(256), 0, stream, 1, x, w, (float*)out, rows, d, eps);
   }
-  return launch_status();
+  if (out_is_bf16) return launch_k(rmsnorm_kernel<bf16, 64>, grid, dim3(64), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+  return launch_k(rmsnorm_kernel<float, 64>, grid, dim3(64), 0, stream, 1, x, w, (float*)out, rows, d, eps);
 }
 
 // ---------------------------------------------------------------- SiLU gate
 // in [T, 2F]: gate in columns [0,F), up in [F,2F); out [T,F] = gate/(1+exp(-gate)) * up.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int F) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t n = (size_t)rows * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     size_t r = i / F; int c = (int)(i - r * F);
@@ -93,7 +96,6 @@ FELLM_API int fellm_silu_mul(const void* gu, void* out, int is_bf16, int rows, i
   if (rows <= 0) return 0;
   size_t n = (size_t)rows * F;
   int blocks = (int)((n + 255) / 256); if (blocks > 148 * 16) blocks = 148 * 16;
-  if (is_bf16) silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, F);
-  else silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, rows, F);
-  return launch_status();
+  if (is_bf16) return launch_k(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, rows, F);
+  return launch_k(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (const float*)gu, (float*)out, rows, F);
 }

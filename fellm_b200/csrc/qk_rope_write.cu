@@ -20,6 +20,8 @@ __global__ void qk_rope_write_kernel(const TA* __restrict__ qkv, const float* __
                                      TC* __restrict__ pool, int layer, int layers_in_group,
                                      int page_tokens, TA* __restrict__ q_out, int T, int H, int G, int hd,
                                      int write_kv, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
   int heads_total = H + 2 * G;
@@ -90,12 +92,10 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
   int threads = 128;
   long long blocks = (warps * 32 + threads - 1) / threads;
   if (act_bf16)
-    qk_rope_write_kernel<bf16, bf16><<<(unsigned)blocks, threads, 0, stream>>>((const bf16*)qkv, q_w, k_w, eps,
-        inv_freq, pairing, positions, row_slot, block_table, max_pages, (bf16*)pool, layer, layers_in_group,
-        page_tokens, (bf16*)q_out, T, H, G, hd, write_kv, status);
-  else
-    qk_rope_write_kernel<float, float><<<(unsigned)blocks, threads, 0, stream>>>((const float*)qkv, q_w, k_w, eps,
-        inv_freq, pairing, positions, row_slot, block_table, max_pages, (float*)pool, layer, layers_in_group,
-        page_tokens, (float*)q_out, T, H, G, hd, write_kv, status);
-  return launch_status();
+    return launch_k(qk_rope_write_kernel<bf16, bf16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
+                    (const bf16*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
+                    (bf16*)pool, layer, layers_in_group, page_tokens, (bf16*)q_out, T, H, G, hd, write_kv, status);
+  return launch_k(qk_rope_write_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
+                  (const float*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
+                  (float*)pool, layer, layers_in_group, page_tokens, (float*)q_out, T, H, G, hd, write_kv, status);
 }

@@ -209,6 +209,8 @@ sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restri
               int* __restrict__ out_tokens, float* __restrict__ out_probs, int update_counts) {
   __shared__ Shared s;
   int row = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   RowParams p = params[row];
   Row r;
   r.logits = logits + (size_t)row * V;
@@ -275,7 +277,7 @@ sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restri
     float x = r.val(v);
     if (key_of(x) > cut.kt) part += expf(x - m);
   }
-  float sum1 = block_sum(part, s.red) + (float)cut.q * expf(val_of(cut.kt) - m);
+  float sum1 = block_sum(part, s.red) + (cut.q ? (float)cut.q * expf(val_of(cut.kt) - m) : 0.f);
   Weigher pg; pg.mode = 1; pg.m = m; pg.sum1 = sum1; pg.sum2 = 1.f; pg.use_sum2 = false;
 
   // min-p: drop p < p_max * min_p, renormalise
@@ -287,8 +289,8 @@ sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restri
       float x = r.val(v);
       if (key_of(x) > cut.kt) { float q = pg.prob(x); if (q >= minp_thr) part += q; }
     }
-    float tq = pg.prob(val_of(cut.kt));
-    float sum2 = block_sum(part, s.red) + (tq >= minp_thr ? (float)cut.q * tq : 0.f);
+    float tq = cut.q ? pg.prob(val_of(cut.kt)) : 0.f;
+    float sum2 = block_sum(part, s.red) + ((cut.q && tq >= minp_thr) ? (float)cut.q * tq : 0.f);
     if (sum2 > 0.f) { pg.sum2 = sum2; pg.use_sum2 = true; }
   }
   Weigher base = pg;                                     // p before the min-p renormalisation:
@@ -303,8 +305,8 @@ sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restri
       float x = r.val(v);
       if (key_of(x) > cut.kt) { float q = pg.prob(x); if (!(minp_thr > 0.f && base.prob(x) < minp_thr)) part += q; }
     }
-    float tq = pg.prob(val_of(cut.kt));
-    bool tie_ok = !(minp_thr > 0.f && base.prob(val_of(cut.kt)) < minp_thr);
+    float tq = cut.q ? pg.prob(val_of(cut.kt)) : 0.f;
+    bool tie_ok = cut.q && !(minp_thr > 0.f && base.prob(val_of(cut.kt)) < minp_thr);
     sum3 = block_sum(part, s.red) + (tie_ok ? (float)cut.q * tq : 0.f);
     use_sum3 = sum3 > 0.f;
   }
@@ -360,9 +362,8 @@ FELLM_API int fellm_sample(const float* logits, int rows, int V, const void* par
                            int update_counts, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!logits || !params || !out_tokens || V < 1) return FELLM_ERR_ARG;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, V, (const RowParams*)params, counts, bias_tok,
-                                                    bias_val, out_tokens, out_probs, update_counts);
-  return launch_status();
+  return launch_k(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1, logits, V, (const RowParams*)params,
+                  counts, bias_tok, bias_val, out_tokens, out_probs, update_counts);
 }
 
 FELLM_API int fellm_count_tokens(int* counts, int V, const int* slots, const int* tokens, int n,

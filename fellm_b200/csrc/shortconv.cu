@@ -26,13 +26,15 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
                                  const int* __restrict__ item_start, const int* __restrict__ row_item,
                                  TA* __restrict__ y, int T, int n_items, int d, int Lc, int n_body_tiles) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
   if (c >= d) return;
   const int H = Lc - 1;
   float wt[MAX_LC];
 #pragma unroll
-  for (int t = 0; t < MAX_LC; ++t) wt[t] = t < Lc ? w[(size_t)c * Lc + t] : 0.f;
+  for (int t = 0; t < MAX_LC; ++t) wt[t] = t < Lc ? w[(size_t)c * Lc + t] : 0.f;      // weights: before the wait
   const float wlast = w[(size_t)c * Lc + (Lc - 1)];
   float bias = conv_bias ? conv_bias[c] : 0.f;
+  pdl_wait();
   const size_t ld = (size_t)3 * d;
 
   if ((int)blockIdx.y < n_body_tiles) {
@@ -106,10 +108,8 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   int n_body = all_single ? 0 : ceil_div(T, BODY_ROWS);    // every item has one token: heads only
   dim3 grid(ceil_div(d, threads), n_body + n_items);
   if (is_bf16)
-    shortconv_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)bcx, w, conv_bias, state, slot_stride,
-        item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
-  else
-    shortconv_kernel<float><<<grid, threads, 0, stream>>>((const float*)bcx, w, conv_bias, state, slot_stride,
-        item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body);
-  return launch_status();
+    return launch_k(shortconv_kernel<bf16>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
+  return launch_k(shortconv_kernel<float>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
+                  slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body);
 }

@@ -64,7 +64,7 @@ class Engine:
                                   device=self.device)
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
-                               device=self.device)
+                               device=self.device, cuda_graphs=options.cuda_graphs)
         self.sampler = Sampler(spec.vocab_size, options.max_requests, options.max_requests, self.device)
         self._tok_host = torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True)
         self._scheduler: Optional[Scheduler] = None
@@ -117,8 +117,8 @@ class Engine:
     def release(self, req):
         self.cache.release(req)
 
-    def step(self, items: List[StepItem]) -> torch.Tensor:
-        return self.stepper.step(items)
+    def step(self, items: List[StepItem], device_tokens=None) -> torch.Tensor:
+        return self.stepper.step(items, device_tokens)
 
     def check_status(self):
         self.stepper.check_status()

@@ -39,7 +39,7 @@ class StepContext:
     """
     __slots__ = ("tokens", "positions", "row_item", "row_slot", "item_start", "item_slot", "item_len",
                  "logit_rows", "n_rows", "n_items", "n_logit_rows", "all_single", "max_item_rows",
-                 "max_len", "status", "host")
+                 "max_len", "status", "host", "logits_all")
 
 
 class StepBuffers:
@@ -93,6 +93,7 @@ class StepBuffers:
             self.ring_used[k] = True
         ctx.n_rows, ctx.n_items, ctx.n_logit_rows = T, n, W
         ctx.all_single = (T == n)
+        ctx.logits_all = (W == T and list(logit_rows) == list(range(T)))
         ctx.max_item_rows, ctx.max_len = max_item_rows, max_len
         ctx.status = self.status
         ctx.host = None
@@ -100,19 +101,35 @@ class StepBuffers:
 
 
 class Stepper:
-    """Owns the model, the cache manager and the step buffers; `step()` is the step function."""
+    """Owns the model, the cache manager and the step buffers; `step()` is the step function.
 
-    def __init__(self, model, cache, *, max_rows: int, max_items: int, device):
+    Steps in which every item brings one token (decode) are replayed from CUDA graphs when
+    `cuda_graphs` is on: FeLLM captures one decode step the same way
+    (crates/backend-cuda/src/graph.rs:39-160, crates/fellm-runtime/src/engine.rs:3195-3233).  A
+    graph is keyed by the number of items, the number of wanted rows and the longest context
+    rounded up to 1024 (the key-range split of decode attention follows it); the first step with a
+    new key runs directly (kernels get loaded), the second is captured, later ones are replayed.
+    Index arrays and block tables live at fixed device addresses and are refreshed by copies before
+    the replay."""
+
+    def __init__(self, model, cache, *, max_rows: int, max_items: int, device, cuda_graphs: bool = False):
         self.model, self.cache, self.device = model, cache, device
         self.buffers = StepBuffers(max_rows, max_items, device)
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
-        self.kernel_launch_hook = None
+        self.cuda_graphs = bool(cuda_graphs)
+        self.graphs = {}
+        self.graph_seen = {}
+        self.graph_pool = None
+        self.launches = 0                      # kernels of ours launched, replays included
 
-    def step(self, items: List[StepItem]) -> torch.Tensor:
+    def step(self, items: List[StepItem], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs exactly the given tokens as one batch and returns float32 logits
         [sum(len(want)), vocab] on the device, in the order of the items and of each `want`.
-        Nothing is changed when the step cannot be placed (unknown request, no pages)."""
+        Nothing is changed when the step cannot be placed (unknown request, no pages).
+
+        device_tokens: int32 [rows] on the device to use instead of the items' token ids (which
+        are then placeholders): lets a decode loop feed sampled tokens back without the host."""
         if not items:
             raise FellmError("a step needs at least one item")
         cache = self.cache
@@ -160,11 +177,44 @@ class Stepper:
         ctx = self.buffers.fill(np.concatenate(tok_parts), np.concatenate(pos_parts), np.concatenate(ri_parts),
                                 np.concatenate(rs_parts), item_start, item_slot, item_len, logit_rows,
                                 max_rows, max_len)
+        if device_tokens is not None:
+            ctx.tokens.copy_(device_tokens[:ctx.n_rows])
         cache.flush()
-        logits = self.model.forward(ctx, cache.views(ctx.item_slot))
+        logits = self._run(ctx)
         for req, n in asks:
             cache.advance(req, n)
         self.steps_run += 1
+        return logits
+
+    def _run(self, ctx) -> torch.Tensor:
+        from .. import ops
+        views = self.cache.views(ctx.item_slot)
+        if not (self.cuda_graphs and ctx.all_single):
+            before = ops.launch_count()
+            logits = self.model.forward(ctx, views)
+            self.launches += ops.launch_count() - before
+            return logits
+        key = (ctx.n_items, ctx.n_logit_rows, -(-ctx.max_len // 1024))
+        entry = self.graphs.get(key)
+        if entry is None:
+            n_seen = self.graph_seen.get(key, 0)
+            self.graph_seen[key] = n_seen + 1
+            if n_seen == 0:
+                before = ops.launch_count()
+                logits = self.model.forward(ctx, views)
+                self.launches += ops.launch_count() - before
+                return logits
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self.graph_pool):
+                logits = self.model.forward(ctx, views)
+            if self.graph_pool is None:
+                self.graph_pool = graph.pool()
+            entry = (graph, logits, ops.launch_count() - before)
+            self.graphs[key] = entry
+        graph, logits, n_launches = entry
+        graph.replay()
+        self.launches += n_launches
         return logits
 
     def check_status(self):

@@ -14,7 +14,15 @@ import torch
 
 from ..config.errors import ConfigError
 from ..parts.base import ParamDecl, build_part
+from ..parts.linear import LazyNorm
 from ..parts.spec import ModelSpec
+
+
+def _normed(x, norm, consumer, act_dtype):
+    """The consumer's input: normed now, or left to the consumer's first product."""
+    if getattr(consumer, "takes_lazy_norm", False):
+        return LazyNorm(x, norm, act_dtype)
+    return norm.forward(x, act_dtype)
 
 
 class Block:
@@ -35,8 +43,8 @@ class Block:
     def forward(self, x, ctx, cache, act_dtype, reads_only=False):
         """x: float32 residual stream [T, d], updated in place:
         x += mixer(norm1(x)); x += ffn(norm2(x))."""
-        self.mixer.forward(self.norm1.forward(x, act_dtype), ctx, cache, x, reads_only=reads_only)
-        self.ffn.forward(self.norm2.forward(x, act_dtype), ctx, x)
+        self.mixer.forward(_normed(x, self.norm1, self.mixer, act_dtype), ctx, cache, x, reads_only=reads_only)
+        self.ffn.forward(_normed(x, self.norm2, self.ffn, act_dtype), ctx, x)
         return x
 
 
@@ -102,6 +110,8 @@ class Model:
                                            reads_only=run.cache_of is not None)
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
+        if ctx.logits_all and getattr(self.head, "takes_lazy_norm", False):
+            return self.head.forward(LazyNorm(x, self.final_norm, self.act_dtype))
         xf = self.final_norm.forward(x, self.act_dtype, rows=ctx.logit_rows)
         return self.head.forward(xf)
 

@@ -35,7 +35,17 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Launcher calls so far (each is one kernel launch of this package, or a refusal)."""
+    return _launches
+
+
 def _check(code: int, what: str):
+    global _launches
+    _launches += 1
     if code == 0:
         return
     if code == -1:
@@ -231,6 +241,8 @@ def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale
 _EPI_STORE, _EPI_ACC, _EPI_SWIGLU, _EPI_F32 = 0, 1, 2, 3
 SKINNY_MAX_ROWS = 64
 _GEMM_ARGS = [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
+_SKINNY_ARGS = [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
+NORM_FUSE_MAX_ROWS = 16
 
 
 def has_fast_gemm() -> bool:
@@ -247,16 +259,30 @@ def fast_gemm_takes(x, w) -> bool:
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1)
 
 
-def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False):
+def norm_fusable(x_f32, w, norm_w) -> bool:
+    """Whether RMSNorm of the float32 rows x can run inside the product with w (few rows, the whole
+    K range in one CTA's shared memory)."""
+    M, K = x_f32.shape
+    return (M <= NORM_FUSE_MAX_ROWS and w.dtype == torch.bfloat16 and x_f32.dtype == torch.float32
+            and norm_w.dtype == torch.float32 and K % 8 == 0 and K <= 8192 and w.stride(0) % 8 == 0
+            and x_f32.stride(1) == 1 and x_f32.stride(0) % 4 == 0 and w.stride(1) == 1)
+
+
+def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False, norm=None):
     """out = x[M,K] @ w[N,K]^T (+bias) on tensor cores, bfloat16 in, float32 sums.
     accumulate: out (float32 [M,N]) += ; swiglu: w's rows are interleaved in blocks of 8 gate / 8 up
-    and out is bfloat16 [M, N/2] = silu(gate)*up; out_dtype float32: float32 store."""
+    and out is bfloat16 [M, N/2] = silu(gate)*up; out_dtype float32: float32 store.
+    norm=(weight float32 [K], eps): x is the float32 residual stream and is RMS-normed on its way
+    into the product (see norm_fusable)."""
     _dev(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: x is [{M},{K}] but w is {list(w.shape)}")
-    if not fast_gemm_takes(x, w):
+    if norm is not None:
+        if not norm_fusable(x, w, norm[0]):
+            raise KernelError("gemm_bf16: this product cannot take a fused RMSNorm")
+    elif not fast_gemm_takes(x, w):
         raise KernelError(f"gemm_bf16: K={K} and the row strides must be multiples of 8 bfloat16 elements")
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
@@ -270,7 +296,7 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
         if out is None:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
         assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2)
-    elif (out_dtype or (out.dtype if out is not None else x.dtype)) == torch.float32:
+    elif (out_dtype or (out.dtype if out is not None else torch.bfloat16)) == torch.float32:
         epi = _EPI_F32
         if out is None:
             out = torch.empty((M, N), dtype=torch.float32, device=x.device)
@@ -282,9 +308,19 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     assert out.stride(1) == 1
     if M == 0:
         return out
-    mod, name = ("gemm_skinny", "fellm_gemm_skinny") if M <= SKINNY_MAX_ROWS else ("gemm_tiled", "fellm_gemm_tiled")
-    f = _fn(mod, name, _GEMM_ARGS)
-    _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()), name)
+    if M <= SKINNY_MAX_ROWS:
+        f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
+        if norm is not None:
+            code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0),
+                     w.stride(0), out.stride(0), _stream())
+        else:
+            code = f(_p(x), None, None, 0.0, _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0),
+                     out.stride(0), _stream())
+        _check(code, "gemm_skinny")
+    else:
+        f = _fn("gemm_tiled", "fellm_gemm_tiled", _GEMM_ARGS)
+        _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
+               "gemm_tiled")
     return out
 
 
@@ -305,13 +341,14 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
     """Scratch of the split-KV decode kernel: partial results of every (row, head, key range) and
     one counter per (row, kv head).  Allocated before any CUDA graph is captured, grown never
     during one."""
-    need = rows * heads * max_splits * (head_dim + 2)
+    need = max(rows * heads * max_splits * (head_dim + 2), 1 << 21)     # at least 8 MB: growth is rare
     cur = _decode_scratch.get(device)
     if cur is None or cur[0].numel() < need or cur[1].numel() < rows * kv_heads:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("decode attention scratch must be reserved before graph capture")
         scratch = torch.empty(max(need, cur[0].numel() if cur else 0), dtype=torch.float32, device=device)
-        counters = torch.zeros(max(rows * kv_heads, cur[1].numel() if cur else 0), dtype=torch.int32, device=device)
+        counters = torch.zeros(max(rows * kv_heads, 1 << 16, cur[1].numel() if cur else 0), dtype=torch.int32,
+                               device=device)
         _decode_scratch[device] = (scratch, counters)
     return _decode_scratch[device]
 

@@ -41,6 +41,8 @@ class Attention(Mixer):
             if not self.shares_cache:
                 self.decls["k_norm.weight"] = ParamDecl((hd,), role="vector", init=("ones",))
 
+    takes_lazy_norm = True
+
     def cache_need(self):
         return PagedKV(self.G, self.hd, self.window)
 

@@ -34,6 +34,8 @@ class LinearHead(Head):
         self.vocab, self.size, self.tied = int(vocab), int(size), bool(tied)
         self.decls = {} if self.tied else {"weight": ParamDecl((self.vocab, self.size))}
 
+    takes_lazy_norm = True
+
     def forward(self, xf):
         return linear(xf, self.w["weight"], out_dtype=torch.float32)
 

@@ -28,6 +28,8 @@ class ShortConv(Mixer):
                                "conv.bias": ParamDecl((d,), role="vector", init=("normal", 0.01)),
                                "out_proj.bias": ParamDecl((d,), role="vector", init=("normal", 0.01))})
 
+    takes_lazy_norm = True
+
     def cache_need(self):
         return FixedState((self.taps - 1, self.size))
 

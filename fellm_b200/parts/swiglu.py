@@ -6,7 +6,7 @@ import torch
 
 from .. import ops
 from .base import FeedForward, ParamDecl, register_part
-from .linear import linear, linear_modules
+from .linear import LazyNorm, linear, linear_modules
 
 
 @register_part("feed_forward", "swiglu")
@@ -31,9 +31,11 @@ class SwiGLU(FeedForward):
         else:
             self.w["gate_up.weight"] = torch.cat([g, u], dim=0).contiguous()
 
+    takes_lazy_norm = True
+
     def forward(self, hn, ctx, out):
-        if self.fused and ops.fast_gemm_takes(hn, self.w["gate_up.weight"]):
-            z = ops.gemm_bf16(hn, self.w["gate_up.weight"], swiglu=True)
+        if self.fused:
+            z = linear(hn, self.w["gate_up.weight"], swiglu=True)
         else:
             z = ops.silu_mul(linear(hn, self.w["gate_up.weight"]))
         linear(z, self.w["down.weight"], out=out, accumulate=True)

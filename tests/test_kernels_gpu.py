@@ -366,3 +366,20 @@ def test_attention_decode_finds_one_far_key(far):
     got = got.float().cpu().reshape(H, hd)
     for h in range(H):
         assert torch.allclose(got[h], values[far, h // 2].bfloat16().float(), atol=2e-2), (far, h)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 1024), (8, 640, 144), (16, 200, 328), (3, 65536, 64), (8, 9216, 1024)])
+def test_gemm_bf16_fused_rmsnorm_prologue(M, N, K):
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(M, K, generator=g) * 2
+    nw = torch.rand(K, generator=g) + 0.5
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    xn = P.rmsnorm(x, nw, 1e-5).bfloat16()                       # the normed rows are rounded to bfloat16
+    want = xn.double() @ w.double().T
+    assert ops.norm_fusable(x.to(DEV), w.to(DEV), nw.to(DEV))
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32, norm=(nw.to(DEV), 1e-5))
+    # a normed value that sits on a bfloat16 rounding boundary may round the other way: allow one such flip
+    assert torch.allclose(got.double().cpu(), want, rtol=2e-3, atol=2e-2 * 0.05 * math.sqrt(K) / 8)
+    unfused = ops.gemm_bf16(ops.rmsnorm(x.to(DEV), nw.to(DEV), 1e-5, torch.bfloat16), w.to(DEV), out_dtype=torch.float32)
+    assert torch.allclose(got, unfused, rtol=2e-3, atol=2e-2 * 0.05 * math.sqrt(K) / 8)
+    assert not ops.norm_fusable(torch.zeros(17, K, device=DEV), w.to(DEV), nw.to(DEV))
