@@ -1,0 +1,479 @@
+// Causal GQA attention over the paged cache on tensor cores (mma.sync.m16n8k16, ldmatrix,
+// cp.async), bfloat16 queries and cache, float32 softmax and sums; compiled for one head size
+// (-DHD=...).  Two kernels share one inner step ("a 16-row block of queries against a tile of
+// keys in shared memory"):
+//
+//  * prefill: portions of prompts (and any mix of item lengths).  A CTA takes one item, one kv
+//    head and a block of tokens; its 64 query rows are (token, head of the kv head's group), so K
+//    and V are read once for all H/G heads.  Key tiles of 64 go through a two-stage cp.async
+//    ring shared by the CTA's four warps.
+//  * decode: one token per item against thousands of keys, bound by reading K and V once.  A CTA
+//    takes one row, one kv head and one range of keys ("split-KV"); its rows are the H/G heads of
+//    the group; each warp streams its own 32-key tiles through its own cp.async ring.  Partial
+//    (m, l, acc) of the ranges go to a scratch buffer; the CTA that finishes last for a (row, kv
+//    head) merges them in range order.
+//
+// Formulas: crates/fellm-plugin-abi/src/attention_provider.rs:175-237 (scores scaled by
+// 1/sqrt(hd), online softmax with m, l and rescaling, out = acc / l).  FeLLM's kernels:
+// attention_fa2_prefill_paged (plugins/cuda_kernels/src/oxide_kernels.rs:4673, one warp per query
+// row), attention_fa2_decode_paged (5107, one block per head over all keys).
+#include "common.cuh"
+
+#ifndef HD
+#define HD 64
+#endif
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size: a multiple of 16 in 16..256");
+
+constexpr int CPR = HD / 8;                         // 16-byte chunks per row
+constexpr bool SWZ = (CPR % 8 == 0);                // rows of whole 128-byte lines: XOR swizzle
+constexpr int ROWB = HD * 2 + (SWZ ? 0 : 16);       // else 16 bytes of padding spread the banks
+constexpr int KS = HD / 16;                         // k16 steps over the head size
+constexpr int DN = HD / 8;                          // n8 tiles over the head size
+
+__device__ __forceinline__ int tile_off(int row, int chunk) {
+  return row * ROWB + ((SWZ ? (chunk ^ (row & 7)) : chunk) << 4);
+}
+__device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem));
+}
+__device__ __forceinline__ void st_shared_zero16(unsigned smem_addr) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"(smem_addr), "r"(0u));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned* r, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned* r, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* d, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(unsigned*)&v;
+}
+
+// One 16-row block of queries (fragments qf) against NKT*8 keys staged at k_s / v_s (shared-memory
+// addresses of [keys][ROWB] tiles).  Thread (g = lane/4, c = lane%4) owns rows g and g+8; a key at
+// tile index i (absolute index key0 + i) counts for row r iff lo[r] <= key0 + i <= hi[r].
+// m, l: running maximum (log2 domain) and this thread's share of the running sum per row.
+template <int NKT>
+__device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigned k_s, unsigned v_s, int key0,
+                                            const int (&lo)[2], const int (&hi)[2], float scale_log2,
+                                            float (&o)[DN][4], float (&m)[2], float (&l)[2], int lane) {
+  const int c = lane & 3;
+  float s[NKT][4];
+#pragma unroll
+  for (int n = 0; n < NKT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+  // S = Q K^T: matrices of one ldmatrix.x4 = (keys 0-7, k lo) (keys 0-7, k hi) (keys 8-15, k lo) (keys 8-15, k hi)
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int np = 0; np < NKT / 2; ++np) {
+      int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+      int chunk = ks * 2 + ((lane >> 3) & 1);
+      unsigned r[4];
+      ldsm_x4(r, k_s + tile_off(row, chunk));
+      mma16816(s[2 * np], qf[ks], r[0], r[1]);
+      mma16816(s[2 * np + 1], qf[ks], r[2], r[3]);
+    }
+  }
+  // scale, mask, running maximum
+  float mx[2] = {m[0], m[1]};
+#pragma unroll
+  for (int n = 0; n < NKT; ++n) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int key = key0 + n * 8 + 2 * c + (e & 1);
+      int r = e >> 1;
+      float v = (key >= lo[r] && key <= hi[r]) ? s[n][e] * scale_log2 : -INFINITY;
+      s[n][e] = v;
+      mx[r] = fmaxf(mx[r], v);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+  }
+  float corr[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    corr[r] = (mx[r] == -INFINITY) ? 1.f : exp2f(m[r] - mx[r]);       // nothing seen yet: keep the zeros
+    m[r] = mx[r];
+    l[r] *= corr[r];
+  }
+#pragma unroll
+  for (int d = 0; d < DN; ++d) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+#pragma unroll
+  for (int n = 0; n < NKT; ++n) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int r = e >> 1;
+      float p = (mx[r] == -INFINITY) ? 0.f : exp2f(s[n][e] - mx[r]);
+      s[n][e] = p;
+      l[r] += p;
+    }
+  }
+  // O += P V: P's accumulators are the A fragments; V^T comes from ldmatrix.trans:
+  // (keys 0-7, dims lo) (keys 8-15, dims lo) (keys 0-7, dims hi) (keys 8-15, dims hi)
+#pragma unroll
+  for (int j = 0; j < NKT / 2; ++j) {
+    unsigned a[4] = {pack_bf16(s[2 * j][0], s[2 * j][1]), pack_bf16(s[2 * j][2], s[2 * j][3]),
+                     pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]), pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3])};
+#pragma unroll
+    for (int dn = 0; dn < DN / 2; ++dn) {
+      int row = j * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      int chunk = dn * 2 + (lane >> 4);
+      unsigned r[4];
+      ldsm_x4_trans(r, v_s + tile_off(row, chunk));
+      mma16816(o[2 * dn], a, r[0], r[1]);
+      mma16816(o[2 * dn + 1], a, r[2], r[3]);
+    }
+  }
+}
+
+// Query fragments of a 16-row block: row_ptr(i) gives the address of row i's HD elements (null:
+// a padding row of zeros).
+template <typename F>
+__device__ __forceinline__ void load_q(unsigned (&qf)[KS][4], F row_ptr, int lane) {
+  const int g = lane >> 2, c = lane & 3;
+  const bf16* r0 = row_ptr(g);
+  const bf16* r1 = row_ptr(g + 8);
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qf[ks][0] = r0 ? *(const unsigned*)(r0 + ks * 16 + 2 * c) : 0u;
+    qf[ks][1] = r1 ? *(const unsigned*)(r1 + ks * 16 + 2 * c) : 0u;
+    qf[ks][2] = r0 ? *(const unsigned*)(r0 + ks * 16 + 8 + 2 * c) : 0u;
+    qf[ks][3] = r1 ? *(const unsigned*)(r1 + ks * 16 + 8 + 2 * c) : 0u;
+  }
+}
+
+struct AttnArgs {
+  const bf16* q; const bf16* pool; const int* block_table; const int* positions; const int* row_slot;
+  const int* item_start;          // prefill: rows of item i are item_start[i] .. item_start[i+1]
+  bf16* out; float* scratch; int* counters;
+  int max_pages, T, H, G, page_tokens, layer, layers_in_group, window, split_len, max_splits, n_items;
+  float scale_log2;
+};
+
+__device__ __forceinline__ const bf16* key_row(const AttnArgs& a, const int* bt, int g, int key) {
+  int lp = key / a.page_tokens;
+  int page = bt[lp];
+  return a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * ((size_t)a.page_tokens * HD)
+         + (size_t)(key - lp * a.page_tokens) * HD;
+}
+
+// ------------------------------------------------------------------------------------ prefill
+#define PF_WARPS 4
+#define PF_TK 64                 // keys per tile
+#define PF_STAGES 2
+
+__global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int item = blockIdx.z, g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, c = lane & 3;
+  const int R = a.H / a.G;
+  const int tokb = max(1, (PF_WARPS * 16) / R);               // tokens per CTA
+  pdl_launch_dependents();
+  const int row_begin = a.item_start[item], n_rows = a.item_start[item + 1] - row_begin;
+  const int tok0 = blockIdx.x * tokb;
+  if (tok0 >= n_rows) return;
+  const int n_tok = min(tokb, n_rows - tok0);
+  const int pos0 = a.positions[row_begin] + tok0;              // position of the block's first token
+  const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
+  pdl_wait();
+
+  // this thread's two rows: (token, head of the group)
+  int tok[2], hr[2], lo[2], hi[2];
+  bool valid[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    int rho = warp * 16 + gq + 8 * r;
+    tok[r] = rho / R; hr[r] = rho - tok[r] * R;
+    valid[r] = tok[r] < n_tok;
+    int pos = pos0 + tok[r];
+    hi[r] = valid[r] ? pos : -1;
+    lo[r] = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    if (!valid[r]) lo[r] = 1 << 30;
+  }
+  unsigned qf[KS][4];
+  load_q(qf, [&](int i) -> const bf16* {
+    int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
+    return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
+  }, lane);
+
+  float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+  // keys of the whole block: from the first token's window start to the last token's position
+  const int k_first = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
+  const int k_last = pos0 + n_tok - 1;
+  const int n_tiles = (k_last - k_first) / PF_TK + 1;
+  const unsigned s_base = (unsigned)__cvta_generic_to_shared(smem);
+  constexpr int TILE_B = PF_TK * ROWB;                         // bytes of one K (or V) tile
+  auto issue = [&](int j) {
+    if (j < n_tiles) {
+      unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+      int key0 = k_first + j * PF_TK;
+      for (int i = threadIdx.x; i < PF_TK * CPR; i += PF_WARPS * 32) {
+        int row = i / CPR, ch = i - row * CPR;
+        int key = key0 + row;
+        if (key <= k_last) {
+          const bf16* kp = key_row(a, bt, g, key) + ch * 8;
+          cp_async16(ks + tile_off(row, ch), kp);
+          cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * a.page_tokens * HD);
+        } else {                       // past the last key: zeros, so that 0 * V stays 0
+          st_shared_zero16(ks + tile_off(row, ch));
+          st_shared_zero16(vs + tile_off(row, ch));
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  issue(0);
+  for (int j = 0; j < n_tiles; ++j) {
+    issue(j + 1);
+    cp_async_wait<1>();
+    __syncthreads();
+    unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+    int key0 = k_first + j * PF_TK;
+    // a warp whose rows all end before this tile has nothing to add (warp-uniform test)
+    int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
+    if (key0 <= warp_hi && warp * 16 < n_tok * R)
+      attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
+    __syncthreads();                                           // the stage is refilled by the next issue
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    if (!valid[r]) continue;
+    float inv = 1.0f / l[r];
+    bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
+#pragma unroll
+    for (int d = 0; d < DN; ++d)
+      *(unsigned*)(dst + d * 8 + 2 * c) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------------------------ decode
+#define DC_WARPS 4
+#define DC_TK (HD <= 64 ? 32 : 16)   // keys per warp tile: 4 KB (8 KB at the largest heads) of K and of V
+#define DC_STAGES 3
+#define DC_MAX_PAGES 256
+
+__global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int sm_pages[DC_MAX_PAGES];
+  __shared__ int sm_last;
+  const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, c = lane & 3;
+  // positions, slots and block tables are written by copies before the step's kernels, not by a
+  // kernel: they may be read before the wait
+  const int pos = a.positions[t];
+  const int kb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int s_lo = kb / a.split_len, s_hi = pos / a.split_len;
+  pdl_launch_dependents();
+  if (s < s_lo || s > s_hi) return;
+  const int n_active = s_hi - s_lo + 1;
+  const int k0 = max(kb, s * a.split_len), k1 = min(pos + 1, (s + 1) * a.split_len);
+  const int R = a.H / a.G;
+  const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
+  const int pg0 = k0 / a.page_tokens, n_pg = (k1 - 1) / a.page_tokens - pg0 + 1;
+  const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = threadIdx.x; i < n_pg; i += DC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
+  pdl_wait();
+  __syncthreads();
+  constexpr int TILE_B = DC_TK * ROWB;
+  const unsigned ring = (unsigned)__cvta_generic_to_shared(smem) + warp * DC_STAGES * 2 * TILE_B;
+  float* merge = (float*)smem;       // [warp][16][HD + 2], over the rings once every warp is done with them
+  const int SW = HD + 2;
+  const int cta_step = DC_WARPS * DC_TK;
+  const int n_tiles = (k1 - k0 - warp * DC_TK + cta_step - 1) / cta_step;          // may be <= 0
+  const size_t page_elems = (size_t)a.page_tokens * HD;
+  auto issue = [&](int j) {
+    if (j < n_tiles) {
+      unsigned ks = ring + (j % DC_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+      int key0 = k0 + (j * DC_WARPS + warp) * DC_TK;
+      for (int i = lane; i < DC_TK * CPR; i += 32) {
+        int row = i / CPR, ch = i - row * CPR;
+        int key = key0 + row;
+        if (key < k1) {
+          int lp = key / a.page_tokens;
+          int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
+          const bf16* kp = a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * page_elems
+                           + (size_t)(key - lp * a.page_tokens) * HD + ch * 8;
+          cp_async16(ks + tile_off(row, ch), kp);
+          cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * page_elems);
+        } else {                       // past the range: zeros, so that 0 * V stays 0
+          st_shared_zero16(ks + tile_off(row, ch));
+          st_shared_zero16(vs + tile_off(row, ch));
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  for (int r0 = 0; r0 < R; r0 += 16) {                         // groups of more than 16 heads: in blocks
+#pragma unroll
+    for (int j = 0; j < DC_STAGES - 1; ++j) issue(j);
+    unsigned qf[KS][4];
+    load_q(qf, [&](int i) -> const bf16* {
+      return r0 + i < R ? a.q + ((size_t)t * a.H + g * R + r0 + i) * HD : nullptr;
+    }, lane);
+    float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    int lo[2] = {k0, k0}, hi[2] = {k1 - 1, k1 - 1};
+    for (int j = 0; j < n_tiles; ++j) {
+      issue(j + DC_STAGES - 1);
+      cp_async_wait<DC_STAGES - 1>();
+      __syncwarp();
+      unsigned ks = ring + (j % DC_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+      attend_tile<DC_TK / 8>(qf, ks, vs, k0 + (j * DC_WARPS + warp) * DC_TK, lo, hi, a.scale_log2, o, m, l, lane);
+      __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                           // every warp has left its ring
+    // warp result -> shared memory
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      float* rec = merge + ((size_t)warp * 16 + gq + 8 * r) * SW;
+#pragma unroll
+      for (int d = 0; d < DN; ++d) { rec[d * 8 + 2 * c] = o[d][2 * r]; rec[d * 8 + 2 * c + 1] = o[d][2 * r + 1]; }
+      if (c == 0) { rec[HD] = m[r]; rec[HD + 1] = l[r]; }
+    }
+    __syncthreads();
+    const int rows_here = min(16, R - r0);
+    for (int i = threadIdx.x; i < rows_here * HD; i += DC_WARPS * 32) {
+      int row = i / HD, d = i - row * HD;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < DC_WARPS; ++w) mx = fmaxf(mx, merge[((size_t)w * 16 + row) * SW + HD]);
+      float lt = 0.f, at = 0.f;
+#pragma unroll
+      for (int w = 0; w < DC_WARPS; ++w) {
+        const float* rec = merge + ((size_t)w * 16 + row) * SW;
+        float cw = rec[HD] == -INFINITY ? 0.f : exp2f(rec[HD] - mx);
+        lt += rec[HD + 1] * cw;
+        at += rec[d] * cw;
+      }
+      int h = g * R + r0 + row;
+      if (n_active == 1) {
+        a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
+      } else {
+        float* rec = a.scratch + (((size_t)t * a.H + h) * a.max_splits + (s - s_lo)) * SW;
+        rec[d] = at;
+        if (d == 0) { rec[HD] = mx; rec[HD + 1] = lt; }
+      }
+    }
+    __syncthreads();
+  }
+  if (n_active == 1) return;
+
+  // the last CTA of this (row, kv head) merges the ranges in order
+  __threadfence();                                      // every writer publishes its records ...
+  __syncthreads();                                      // ... before thread 0 counts this CTA in
+  if (threadIdx.x == 0) {
+    int old = atomicAdd(&a.counters[t * a.G + g], 1);
+    sm_last = (old == n_active - 1);
+    if (sm_last) a.counters[t * a.G + g] = 0;          // ready for the next launch
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < R * HD; i += DC_WARPS * 32) {
+    int r = i / HD, d = i - r * HD;
+    int h = g * R + r;
+    const float* rec = a.scratch + ((size_t)t * a.H + h) * a.max_splits * SW;
+    float mx = -INFINITY;
+    for (int j = 0; j < n_active; ++j) mx = fmaxf(mx, rec[(size_t)j * SW + HD]);
+    float lt = 0.f, at = 0.f;
+    for (int j = 0; j < n_active; ++j) {
+      float cj = exp2f(rec[(size_t)j * SW + HD] - mx);
+      lt += rec[(size_t)j * SW + HD + 1] * cj;
+      at += rec[(size_t)j * SW + d] * cj;
+    }
+    a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
+  }
+}
+
+static int fill_args(AttnArgs& a, const void* q, const void* pool, const int* block_table, int max_pages,
+                     const int* positions, const int* row_slot, void* out, int T, int H, int G, int hd,
+                     int page_tokens, int layer, int layers_in_group, float scale, int window) {
+  if (hd != HD) return FELLM_ERR_SIZE;
+  if (G < 1 || H % G) return FELLM_ERR_SIZE;
+  if (!q || !pool || !block_table || !positions || !row_slot || !out) return FELLM_ERR_ARG;
+  a.q = (const bf16*)q; a.pool = (const bf16*)pool; a.block_table = block_table; a.positions = positions;
+  a.row_slot = row_slot; a.out = (bf16*)out; a.max_pages = max_pages; a.T = T; a.H = H; a.G = G;
+  a.page_tokens = page_tokens; a.layer = layer; a.layers_in_group = layers_in_group; a.window = window;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.item_start = nullptr; a.scratch = nullptr; a.counters = nullptr; a.split_len = 1; a.max_splits = 1; a.n_items = 0;
+  return 0;
+}
+
+FELLM_API int fellm_attn_head_dim() { return HD; }
+
+// q [T, H, hd], out [T, H*hd]; rows of item i are item_start[i]..item_start[i+1], its positions are
+// consecutive from positions[item_start[i]]; max_item_rows: the longest item of the step.
+FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int* block_table, int max_pages,
+                                     const int* positions, const int* row_slot, const int* item_start, int n_items,
+                                     int max_item_rows, void* out, int T, int H, int G, int hd, int page_tokens,
+                                     int layer, int layers_in_group, float scale, int window, cudaStream_t stream) {
+  if (T <= 0 || n_items <= 0) return 0;
+  AttnArgs a;
+  int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
+                    layers_in_group, scale, window);
+  if (e) return e;
+  if (!item_start) return FELLM_ERR_ARG;
+  int R = H / G;
+  if (R > PF_WARPS * 16) return FELLM_ERR_SIZE;
+  a.item_start = item_start; a.n_items = n_items;
+  int tokb = (PF_WARPS * 16) / R; if (tokb < 1) tokb = 1;
+  size_t smem = (size_t)PF_STAGES * 2 * PF_TK * ROWB;
+  auto kern = attention_prefill_kernel;
+  if (smem > 48 * 1024) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb), G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, a);
+}
+
+// One query row per item.  scratch: float32 [T*H*max_splits*(hd+2)]; counters: int32 [T*G], zero
+// before the first launch (the kernel leaves them zero).  max_splits >= ceil(longest context / split_len).
+FELLM_API int fellm_attn_decode_mma(const void* q, const void* pool, const int* block_table, int max_pages,
+                                    const int* positions, const int* row_slot, void* out, float* scratch,
+                                    int* counters, int T, int H, int G, int hd, int page_tokens, int layer,
+                                    int layers_in_group, float scale, int window, int split_len, int max_splits,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  AttnArgs a;
+  int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
+                    layers_in_group, scale, window);
+  if (e) return e;
+  if (!scratch || !counters || split_len < 1 || max_splits < 1) return FELLM_ERR_ARG;
+  a.scratch = scratch; a.counters = counters; a.split_len = split_len; a.max_splits = max_splits;
+  size_t ring = (size_t)DC_WARPS * DC_STAGES * 2 * DC_TK * ROWB, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
+  size_t smem = ring > mrg ? ring : mrg;
+  auto kern = attention_decode_kernel;
+  if (smem > 48 * 1024) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  return launch_k(kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, a);
+}

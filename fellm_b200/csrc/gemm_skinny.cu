@@ -1,15 +1,18 @@
 // y[M,N] = x[M,K] W[N,K]^T for few rows (decode: M <= 64), bfloat16 operands, float32 sums:
 // a weight-streaming kernel.
 //
-//  * A CTA owns 16 rows of W (one m16 slab, "swap-AB": W is the A operand of mma.m16n8k16, the
-//    tokens are the B operand's columns).  Its 4 warps split the CTA's K range; a thread-block
-//    cluster splits K further where N alone gives too few CTAs.  Partial tiles are summed through
-//    shared memory in warp order and through distributed shared memory in rank order: no atomics,
-//    no scratch in global memory, the same bits every run.
-//  * The weights are read once from HBM with 16-byte loads straight into tensor-core fragments,
-//    and the first 8 KB per warp are requested BEFORE the kernel waits for its predecessor
-//    (programmatic dependent launch): weights do not depend on the step, so HBM keeps streaming
-//    across kernel boundaries.
+//  * Work item: a 16-row slab of W ("swap-AB": the slab is the A operand of mma.m16n8k16, the
+//    tokens are the B operand's columns) times one slice of K.  A warp keeps two rounds of five
+//    32-wide chunks (10 KB) of its item in flight.  Matrices of the decode step are small enough
+//    that the launcher cuts K so finely (over the warps of a CTA, then over a thread-block
+//    cluster) that every item is two rounds and the WHOLE matrix is in flight at once: one trip
+//    to HBM.  Matrices too large for that (the vocabulary head) are streamed, slab after slab.
+//  * A CTA stages its slice of x once, for all its warps.
+//  * The first weights are requested BEFORE the kernel waits for its predecessor (programmatic
+//    dependent launch): weights do not depend on the step, so HBM keeps streaming across kernel
+//    boundaries.
+//  * Split-K partial tiles are summed through distributed shared memory in rank order: no
+//    atomics, no scratch in global memory, the same bits every run.
 //  * Prologue, optional: RMSNorm of the float32 residual stream fused into the staging of x.
 //  * Epilogues: store bfloat16; add into the float32 residual stream; SiLU(gate)*up over weight
 //    rows interleaved in blocks of 8; float32 store (logits).
@@ -27,10 +30,10 @@
 namespace cg = cooperative_groups;
 
 #define SK_ROWS 16
-#define SK_WARPS 4
+#define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 #define KCHUNK 32
-#define SK_U 8                       // chunks a warp keeps in flight: 16 x 16 B per thread
+#define SK_U 5                       // chunks per round: 10 x 16 B per thread, two rounds in flight
 
 enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
 
@@ -54,33 +57,83 @@ struct SkinnyArgs {
   const float* norm_w;      // [K]
   float eps;
   const bf16* W; const float* bias; void* out;
-  int M, N, K, lda, ldw, ldo, k_per_cta, xs_stride, splits;
+  int M, N, K, lda, ldw, ldo, k_per_cta, xs_stride, splits, warps_k, n_tiles, tiles_per_warp;
 };
+
+template <int MT, int EPI>
+__device__ __forceinline__ void epilogue_direct(const SkinnyArgs& a, float (*acc)[4], int n0, int g, int c) {
+  // thread holds rows n0+g, n0+g+8 and tokens t*8 + 2c, 2c+1
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      int m = t * 8 + 2 * c + e;
+      if (m >= a.M) continue;
+      if (EPI == EPI_SWIGLU) {
+        int n = n0 + g;                                   // gate row; the up row is n + 8
+        if (n < a.N) {
+          float gs = acc[t][e], us = acc[t][2 + e];
+          if (a.bias) { gs += a.bias[n]; us += a.bias[n + 8]; }
+          ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + g] = __float2bfloat16_rn((gs / (1.0f + expf(-gs))) * us);
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          int n = n0 + g + 8 * h;
+          if (n >= a.N) continue;
+          float v = acc[t][2 * h + e];
+          if (a.bias) v += a.bias[n];
+          size_t o = (size_t)m * a.ldo + n;
+          if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v);
+          else if (EPI == EPI_ACC) ((float*)a.out)[o] += v;
+          else ((float*)a.out)[o] = v;
+        }
+      }
+    }
+  }
+}
 
 // MT: token tiles of 8 (M <= 8*MT).
 template <int MT, int EPI>
 __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
   __shared__ float row_scale[MT * 8];
+  constexpr int MP = MT * 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = a.splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
-  const int n0 = blockIdx.y * SK_ROWS;
+  // the CTA's warps: wn = which slab of the CTA's pass, wk = which slice of the CTA's K range
+  const int warps_n = SK_WARPS / a.warps_k;
+  const int wn = warp / a.warps_k, wk = warp - wn * a.warps_k;
   const int k_cta = split * a.k_per_cta;
-  const int k_per_warp = a.k_per_cta / SK_WARPS;                    // a multiple of 32
-  const int k_begin = k_cta + warp * k_per_warp;
+  const int k_per_warp = a.k_per_cta / a.warps_k;                    // a multiple of 32
+  const int k_begin = k_cta + wk * k_per_warp;
   const int k_len = max(min(a.K, k_begin + k_per_warp) - k_begin, 0);
   const int n_chunks = (k_len + KCHUNK - 1) / KCHUNK;
+  const int rounds_per_tile = max((n_chunks + SK_U - 1) / SK_U, 1);
+  // this warp's slabs: first_tile, first_tile + tile_stride, ...
+  const int first_tile = blockIdx.y * warps_n + wn;
+  const int tile_stride = gridDim.y * warps_n;
+  int my_tiles = first_tile < a.n_tiles ? (a.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+  const int total_rounds = my_tiles * rounds_per_tile;
+
+  auto load_round = [&](int r, uint4* w0, uint4* w1) {
+    int tl = r / rounds_per_tile, rr = r - tl * rounds_per_tile;
+    int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
+    const bf16* p0 = a.W + (size_t)min(n0 + g, a.N - 1) * a.ldw + k_begin + c * 8;      // rows past N: clamped, never stored
+    const bf16* p1 = a.W + (size_t)min(n0 + g + 8, a.N - 1) * a.ldw + k_begin + c * 8;
+#pragma unroll
+    for (int u = 0; u < SK_U; ++u) {
+      int kk = (rr * SK_U + u) * KCHUNK;
+      if (kk + c * 8 < k_len) { w0[u] = ldg_stream(p0 + kk); w1[u] = ldg_stream(p1 + kk); }
+      else { w0[u] = make_uint4(0, 0, 0, 0); w1[u] = w0[u]; }
+    }
+  };
 
   // ---- weights first: they do not depend on the kernel before this one
-  const bf16* w0 = a.W + (size_t)min(n0 + g, a.N - 1) * a.ldw + k_begin + c * 8;     // rows past N: clamped, never stored
-  const bf16* w1 = a.W + (size_t)min(n0 + g + 8, a.N - 1) * a.ldw + k_begin + c * 8;
-  uint4 a0[SK_U], a1[SK_U];
-#pragma unroll
-  for (int u = 0; u < SK_U; ++u) {
-    if (u * KCHUNK + c * 8 < k_len) { a0[u] = ldg_stream(w0 + u * KCHUNK); a1[u] = ldg_stream(w1 + u * KCHUNK); }
-    else { a0[u] = make_uint4(0, 0, 0, 0); a1[u] = a0[u]; }
-  }
+  uint4 wA0[SK_U], wA1[SK_U], wB0[SK_U], wB1[SK_U];
+  if (total_rounds > 0) load_round(0, wA0, wA1);
+  if (total_rounds > 1) load_round(1, wB0, wB1);
   pdl_launch_dependents();
   pdl_wait();
 
@@ -88,7 +141,7 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
   bf16* xs = (bf16*)smem;
   const int vec_per_row = a.k_per_cta / 8;
   if (a.xf) {
-    // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39): the CTA holds the whole K range
+    // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39) over the whole row, whatever the slice
     for (int r = warp; r < a.M; r += SK_WARPS) {
       const float4* xr = (const float4*)(a.xf + (size_t)r * a.lda);
       float ss = 0.f;
@@ -125,25 +178,23 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
   }
   __syncthreads();
 
-  // ---- this warp's K slice of the CTA's 16 rows
+  // ---- rounds of SK_U chunks; the round after next is requested before this one is multiplied
   float acc[MT][4];
 #pragma unroll
   for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
-  const bf16* xw = xs + (size_t)g * a.xs_stride + warp * k_per_warp + c * 8;
-  for (int ch0 = 0; ch0 < n_chunks; ch0 += SK_U) {
-    if (ch0 > 0) {
-#pragma unroll
-      for (int u = 0; u < SK_U; ++u) {
-        if ((ch0 + u) * KCHUNK + c * 8 < k_len) { a0[u] = ldg_stream(w0 + (ch0 + u) * KCHUNK); a1[u] = ldg_stream(w1 + (ch0 + u) * KCHUNK); }
-        else { a0[u] = make_uint4(0, 0, 0, 0); a1[u] = a0[u]; }
-      }
-    }
+  float* slots = (float*)(smem + (size_t)MT * 8 * a.xs_stride * sizeof(bf16));      // [warp][tile of warp][16][MP], split-K only
+  const bf16* xw = xs + (size_t)g * a.xs_stride + wk * k_per_warp + c * 8;
+  const bool direct = a.splits == 1 && a.warps_k == 1;
+
+  auto compute_round = [&](int r, const uint4* w0, const uint4* w1) {
+    int tl = r / rounds_per_tile, rr = r - tl * rounds_per_tile;
 #pragma unroll
     for (int u = 0; u < SK_U; ++u) {
-      if (ch0 + u < n_chunks) {
-        unsigned fa[4] = {a0[u].x, a1[u].x, a0[u].y, a1[u].y};
-        unsigned fb[4] = {a0[u].z, a1[u].z, a0[u].w, a1[u].w};
-        const bf16* xr = xw + (ch0 + u) * KCHUNK;
+      int ch = rr * SK_U + u;
+      if (ch < n_chunks) {
+        unsigned fa[4] = {w0[u].x, w1[u].x, w0[u].y, w1[u].y};
+        unsigned fb[4] = {w0[u].z, w1[u].z, w0[u].w, w1[u].w};
+        const bf16* xr = xw + ch * KCHUNK;
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
           uint4 b = *(const uint4*)(xr + (size_t)t * 8 * a.xs_stride);
@@ -152,99 +203,100 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
         }
       }
     }
-  }
-
-  // ---- warps' partial tiles -> shared memory -> the CTA's tile red[row][token]
-  __syncthreads();                                   // x staging is done with; reuse the buffer
-  constexpr int MP = MT * 8;
-  float* part = (float*)smem;                        // [warp][16][MP]
-  float* red = part + SK_WARPS * SK_ROWS * MP;       // [16][MP]
-  {
-    float* p = part + (size_t)warp * SK_ROWS * MP;
+    if (rr == rounds_per_tile - 1) {                      // the slab is done
+      int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
+      if (direct) {
+        epilogue_direct<MT, EPI>(a, acc, n0, g, c);
+      } else {
+        float* p = slots + ((size_t)warp * a.tiles_per_warp + tl) * SK_ROWS * MP;
 #pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      p[g * MP + t * 8 + 2 * c] = acc[t][0];
-      p[g * MP + t * 8 + 2 * c + 1] = acc[t][1];
-      p[(g + 8) * MP + t * 8 + 2 * c] = acc[t][2];
-      p[(g + 8) * MP + t * 8 + 2 * c + 1] = acc[t][3];
+        for (int t = 0; t < MT; ++t) {
+          p[g * MP + t * 8 + 2 * c] = acc[t][0];
+          p[g * MP + t * 8 + 2 * c + 1] = acc[t][1];
+          p[(g + 8) * MP + t * 8 + 2 * c] = acc[t][2];
+          p[(g + 8) * MP + t * 8 + 2 * c + 1] = acc[t][3];
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+    }
+  };
+
+  for (int r = 0; r < total_rounds; r += 2) {
+    compute_round(r, wA0, wA1);
+    if (r + 2 < total_rounds) load_round(r + 2, wA0, wA1);
+    if (r + 1 < total_rounds) {
+      compute_round(r + 1, wB0, wB1);
+      if (r + 3 < total_rounds) load_round(r + 3, wB0, wB1);
     }
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < SK_ROWS * MP; i += SK_THREADS) {
-    float v = part[i];
-#pragma unroll
-    for (int w = 1; w < SK_WARPS; ++w) v += part[w * SK_ROWS * MP + i];
-    red[i] = v;
-  }
+  if (direct) return;
+
+  // ---- split K: sum the partial slabs over the cluster's ranks and the CTA's K warps, in that
+  // order; every (rank, K warp) finishes a share of each slab's rows
   if (a.splits > 1) cg::this_cluster().sync(); else __syncthreads();
-
-  // ---- sum over the cluster in rank order, epilogue; each rank finishes a share of the rows
-  if (EPI == EPI_SWIGLU) {
-    // rows 0-7 are gate, rows 8-15 the up rows of the same 8 features
-    const int per_rank = 8 / a.splits, j0 = split * per_rank;
-    for (int i = threadIdx.x; i < per_rank * a.M; i += SK_THREADS) {
-      int m = i / per_rank, j = j0 + (i - m * per_rank);
-      float gs = 0.f, us = 0.f;
+  const int workers = a.splits * a.warps_k, me = split * a.warps_k + wk;
+  const float* slab_slots = slots + (size_t)(wn * a.warps_k) * a.tiles_per_warp * SK_ROWS * MP;   // K warp 0 of this slab
+  const size_t warp_stride = (size_t)a.tiles_per_warp * SK_ROWS * MP;
+  for (int tl = 0; tl < my_tiles; ++tl) {
+    int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
+    const float* mine = slab_slots + (size_t)tl * SK_ROWS * MP;
+    const int units = (EPI == EPI_SWIGLU ? 8 : SK_ROWS) * a.M;          // outputs of the slab
+    for (int i = me * 32 + lane; i < units; i += workers * 32) {
+      int m, j;
+      if (EPI == EPI_SWIGLU) { m = i >> 3; j = i & 7; } else { m = i >> 4; j = i & 15; }
+      float v0 = 0.f, v1 = 0.f;
       for (int s = 0; s < a.splits; ++s) {
-        const float* p = a.splits > 1 ? cg::this_cluster().map_shared_rank(red, s) : red;
-        gs += p[j * MP + m];
-        us += p[(j + 8) * MP + m];
+        const float* p = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine, s) : mine;
+        for (int w = 0; w < a.warps_k; ++w) {
+          v0 += p[w * warp_stride + j * MP + m];
+          if (EPI == EPI_SWIGLU) v1 += p[w * warp_stride + (j + 8) * MP + m];
+        }
       }
       int n = n0 + j;
-      if (n < a.N) {
-        if (a.bias) { gs += a.bias[n]; us += a.bias[n + 8]; }
-        ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((gs / (1.0f + expf(-gs))) * us);
-      }
-    }
-  } else {
-    const int per_rank = SK_ROWS / a.splits, j0 = split * per_rank;
-    for (int i = threadIdx.x; i < per_rank * a.M; i += SK_THREADS) {
-      int m = i / per_rank, j = j0 + (i - m * per_rank);
-      float v = 0.f;
-      for (int s = 0; s < a.splits; ++s) {
-        const float* p = a.splits > 1 ? cg::this_cluster().map_shared_rank(red, s) : red;
-        v += p[j * MP + m];
-      }
-      int n = n0 + j;
-      if (n < a.N) {
-        if (a.bias) v += a.bias[n];
+      if (n >= a.N) continue;
+      if (EPI == EPI_SWIGLU) {
+        if (a.bias) { v0 += a.bias[n]; v1 += a.bias[n + 8]; }
+        ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((v0 / (1.0f + expf(-v0))) * v1);
+      } else {
+        if (a.bias) v0 += a.bias[n];
         size_t o = (size_t)m * a.ldo + n;
-        if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v);
-        else if (EPI == EPI_ACC) ((float*)a.out)[o] += v;
-        else ((float*)a.out)[o] = v;
+        if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
+        else if (EPI == EPI_ACC) ((float*)a.out)[o] += v0;
+        else ((float*)a.out)[o] = v0;
       }
     }
   }
-  if (a.splits > 1) cg::this_cluster().sync();         // nobody leaves while its tile is being read
+  if (a.splits > 1) cg::this_cluster().sync();           // nobody leaves while its slabs are being read
 }
 
 // Staged x rows are k_per_cta + pad elements apart, with the stride in bytes = 64 (mod 128): the 8
 // threads of a quarter warp then read 16 bytes each from 8 different bank groups.
 static inline int x_stride(int k_per_cta) { return k_per_cta + ((k_per_cta % 64 == 0) ? 32 : 0); }
 
-static inline size_t smem_bytes(int mt, int k_per_cta) {
+static inline size_t smem_bytes(int mt, int k_per_cta, bool direct, int tiles_per_warp) {
   size_t sx = (size_t)mt * 8 * x_stride(k_per_cta) * sizeof(bf16);
-  size_t sp = (size_t)(SK_WARPS + 1) * SK_ROWS * mt * 8 * sizeof(float);
-  return sx > sp ? sx : sp;
+  size_t sp = direct ? 0 : (size_t)SK_WARPS * tiles_per_warp * SK_ROWS * mt * 8 * sizeof(float);
+  return sx + sp;
 }
 
 template <int MT, int EPI>
-static int launch(const SkinnyArgs& a, cudaStream_t stream) {
-  size_t smem = smem_bytes(MT, a.k_per_cta);
+static int launch(const SkinnyArgs& a, int ctas_y, cudaStream_t stream) {
+  size_t smem = smem_bytes(MT, a.k_per_cta, a.splits == 1 && a.warps_k == 1, a.tiles_per_warp);
   auto kern = gemm_skinny_kernel<MT, EPI>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_k(kern, dim3(a.splits, ceil_div(a.N, SK_ROWS), 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+  return launch_k(kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
 }
 
 template <int EPI>
-static int dispatch_mt(const SkinnyArgs& a, cudaStream_t s) {
-  if (a.M <= 8) return launch<1, EPI>(a, s);
-  if (a.M <= 16) return launch<2, EPI>(a, s);
-  if (a.M <= 32) return launch<4, EPI>(a, s);
-  return launch<8, EPI>(a, s);
+static int dispatch_mt(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
+  if (a.M <= 8) return launch<1, EPI>(a, ctas_y, s);
+  if (a.M <= 16) return launch<2, EPI>(a, ctas_y, s);
+  if (a.M <= 32) return launch<4, EPI>(a, ctas_y, s);
+  return launch<8, EPI>(a, ctas_y, s);
 }
 
 // epi: 0 store bf16 [M,N]; 1 add into float32 [M,N]; 2 SiLU(gate)*up -> bf16 [M,N/2], W rows
@@ -258,28 +310,59 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   if (xf && !norm_w) return FELLM_ERR_ARG;
   if (M > 64 || (K % 8) || (ldw % 8)) return FELLM_ERR_SIZE;
   if (x && (lda % 8)) return FELLM_ERR_SIZE;
-  if (xf && ((lda % 4) || (K % 8))) return FELLM_ERR_SIZE;
+  if (xf && (lda % 4)) return FELLM_ERR_SIZE;
   if (epi == EPI_SWIGLU && (N % 16)) return FELLM_ERR_SIZE;
   int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
-  const size_t smem_cap = 160 * 1024;
-  // split K over a cluster while N alone gives too few CTAs and the slices stay worth a warp's while
-  int tiles = ceil_div(N, SK_ROWS);
-  int splits = 1;
-  auto kpc = [&](int s) { return ceil_div(ceil_div(K, s), SK_WARPS * KCHUNK) * SK_WARPS * KCHUNK; };
-  if (!xf) {
-    while (splits < 8 && tiles * splits < 256 && K / (splits * 2) >= 256) splits *= 2;
+  const size_t smem_cap = 100 * 1024;                     // two CTAs per SM
+  const int resident_warps = 148 * 2 * SK_WARPS;
+  const int in_flight = 2 * SK_U * KCHUNK;                // k a warp holds in flight: two rounds
+  int n_tiles = ceil_div(N, SK_ROWS);
+  auto round_k = [&](int k) { return ceil_div(k, KCHUNK) * KCHUNK; };
+  // Plan A, "all in flight": cut K into power-of-two many slices of at most `in_flight`, first over
+  // the warps of a CTA (up to 8), then over a cluster (up to 8); taken when every (slab, slice)
+  // item finds a warp of its own, so that the whole matrix is requested at once.
+  // Plan B, "streaming": a warp walks over whole-K slabs, two rounds ahead.
+  int slices = 1;
+  while (slices < 64 && ceil_div(K, slices) > in_flight) slices *= 2;
+  int warps_k = slices < SK_WARPS ? slices : SK_WARPS, splits = slices / warps_k;
+  bool plan_a = (long long)n_tiles * slices <= resident_warps + resident_warps / 4;
+  int ctas_y = 1, tiles_per_warp = 1, k_per_cta = 0;
+  if (plan_a) {
+    k_per_cta = round_k(ceil_div(K, slices)) * warps_k;
+    ctas_y = ceil_div(n_tiles, SK_WARPS / warps_k);
+    if (ctas_y > (148 * 2) / splits) ctas_y = (148 * 2) / splits;
+    tiles_per_warp = ceil_div(n_tiles, ctas_y * (SK_WARPS / warps_k));
+    if (smem_bytes(mt, k_per_cta, slices == 1, tiles_per_warp) > 200 * 1024) plan_a = false;
   }
-  while (splits < 8 && smem_bytes(mt, kpc(splits)) > smem_cap && !xf) splits *= 2;
-  if (smem_bytes(mt, kpc(splits)) > 200 * 1024) return FELLM_ERR_SIZE;
+  if (!plan_a) {
+    // whole K per warp where x fits; else split K over a cluster until it does (two CTAs per SM if
+    // that can be had, one otherwise)
+    warps_k = 1;
+    bool found = false;
+    for (int pass = 0; pass < 2 && !found; ++pass) {
+      size_t cap = pass == 0 ? smem_cap : (size_t)200 * 1024;
+      for (splits = 1; splits <= 8; splits *= 2) {
+        k_per_cta = round_k(ceil_div(K, splits));
+        ctas_y = ceil_div(n_tiles, SK_WARPS);
+        if (ctas_y > (148 * 2) / splits) ctas_y = (148 * 2) / splits;
+        if (ctas_y < 1) ctas_y = 1;
+        tiles_per_warp = ceil_div(n_tiles, ctas_y * SK_WARPS);
+        if (smem_bytes(mt, k_per_cta, splits == 1, tiles_per_warp) <= cap) { found = true; break; }
+      }
+    }
+    if (!found) splits = 16;
+    if (splits > 8) return FELLM_ERR_SIZE;
+  }
   SkinnyArgs a;
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = out;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo; a.splits = splits;
-  a.k_per_cta = kpc(splits); a.xs_stride = x_stride(a.k_per_cta);
+  a.warps_k = warps_k; a.k_per_cta = k_per_cta; a.xs_stride = x_stride(k_per_cta);
+  a.n_tiles = n_tiles; a.tiles_per_warp = tiles_per_warp;
   switch (epi) {
-    case EPI_STORE: return dispatch_mt<EPI_STORE>(a, stream);
-    case EPI_ACC: return dispatch_mt<EPI_ACC>(a, stream);
-    case EPI_SWIGLU: return dispatch_mt<EPI_SWIGLU>(a, stream);
-    case EPI_F32: return dispatch_mt<EPI_F32>(a, stream);
+    case EPI_STORE: return dispatch_mt<EPI_STORE>(a, ctas_y, stream);
+    case EPI_ACC: return dispatch_mt<EPI_ACC>(a, ctas_y, stream);
+    case EPI_SWIGLU: return dispatch_mt<EPI_SWIGLU>(a, ctas_y, stream);
+    case EPI_F32: return dispatch_mt<EPI_F32>(a, ctas_y, stream);
     default: return FELLM_ERR_ARG;
   }
 }

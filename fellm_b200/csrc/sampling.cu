@@ -373,4 +373,64 @@ FELLM_API int fellm_count_tokens(int* counts, int V, const int* slots, const int
   return launch_status();
 }
 
+// ---- greedy fast path: rows without penalties or bias.  Two launches: every row is cut into
+// ARGMAX_CHUNKS pieces reduced by one block each, then one warp per row reduces the pieces.
+// Ties go to the lower id at both stages (sampling.rs:588-604).
+#define ARGMAX_CHUNKS 64
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ pval, int* __restrict__ pidx) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int row = blockIdx.y, chunk = blockIdx.x;
+  int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  int lo = chunk * per, hi = min(V, lo + per);
+  const float* lg = logits + (size_t)row * V;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int v = lo + threadIdx.x; v < hi; v += 256) {
+    float x = lg[v];
+    if (x > best) { best = x; bi = v; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  __shared__ float sb[8]; __shared__ int si[8];
+  if ((threadIdx.x & 31) == 0) { sb[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sb[w] > best || (sb[w] == best && si[w] < bi)) { best = sb[w]; bi = si[w]; }
+    pval[row * ARGMAX_CHUNKS + chunk] = best;
+    pidx[row * ARGMAX_CHUNKS + chunk] = bi;
+  }
+}
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int row = blockIdx.x, lane = threadIdx.x;
+  float best = -INFINITY; int bi = 0x7fffffff;
+  for (int c = lane; c < ARGMAX_CHUNKS; c += 32) {
+    float x = pval[row * ARGMAX_CHUNKS + c]; int i = pidx[row * ARGMAX_CHUNKS + c];
+    if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  if (lane == 0) out_tokens[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// pval / pidx: scratch of rows * 64 entries each.
+FELLM_API int fellm_argmax_rows(const float* logits, int rows, int V, float* pval, int* pidx, int* out_tokens,
+                                cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!logits || !pval || !pidx || !out_tokens || V < 1) return FELLM_ERR_ARG;
+  int e = launch_k(argmax_partial_kernel, dim3(ARGMAX_CHUNKS, rows), dim3(256), 0, stream, 1, logits, V, pval, pidx);
+  if (e) return e;
+  return launch_k(argmax_final_kernel, dim3(rows), dim3(32), 0, stream, 1, (const float*)pval, (const int*)pidx, out_tokens);
+}
+
 FELLM_API int fellm_sample_params_size() { return (int)sizeof(RowParams); }

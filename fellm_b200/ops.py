@@ -366,40 +366,74 @@ def decode_split(max_len: int, rows: int, kv_heads: int):
     return split_len, -(-bucket // split_len)
 
 
-def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, window, max_len, out=None):
-    """One query row per request (bfloat16): split-KV decode attention.  q [T, H, hd]."""
-    _dev(q, pool, block_table, positions, row_slot)
+def _mma_checks(q, pool, what):
     T, H, hd = q.shape
-    G, page_tokens = pool.shape[3], pool.shape[4]
     if q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16:
-        raise KernelError("attention_decode takes bfloat16 queries and cache")
-    if hd % 8 or hd > 256:
-        raise KernelError(f"attention_decode: head_dim {hd} must be a multiple of 8, at most 256")
+        raise KernelError(f"{what} takes bfloat16 queries and cache")
+    if hd % 16 or not 16 <= hd <= 256:
+        raise KernelError(f"{what}: head_dim {hd} must be a multiple of 16 in 16..256")
+    G = pool.shape[3]
+    if H % G:
+        raise KernelError(f"{what}: {H} heads are not a multiple of {G} kv heads")
+    assert q.is_contiguous() and pool.is_contiguous() and pool.shape[5] == hd
+    return T, H, G, hd, pool.shape[4]
+
+
+def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, window, max_len, out=None):
+    """One query row per request (bfloat16): split-KV decode attention on tensor cores.
+    q [T, H, hd] -> [T, H*hd].  The kernel library is compiled for this head size."""
+    _dev(q, pool, block_table, positions, row_slot)
+    T, H, G, hd, page_tokens = _mma_checks(q, pool, "attention_decode")
     split_len, max_splits = decode_split(max_len, T, G)
     scratch, counters = reserve_decode_scratch(q.device, T, H, G, hd, max_splits)
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
-    f = _fn("attention_decode", "fellm_attention_decode",
+    f = _fn("attention_mma", "fellm_attn_decode_mma",
             [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_f, _c_int, _c_int, _c_int, _c_p])
+             _c_int, _c_f, _c_int, _c_int, _c_int, _c_p], defines={"HD": hd})
     _check(f(_p(q), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(out),
              _p(scratch), _p(counters), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
              int(window or 0), split_len, max_splits, _stream()), "attention_decode")
     return out
 
 
+def attention_prefill(q, pool, block_table, positions, row_slot, item_start, n_items, max_item_rows, layer, scale,
+                      window, out=None):
+    """Portions of prompts (items of any length, one token included) on tensor cores (bfloat16).
+    Rows of item i are item_start[i]..item_start[i+1] with consecutive positions."""
+    _dev(q, pool, block_table, positions, row_slot, item_start)
+    T, H, G, hd, page_tokens = _mma_checks(q, pool, "attention_prefill")
+    if H // G > 64:
+        raise KernelError(f"attention_prefill: {H // G} heads per kv head exceed the kernel's 64")
+    _i32(item_start, "item_start")
+    if out is None:
+        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    f = _fn("attention_mma", "fellm_attn_prefill_mma",
+            [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_f, _c_int, _c_p], defines={"HD": hd})
+    _check(f(_p(q), _p(pool), _p(block_table), block_table.shape[1], _p(positions), _p(row_slot), _p(item_start),
+             n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
+             int(window or 0), _stream()), "attention_prefill")
+    return out
+
+
 def attention_modules(dtype: str, head_dim: int):
     mods = [("attention_simt", None)]
     if dtype == "bfloat16":
-        mods.append(("attention_decode", None))
+        mods.append(("attention_mma", {"HD": head_dim}))
     return mods
 
 
 def paged_attention(q, cache, ctx, scale, window=None):
-    """Attention of the step's rows over their items' cache pages; picks the kernel."""
-    if q.dtype == torch.bfloat16 and ctx.all_single:
-        return attention_decode(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
-                                scale, window, ctx.max_len)
+    """Attention of the step's rows over their items' cache pages; picks the kernel: the float32
+    engine runs on CUDA cores; bfloat16 on tensor cores, split over the keys when every item
+    brings one token."""
+    if q.dtype == torch.bfloat16:
+        if ctx.all_single:
+            return attention_decode(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
+                                    scale, window, ctx.max_len)
+        return attention_prefill(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, ctx.item_start,
+                                 ctx.n_items, ctx.max_item_rows, cache.layer, scale, window)
     return paged_attention_simt(q, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
                                 scale, window)
 
@@ -422,6 +456,16 @@ def sample(logits, params_dev, counts, bias_tok, bias_val, out_tokens, out_probs
     f = _fn("sampling", "fellm_sample", [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p])
     _check(f(_p(logits), B, V, _p(params_dev), _p(counts), _p(bias_tok), _p(bias_val), _p(out_tokens),
              _p(out_probs), int(update_counts), _stream()), "sample")
+    return out_tokens
+
+
+def argmax_rows(logits, pval, pidx, out_tokens):
+    """Greedy tokens of float32 logits [B, V], ties to the lower id; pval/pidx: scratch [B*64]."""
+    _dev(logits, pval, pidx, out_tokens)
+    B, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and pval.numel() >= B * 64 and pidx.numel() >= B * 64
+    f = _fn("sampling", "fellm_argmax_rows", [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p])
+    _check(f(_p(logits), B, V, _p(pval), _p(pidx), _p(out_tokens), _stream()), "argmax_rows")
     return out_tokens
 
 

@@ -31,6 +31,8 @@ class Sampler:
         self.params_dev = torch.zeros(max_rows * size, dtype=torch.uint8, device=device)
         self.out_tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
+        self.arg_val = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
+        self.arg_idx = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
         self.counts: Optional[torch.Tensor] = None
         self._copy_done = torch.cuda.Event()
         self._copy_pending = False
@@ -57,6 +59,10 @@ class Sampler:
         assert logits.shape[0] == n and logits.dtype == torch.float32 and logits.is_contiguous()
         if n > self.max_rows:
             raise KernelError(f"{n} rows to sample exceed the sampler's {self.max_rows}")
+        if not return_probs and all(p.is_greedy() and not p.uses_history() and not p.logit_bias for _, p, _ in rows):
+            # plain argmax: no per-row parameters to ship, the row is reduced by 64 blocks at once
+            ops.argmax_rows(logits, self.arg_val, self.arg_idx, self.out_tokens)
+            return self.out_tokens[:n]
         if self._copy_pending:
             self._copy_done.synchronize()
         rec = self.params_np

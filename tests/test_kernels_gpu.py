@@ -383,3 +383,68 @@ def test_gemm_bf16_fused_rmsnorm_prologue(M, N, K):
     unfused = ops.gemm_bf16(ops.rmsnorm(x.to(DEV), nw.to(DEV), 1e-5, torch.bfloat16), w.to(DEV), out_dtype=torch.float32)
     assert torch.allclose(got, unfused, rtol=2e-3, atol=2e-2 * 0.05 * math.sqrt(K) / 8)
     assert not ops.norm_fusable(torch.zeros(17, K, device=DEV), w.to(DEV), nw.to(DEV))
+
+
+@pytest.mark.parametrize("H,G,hd,page_tokens,window", [(16, 8, 64, 64, None), (6, 1, 48, 16, None), (4, 4, 128, 32, None),
+                                                       (24, 8, 64, 16, None), (8, 1, 16, 16, 70), (5, 5, 80, 8, None),
+                                                       (2, 1, 256, 64, 300), (20, 1, 32, 16, None)])
+def test_attention_prefill_mma(H, G, hd, page_tokens, window):
+    """Items of mixed lengths in one launch (a portion that starts mid-sequence, a whole prompt, a
+    single decoded token, two tokens), pages out of order, against the plain attention."""
+    torch.manual_seed(H * 3 + hd)
+    ctx_before = [150, 0, 700, 33, 0]           # cached positions before this step's rows
+    new = [97, 130, 1, 2, 64]                   # rows each item brings
+    n = len(new)
+    total = [a + b for a, b in zip(ctx_before, new)]
+    n_pg = [-(-t // page_tokens) for t in total]
+    perm = torch.randperm(sum(n_pg), generator=torch.Generator().manual_seed(2)).tolist()
+    pool = torch.randn(sum(n_pg) + 1, 2, 2, G, page_tokens, hd, device=DEV).bfloat16()
+    table = torch.full((n + 1, max(n_pg) + 1), -1, dtype=torch.int32)
+    keys, values, at = [], [], 0
+    for r in range(n):
+        k, v = torch.randn(total[r], G, hd).bfloat16(), torch.randn(total[r], G, hd).bfloat16()
+        keys.append(k); values.append(v)
+        for p in range(n_pg[r]):
+            page = perm[at] + 1; at += 1
+            table[r + 1, p] = page
+            lo, hi = p * page_tokens, min(total[r], (p + 1) * page_tokens)
+            pool[page, 1, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1).to(DEV)
+            pool[page, 1, 1, :, :hi - lo] = v[lo:hi].transpose(0, 1).to(DEV)
+    T = sum(new)
+    q = torch.randn(T, H, hd).bfloat16()
+    starts = [0]
+    for x in new:
+        starts.append(starts[-1] + x)
+    positions = [ctx_before[r] + j for r in range(n) for j in range(new[r])]
+    row_slot = [r + 1 for r in range(n) for _ in range(new[r])]
+    got = ops.attention_prefill(q.to(DEV), pool, table.to(DEV), i32(positions), i32(row_slot), i32(starts), n,
+                                max(new), 1, hd ** -0.5, window)
+    got = got.float().cpu().reshape(T, H, hd)
+    for r in range(n):
+        rows = slice(starts[r], starts[r + 1])
+        want = P.paged_attention_rows(q[rows].float(), keys[r].float(), values[r].float(),
+                                      torch.tensor(positions[rows]), scale=hd ** -0.5, window=window)
+        assert torch.allclose(got[rows], want, rtol=2e-2, atol=2e-2), (r, (got[rows] - want).abs().max())
+    # and the float32-arithmetic kernel agrees on the same cache
+    simt = ops.paged_attention_simt(q.to(DEV), pool, table.to(DEV), i32(positions), i32(row_slot), 1, hd ** -0.5, window)
+    assert torch.allclose(simt.float().cpu().reshape(T, H, hd), got, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("far,qpos", [(0, 999), (63, 999), (64, 999), (935, 999), (936, 1000), (999, 999)])
+def test_attention_prefill_finds_one_far_key(far, qpos):
+    """One key stands out among a thousand; the query block straddles it or lies far behind it."""
+    H, G, hd, pt, C = 4, 2, 64, 64, 1001
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    d = torch.randn(hd); d = d / d.norm()
+    keys[far] = d * 30.0
+    n_new = 70
+    q = torch.randn(n_new, H, hd) * 0.1
+    row = qpos - (C - n_new)
+    q[row] = d * 30.0
+    pool, table = build_cache(keys, values, pt, list(range(1, 1 + -(-C // pt))), torch.bfloat16)
+    positions = list(range(C - n_new, C))
+    got = ops.attention_prefill(q.to(DEV).bfloat16(), pool, table, i32(positions), i32([1] * n_new), i32([0, n_new]), 1,
+                                n_new, 1, hd ** -0.5, None)
+    got = got.float().cpu().reshape(n_new, H, hd)
+    for h in range(H):
+        assert torch.allclose(got[row, h], values[far, h // 2].bfloat16().float(), atol=2e-2), (far, h)

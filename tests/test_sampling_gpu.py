@@ -90,3 +90,15 @@ def test_penalties_and_bias():
     assert torch.allclose(probs[0], torch.softmax(adj, 0), rtol=1e-4, atol=1e-7)
     s.start_request(1, [3], GenParams.greedy())             # the slot's history starts again
     assert int(s.counts[1].sum()) == 0
+
+
+@pytest.mark.parametrize("V", [515, 65536, 70001])
+def test_greedy_fast_path_equals_the_general_kernel(V):
+    s = Sampler(V, 4, 16, DEV)
+    logits = torch.randn(9, V)
+    logits[3, 100] = logits[3, V - 1] = 40.0                # tie across chunks: the lower id
+    logits[4, :] = -float("inf")
+    fast = s.sample(logits.to(DEV), [(0, GenParams.greedy(), 0)] * 9).cpu().tolist()
+    slow, _ = s.sample(logits.to(DEV), [(0, GenParams.greedy(), 0)] * 9, return_probs=True)
+    assert fast == slow.cpu().tolist()
+    assert fast[3] == 100 and fast[4] == 0 and fast[0] == int(torch.argmax(logits[0]))
