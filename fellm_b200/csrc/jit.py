@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -88,7 +89,13 @@ def _source_hash(name: str, dkey: Tuple) -> str:
     src = CSRC / f"{name}.cu"
     if not src.exists():
         raise KernelError(f"no kernel source {src}")
-    h.update(src.read_bytes())
+    text = src.read_bytes()
+    h.update(text)
+    for inc in sorted(set(re.findall(rb'#include\s+"([^"]+\.(?:cu|h))"', text))):      # sources a module pulls in
+        f = CSRC / inc.decode()
+        if f.exists():
+            h.update(inc)
+            h.update(f.read_bytes())
     for hdr in sorted(CSRC.glob("*.cuh")):
         h.update(hdr.name.encode())
         h.update(hdr.read_bytes())
