@@ -65,7 +65,7 @@ class Engine:
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
                                device=self.device, cuda_graphs=options.cuda_graphs)
-        self.sampler = Sampler(spec.vocab_size, options.max_requests, options.max_requests, self.device)
+        self._sampler: Optional[Sampler] = None
         self._tok_host = torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True)
         self._scheduler: Optional[Scheduler] = None
 
@@ -109,6 +109,14 @@ class Engine:
         cap = self.options.max_requests * self.n_ctx
         tokens = max(min(tokens, cap), self.options.page_tokens)
         return tokens - tokens % self.options.page_tokens
+
+    @property
+    def sampler(self) -> Sampler:
+        """Made on first use: replaying a trace samples nothing and need not build the sampling kernels."""
+        if self._sampler is None:
+            self._sampler = Sampler(self.spec.vocab_size, self.options.max_requests, self.options.max_requests,
+                                    self.device)
+        return self._sampler
 
     # ---- the step function and request bookkeeping around it
     def add_request(self, req):
