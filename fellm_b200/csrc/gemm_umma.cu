@@ -1,0 +1,273 @@
+// C[M,N] = A[M,K] W[N,K]^T for many rows (prefill), bfloat16 operands, float32 accumulation in
+// tensor memory: the Blackwell path.  tcgen05.mma (cta_group::1, kind::f16, 128x128x16) issued by
+// one thread, operands brought by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of
+// four 32 KB stages, accumulator read back with tcgen05.ld for a fused epilogue: store, add into
+// the float32 residual stream, SiLU(gate)*up over weight rows interleaved in blocks of 8, float32
+// store.
+//
+// Roles in a CTA of 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane)
+// and owner of the tensor-memory allocation, warps 2-5 = epilogue (TMEM lane quarter = warp % 4).
+// Every wait on an mbarrier is bounded: after a second of polling a role records the barrier it gave up
+// on in `status`, and all roles fall through to the common exit, where tensor memory is freed.
+//
+// FeLLM counterpart: bf16_matmul_rows, one thread per output
+// (plugins/cuda_kernels/src/oxide_kernels.rs:3165).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define UM_BM 128
+#define UM_BN 128
+#define UM_BK 64                      // one 128-byte swizzle atom of bfloat16 per row
+#define UM_STAGES 4
+#define UM_THREADS 192
+#define UM_STAGE_BYTES ((UM_BM + UM_BN) * UM_BK * 2)
+#define UM_SPIN_LIMIT (1u << 26)
+#define UM_WAIT_NS 1000000000ull       // one second: far beyond any healthy wait, short enough to stay responsive
+
+enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait: false (and *status set) if the phase has not completed after UM_WAIT_NS.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned i = 0; i < UM_SPIN_LIMIT; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 63) == 63 && global_ns() - t0 > UM_WAIT_NS) break;
+  }
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);          // start address
+  d |= (unsigned long long)(1024 >> 4) << 32;                     // stride byte offset: next 8-row group
+  d |= 1ull << 46;                                                // descriptor version (sm_100)
+  d |= 2ull << 61;                                                // SWIZZLE_128B
+  return d;
+}
+// kind::f16: D float32, A and B bfloat16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ unsigned umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                         unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
+  unsigned* r = reinterpret_cast<unsigned*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+struct UmmaArgs {
+  const float* bias; void* out; int* status;
+  int M, N, K, ldo;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(UM_THREADS)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * UM_STAGES + 1];    // full[], empty[], accumulator
+  __shared__ unsigned tmem_base_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the dynamic buffer is aligned by hand: swizzled TMA tiles want 1024 bytes
+  unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[UM_STAGES]), accbar = smem_u32(&bars[2 * UM_STAGES]);
+  const int m0 = blockIdx.y * UM_BM, n0 = blockIdx.x * UM_BN;
+  const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(accbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {                   // tensor memory: 128 columns of float32 for the 128x128 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(UM_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+  pdl_launch_dependents();
+  pdl_wait();                        // A is the output of the kernel before this one
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        int s = kb % UM_STAGES;
+        unsigned round = kb / UM_STAGES;
+        if (kb >= UM_STAGES && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.status, 101)) break;
+        unsigned dst = tiles + s * UM_STAGE_BYTES;
+        mbar_expect_tx(full0 + 8 * s, UM_STAGE_BYTES);
+        tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
+        tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = umma_idesc(UM_BM, UM_BN);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        int s = kb % UM_STAGES;
+        ok = mbar_wait(full0 + 8 * s, (kb / UM_STAGES) & 1, a.status, 102);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        unsigned sa = tiles + s * UM_STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
+        unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+        for (int k = 0; k < UM_BK / 16; ++k)            // 32 bytes further along K inside the swizzle atom
+          umma_f16(tmem_base, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
+      }
+      umma_commit(accbar);                              // arrives when every MMA issued so far is done
+    }
+  } else {
+    // epilogue warps: TMEM lanes 32*(warp%4) .. +32 = output rows
+    const int q = warp & 3;
+    bool ok = mbar_wait(accbar, 0, a.status, 103);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const int m = m0 + q * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < UM_BN; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);      // whole warp, also for rows past M
+        if (m >= a.M) continue;
+        const int n = n0 + c0;
+        if (EPI == EPI_SWIGLU) {
+          // columns: 8 gate, 8 up, 8 gate, 8 up -> 16 features
+          bf16* dst = (bf16*)a.out + (size_t)m * a.ldo + (n >> 1);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (n + 16 * h >= a.N) break;
+            unsigned packed[4];
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+              float g0 = v[16 * h + j], g1 = v[16 * h + j + 1], u0 = v[16 * h + 8 + j], u1 = v[16 * h + 9 + j];
+              if (a.bias) { g0 += a.bias[n + 16 * h + j]; g1 += a.bias[n + 16 * h + j + 1]; u0 += a.bias[n + 16 * h + 8 + j]; u1 += a.bias[n + 16 * h + 9 + j]; }
+              __nv_bfloat162 p = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+              packed[j >> 1] = *(unsigned*)&p;
+            }
+            *(uint4*)(dst + 8 * h) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n + j >= a.N) break;
+            float x = v[j];
+            if (a.bias) x += a.bias[n + j];
+            size_t o = (size_t)m * a.ldo + n + j;
+            if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(x);
+            else if (EPI == EPI_ACC) ((float*)a.out)[o] += x;
+            else ((float*)a.out)[o] = x;
+          }
+        }
+      }
+    }
+  }
+  // common exit: every role comes here, also after a wait that gave up
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(UM_BN) : "memory");
+  }
+}
+
+// ---- host side: tensor maps through the driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+// rows x K bfloat16, row stride ld elements; box = 64 k x 128 rows, 128-byte swizzle, zeros outside
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FELLM_ERR_ARG;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {UM_BK, UM_BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, cudaStream_t stream) {
+  size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES + 1024;
+  auto kern = gemm_umma_kernel<EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  return launch_k(kern, dim3(ceil_div(a.N, UM_BN), ceil_div(a.M, UM_BM), 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
+}
+
+// status: device int32 that a role sets (101 producer, 102 MMA, 103 epilogue) if a wait ran out.
+FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
+                              int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!A || !W || !out || K <= 0) return FELLM_ERR_ARG;
+  // TMA: 16-byte aligned bases and row strides
+  if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
+  if (epi == EPI_SWIGLU && ((N % 16) || (ldo % 8))) return FELLM_ERR_SIZE;
+  CUtensorMap ma, mw;
+  int e = make_map(&ma, A, M, K, lda);
+  if (e) return e;
+  e = make_map(&mw, W, N, K, ldw);
+  if (e) return e;
+  UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
+  switch (epi) {
+    case EPI_STORE: return launch<EPI_STORE>(ma, mw, a, stream);
+    case EPI_ACC: return launch<EPI_ACC>(ma, mw, a, stream);
+    case EPI_SWIGLU: return launch<EPI_SWIGLU>(ma, mw, a, stream);
+    case EPI_F32: return launch<EPI_F32>(ma, mw, a, stream);
+    default: return FELLM_ERR_ARG;
+  }
+}

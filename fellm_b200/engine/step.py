@@ -220,6 +220,8 @@ class Stepper:
     def check_status(self):
         """Reads the device status word (synchronises).  Kernels set it instead of faulting:
         1 = a token id outside the embedding table, 2 = a cache write with no page mapped."""
+        from .. import ops
+        ops.check_umma_status(self.device)
         code = int(self.buffers.status.item())
         if code:
             self.buffers.status.zero_()

@@ -5,6 +5,7 @@ code into a KernelError.  There is no CPU path and no library fallback behind an
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -250,7 +251,32 @@ def has_fast_gemm() -> bool:
 
 
 def fast_gemm_modules():
-    return [("gemm_skinny", None), ("gemm_tiled", None)]
+    return [("gemm_skinny", None), ("gemm_tiled", None), ("gemm_umma", None)]
+
+
+_umma_status = {}
+USE_UMMA = os.environ.get("FELLM_B200_UMMA", "1") != "0"
+
+
+def umma_status(device) -> torch.Tensor:
+    """Device int32 the tcgen05 product sets when one of its bounded waits ran out (101 TMA
+    producer, 102 MMA issuer, 103 epilogue); zero otherwise."""
+    key = torch.device(device).index or 0
+    t = _umma_status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _umma_status[key] = t
+    return t
+
+
+def check_umma_status(device):
+    """Reads the status word (synchronises)."""
+    t = _umma_status.get(torch.device(device).index or 0)
+    if t is not None:
+        code = int(t.item())
+        if code:
+            t.zero_()
+            raise KernelError(f"the tcgen05 product gave up waiting on a barrier (role {code})")
 
 
 def fast_gemm_takes(x, w) -> bool:
@@ -317,10 +343,23 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
             code = f(_p(x), None, None, 0.0, _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0),
                      out.stride(0), _stream())
         _check(code, "gemm_skinny")
+    elif USE_UMMA and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (epi != _EPI_SWIGLU or out.stride(0) % 8 == 0):
+        f = _fn("gemm_umma", "fellm_gemm_umma", _GEMM_ARGS[:-1] + [_c_p, _c_p])
+        _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                 _p(umma_status(x.device)), _stream()), "gemm_umma")
     else:
         f = _fn("gemm_tiled", "fellm_gemm_tiled", _GEMM_ARGS)
         _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
                "gemm_tiled")
+    return out
+
+
+def gemm_tiled(x, w, bias=None, *, out, epi: int):
+    """The mma.sync product, callable by itself (tests compare the tcgen05 product with it)."""
+    M, K = x.shape
+    f = _fn("gemm_tiled", "fellm_gemm_tiled", _GEMM_ARGS)
+    _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, w.shape[0], K, x.stride(0), w.stride(0), out.stride(0), _stream()),
+           "gemm_tiled")
     return out
 
 

@@ -448,3 +448,24 @@ def test_attention_prefill_finds_one_far_key(far, qpos):
     got = got.float().cpu().reshape(n_new, H, hd)
     for h in range(H):
         assert torch.allclose(got[row, h], values[far, h // 2].bfloat16().float(), atol=2e-2), (far, h)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 144, 144), (300, 1000, 1000), (2048, 1024, 4608),
+                                   (513, 3072, 1024), (1000, 200, 72)])
+def test_gemm_umma_tcgen05(M, N, K):
+    """The tcgen05 / TMEM / TMA product by itself: against float64, against the mma.sync product,
+    and its bounded waits must not have run out."""
+    x, w, want = _gemm_case(M, N, K, seed=5)
+    xd, wd = x.to(DEV), w.to(DEV)
+    got = ops.gemm_bf16(xd, wd, out_dtype=torch.float32)
+    ops.check_umma_status(DEV)
+    assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4), (got.double().cpu() - want).abs().max()
+    ref = torch.empty(M, N, device=DEV)
+    ops.gemm_tiled(xd, wd, out=ref, epi=3)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-5)
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    out = res.clone()
+    ops.gemm_bf16(xd, wd, bias, out=out, accumulate=True)
+    assert torch.allclose(out.double().cpu(), res.double().cpu() + want + bias.double().cpu(), rtol=1e-4, atol=1e-4)
+    ops.check_umma_status(DEV)
