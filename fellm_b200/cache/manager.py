@@ -206,6 +206,8 @@ class CacheManager:
             else:
                 raise CacheError(f"schedule entry {n}: unknown cache need {need!r}")
         self.n_entries = len(needs)
+        self._views_key, self._views = None, None
+        self.has_windows = any(g.need.window is not None for g in self.paged)
         self.req_slot: Dict[object, int] = {}
         self.req_len: Dict[object, int] = {}
 
@@ -295,12 +297,17 @@ class CacheManager:
 
     def views(self, item_slot: Optional[torch.Tensor]):
         """Cache views per schedule entry for one step (None where an entry keeps nothing)."""
+        key = None if item_slot is None else (item_slot.data_ptr(), item_slot.numel())
+        if key is not None and self._views_key == key:
+            return self._views
         out = []
         for n in range(self.n_entries):
             v = self._entry_view.get(n)
             if isinstance(v, StateView):
                 v = StateView(v.states, item_slot)
             out.append(v)
+        if key is not None:
+            self._views_key, self._views = key, out
         return out
 
     # ---- checks used by tests

@@ -1,7 +1,7 @@
 // C[M,N] = A[M,K] W[N,K]^T for many rows (prefill), bfloat16 operands, float32 accumulation in
 // tensor memory: the Blackwell path.  tcgen05.mma (cta_group::1, kind::f16, 128x128x16) issued by
 // one thread, operands brought by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of
-// four 32 KB stages, accumulator read back with tcgen05.ld for a fused epilogue: store, add into
+// three 32 KB stages, accumulator read back with tcgen05.ld for a fused epilogue: store, add into
 // the float32 residual stream, SiLU(gate)*up over weight rows interleaved in blocks of 8, float32
 // store.
 //
@@ -19,7 +19,7 @@
 #define UM_BM 128
 #define UM_BN 128
 #define UM_BK 64                      // one 128-byte swizzle atom of bfloat16 per row
-#define UM_STAGES 4
+#define UM_STAGES 3                   // 96 KB of stages: two CTAs share an SM, one's epilogue under the other's MMAs
 #define UM_THREADS 192
 #define UM_STAGE_BYTES ((UM_BM + UM_BN) * UM_BK * 2)
 #define UM_SPIN_LIMIT (1u << 26)
@@ -189,15 +189,36 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             *(uint4*)(dst + 8 * h) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
         } else {
+          const bool whole = n + 32 <= a.N;
+          if (a.bias) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (n + j >= a.N) break;
-            float x = v[j];
-            if (a.bias) x += a.bias[n + j];
-            size_t o = (size_t)m * a.ldo + n + j;
-            if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(x);
-            else if (EPI == EPI_ACC) ((float*)a.out)[o] += x;
-            else ((float*)a.out)[o] = x;
+            for (int j = 0; j < 32; ++j) if (n + j < a.N) v[j] += a.bias[n + j];
+          }
+          if (EPI == EPI_STORE && whole && (a.ldo % 8) == 0) {
+            uint4* dst = (uint4*)((bf16*)a.out + (size_t)m * a.ldo + n);         // 64 contiguous bytes of this row
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+              dst[j] = make_uint4(*(unsigned*)&p0, *(unsigned*)&p1, *(unsigned*)&p2, *(unsigned*)&p3);
+            }
+          } else if (EPI != EPI_STORE && whole && (a.ldo % 4) == 0) {
+            float4* dst = (float4*)((float*)a.out + (size_t)m * a.ldo + n);       // 128 contiguous bytes of this row
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (EPI == EPI_ACC) { float4 o = dst[j]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
+              dst[j] = r;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n + j >= a.N) break;
+              size_t o = (size_t)m * a.ldo + n + j;
+              if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v[j]);
+              else if (EPI == EPI_ACC) ((float*)a.out)[o] += v[j];
+              else ((float*)a.out)[o] = v[j];
+            }
           }
         }
       }

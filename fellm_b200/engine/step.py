@@ -57,6 +57,8 @@ class StepBuffers:
         self.ring_events = [torch.cuda.Event() if self.on_gpu else None for _ in self.ring]
         self.ring_used = [False] * len(self.ring)
         self.ring_next = 0
+        self.ring_sig = [None] * len(self.ring)
+        self._decode_ctx = {}
         self.dev = torch.zeros(self.capacity, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -73,6 +75,7 @@ class StepBuffers:
         if self.on_gpu and self.ring_used[k]:
             self.ring_events[k].synchronize()
         h, d = self.ring_np[k], self.dev
+        self.ring_sig[k] = None
 
         def put(name, arr, count):
             nonlocal off
@@ -100,6 +103,58 @@ class StepBuffers:
         return ctx
 
 
+def _fill_decode(self, plan, wants, toks, lens) -> StepContext:
+    """The decode form of fill(): n items of one row each.  The layout of the buffer is the one
+    fill() makes for T = n; the parts that only depend on the composition are written once per
+    staging buffer."""
+    n = len(lens)
+    if n > self.max_items or n > self.max_rows:
+        raise FellmError(f"a step of {n} items exceeds the engine's buffers")
+    k = self.ring_next
+    self.ring_next = (k + 1) % len(self.ring)
+    if self.on_gpu and self.ring_used[k]:
+        self.ring_events[k].synchronize()
+    h, d = self.ring_np[k], self.dev
+    logit_rows = [i for i, w in enumerate(wants) if w]
+    W = len(logit_rows)
+    o_tok, o_pos, o_ri, o_rs = 0, n, 2 * n, 3 * n
+    o_is, o_slot, o_len, o_lr = 4 * n, 5 * n + 1, 6 * n + 1, 7 * n + 1
+    total = o_lr + W
+    sig = (id(plan), wants)
+    if plan["ring"][k] != sig or self.ring_sig[k] != sig:
+        h[o_ri:o_ri + n] = plan["arange"][:n]
+        h[o_rs:o_rs + n] = plan["slots"]
+        h[o_is:o_is + n + 1] = plan["arange"]
+        h[o_slot:o_slot + n] = plan["slots"]
+        h[o_lr:o_lr + W] = logit_rows
+        plan["ring"][k] = sig
+        self.ring_sig[k] = sig
+    if toks is not None:
+        h[o_tok:o_tok + n] = toks
+    h[o_pos:o_pos + n] = lens
+    h[o_len:o_len + n] = lens + 1
+    d[:total].copy_(self.ring[k][:total], non_blocking=True)
+    if self.on_gpu:
+        self.ring_events[k].record()
+        self.ring_used[k] = True
+    ctx = self._decode_ctx.get((n, W))
+    if ctx is None:
+        ctx = StepContext()
+        ctx.tokens, ctx.positions, ctx.row_item, ctx.row_slot = d[o_tok:o_tok + n], d[o_pos:o_pos + n], d[o_ri:o_ri + n], d[o_rs:o_rs + n]
+        ctx.item_start, ctx.item_slot, ctx.item_len = d[o_is:o_is + n + 1], d[o_slot:o_slot + n], d[o_len:o_len + n]
+        ctx.logit_rows = d[o_lr:o_lr + W]
+        ctx.n_rows, ctx.n_items, ctx.n_logit_rows = n, n, W
+        ctx.all_single, ctx.max_item_rows = True, 1
+        ctx.status, ctx.host = self.status, None
+        self._decode_ctx[(n, W)] = ctx
+    ctx.logits_all = (W == n)
+    ctx.max_len = int(lens.max()) + 1
+    return ctx
+
+
+StepBuffers.fill_decode = _fill_decode
+
+
 class Stepper:
     """Owns the model, the cache manager and the step buffers; `step()` is the step function.
 
@@ -122,6 +177,7 @@ class Stepper:
         self.graph_seen = {}
         self.graph_pool = None
         self.launches = 0                      # kernels of ours launched, replays included
+        self._decode_plans = {}
 
     def step(self, items: List[StepItem], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs exactly the given tokens as one batch and returns float32 logits
@@ -132,6 +188,10 @@ class Stepper:
         are then placeholders): lets a decode loop feed sampled tokens back without the host."""
         if not items:
             raise FellmError("a step needs at least one item")
+        if all(len(it.tokens) == 1 for it in items):
+            fast = self._step_decode(items, device_tokens)
+            if fast is not None:
+                return fast
         cache = self.cache
         seen = set()
         for it in items:
@@ -183,6 +243,58 @@ class Stepper:
         logits = self._run(ctx)
         for req, n in asks:
             cache.advance(req, n)
+        self.steps_run += 1
+        return logits
+
+    def _step_decode(self, items: List[StepItem], device_tokens) -> Optional[torch.Tensor]:
+        """Every item brings one token: the host work is a handful of numpy writes.  What does
+        not change while the same requests decode together (slots, offsets, the wanted rows) is
+        kept per composition; positions and lengths come from the cache's own counters.  Returns
+        None when the general path has to look at the step (unknown request, page or context
+        limits, windows to trim)."""
+        cache = self.cache
+        key = tuple(it.req for it in items)
+        plan = self._decode_plans.get(key)
+        n = len(items)
+        lens_d = cache.req_len
+        try:
+            lens = np.fromiter((lens_d[r] for r in key), dtype=np.int64, count=n)
+        except KeyError:
+            return None
+        if plan is None:
+            if len(set(key)) != n:
+                return None
+            if len(self._decode_plans) > 64:
+                self._decode_plans.clear()
+            slots = np.array([cache.slot(r) for r in key], dtype=np.int64)
+            plan = {"slots": slots, "arange": np.arange(n + 1), "ring": [None] * len(self.buffers.ring)}
+            self._decode_plans[key] = plan
+        wants = tuple(bool(it.want) for it in items)
+        if int(lens.max()) + 1 > cache.n_ctx:
+            return None
+        if cache.has_windows:
+            return None
+        if device_tokens is None:
+            toks = np.fromiter((it.tokens[0] for it in items), dtype=np.int64, count=n)
+            if toks.min() < 0 or toks.max() >= self.vocab:
+                raise FellmError(f"token id outside the vocabulary of {self.vocab}")
+        else:
+            toks = None
+        pt = cache.page_tokens
+        if (lens % pt == 0).any():                          # somebody starts a page
+            asks = [(r, 1) for r in key]
+            if not cache.can_reserve(asks):
+                raise CacheError("out of cache pages for this step")
+            for r, l in zip(key, lens):
+                if l % pt == 0:
+                    cache.reserve(r, 1)
+        ctx = self.buffers.fill_decode(plan, wants, toks, lens)
+        if device_tokens is not None:
+            ctx.tokens.copy_(device_tokens[:n])
+        cache.flush()
+        logits = self._run(ctx)
+        for r in key:
+            lens_d[r] += 1
         self.steps_run += 1
         return logits
 
