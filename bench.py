@@ -198,6 +198,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print a short line (for profiling a small case; not a bench value)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -229,6 +231,15 @@ def main():
     clocks = ClockSampler()
     clocks.start()
 
+    if args.only:
+        if args.only == "decode":
+            v, ms, _, _ = run_decode(engine, args.batch, steps, warmup, rng)
+            print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg["num_hidden_layers"], "tokens_per_s": round(v, 1), "ms_per_step": round(ms, 4)}))
+        else:
+            ms = run_prefill(engine, PREFILL_TOKENS, max(1, min(steps, 5)), rng)
+            print(json.dumps({"only": "prefill", "layers": cfg["num_hidden_layers"], "tokens": PREFILL_TOKENS, "ms": round(ms, 4)}))
+        clocks.stop()
+        return 0
     value, ms_step, launches, mean_ctx = run_decode(engine, args.batch, steps, warmup, rng)
     prefill_ms = run_prefill(engine, PREFILL_TOKENS, 5, rng)
     e2e, h2d, d2h = run_e2e(engine, args.batch, min(steps, 512), warmup, rng)
