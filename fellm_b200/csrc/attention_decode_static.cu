@@ -60,7 +60,7 @@ FELLM_API int fellm_attn_decode_static(const void* q, const void* pool, const in
       if (ce != cudaSuccess) return say(err, err_len, (int)ce, "cudaGetSymbolAddress(scratch) failed (%lld)", (long long)ce);
       ce = cudaGetSymbolAddress((void**)&s_counter_ptr[dev], g_static_counters);
       if (ce != cudaSuccess) return say(err, err_len, (int)ce, "cudaGetSymbolAddress(counters) failed (%lld)", (long long)ce);
-      if (smem > 48 * 1024) {
+      if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default too
         ce = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (ce != cudaSuccess) return say(err, err_len, (int)ce, "cudaFuncSetAttribute failed (%lld)", (long long)ce);
       }

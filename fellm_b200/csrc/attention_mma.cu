@@ -9,7 +9,7 @@
 //    ring shared by the CTA's four warps.
 //  * decode: one token per item against thousands of keys, bound by reading K and V once.  A CTA
 //    takes one row, one kv head and one range of keys ("split-KV"); its rows are the H/G heads of
-//    the group; each warp streams its own 32-key tiles through its own cp.async ring.  Partial
+//    the group; each warp streams its own 16-key tiles through its own cp.async ring.  Partial
 //    (m, l, acc) of the ranges go to a scratch buffer; the CTA that finishes last for a (row, kv
 //    head) merges them in range order.
 //
@@ -269,7 +269,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
 
 // ------------------------------------------------------------------------------------ decode
 #define DC_WARPS 4
-#define DC_TK (HD <= 64 ? 32 : 16)   // keys per warp tile: 4 KB (8 KB at the largest heads) of K and of V
+#define DC_TK 16                 // keys per warp tile; with three stages a CTA's rings take 48 KB at head size 64:
+                                 // four CTAs per SM, so that a decode batch's CTAs fit one wave
 #define DC_STAGES 3
 #define DC_MAX_PAGES 256
 
@@ -447,7 +448,7 @@ FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int*
   int tokb = (PF_WARPS * 16) / R; if (tokb < 1) tokb = 1;
   size_t smem = (size_t)PF_STAGES * 2 * PF_TK * ROWB;
   auto kern = attention_prefill_kernel;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default too
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
   }
@@ -471,7 +472,7 @@ FELLM_API int fellm_attn_decode_mma(const void* q, const void* pool, const int* 
   size_t ring = (size_t)DC_WARPS * DC_STAGES * 2 * DC_TK * ROWB, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
   size_t smem = ring > mrg ? ring : mrg;
   auto kern = attention_decode_kernel;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {        // static shared memory counts against the 48 KB default too
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
   }

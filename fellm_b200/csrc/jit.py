@@ -104,9 +104,14 @@ def _source_hash(name: str, dkey: Tuple) -> str:
     return h.hexdigest()[:16]
 
 
+def _stem(name: str, dkey: Tuple) -> str:
+    tag = "".join(f"_{k}{v}" for k, v in dkey)
+    return f"fellm_{name}{re.sub(r'[^A-Za-z0-9_]', '', tag)}"
+
+
 def library_path(name: str, defines: Optional[dict] = None) -> Path:
     dkey = _defines_key(defines)
-    return build_dir() / f"fellm_{name}-{_source_hash(name, dkey)}.so"
+    return build_dir() / f"{_stem(name, dkey)}-{_source_hash(name, dkey)}.so"
 
 
 def compile_module(name: str, defines: Optional[dict] = None, verbose_ptxas: bool = False) -> Path:
@@ -143,6 +148,12 @@ def compile_module(name: str, defines: Optional[dict] = None, verbose_ptxas: boo
             pass
         raise KernelError(f"nvcc failed for {label} (exit {proc.returncode}):\n{log}")
     os.replace(tmp, out)
+    for old in out.parent.glob(f"{_stem(name, dkey)}-*.so"):      # libraries of earlier versions of these sources
+        if old != out and re.fullmatch(rf"{re.escape(_stem(name, dkey))}-[0-9a-f]{{16}}\.so", old.name):
+            try:
+                old.unlink()
+            except OSError:
+                pass
     _say(f"compiled {label} in {time.time() - t0:.1f} s")
     if verbose_ptxas:
         _say(log)
