@@ -24,6 +24,7 @@ class EngineOptions:
     max_tokens: Optional[int] = None    # cache pool size in tokens; None = from memory
     kv_memory_fraction: float = 0.25    # fabric.rs:40-48 (share of free memory when max_tokens is None)
     cuda_graphs: bool = True
+    mega_decode: bool = True        # bfloat16 decode steps of up to 16 requests run as one persistent kernel
     device: str = "cuda:0"
 
     def validate(self):

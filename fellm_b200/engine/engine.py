@@ -64,7 +64,10 @@ class Engine:
                                   device=self.device)
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
-                               device=self.device, cuda_graphs=options.cuda_graphs)
+                               device=self.device, cuda_graphs=options.cuda_graphs,
+                               mega_decode=options.mega_decode and options.dtype == "bfloat16")
+        if self.stepper.mega is not None:
+            jit.compile_many(self.stepper.mega.kernel_modules())
         self._sampler: Optional[Sampler] = None
         self._tok_host = torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True)
         self._scheduler: Optional[Scheduler] = None

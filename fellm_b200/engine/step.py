@@ -39,7 +39,7 @@ class StepContext:
     """
     __slots__ = ("tokens", "positions", "row_item", "row_slot", "item_start", "item_slot", "item_len",
                  "logit_rows", "n_rows", "n_items", "n_logit_rows", "all_single", "max_item_rows",
-                 "max_len", "status", "host", "logits_all")
+                 "max_len", "status", "host", "logits_all", "fixed_addresses")
 
 
 class StepBuffers:
@@ -100,6 +100,7 @@ class StepBuffers:
         ctx.max_item_rows, ctx.max_len = max_item_rows, max_len
         ctx.status = self.status
         ctx.host = None
+        ctx.fixed_addresses = False
         return ctx
 
 
@@ -146,6 +147,7 @@ def _fill_decode(self, plan, wants, toks, lens) -> StepContext:
         ctx.n_rows, ctx.n_items, ctx.n_logit_rows = n, n, W
         ctx.all_single, ctx.max_item_rows = True, 1
         ctx.status, ctx.host = self.status, None
+        ctx.fixed_addresses = True
         self._decode_ctx[(n, W)] = ctx
     ctx.logits_all = (W == n)
     ctx.max_len = int(lens.max()) + 1
@@ -167,8 +169,14 @@ class Stepper:
     Index arrays and block tables live at fixed device addresses and are refreshed by copies before
     the replay."""
 
-    def __init__(self, model, cache, *, max_rows: int, max_items: int, device, cuda_graphs: bool = False):
+    def __init__(self, model, cache, *, max_rows: int, max_items: int, device, cuda_graphs: bool = False,
+                 mega_decode: bool = False):
         self.model, self.cache, self.device = model, cache, device
+        self.mega = None
+        if mega_decode:
+            from .mega import MegaDecoder
+            mega = MegaDecoder(model, cache, device)
+            self.mega = mega if mega.supported else None
         self.buffers = StepBuffers(max_rows, max_items, device)
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
@@ -301,6 +309,9 @@ class Stepper:
     def _run(self, ctx) -> torch.Tensor:
         from .. import ops
         views = self.cache.views(ctx.item_slot)
+        if self.mega is not None and self.mega.takes(ctx):
+            self.launches += 1
+            return self.mega.run(ctx, views)
         if not (self.cuda_graphs and ctx.all_single):
             before = ops.launch_count()
             logits = self.model.forward(ctx, views)

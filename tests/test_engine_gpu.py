@@ -92,3 +92,34 @@ def test_step_refuses_what_it_cannot_place():
         eng.step([StepItem("a", tiny.tokens("A", 40, 1), [])])
     assert eng.cache.length("a") == 0 and eng.cache.free_pages() == 2
     eng.cache.audit()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_fused_decode_step_equals_the_per_kernel_path(name):
+    """bfloat16 decode through the one-launch persistent kernel against the per-kernel path and
+    the plain implementation: several requests of different lengths decoded together, far enough
+    to cross pages."""
+    lens = [3, 17, 40]
+    n_dec = 45
+    toks = [tiny.tokens(name, n + n_dec, 70 + i) for i, n in enumerate(lens)]
+    outs = {}
+    for mode in ("fused", "kernels"):
+        eng = tiny.make_engine(name, "bfloat16", mega_decode=(mode == "fused"))
+        assert (eng.stepper.mega is not None) == (mode == "fused")
+        for i, n in enumerate(lens):
+            eng.add_request(i)
+            eng.step([StepItem(i, toks[i][:n], [])])
+        rows = []
+        for t in range(n_dec):
+            rows.append(eng.step([StepItem(i, [toks[i][lens[i] + t]], [0]) for i in range(len(lens))]).clone())
+        eng.check_status()
+        if mode == "fused":
+            assert eng.stepper.mega.launches == n_dec
+        outs[mode] = torch.stack(rows)                    # [n_dec, requests, vocab]
+    for i, n in enumerate(lens):
+        want = tiny.plain_logits(name, n + n_dec, 70 + i)[n:]
+        for mode in outs:
+            ok, err, tol = tiny.close(outs[mode][:, i], want, "bfloat16")
+            assert ok, (mode, i, err, tol)
+    ok, err, tol = tiny.close(outs["fused"].reshape(-1, outs["fused"].shape[-1]), outs["kernels"].reshape(-1, outs["kernels"].shape[-1]).cpu(), "bfloat16")
+    assert ok, (err, tol)
