@@ -45,19 +45,25 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Grid barrier: one release-add on a counter in global memory per CTA, then one thread polls it
+// with acquire loads (cooperative launch guarantees that every CTA is resident).  The spin is
+// bounded: after 2 s the CTA records code 201 in the status word and goes on.
 __device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int* status) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(counter, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(counter) : "memory");
     const unsigned long long t0 = mg_ns();
     unsigned it = 0;
     while (ld_acquire_u32(counter) < target) {
       if ((++it & 1023u) == 0 && mg_ns() - t0 > 2000000000ull) { atomicExch(status, 201); break; }
     }
-    __threadfence();
   }
   __syncthreads();
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 __device__ __forceinline__ uint4 mg_ldg_stream(const void* p) {
   uint4 v;
@@ -165,6 +171,8 @@ __device__ void gemm_stage(const Stage& st, unsigned char* smem, float* row_scal
     }
   }
 
+  if (cta * (MG_WARPS / warps_k) >= SI(18)) return;      // no slab for this CTA (the same for all its threads)
+
   // ---- stage x[:, 0:K] as bfloat16 (rows >= M zero)
   bf16* xs = (bf16*)smem;
   const int k_cta = warps_k * k_per_warp, vec_per_row = k_cta / 8;
@@ -203,18 +211,29 @@ __device__ void gemm_stage(const Stage& st, unsigned char* smem, float* row_scal
     const long long sstride = st.v[24];
     const int Lc = SI(25), H = Lc - 1;
     const int* islot = SP(const int*, 26);
-    for (int i = threadIdx.x; i < MT * 8 * k_cta; i += MG_THREADS) {
-      int r = i / k_cta, ch = i - r * k_cta;
-      float y = 0.f;
-      if (r < M && ch < K) {
+    for (int i = threadIdx.x; i < MT * 8 * vec_per_row; i += MG_THREADS) {      // 8 channels a thread
+      int r = i / vec_per_row, ch0 = (i - r * vec_per_row) * 8;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < M && ch0 < K) {
         const bf16* row = bcx + (size_t)r * 3 * K;
-        float bx = __bfloat162float(row[ch]) * __bfloat162float(row[2 * K + ch]);
+        float bf_[8], cf_[8], xf_[8], conv[8];
+        uint4 bv = *(const uint4*)(row + ch0), cv = *(const uint4*)(row + K + ch0), xv = *(const uint4*)(row + 2 * K + ch0);
+        unpack8(bv, bf_); unpack8(cv, cf_); unpack8(xv, xf_);
         const float* s = state + (size_t)islot[r] * sstride;
-        float conv = bx * cw[(size_t)ch * Lc + H];
-        for (int t = 0; t < H; ++t) conv = fmaf(s[(size_t)t * K + ch], cw[(size_t)ch * Lc + t], conv);
-        y = __bfloat162float(row[K + ch]) * (conv + (cb ? cb[ch] : 0.f));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) conv[e] = (bf_[e] * xf_[e]) * cw[(size_t)(ch0 + e) * Lc + H];
+        for (int t = 0; t < H; ++t) {
+          float4 s0 = *(const float4*)(s + (size_t)t * K + ch0), s1 = *(const float4*)(s + (size_t)t * K + ch0 + 4);
+          float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) conv[e] = fmaf(sv[e], cw[(size_t)(ch0 + e) * Lc + t], conv[e]);
+        }
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = cf_[e] * (conv[e] + (cb ? cb[ch0 + e] : 0.f));
+        val.x = pack_bf16(y[0], y[1]); val.y = pack_bf16(y[2], y[3]); val.z = pack_bf16(y[4], y[5]); val.w = pack_bf16(y[6], y[7]);
       }
-      xs[(size_t)r * xs_stride + ch] = __float2bfloat16_rn(y);
+      *(uint4*)(xs + (size_t)r * xs_stride + ch0) = val;
     }
   } else {
     const bf16* x = SP(const bf16*, 2);
@@ -587,21 +606,26 @@ __device__ __noinline__ void argmax_fin_stage(const Stage& st, int cta, int n_ct
 
 // ------------------------------------------------------------------------------------ the kernel
 __global__ void __launch_bounds__(MG_THREADS, 1)
-decode_mega_kernel(const Stage* __restrict__ program, int n_stages, unsigned* barrier, int* status) {
+decode_mega_kernel(const Stage* __restrict__ program, int n_stages, unsigned* barrier, int* status,
+                   unsigned long long* trace) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ float row_scale[16];
   __shared__ int sm_pages[4 * DC_MAX_PAGES];
   __shared__ int sm_last[4];
   __shared__ float sb[MG_WARPS];
   __shared__ int si[MG_WARPS];
-  __shared__ Stage cur;
+  __shared__ Stage sbuf[2];                               // this stage's record and the next one's
   const int cta = blockIdx.x, n_ctas = gridDim.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint4 wA0[MG_U], wA1[MG_U], wB0[MG_U], wB1[MG_U];
   bool have = false;
+  if (threadIdx.x < MG_SLOTS) sbuf[0].v[threadIdx.x] = program[0].v[threadIdx.x];
+  __syncthreads();
   for (int i = 0; i < n_stages; ++i) {
-    for (int k = threadIdx.x; k < MG_SLOTS; k += MG_THREADS) cur.v[k] = program[i].v[k];
-    __syncthreads();
-    const Stage& st = cur;
+    const Stage& st = sbuf[i & 1];
+    // the next record travels while this stage runs
+    long long next_field = 0;
+    if (i + 1 < n_stages && threadIdx.x < MG_SLOTS) next_field = program[i + 1].v[threadIdx.x];
+    if (trace && cta == 0 && threadIdx.x == 0) trace[2 * i] = mg_ns();            // stage opens (CTA 0's clock)
     const int kind = SI(0);
     if (kind == K_GEMM) {
       if (!have) {
@@ -616,15 +640,16 @@ decode_mega_kernel(const Stage* __restrict__ program, int n_stages, unsigned* ba
     else if (kind == K_ARGMAX_PART) argmax_part_stage(st, sb, si, cta, n_ctas);
     else if (kind == K_ARGMAX_FIN) argmax_fin_stage(st, cta, n_ctas);
     have = false;
+    if (trace && cta == 0) { __syncthreads(); if (threadIdx.x == 0) trace[2 * i + 1] = mg_ns(); }   // CTA 0 is done with it
     if (i + 1 < n_stages) {
+      if (threadIdx.x < MG_SLOTS) sbuf[(i + 1) & 1].v[threadIdx.x] = next_field;
+      __syncthreads();
       // weights of the next product: requested now, landed by the time the barrier opens
-      if ((int)program[i + 1].v[0] == K_GEMM) {
-        __syncthreads();                                 // everyone is done reading `cur`
-        for (int k = threadIdx.x; k < MG_SLOTS; k += MG_THREADS) cur.v[k] = program[i + 1].v[k];
-        __syncthreads();
-        GemmGeom q = gemm_geom(cur, warp, cta, n_ctas);
-        if (q.total_rounds > 0) gemm_load_round(cur, q, 0, lane, wA0, wA1);
-        if (q.total_rounds > 1) gemm_load_round(cur, q, 1, lane, wB0, wB1);
+      const Stage& nx = sbuf[(i + 1) & 1];
+      if ((int)nx.v[0] == K_GEMM) {
+        GemmGeom q = gemm_geom(nx, warp, cta, n_ctas);
+        if (q.total_rounds > 0) gemm_load_round(nx, q, 0, lane, wA0, wA1);
+        if (q.total_rounds > 1) gemm_load_round(nx, q, 1, lane, wB0, wB1);
         have = true;
       }
       grid_barrier(barrier, (unsigned)(i + 1) * (unsigned)n_ctas, status);
@@ -640,8 +665,10 @@ FELLM_API int fellm_decode_mega_slots() { return MG_SLOTS; }
 
 // program: n_stages records of MG_SLOTS 8-byte fields on the device; barrier: one uint32 (cleared
 // here); smem_bytes: fellm_decode_mega_smem(the largest staged x + slab slots of the program).
+// trace: null, or 2*n_stages uint64 that receive, from CTA 0, the time (ns) each stage opened and the time
+// CTA 0 finished its share of it.
 FELLM_API int fellm_decode_mega(const void* program, int n_stages, unsigned* barrier, int* status, int smem_bytes,
-                                cudaStream_t stream) {
+                                unsigned long long* trace, cudaStream_t stream) {
   if (n_stages <= 0) return 0;
   if (!program || !barrier || !status) return FELLM_ERR_ARG;
   if (smem_bytes > 220 * 1024) return FELLM_ERR_SIZE;
@@ -665,7 +692,7 @@ FELLM_API int fellm_decode_mega(const void* program, int n_stages, unsigned* bar
   e = cudaMemsetAsync(barrier, 0, sizeof(unsigned), stream);
   if (e != cudaSuccess) return (int)e;
   const Stage* prog = (const Stage*)program;
-  void* args[] = {(void*)&prog, (void*)&n_stages, (void*)&barrier, (void*)&status};
+  void* args[] = {(void*)&prog, (void*)&n_stages, (void*)&barrier, (void*)&status, (void*)&trace};
   e = cudaLaunchCooperativeKernel((void*)decode_mega_kernel, dim3(n_sm), dim3(MG_THREADS), args, (size_t)smem_bytes, stream);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();

@@ -49,9 +49,12 @@ class MegaDecoder:
         self.reason = self._unsupported_reason()
         self.supported = self.reason is None
         self.programs: Dict[tuple, dict] = {}
-        self.barrier = torch.zeros(1, dtype=torch.int32, device=device) if self.supported else None
+        self.barrier = torch.zeros(self.n_sm, dtype=torch.int32, device=device) if self.supported else None
         self._fn = None
         self.launches = 0
+        self.trace_next = False          # set to True to have the next step record per-stage times (last_trace)
+        self.last_trace = None
+        self.last_kinds = None
 
     # ------------------------------------------------------------------ can this model be fused?
     def _unsupported_reason(self) -> Optional[str]:
@@ -205,7 +208,9 @@ class MegaDecoder:
         prog = torch.from_numpy(np.array(stages, dtype=np.int64)).to(dev)
         smem_fn = self._lib().fellm_decode_mega_smem
         smem_fn.restype, smem_fn.argtypes = ctypes.c_int, [ctypes.c_int]
-        return {"program": prog, "n": len(stages), "smem": int(smem_fn(int(smem))), "logits": logits, "keep": keep}
+        kinds = [(r[0], r[9], r[10], r[11]) if r[0] == K_GEMM else (r[0], 0, 0, 0) for r in stages]
+        return {"program": prog, "n": len(stages), "smem": int(smem_fn(int(smem))), "logits": logits, "keep": keep,
+                "kinds": kinds}
 
     def _lib(self):
         from ..csrc import jit
@@ -223,7 +228,7 @@ class MegaDecoder:
         """ctx must be the decode context whose arrays live at fixed device addresses.  Returns the
         step's float32 logits [rows, vocab] (a buffer the next step overwrites)."""
         G = max((b.mixer.G for b in self.model.blocks if isinstance(b.mixer, Attention)), default=1)
-        split = ops.decode_split(ctx.max_len, ctx.n_rows, G)
+        split = ops.decode_split(ctx.max_len, ctx.n_rows, G, target=2 * self.n_sm)      # two virtual CTAs per SM
         key = (ctx.n_rows, split, ctx.tokens.data_ptr())
         p = self.programs.get(key)
         if p is None:
@@ -234,10 +239,15 @@ class MegaDecoder:
         if self._fn is None:
             f = self._lib().fellm_decode_mega
             f.restype = ctypes.c_int
-            f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+            f.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                          ctypes.c_void_p]
             self._fn = f
+        trace = None
+        if self.trace_next:
+            trace = torch.zeros(2 * p["n"], dtype=torch.int64, device=self.device)
+            self.last_trace, self.last_kinds, self.trace_next = trace, p["kinds"], False
         code = self._fn(p["program"].data_ptr(), p["n"], self.barrier.data_ptr(), ctx.status.data_ptr(), p["smem"],
-                        torch.cuda.current_stream().cuda_stream)
+                        None if trace is None else trace.data_ptr(), torch.cuda.current_stream().cuda_stream)
         if code:
             raise KernelError(f"decode_mega: launch failed with code {code}")
         self.launches += 1

@@ -395,12 +395,12 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
 DECODE_TARGET_CTAS = 148 * 4
 
 
-def decode_split(max_len: int, rows: int, kv_heads: int):
+def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     """(split_len, max_splits): key ranges of a multiple of 64 keys, enough of them to fill the
     machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
     while contexts grow."""
     bucket = -(-max(max_len, 1) // 1024) * 1024
-    want = max(1, DECODE_TARGET_CTAS // max(rows * kv_heads, 1))
+    want = max(1, (target or DECODE_TARGET_CTAS) // max(rows * kv_heads, 1))
     split_len = max(64, -(-(-(-bucket // want)) // 64) * 64)
     return split_len, -(-bucket // split_len)
 

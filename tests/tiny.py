@@ -62,7 +62,7 @@ def plain_logits(name: str, length: int, seed: int) -> torch.Tensor:
 def make_engine(name: str, dtype: str, **opts):
     from fellm_b200.config.options import EngineOptions
     from fellm_b200.engine import Engine
-    o = dict(dtype=dtype, n_ctx=0, max_requests=8, max_tokens=4096, page_tokens=16, cuda_graphs=False, mega_decode=False)
+    o = dict(dtype=dtype, n_ctx=0, max_requests=8, max_tokens=4096, page_tokens=16, cuda_graphs=False)
     o.update(opts)
     return Engine.open(model_folder(name), EngineOptions(**o))
 
