@@ -1,12 +1,13 @@
 // C[M,N] = A[M,K] W[N,K]^T for many rows (prefill), bfloat16 operands, float32 accumulation in
 // tensor memory: the Blackwell path.  tcgen05.mma (cta_group::1, kind::f16, 128x128x16) issued by
 // one thread, operands brought by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of
-// three 32 KB stages, accumulator read back with tcgen05.ld for a fused epilogue: store, add into
+// five 32 KB stages, accumulator read back with tcgen05.ld for a fused epilogue: store, add into
 // the float32 residual stream, SiLU(gate)*up over weight rows interleaved in blocks of 8, float32
 // store.
 //
-// Roles in a CTA of 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane)
-// and owner of the tensor-memory allocation, warps 2-5 = epilogue (TMEM lane quarter = warp % 4).
+// Roles in a CTA of 320 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane)
+// and owner of the tensor-memory allocation, warps 2-9 = epilogue (TMEM lane quarter = warp % 4,
+// column half = (warp - 2) / 4).
 // Every wait on an mbarrier is bounded: after a second of polling a role records the barrier it gave up
 // on in `status`, and all roles fall through to the common exit, where tensor memory is freed.
 //
@@ -19,8 +20,8 @@
 #define UM_BM 128
 #define UM_BN 128
 #define UM_BK 64                      // one 128-byte swizzle atom of bfloat16 per row
-#define UM_STAGES 3                   // 96 KB of stages: two CTAs share an SM, one's epilogue under the other's MMAs
-#define UM_THREADS 192
+#define UM_STAGES 5                   // 160 KB of stages in flight ahead of the MMA thread; one persistent CTA per SM
+#define UM_THREADS 320                // TMA warp, MMA warp, 8 epilogue warps
 #define UM_STAGE_BYTES ((UM_BM + UM_BN) * UM_BK * 2)
 #define UM_SPIN_LIMIT (1u << 26)
 #define UM_WAIT_NS 1000000000ull       // one second: far beyond any healthy wait, short enough to stay responsive
@@ -100,26 +101,84 @@ struct UmmaArgs {
   int M, N, K, ldo;
 };
 
+// One 32-column chunk of an output row: v[j] is C[m][n + j].
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, int n) {
+  if (EPI == EPI_SWIGLU) {
+    // columns: 8 gate, 8 up, 8 gate, 8 up -> 16 features
+    bf16* dst = (bf16*)a.out + (size_t)m * a.ldo + (n >> 1);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (n + 16 * h >= a.N) break;
+      unsigned packed[4];
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        float g0 = v[16 * h + j], g1 = v[16 * h + j + 1], u0 = v[16 * h + 8 + j], u1 = v[16 * h + 9 + j];
+        if (a.bias) { g0 += a.bias[n + 16 * h + j]; g1 += a.bias[n + 16 * h + j + 1]; u0 += a.bias[n + 16 * h + 8 + j]; u1 += a.bias[n + 16 * h + 9 + j]; }
+        __nv_bfloat162 p = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+        packed[j >> 1] = *(unsigned*)&p;
+      }
+      *(uint4*)(dst + 8 * h) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    return;
+  }
+  const bool whole = n + 32 <= a.N;
+  if (a.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) if (n + j < a.N) v[j] += a.bias[n + j];
+  }
+  if (EPI == EPI_STORE && whole && (a.ldo % 8) == 0) {
+    uint4* dst = (uint4*)((bf16*)a.out + (size_t)m * a.ldo + n);         // 64 contiguous bytes of this row
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+      dst[j] = make_uint4(*(unsigned*)&p0, *(unsigned*)&p1, *(unsigned*)&p2, *(unsigned*)&p3);
+    }
+  } else if (EPI != EPI_STORE && whole && (a.ldo % 4) == 0) {
+    float4* dst = (float4*)((float*)a.out + (size_t)m * a.ldo + n);       // 128 contiguous bytes of this row
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      if (EPI == EPI_ACC) { float4 o = dst[j]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
+      dst[j] = r;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (n + j >= a.N) break;
+      size_t o = (size_t)m * a.ldo + n + j;
+      if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v[j]);
+      else if (EPI == EPI_ACC) ((float*)a.out)[o] += v[j];
+      else ((float*)a.out)[o] = v[j];
+    }
+  }
+}
+
+// Persistent: a CTA walks over output tiles t = blockIdx.x, + gridDim.x, ... (tiles that follow one another share
+// their weight tile).  Two accumulators in tensor memory: while the epilogue warps read tile i out of one, the MMA
+// thread fills the other with tile i+1, and the TMA thread is already fetching operands further ahead.
 template <int EPI>
 __global__ void __launch_bounds__(UM_THREADS)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[2 * UM_STAGES + 1];    // full[], empty[], accumulator
+  __shared__ __align__(8) unsigned long long bars[2 * UM_STAGES + 4];    // full[], empty[], acc_full[2], acc_empty[2]
   __shared__ unsigned tmem_base_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the dynamic buffer is aligned by hand: swizzled TMA tiles want 1024 bytes
   unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[UM_STAGES]), accbar = smem_u32(&bars[2 * UM_STAGES]);
-  const int m0 = blockIdx.y * UM_BM, n0 = blockIdx.x * UM_BN;
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[UM_STAGES]);
+  const unsigned accfull0 = smem_u32(&bars[2 * UM_STAGES]), accempty0 = smem_u32(&bars[2 * UM_STAGES + 2]);
   const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
+  const int m_tiles = (a.M + UM_BM - 1) / UM_BM, n_tiles = (a.N + UM_BN - 1) / UM_BN, total = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < UM_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(accbar, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(accfull0 + 8 * b, 1); mbar_init(accempty0 + 8 * b, 8); }   // 8 epilogue warps
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 1) {                   // tensor memory: 128 columns of float32 for the 128x128 accumulator
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(UM_BN) : "memory");
+  if (warp == 1) {                   // tensor memory: two 128x128 float32 accumulators = 256 columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * UM_BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -131,97 +190,67 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < k_blocks; ++kb) {
-        int s = kb % UM_STAGES;
-        unsigned round = kb / UM_STAGES;
-        if (kb >= UM_STAGES && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, a.status, 101)) break;
-        unsigned dst = tiles + s * UM_STAGE_BYTES;
-        mbar_expect_tx(full0 + 8 * s, UM_STAGE_BYTES);
-        tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
-        tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
+      unsigned it = 0;               // k-blocks issued so far, over all tiles: stage = it % STAGES
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * UM_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          int s = it % UM_STAGES;
+          if (it >= UM_STAGES && !mbar_wait(empty0 + 8 * s, (it / UM_STAGES - 1) & 1, a.status, 101)) { ok = false; break; }
+          unsigned dst = tiles + s * UM_STAGE_BYTES;
+          mbar_expect_tx(full0 + 8 * s, UM_STAGE_BYTES);
+          tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
+          tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const unsigned idesc = umma_idesc(UM_BM, UM_BN);
+      unsigned it = 0, use = 0;      // use: tiles done so far; accumulator = use & 1
       bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; ++kb) {
-        int s = kb % UM_STAGES;
-        ok = mbar_wait(full0 + 8 * s, (kb / UM_STAGES) & 1, a.status, 102);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        unsigned sa = tiles + s * UM_STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
-        unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++use) {
+        const unsigned acc = use & 1, d_tmem = tmem_base + acc * UM_BN;
+        if (use >= 2) {              // the epilogue must have drained this accumulator's previous tile
+          ok = mbar_wait(accempty0 + 8 * acc, ((use >> 1) - 1) & 1, a.status, 104);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          int s = it % UM_STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / UM_STAGES) & 1, a.status, 102);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          unsigned sa = tiles + s * UM_STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
+          unsigned long long da = umma_desc(sa), db = umma_desc(sb);
 #pragma unroll
-        for (int k = 0; k < UM_BK / 16; ++k)            // 32 bytes further along K inside the swizzle atom
-          umma_f16(tmem_base, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
-        umma_commit(empty0 + 8 * s);                    // the stage is free once these MMAs have read it
+          for (int k = 0; k < UM_BK / 16; ++k)          // 32 bytes further along K inside the swizzle atom
+            umma_f16(d_tmem, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);                  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(accfull0 + 8 * acc);        // arrives when every MMA of this tile is done
       }
-      umma_commit(accbar);                              // arrives when every MMA issued so far is done
     }
   } else {
-    // epilogue warps: TMEM lanes 32*(warp%4) .. +32 = output rows
-    const int q = warp & 3;
-    bool ok = mbar_wait(accbar, 0, a.status, 103);
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    const int m = m0 + q * 32 + lane;
-    if (ok) {
+    // epilogue warps: TMEM lanes 32*(warp%4) .. +32 = output rows; two warps share a quarter, a column half each
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    unsigned use = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++use) {
+      const unsigned acc = use & 1;
+      const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * UM_BN;
+      if (!mbar_wait(accfull0 + 8 * acc, (use >> 1) & 1, a.status, 103)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int m = m0 + q * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < UM_BN; c0 += 32) {
+      for (int c0 = half * (UM_BN / 2); c0 < (half + 1) * (UM_BN / 2); c0 += 32) {
         float v[32];
-        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);      // whole warp, also for rows past M
-        if (m >= a.M) continue;
-        const int n = n0 + c0;
-        if (EPI == EPI_SWIGLU) {
-          // columns: 8 gate, 8 up, 8 gate, 8 up -> 16 features
-          bf16* dst = (bf16*)a.out + (size_t)m * a.ldo + (n >> 1);
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (n + 16 * h >= a.N) break;
-            unsigned packed[4];
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              float g0 = v[16 * h + j], g1 = v[16 * h + j + 1], u0 = v[16 * h + 8 + j], u1 = v[16 * h + 9 + j];
-              if (a.bias) { g0 += a.bias[n + 16 * h + j]; g1 += a.bias[n + 16 * h + j + 1]; u0 += a.bias[n + 16 * h + 8 + j]; u1 += a.bias[n + 16 * h + 9 + j]; }
-              __nv_bfloat162 p = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
-              packed[j >> 1] = *(unsigned*)&p;
-            }
-            *(uint4*)(dst + 8 * h) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          }
-        } else {
-          const bool whole = n + 32 <= a.N;
-          if (a.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) if (n + j < a.N) v[j] += a.bias[n + j];
-          }
-          if (EPI == EPI_STORE && whole && (a.ldo % 8) == 0) {
-            uint4* dst = (uint4*)((bf16*)a.out + (size_t)m * a.ldo + n);         // 64 contiguous bytes of this row
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), p1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), p3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-              dst[j] = make_uint4(*(unsigned*)&p0, *(unsigned*)&p1, *(unsigned*)&p2, *(unsigned*)&p3);
-            }
-          } else if (EPI != EPI_STORE && whole && (a.ldo % 4) == 0) {
-            float4* dst = (float4*)((float*)a.out + (size_t)m * a.ldo + n);       // 128 contiguous bytes of this row
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (EPI == EPI_ACC) { float4 o = dst[j]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
-              dst[j] = r;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (n + j >= a.N) break;
-              size_t o = (size_t)m * a.ldo + n + j;
-              if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v[j]);
-              else if (EPI == EPI_ACC) ((float*)a.out)[o] += v[j];
-              else ((float*)a.out)[o] = v[j];
-            }
-          }
-        }
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * UM_BN + (unsigned)c0, v);      // whole warp, also for rows past M
+        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0);
       }
+      // this warp has read its part of the accumulator: one of the eight arrivals that free it
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(accempty0 + 8 * acc) : "memory");
     }
   }
   // common exit: every role comes here, also after a wait that gave up
@@ -229,7 +258,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(UM_BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * UM_BN) : "memory");
   }
 }
 
@@ -267,10 +296,17 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& 
   auto kern = gemm_umma_kernel<EPI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return launch_k(kern, dim3(ceil_div(a.N, UM_BN), ceil_div(a.M, UM_BM), 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
+  }
+  int total = ceil_div(a.N, UM_BN) * ceil_div(a.M, UM_BM);
+  return launch_k(kern, dim3(total < n_sm ? total : n_sm, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
 }
 
-// status: device int32 that a role sets (101 producer, 102 MMA, 103 epilogue) if a wait ran out.
+// status: device int32 that a role sets (101 producer, 102/104 MMA, 103 epilogue) if a wait ran out.
 FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
                               int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;

@@ -123,3 +123,21 @@ def test_fused_decode_step_equals_the_per_kernel_path(name):
             assert ok, (mode, i, err, tol)
     ok, err, tol = tiny.close(outs["fused"].reshape(-1, outs["fused"].shape[-1]), outs["kernels"].reshape(-1, outs["kernels"].shape[-1]).cpu(), "bfloat16")
     assert ok, (err, tol)
+
+
+def test_command_line_run_prints_tokens_and_timing_lines():
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    prompt = tiny.tokens("A", 9, 80)
+    cfg, w = tiny.plain_model("A")
+    want = plain_lfm2.greedy(cfg, w, prompt, 5)
+    p = subprocess.run([sys.executable, str(root / "bin" / "fellm"), "run", tiny.model_folder("A"), "--prompt",
+                        ",".join(map(str, prompt)), "--max-tokens", "5", "--temperature", "0", "--repetition-penalty", "1.0",
+                        "--dtype", "float32", "--ctx-size", "0", "--page-tokens", "16"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(t) for t in p.stdout.split()] == want
+    for line in ("prompt eval: 9 tok in", "eval: 5 tok in", "TTFT:", "total:"):       # crates/fellm-cli/src/main.rs:953-967
+        assert line in p.stderr, p.stderr[-1000:]
