@@ -185,85 +185,95 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
   const int tokb = max(1, (PF_WARPS * 16) / R);               // tokens per CTA
   pdl_launch_dependents();
   const int row_begin = a.item_start[item], n_rows = a.item_start[item + 1] - row_begin;
-  const int tok0 = blockIdx.x * tokb;
-  if (tok0 >= n_rows) return;
-  const int n_tok = min(tokb, n_rows - tok0);
-  const int pos0 = a.positions[row_begin] + tok0;              // position of the block's first token
+  const int n_blocks = (n_rows + tokb - 1) / tokb;
+  if ((int)blockIdx.x >= (n_blocks + 1) / 2) return;
+  const int item_pos0 = a.positions[row_begin];
   const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
   pdl_wait();
-
-  // this thread's two rows: (token, head of the group)
-  int tok[2], hr[2], lo[2], hi[2];
-  bool valid[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    int rho = warp * 16 + gq + 8 * r;
-    tok[r] = rho / R; hr[r] = rho - tok[r] * R;
-    valid[r] = tok[r] < n_tok;
-    int pos = pos0 + tok[r];
-    hi[r] = valid[r] ? pos : -1;
-    lo[r] = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-    if (!valid[r]) lo[r] = 1 << 30;
-  }
-  unsigned qf[KS][4];
-  load_q(qf, [&](int i) -> const bf16* {
-    int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
-    return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
-  }, lane);
-
-  float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-#pragma unroll
-  for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
-
-  // keys of the whole block: from the first token's window start to the last token's position
-  const int k_first = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
-  const int k_last = pos0 + n_tok - 1;
-  const int n_tiles = (k_last - k_first) / PF_TK + 1;
   const unsigned s_base = (unsigned)__cvta_generic_to_shared(smem);
   constexpr int TILE_B = PF_TK * ROWB;                         // bytes of one K (or V) tile
-  auto issue = [&](int j) {
-    if (j < n_tiles) {
-      unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
-      int key0 = k_first + j * PF_TK;
-      for (int i = threadIdx.x; i < PF_TK * CPR; i += PF_WARPS * 32) {
-        int row = i / CPR, ch = i - row * CPR;
-        int key = key0 + row;
-        if (key <= k_last) {
-          const bf16* kp = key_row(a, bt, g, key) + ch * 8;
-          cp_async16(ks + tile_off(row, ch), kp);
-          cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * a.page_tokens * HD);
-        } else {                       // past the last key: zeros, so that 0 * V stays 0
-          st_shared_zero16(ks + tile_off(row, ch));
-          st_shared_zero16(vs + tile_off(row, ch));
+
+  // Causal work grows with the block's position: a CTA takes block bx and then its mirror
+  // n_blocks-1-bx, so that every CTA of an item has the same number of key tiles to go through.
+  for (int pass = 0; pass < 2; ++pass) {
+    const int blk = pass == 0 ? (int)blockIdx.x : n_blocks - 1 - (int)blockIdx.x;
+    if (pass == 1 && blk <= (int)blockIdx.x) break;
+    const int tok0 = blk * tokb;
+    const int n_tok = min(tokb, n_rows - tok0);
+    const int pos0 = item_pos0 + tok0;                         // position of the block's first token
+
+    // this thread's two rows: (token, head of the group)
+    int tok[2], hr[2], lo[2], hi[2];
+    bool valid[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      int rho = warp * 16 + gq + 8 * r;
+      tok[r] = rho / R; hr[r] = rho - tok[r] * R;
+      valid[r] = tok[r] < n_tok;
+      int pos = pos0 + tok[r];
+      hi[r] = valid[r] ? pos : -1;
+      lo[r] = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+      if (!valid[r]) lo[r] = 1 << 30;
+    }
+    unsigned qf[KS][4];
+    load_q(qf, [&](int i) -> const bf16* {
+      int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
+      return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
+    }, lane);
+
+    float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+    // keys of the whole block: from the first token's window start to the last token's position
+    const int k_first = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
+    const int k_last = pos0 + n_tok - 1;
+    const int n_tiles = (k_last - k_first) / PF_TK + 1;
+    auto issue = [&](int j) {
+      if (j < n_tiles) {
+        unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+        int key0 = k_first + j * PF_TK;
+        for (int i = threadIdx.x; i < PF_TK * CPR; i += PF_WARPS * 32) {
+          int row = i / CPR, ch = i - row * CPR;
+          int key = key0 + row;
+          if (key <= k_last) {
+            const bf16* kp = key_row(a, bt, g, key) + ch * 8;
+            cp_async16(ks + tile_off(row, ch), kp);
+            cp_async16(vs + tile_off(row, ch), kp + (size_t)a.G * a.page_tokens * HD);
+          } else {                       // past the last key: zeros, so that 0 * V stays 0
+            st_shared_zero16(ks + tile_off(row, ch));
+            st_shared_zero16(vs + tile_off(row, ch));
+          }
         }
       }
+      cp_async_commit();
+    };
+    __syncthreads();                                           // the pass before is done with the stages
+    issue(0);
+    for (int j = 0; j < n_tiles; ++j) {
+      issue(j + 1);
+      cp_async_wait<1>();
+      __syncthreads();
+      unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
+      int key0 = k_first + j * PF_TK;
+      // a warp whose rows all end before this tile has nothing to add (warp-uniform test)
+      int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
+      if (key0 <= warp_hi && warp * 16 < n_tok * R)
+        attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      __syncthreads();                                         // the stage is refilled by the next issue
     }
-    cp_async_commit();
-  };
-  issue(0);
-  for (int j = 0; j < n_tiles; ++j) {
-    issue(j + 1);
-    cp_async_wait<1>();
-    __syncthreads();
-    unsigned ks = s_base + (j % PF_STAGES) * 2 * TILE_B, vs = ks + TILE_B;
-    int key0 = k_first + j * PF_TK;
-    // a warp whose rows all end before this tile has nothing to add (warp-uniform test)
-    int warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
-    if (key0 <= warp_hi && warp * 16 < n_tok * R)
-      attend_tile<PF_TK / 8>(qf, ks, vs, key0, lo, hi, a.scale_log2, o, m, l, lane);
-    __syncthreads();                                           // the stage is refilled by the next issue
-  }
-  cp_async_wait<0>();
+    cp_async_wait<0>();
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    if (!valid[r]) continue;
-    float inv = 1.0f / l[r];
-    bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      if (!valid[r]) continue;
+      float inv = 1.0f / l[r];
+      bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
 #pragma unroll
-    for (int d = 0; d < DN; ++d)
-      *(unsigned*)(dst + d * 8 + 2 * c) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+      for (int d = 0; d < DN; ++d)
+        *(unsigned*)(dst + d * 8 + 2 * c) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+    }
   }
 }
 
@@ -452,7 +462,7 @@ FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int*
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
   }
-  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb), G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, a);
+  return launch_k(kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, a);
 }
 
 // One query row per item.  scratch: float32 [T*H*max_splits*(hd+2)]; counters: int32 [T*G], zero

@@ -240,7 +240,7 @@ def paged_attention_simt(q, pool, block_table, positions, row_slot, layer, scale
 # ------------------------------------------------------------------------------ tensor-core products
 
 _EPI_STORE, _EPI_ACC, _EPI_SWIGLU, _EPI_F32 = 0, 1, 2, 3
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 32      # measured on B200 (350M shapes): above 32 rows the tcgen05 product wins on every shape
 _GEMM_ARGS = [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
 _SKINNY_ARGS = [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
 NORM_FUSE_MAX_ROWS = 16
@@ -334,7 +334,11 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     assert out.stride(1) == 1
     if M == 0:
         return out
-    if M <= SKINNY_MAX_ROWS:
+    umma_ok = (USE_UMMA and norm is None and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+               and (epi != _EPI_SWIGLU or out.stride(0) % 8 == 0))
+    # few rows: the weight-streaming kernel; 17..32 rows: it too, except for very wide products
+    skinny = M <= 64 and (M <= 16 or not umma_ok or (M <= SKINNY_MAX_ROWS and N < 8192))
+    if skinny:
         f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
         if norm is not None:
             code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0),
@@ -343,7 +347,7 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
             code = f(_p(x), None, None, 0.0, _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0),
                      out.stride(0), _stream())
         _check(code, "gemm_skinny")
-    elif USE_UMMA and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (epi != _EPI_SWIGLU or out.stride(0) % 8 == 0):
+    elif umma_ok:
         f = _fn("gemm_umma", "fellm_gemm_umma", _GEMM_ARGS[:-1] + [_c_p, _c_p])
         _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0),
                  _p(umma_status(x.device)), _stream()), "gemm_umma")

@@ -264,7 +264,7 @@ def _gemm_case(M, N, K, seed=0):
     return x, w, x.double() @ w.double().T
 
 
-# M <= 64 runs the weight-streaming kernel, larger M the tiled one
+# M <= 16 runs the weight-streaming kernel, 17..32 it or the tcgen05 product by width, larger M the tcgen05 product
 GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (3, 515, 144), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
                (64, 2048, 200), (5, 65536, 64), (65, 144, 144), (128, 515, 320), (300, 1000, 1000), (2048, 256, 136)]
 
@@ -469,3 +469,12 @@ def test_gemm_umma_tcgen05(M, N, K):
     ops.gemm_bf16(xd, wd, bias, out=out, accumulate=True)
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want + bias.double().cpu(), rtol=1e-4, atol=1e-4)
     ops.check_umma_status(DEV)
+
+
+@pytest.mark.parametrize("M,N,K", [(33, 200, 328), (48, 1024, 1024), (64, 2048, 200), (64, 515, 144)])
+def test_gemm_skinny_up_to_64_rows(M, N, K, monkeypatch):
+    """The weight-streaming kernel takes up to 64 rows (it is the fallback where the tcgen05 product cannot run)."""
+    monkeypatch.setattr(ops, "USE_UMMA", False)
+    x, w, want = _gemm_case(M, N, K, seed=9)
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4)
