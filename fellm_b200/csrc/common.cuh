@@ -38,21 +38,23 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <cstdlib>
-static inline bool pdl_enabled() {
+static inline bool pdl_enabled(int launch_class) {
   static int on = -1;
   // off unless FELLM_B200_PDL=1: measured on B200, a decode step of ~90 dependent launches replayed from a
   // CUDA graph takes 686 us with the attribute and 649 us without (the early-launched kernels wait
   // on the SMs while the predecessor still needs them); the kernels keep their wait/trigger calls,
   // which are no-ops in an ordinary launch
-  if (on < 0) { const char* e = getenv("FELLM_B200_PDL"); on = (e && e[0] == '1') ? 1 : 0; }
-  return on == 1;
+  // FELLM_B200_PDL=2: only launches of class 1 (weight-streaming products, which request their
+  // weights before they wait for the kernel before them)
+  if (on < 0) { const char* e = getenv("FELLM_B200_PDL"); on = (e && e[0] >= '1' && e[0] <= '2') ? e[0] - '0' : 0; }
+  return on == 1 || (on == 2 && launch_class == 1);
 }
 
 // Launches `kernel` with an optional cluster along x and, with FELLM_B200_PDL=1, as a
 // programmatic dependent of the kernel before it.  Returns a cudaError_t as int.
 template <typename... KArgs, typename... Args>
-static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                    int cluster_x, Args... args) {
+static int launch_k_class(int launch_class, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, int cluster_x, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -62,7 +64,7 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
     attr[n].val.clusterDim.x = cluster_x; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
     ++n;
   }
-  if (pdl_enabled()) {
+  if (pdl_enabled(launch_class)) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -71,6 +73,11 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
+}
+template <typename... KArgs, typename... Args>
+static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                    int cluster_x, Args... args) {
+  return launch_k_class(0, kernel, grid, block, smem, stream, cluster_x, args...);
 }
 
 static inline int launch_status() {

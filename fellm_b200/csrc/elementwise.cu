@@ -64,10 +64,73 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < d; i += THREADS) o[i] = from_f<TO>((xr[i] * scale) * w[i]);
 }
 
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float e) { *(float4*)o = make_float4(a, b, c, e); }
+__device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float e) {
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(a, b), p1 = __floats2bfloat162_rn(c, e);
+  uint2 v; v.x = *(unsigned*)&p0; v.y = *(unsigned*)&p1;
+  *(uint2*)o = v;
+}
+
+// d % 4 == 0: a warp per row, 16-byte loads; up to VPL vectors of a lane stay in registers between
+// the sum and the scaling (rows longer than 128*VPL are read a second time).  A row's sum has the
+// same order whatever else is in the batch.
+template <typename TO, int VPL>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int d, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int orow = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (orow >= n_rows) return;
+  const int irow = rows ? rows[orow] : orow;
+  const float4* xr = (const float4*)(x + (size_t)irow * d);
+  const float4* wr = (const float4*)w;
+  const int nv = d >> 2;
+  float4 keep[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int i = lane + j * 32;
+    keep[j] = i < nv ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int j = 0; j < VPL; ++j)
+    ss = fmaf(keep[j].x, keep[j].x, fmaf(keep[j].y, keep[j].y, fmaf(keep[j].z, keep[j].z, fmaf(keep[j].w, keep[j].w, ss))));
+  for (int i = lane + VPL * 32; i < nv; i += 32) {
+    float4 v = xr[i];
+    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+  TO* o = out + (size_t)orow * d;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    int i = lane + j * 32;
+    if (i < nv) {
+      float4 g = wr[i];
+      store4(o + 4 * i, (keep[j].x * scale) * g.x, (keep[j].y * scale) * g.y, (keep[j].z * scale) * g.z, (keep[j].w * scale) * g.w);
+    }
+  }
+  for (int i = lane + VPL * 32; i < nv; i += 32) {
+    float4 v = xr[i], g = wr[i];
+    store4(o + 4 * i, (v.x * scale) * g.x, (v.y * scale) * g.y, (v.z * scale) * g.z, (v.w * scale) * g.w);
+  }
+}
+
 FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_is_bf16,
                             const int* rows, int n_out_rows, int d, float eps, cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
   if (!x || !w || !out) return FELLM_ERR_ARG;
+  if (d % 4 == 0 && d >= 128) {
+    const int warps = 4;
+    dim3 vgrid((n_out_rows + warps - 1) / warps);
+    if (d <= 1024) {
+      if (out_is_bf16) return launch_k(rmsnorm_vec_kernel<bf16, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+      return launch_k(rmsnorm_vec_kernel<float, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+    }
+    if (out_is_bf16) return launch_k(rmsnorm_vec_kernel<bf16, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+    return launch_k(rmsnorm_vec_kernel<float, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+  }
   dim3 grid(n_out_rows);
   if (d >= 512) {
     if (out_is_bf16) return launch_k(rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);

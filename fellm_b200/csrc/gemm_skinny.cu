@@ -288,7 +288,7 @@ static int launch(const SkinnyArgs& a, int ctas_y, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_k(kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
 }
 
 template <int EPI>

@@ -19,7 +19,65 @@
 #define MAX_LC 8
 #define BODY_ROWS 8
 
-template <typename TA>
+__device__ __forceinline__ void sc_unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+
+// Body rows, bfloat16, d % 8 == 0: a thread takes 8 consecutive channels (16-byte loads) of a row;
+// the rows of a tile are independent of one another, so their loads overlap.  Same sums, in the
+// same order, as the scalar path.
+__device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __restrict__ w,
+                                   const float* __restrict__ conv_bias, const int* __restrict__ item_start,
+                                   const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int Lc) {
+  // the tile's threads (all blocks along x) are laid over [rows][groups of 8 channels]
+  const int groups = d / 8, lin = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c0 = (lin % groups) * 8, row_in_tile = lin / groups;
+  const int row_step = (gridDim.x * blockDim.x) / groups;   // >= 8: the grid has a thread per channel
+  const int H = Lc - 1;
+  const size_t ld = (size_t)3 * d;
+  float wt[MAX_LC][8], bias[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+#pragma unroll
+    for (int t = 0; t < MAX_LC; ++t) wt[t][e] = t < Lc ? w[(size_t)(c0 + e) * Lc + t] : 0.f;
+    bias[e] = conv_bias ? conv_bias[c0 + e] : 0.f;
+  }
+  const int r0 = blockIdx.y * BODY_ROWS;
+  for (int r = r0 + row_in_tile; r < r0 + BODY_ROWS; r += row_step) {
+    if (r >= T) break;
+    int j = r - item_start[row_item[r]];
+    if (j < H) continue;                         // head rows belong to the item's head thread
+    const bf16* row = bcx + (size_t)r * ld + c0;
+    float b[8], x[8], cg[8], conv[8];
+    sc_unpack8(*(const uint4*)row, b);
+    sc_unpack8(*(const uint4*)(row + 2 * d), x);
+    sc_unpack8(*(const uint4*)(row + d), cg);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) conv[e] = (b[e] * x[e]) * w[(size_t)(c0 + e) * Lc + H];
+#pragma unroll
+    for (int t = 0; t < MAX_LC - 1; ++t) {
+      if (t < H) {
+        const bf16* pr = bcx + (size_t)(r - H + t) * ld + c0;
+        float pb[8], px[8];
+        sc_unpack8(*(const uint4*)pr, pb);
+        sc_unpack8(*(const uint4*)(pr + 2 * d), px);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) conv[e] = fmaf(pb[e] * px[e], wt[t][e], conv[e]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(cg[0] * (conv[0] + bias[0]), cg[1] * (conv[1] + bias[1]));
+    __nv_bfloat162 p1 = __floats2bfloat162_rn(cg[2] * (conv[2] + bias[2]), cg[3] * (conv[3] + bias[3]));
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(cg[4] * (conv[4] + bias[4]), cg[5] * (conv[5] + bias[5]));
+    __nv_bfloat162 p3 = __floats2bfloat162_rn(cg[6] * (conv[6] + bias[6]), cg[7] * (conv[7] + bias[7]));
+    o.x = *(unsigned*)&p0; o.y = *(unsigned*)&p1; o.z = *(unsigned*)&p2; o.w = *(unsigned*)&p3;
+    *(uint4*)(y + (size_t)r * d + c0) = o;
+  }
+}
+
+template <typename TA, bool VEC>
 __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __restrict__ w,
                                  const float* __restrict__ conv_bias, float* __restrict__ state,
                                  long long slot_stride, const int* __restrict__ item_slot,
@@ -27,6 +85,11 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
                                  TA* __restrict__ y, int T, int n_items, int d, int Lc, int n_body_tiles) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
+  if (VEC && (int)blockIdx.y < n_body_tiles) {
+    pdl_wait();
+    shortconv_body_vec((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, Lc);
+    return;
+  }
   if (c >= d) return;
   const int H = Lc - 1;
   float wt[MAX_LC];
@@ -107,9 +170,12 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   int threads = d >= 128 ? 128 : 64;
   int n_body = all_single ? 0 : ceil_div(T, BODY_ROWS);    // every item has one token: heads only
   dim3 grid(ceil_div(d, threads), n_body + n_items);
-  if (is_bf16)
-    return launch_k(shortconv_kernel<bf16>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+  if (is_bf16 && d % 8 == 0 && n_body > 0)
+    return launch_k(shortconv_kernel<bf16, true>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
-  return launch_k(shortconv_kernel<float>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
+  if (is_bf16)
+    return launch_k(shortconv_kernel<bf16, false>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
+  return launch_k(shortconv_kernel<float, false>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
                   slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body);
 }

@@ -32,7 +32,7 @@ def test_embed_rows(table_dtype):
     assert int(status) == 1 and float(out[1].abs().sum()) == 0 and torch.equal(out[0], table[3].float())
 
 
-@pytest.mark.parametrize("d", [48, 200, 1000, 1536])
+@pytest.mark.parametrize("d", [48, 200, 514, 1000, 1536, 4100])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(d, out_dtype):
     x = torch.randn(37, d, device=DEV) * 3
