@@ -177,6 +177,7 @@ __device__ __forceinline__ const bf16* key_row(const AttnArgs& a, const int* bt,
 #define PF_STAGES 2
 
 __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_PREFILL);
   extern __shared__ __align__(128) unsigned char smem[];
   const int item = blockIdx.z, g = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
   if ((int)blockIdx.x >= (n_blocks + 1) / 2) return;
   const int item_pos0 = a.positions[row_begin];
   const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   const unsigned s_base = (unsigned)__cvta_generic_to_shared(smem);
   constexpr int TILE_B = PF_TK * ROWB;                         // bytes of one K (or V) tile
 
@@ -285,6 +286,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
 #define DC_MAX_PAGES 256
 
 __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int sm_pages[DC_MAX_PAGES];
   __shared__ int sm_last;
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
   const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
   if (pages_in_smem)
     for (int i = threadIdx.x; i < n_pg; i += DC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   __syncthreads();
   constexpr int TILE_B = DC_TK * ROWB;
   const unsigned ring = (unsigned)__cvta_generic_to_shared(smem) + warp * DC_STAGES * 2 * TILE_B;

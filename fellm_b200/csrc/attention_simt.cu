@@ -20,6 +20,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
                             const int* __restrict__ positions, const int* __restrict__ row_slot,
                             TA* __restrict__ out, int T, int H, int G, int hd, int page_tokens, int layer,
                             int layers_in_group, float scale, int window) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_SIMT);
   extern __shared__ float qs_all[];                 // [warps per block][hd]
   int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int warp = blockIdx.x * (blockDim.x >> 5) + wib;

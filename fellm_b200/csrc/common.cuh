@@ -37,6 +37,55 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- kernel timeline (built only with -DFELLM_TRACE=1): thread 0 of every CTA records the global
+// timer at the kernel's entry, after pdl_wait() and at its exit into a buffer that
+// fellm_set_trace() names; without the define the macros are empty.
+enum TraceKernel { TRACE_EMBED_ROWS = 1, TRACE_RMSNORM, TRACE_RMSNORM_VEC, TRACE_SILU_MUL, TRACE_GEMM_SIMT, TRACE_GEMM_TILED,
+                   TRACE_GEMM_UMMA, TRACE_SHORTCONV, TRACE_QK_ROPE_WRITE, TRACE_QK_ROPE_WRITE_VEC, TRACE_ATTENTION_SIMT,
+                   TRACE_ATTENTION_PREFILL, TRACE_ATTENTION_DECODE, TRACE_SAMPLE, TRACE_COUNT_TOKENS, TRACE_ARGMAX_PARTIAL,
+                   TRACE_ARGMAX_FINAL, TRACE_GEMM_SKINNY = 32 /* + 32 * epilogue */ };
+#ifdef FELLM_TRACE
+static __device__ unsigned long long* g_trace_buf;      // [capacity][8]: tag, entry, after wait, exit, 4 marks
+static __device__ unsigned* g_trace_count;
+static __device__ unsigned g_trace_capacity;
+extern "C" __attribute__((visibility("default"))) int fellm_set_trace(void* buf, void* count, unsigned capacity) {
+  cudaError_t e = cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof(buf));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_count, &count, sizeof(count));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_trace_capacity, &capacity, sizeof(capacity));
+  return (int)e;
+}
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+struct TraceScope {
+  unsigned long long* rec;
+  __device__ __forceinline__ TraceScope(int id) : rec(nullptr) {
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0 && g_trace_buf) {
+      unsigned i = atomicAdd(g_trace_count, 1u);
+      if (i < g_trace_capacity) {
+        rec = g_trace_buf + 8 * (size_t)i;
+        unsigned long long blocks = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+        rec[0] = (unsigned long long)id | (blocks << 16);
+        rec[2] = 0; rec[4] = 0; rec[5] = 0; rec[6] = 0; rec[7] = 0;
+        rec[1] = trace_now();
+      }
+    }
+  }
+  __device__ __forceinline__ void waited() { if (rec) rec[2] = trace_now(); }
+  __device__ __forceinline__ void mark(int k) { if (rec) rec[4 + k] = trace_now(); }
+  __device__ __forceinline__ ~TraceScope() { if (rec) rec[3] = trace_now(); }
+};
+#define FELLM_TRACE_SCOPE(id) TraceScope fellm_trace_scope(id)
+#define FELLM_TRACE_WAITED() fellm_trace_scope.waited()
+#define FELLM_TRACE_MARK(k) fellm_trace_scope.mark(k)
+#else
+#define FELLM_TRACE_SCOPE(id) do { } while (0)
+#define FELLM_TRACE_WAITED() do { } while (0)
+#define FELLM_TRACE_MARK(k) do { } while (0)
+#endif
+
 #include <cstdlib>
 static inline bool pdl_enabled(int launch_class) {
   static int on = -1;

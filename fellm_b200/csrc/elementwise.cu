@@ -9,8 +9,9 @@
 template <typename TW>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                                   float* __restrict__ out, int d, int vocab, int* __restrict__ status) {
+  FELLM_TRACE_SCOPE(TRACE_EMBED_ROWS);
   pdl_launch_dependents();
-  pdl_wait();                 // the residual buffer may still be read by the step before
+  pdl_wait(); FELLM_TRACE_WAITED();                 // the residual buffer may still be read by the step before
   int row = blockIdx.x;
   int tok = tokens[row];
   float* o = out + (size_t)row * d;
@@ -40,10 +41,11 @@ FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_i
 template <typename TO, int THREADS>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                TO* __restrict__ out, const int* __restrict__ rows, int d, float eps) {
+  FELLM_TRACE_SCOPE(TRACE_RMSNORM);
   __shared__ float partial[THREADS / 32];
   __shared__ float scale_s;
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   int orow = blockIdx.x;
   int irow = rows ? rows[orow] : orow;
   const float* xr = x + (size_t)irow * d;
@@ -77,8 +79,9 @@ __device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float
 template <typename TO, int VPL>
 __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                    TO* __restrict__ out, const int* __restrict__ rows, int n_rows, int d, float eps) {
+  FELLM_TRACE_SCOPE(TRACE_RMSNORM_VEC);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   const int lane = threadIdx.x & 31;
   const int orow = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (orow >= n_rows) return;
@@ -144,8 +147,9 @@ FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_i
 // in [T, 2F]: gate in columns [0,F), up in [F,2F); out [T,F] = gate/(1+exp(-gate)) * up.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int rows, int F) {
+  FELLM_TRACE_SCOPE(TRACE_SILU_MUL);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   size_t n = (size_t)rows * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     size_t r = i / F; int c = (int)(i - r * F);

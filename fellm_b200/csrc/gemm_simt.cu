@@ -17,6 +17,7 @@ template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_tn_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
                     TO* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_SIMT);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   int tid = threadIdx.x;

@@ -34,6 +34,8 @@ namespace cg = cooperative_groups;
 #define SK_THREADS (SK_WARPS * 32)
 #define KCHUNK 32
 #define SK_U 5                       // chunks per round: 10 x 16 B per thread, two rounds in flight
+#define SK_XF 2048                   // floats of a row that a warp's float32 buffer takes at a time
+#define SK_GAMMA_MAX 2048            // norm weights of up to this many columns are parked in shared memory
 
 enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
 
@@ -43,6 +45,11 @@ __device__ __forceinline__ void mma16816(float* d, const unsigned* a, unsigned b
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+
+__device__ __forceinline__ void sk_cp_async16(unsigned smem_addr, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem));
+}
+__device__ __forceinline__ void sk_cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -57,7 +64,8 @@ struct SkinnyArgs {
   const float* norm_w;      // [K]
   float eps;
   const bf16* W; const float* bias; void* out;
-  int M, N, K, lda, ldw, ldo, k_per_cta, xs_stride, splits, warps_k, n_tiles, tiles_per_warp;
+  int M, N, K, lda, ldw, ldo, k_per_cta, xs_stride, splits, warps_k, n_tiles, tiles_per_warp, gamma_offset, xf_offset,
+      log2_warps_k, k_per_warp, pdl, chunks_per_warp;
 };
 
 template <int MT, int EPI>
@@ -93,108 +101,203 @@ __device__ __forceinline__ void epilogue_direct(const SkinnyArgs& a, float (*acc
   }
 }
 
+// One row of 128*J floats from the warp's piece: RMSNorm in the order of the general path (lane l
+// sums the float4s l, l+32, ... in turn), written as bfloat16.
+template <int J>
+__device__ __forceinline__ void norm_row_fast(const float4* piece, const float4* gamma_s, bf16* row, int lane, int K, float eps) {
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const float4 v = piece[lane + 32 * j];
+    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+  }
+  ss = warp_sum(ss);
+  const float sc = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+  for (int j = 0; j < J; ++j) {                      // read again from shared memory: cheaper than 4*J registers
+    const float4 v = piece[lane + 32 * j], gw = gamma_s[lane + 32 * j];
+    __nv_bfloat162 p0 = __floats2bfloat162_rn((v.x * sc) * gw.x, (v.y * sc) * gw.y);
+    __nv_bfloat162 p1 = __floats2bfloat162_rn((v.z * sc) * gw.z, (v.w * sc) * gw.w);
+    uint2 val; val.x = *(unsigned*)&p0; val.y = *(unsigned*)&p1;
+    *(uint2*)(row + 4 * (lane + 32 * j)) = val;
+  }
+}
+
 // MT: token tiles of 8 (M <= 8*MT).
 template <int MT, int EPI>
-__global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1) gemm_skinny_kernel(SkinnyArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * EPI);
   extern __shared__ __align__(16) unsigned char smem[];
-  __shared__ float row_scale[MT * 8];
   constexpr int MP = MT * 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = a.splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
   // the CTA's warps: wn = which slab of the CTA's pass, wk = which slice of the CTA's K range
-  const int warps_n = SK_WARPS / a.warps_k;
-  const int wn = warp / a.warps_k, wk = warp - wn * a.warps_k;
+  // (warps_k is a power of two; no division by a run-time value on the way to the first load)
+  const int warps_n = SK_WARPS >> a.log2_warps_k;
+  const int wn = warp >> a.log2_warps_k, wk = warp & (a.warps_k - 1);
   const int k_cta = split * a.k_per_cta;
-  const int k_per_warp = a.k_per_cta / a.warps_k;                    // a multiple of 32
-  const int k_begin = k_cta + wk * k_per_warp;
-  const int k_len = max(min(a.K, k_begin + k_per_warp) - k_begin, 0);
+  const int k_begin = k_cta + wk * a.k_per_warp;                     // k_per_warp: a multiple of 32
+  const int k_len = max(min(a.K, k_begin + a.k_per_warp) - k_begin, 0);
   const int n_chunks = (k_len + KCHUNK - 1) / KCHUNK;
   const int rounds_per_tile = max((n_chunks + SK_U - 1) / SK_U, 1);
-  // this warp's slabs: first_tile, first_tile + tile_stride, ...
+  // this warp's slabs: first_tile, first_tile + tile_stride, ...: tiles_per_warp of them, or one less
   const int first_tile = blockIdx.y * warps_n + wn;
   const int tile_stride = gridDim.y * warps_n;
-  int my_tiles = first_tile < a.n_tiles ? (a.n_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+  const int my_tiles = first_tile >= a.n_tiles ? 0
+                       : a.tiles_per_warp - (first_tile + (a.tiles_per_warp - 1) * tile_stride >= a.n_tiles ? 1 : 0);
   const int total_rounds = my_tiles * rounds_per_tile;
+  auto advance = [&](int& tl, int& rr) { if (++rr == rounds_per_tile) { rr = 0; ++tl; } };
 
-  auto load_round = [&](int r, uint4* w0, uint4* w1) {
-    int tl = r / rounds_per_tile, rr = r - tl * rounds_per_tile;
-    int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
-    const bf16* p0 = a.W + (size_t)min(n0 + g, a.N - 1) * a.ldw + k_begin + c * 8;      // rows past N: clamped, never stored
-    const bf16* p1 = a.W + (size_t)min(n0 + g + 8, a.N - 1) * a.ldw + k_begin + c * 8;
+  // a round is SK_U chunks of 32 k; all of them whole (the common case) means no test per load
+  const bool ragged = (k_len & (KCHUNK - 1)) != 0;                   // the last chunk stops inside its 32 k
+  auto load_round = [&](int tl, int rr, uint4* w0, uint4* w1) {
+    const int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
+    const int k0 = k_begin + c * 8 + rr * (SK_U * KCHUNK);
+    const bf16* p0 = a.W + (size_t)min(n0 + g, a.N - 1) * a.ldw + k0;      // rows past N: clamped, never stored
+    const bf16* p1 = a.W + (size_t)min(n0 + g + 8, a.N - 1) * a.ldw + k0;
+    const int n_valid = n_chunks - rr * SK_U;                        // chunks of this round, warp-uniform
+    if (n_valid >= SK_U && !ragged) {
 #pragma unroll
-    for (int u = 0; u < SK_U; ++u) {
-      int kk = (rr * SK_U + u) * KCHUNK;
-      if (kk + c * 8 < k_len) { w0[u] = ldg_stream(p0 + kk); w1[u] = ldg_stream(p1 + kk); }
-      else { w0[u] = make_uint4(0, 0, 0, 0); w1[u] = w0[u]; }
+      for (int u = 0; u < SK_U; ++u) { w0[u] = ldg_stream(p0 + u * KCHUNK); w1[u] = ldg_stream(p1 + u * KCHUNK); }
+    } else {
+      const int rem = k_len - rr * (SK_U * KCHUNK) - c * 8;          // this thread's 8 k of chunk u exist if u*32 < rem
+#pragma unroll
+      for (int u = 0; u < SK_U; ++u) {
+        if (u * KCHUNK < rem) { w0[u] = ldg_stream(p0 + u * KCHUNK); w1[u] = ldg_stream(p1 + u * KCHUNK); }
+        else { w0[u] = make_uint4(0, 0, 0, 0); w1[u] = w0[u]; }
+      }
     }
   };
 
-  // ---- weights first: they do not depend on the kernel before this one
-  uint4 wA0[SK_U], wA1[SK_U], wB0[SK_U], wB1[SK_U];
-  if (total_rounds > 0) load_round(0, wA0, wA1);
-  if (total_rounds > 1) load_round(1, wB0, wB1);
-  pdl_launch_dependents();
-  pdl_wait();
-
-  // ---- stage x[:, k_cta : k_cta + k_per_cta] as bfloat16 (rows >= M zero), normed if asked
+  // ---- x[:, k_cta : k_cta + k_per_cta] goes to shared memory as bfloat16 (rows >= M zero), normed
+  // if asked.  All of it is requested with cp.async before any of it is used: a chain of dependent
+  // round trips to L2 is what a step of a few rows would otherwise spend most of its time on.
   bf16* xs = (bf16*)smem;
-  const int vec_per_row = a.k_per_cta / 8;
-  if (a.xf) {
-    // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39) over the whole row, whatever the slice
-    for (int r = warp; r < a.M; r += SK_WARPS) {
-      const float4* xr = (const float4*)(a.xf + (size_t)r * a.lda);
-      float ss = 0.f;
-      for (int i = lane; i < a.K / 4; i += 32) { float4 v = xr[i]; ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss)))); }
-      ss = warp_sum(ss);
-      if (lane == 0) row_scale[r] = 1.0f / sqrtf(ss / (float)a.K + a.eps);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < MT * 8 * vec_per_row; i += SK_THREADS) {
-      int r = i / vec_per_row, v = i - r * vec_per_row;
-      int k = k_cta + v * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (r < a.M && k < a.K) {
-        const float4* xr = (const float4*)(a.xf + (size_t)r * a.lda + k);
-        const float4* wr = (const float4*)(a.norm_w + k);
-        float4 x0 = xr[0], x1 = xr[1], g0 = wr[0], g1 = wr[1];
-        float sc = row_scale[r];
-        __nv_bfloat162 p0 = __floats2bfloat162_rn((x0.x * sc) * g0.x, (x0.y * sc) * g0.y);
-        __nv_bfloat162 p1 = __floats2bfloat162_rn((x0.z * sc) * g0.z, (x0.w * sc) * g0.w);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn((x1.x * sc) * g1.x, (x1.y * sc) * g1.y);
-        __nv_bfloat162 p3 = __floats2bfloat162_rn((x1.z * sc) * g1.z, (x1.w * sc) * g1.w);
-        val.x = *(unsigned*)&p0; val.y = *(unsigned*)&p1; val.z = *(unsigned*)&p2; val.w = *(unsigned*)&p3;
+  const int vec_per_row = a.k_per_cta >> 3;
+  const int nv = a.K >> 2;                                           // float4s of a float32 row
+  const bool gamma_staged = a.xf && a.K <= SK_GAMMA_MAX;
+  float4* piece = (float4*)(smem + a.xf_offset) + (size_t)warp * (min(a.K, SK_XF) / 4);   // the warp's float32 row piece
+  const unsigned piece_s = (unsigned)__cvta_generic_to_shared(piece);
+  auto request_piece = [&](const float* xrow, int pc) {
+    const int v0 = pc * (SK_XF / 4), v1 = min(nv, v0 + SK_XF / 4);
+    for (int i = v0 + lane; i < v1; i += 32) sk_cp_async16(piece_s + 16u * (i - v0), xrow + 4 * i);
+  };
+  auto request_x = [&]() {
+    if (a.xf) {
+      if (warp < a.M) request_piece(a.xf + (size_t)warp * a.lda, 0);
+    } else {
+      const unsigned xs_s = (unsigned)__cvta_generic_to_shared(xs);
+      const int live_vec = min(vec_per_row, max(a.K - k_cta, 0) >> 3);      // K % 8 == 0: whole vectors
+      for (int r = warp; r < MP; r += SK_WARPS) {
+        bf16* dst = xs + (size_t)r * a.xs_stride;
+        if (r < a.M) {
+          const bf16* src = a.x + (size_t)r * a.lda + k_cta;
+          const unsigned dst_s = xs_s + 2u * (unsigned)(r * a.xs_stride);
+          for (int vv = lane; vv < live_vec; vv += 32) sk_cp_async16(dst_s + 16u * vv, src + vv * 8);
+          for (int vv = live_vec + lane; vv < vec_per_row; vv += 32) *(uint4*)(dst + vv * 8) = make_uint4(0, 0, 0, 0);
+        } else {
+          for (int vv = lane; vv < vec_per_row; vv += 32) *(uint4*)(dst + vv * 8) = make_uint4(0, 0, 0, 0);
+        }
       }
-      *(uint4*)(xs + (size_t)r * a.xs_stride + v * 8) = val;
+    }
+  };
+
+  // ---- requests.  The norm's weights and W are parameters: they never wait for the kernel before
+  // this one.  As a programmatic dependent the kernel asks for W, waits, then asks for x; launched
+  // the ordinary way it asks for the few KB of x first, so that they do not queue behind W.
+  if (gamma_staged) {
+    const unsigned gs = (unsigned)__cvta_generic_to_shared(smem + a.gamma_offset);
+    for (int i = threadIdx.x; i < nv; i += SK_THREADS) sk_cp_async16(gs + 16u * i, a.norm_w + 4 * i);
+  }
+  if (!a.pdl) request_x();
+  uint4 wA0[SK_U], wA1[SK_U], wB0[SK_U], wB1[SK_U];
+  int ltl = 0, lrr = 0;
+  if (total_rounds > 0) { load_round(ltl, lrr, wA0, wA1); advance(ltl, lrr); }
+  if (total_rounds > 1) { load_round(ltl, lrr, wB0, wB1); advance(ltl, lrr); }
+  pdl_launch_dependents();
+  if (a.pdl) {
+    pdl_wait();
+    request_x();
+  }
+  FELLM_TRACE_WAITED();
+
+  if (a.xf) {
+    // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39) over the whole row, whatever the slice:
+    // a warp per row; the row goes through the warp's float32 buffer in pieces of SK_XF floats, lane
+    // l taking the float4s l, l+32, ... of each piece (one piece, read once, when K <= SK_XF)
+    const float4* wr = (const float4*)a.norm_w;
+    const float4* gamma_s = (const float4*)(smem + a.gamma_offset);
+    const int n_pieces = (nv + SK_XF / 4 - 1) / (SK_XF / 4);
+    sk_cp_async_wait_all();
+    if (gamma_staged) __syncthreads(); else __syncwarp();
+    // whole rows of 1024 or 2048 columns in one piece, the norm's weights parked: straight-line code
+    const bool fast8 = gamma_staged && k_cta == 0 && a.k_per_cta >= a.K && nv == 256;
+    const bool fast16 = gamma_staged && k_cta == 0 && a.k_per_cta >= a.K && nv == 512;
+    for (int r = warp; r < MP; r += SK_WARPS) {
+      bf16* row = xs + (size_t)r * a.xs_stride;
+      if (r < a.M && (fast8 || fast16)) {
+        if (r != warp) { __syncwarp(); request_piece(a.xf + (size_t)r * a.lda, 0); sk_cp_async_wait_all(); __syncwarp(); }
+        if (fast8) norm_row_fast<8>(piece, gamma_s, row, lane, a.K, a.eps);
+        else norm_row_fast<16>(piece, gamma_s, row, lane, a.K, a.eps);
+        for (int k = a.K + lane * 4; k < a.k_per_cta; k += 128) *(uint2*)(row + k) = make_uint2(0, 0);
+        continue;
+      }
+      if (r >= a.M) {
+        for (int k = lane * 4; k < a.k_per_cta; k += 128) *(uint2*)(row + k) = make_uint2(0, 0);
+        continue;
+      }
+      const float* xrow = a.xf + (size_t)r * a.lda;
+      float ss = 0.f;
+      for (int pc = 0; pc < n_pieces; ++pc) {
+        if (pc > 0 || r != warp) { __syncwarp(); request_piece(xrow, pc); sk_cp_async_wait_all(); __syncwarp(); }
+        const int cnt = min(nv - pc * (SK_XF / 4), SK_XF / 4);
+        for (int i = lane; i < cnt; i += 32) {
+          float4 v = piece[i];
+          ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+      }
+      ss = warp_sum(ss);
+      const float sc = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+      for (int pc = 0; pc < n_pieces; ++pc) {
+        if (n_pieces > 1) { __syncwarp(); request_piece(xrow, pc); sk_cp_async_wait_all(); __syncwarp(); }
+        const int v0 = pc * (SK_XF / 4), cnt = min(nv - v0, SK_XF / 4);
+        for (int i = lane; i < cnt; i += 32) {
+          int k = 4 * (v0 + i) - k_cta;
+          if (k < 0 || k >= a.k_per_cta) continue;
+          float4 x = piece[i], gw = gamma_staged ? gamma_s[v0 + i] : wr[v0 + i];
+          __nv_bfloat162 p0 = __floats2bfloat162_rn((x.x * sc) * gw.x, (x.y * sc) * gw.y);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn((x.z * sc) * gw.z, (x.w * sc) * gw.w);
+          uint2 val; val.x = *(unsigned*)&p0; val.y = *(unsigned*)&p1;
+          *(uint2*)(row + k) = val;
+        }
+      }
+      // columns of the slice past K (the last split of a K that the splits do not divide)
+      for (int k = max(a.K - k_cta, 0) + lane * 4; k < a.k_per_cta; k += 128) *(uint2*)(row + k) = make_uint2(0, 0);
     }
   } else {
-    for (int i = threadIdx.x; i < MT * 8 * vec_per_row; i += SK_THREADS) {
-      int r = i / vec_per_row, v = i - r * vec_per_row;
-      int k = k_cta + v * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (r < a.M && k < a.K) val = *(const uint4*)(a.x + (size_t)r * a.lda + k);      // K % 8 == 0: whole vectors
-      *(uint4*)(xs + (size_t)r * a.xs_stride + v * 8) = val;
-    }
+    sk_cp_async_wait_all();
   }
   __syncthreads();
+  FELLM_TRACE_MARK(0);
 
   // ---- rounds of SK_U chunks; the round after next is requested before this one is multiplied
   float acc[MT][4];
 #pragma unroll
   for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
   float* slots = (float*)(smem + (size_t)MT * 8 * a.xs_stride * sizeof(bf16));      // [warp][tile of warp][16][MP], split-K only
-  const bf16* xw = xs + (size_t)g * a.xs_stride + wk * k_per_warp + c * 8;
+  const bf16* xw = xs + (size_t)g * a.xs_stride + wk * a.k_per_warp + c * 8;
   const bool direct = a.splits == 1 && a.warps_k == 1;
 
-  auto compute_round = [&](int r, const uint4* w0, const uint4* w1) {
-    int tl = r / rounds_per_tile, rr = r - tl * rounds_per_tile;
+  auto compute_round = [&](int tl, int rr, const uint4* w0, const uint4* w1) {
+    const int n_valid = n_chunks - rr * SK_U;                        // warp-uniform
+    const bf16* xr0 = xw + rr * (SK_U * KCHUNK);
 #pragma unroll
     for (int u = 0; u < SK_U; ++u) {
-      int ch = rr * SK_U + u;
-      if (ch < n_chunks) {
+      if (u < n_valid) {
         unsigned fa[4] = {w0[u].x, w1[u].x, w0[u].y, w1[u].y};
         unsigned fb[4] = {w0[u].z, w1[u].z, w0[u].w, w1[u].w};
-        const bf16* xr = xw + ch * KCHUNK;
+        const bf16* xr = xr0 + u * KCHUNK;
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
           uint4 b = *(const uint4*)(xr + (size_t)t * 8 * a.xs_stride);
@@ -222,22 +325,25 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
     }
   };
 
+  int ctl = 0, crr = 0;
   for (int r = 0; r < total_rounds; r += 2) {
-    compute_round(r, wA0, wA1);
-    if (r + 2 < total_rounds) load_round(r + 2, wA0, wA1);
+    compute_round(ctl, crr, wA0, wA1); advance(ctl, crr);
+    if (r + 2 < total_rounds) { load_round(ltl, lrr, wA0, wA1); advance(ltl, lrr); }
     if (r + 1 < total_rounds) {
-      compute_round(r + 1, wB0, wB1);
-      if (r + 3 < total_rounds) load_round(r + 3, wB0, wB1);
+      compute_round(ctl, crr, wB0, wB1); advance(ctl, crr);
+      if (r + 3 < total_rounds) { load_round(ltl, lrr, wB0, wB1); advance(ltl, lrr); }
     }
   }
+  FELLM_TRACE_MARK(1);
   if (direct) return;
 
   // ---- split K: sum the partial slabs over the cluster's ranks and the CTA's K warps, in that
-  // order; every (rank, K warp) finishes a share of each slab's rows
+  // order; every (rank, K warp) finishes a share of each slab's outputs
   if (a.splits > 1) cg::this_cluster().sync(); else __syncthreads();
-  const int workers = a.splits * a.warps_k, me = split * a.warps_k + wk;
-  const float* slab_slots = slots + (size_t)(wn * a.warps_k) * a.tiles_per_warp * SK_ROWS * MP;   // K warp 0 of this slab
-  const size_t warp_stride = (size_t)a.tiles_per_warp * SK_ROWS * MP;
+  FELLM_TRACE_MARK(2);
+  const int workers = a.splits << a.log2_warps_k, me = (split << a.log2_warps_k) + wk;
+  const float* slab_slots = slots + (size_t)(wn << a.log2_warps_k) * a.tiles_per_warp * SK_ROWS * MP;   // K warp 0 of this slab
+  const int warp_stride = a.tiles_per_warp * SK_ROWS * MP;
   for (int tl = 0; tl < my_tiles; ++tl) {
     int n0 = (first_tile + tl * tile_stride) * SK_ROWS;
     const float* mine = slab_slots + (size_t)tl * SK_ROWS * MP;
@@ -245,24 +351,252 @@ __global__ void __launch_bounds__(SK_THREADS) gemm_skinny_kernel(SkinnyArgs a) {
     for (int i = me * 32 + lane; i < units; i += workers * 32) {
       int m, j;
       if (EPI == EPI_SWIGLU) { m = i >> 3; j = i & 7; } else { m = i >> 4; j = i & 15; }
+      const int n = n0 + j;
+      const bool live = n < a.N;
+      const size_t o = (size_t)m * a.ldo + n;
+      float old = 0.f;
+      if (EPI == EPI_ACC && live) old = ((float*)a.out)[o];          // asked for before the partial sums
+      const float* mine_e = mine + j * MP + m;
+      // partial sums in the order (rank, K warp), requested RG at a time
+      constexpr int RG = 8;
       float v0 = 0.f, v1 = 0.f;
-      for (int s = 0; s < a.splits; ++s) {
-        const float* p = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine, s) : mine;
-        for (int w = 0; w < a.warps_k; ++w) {
-          v0 += p[w * warp_stride + j * MP + m];
-          if (EPI == EPI_SWIGLU) v1 += p[w * warp_stride + (j + 8) * MP + m];
+      for (int q0 = 0; q0 < workers; q0 += RG) {
+        float p0[RG], p1[RG];
+#pragma unroll
+        for (int q = 0; q < RG; ++q) {
+          int idx = q0 + q;
+          p0[q] = 0.f; p1[q] = 0.f;
+          if (idx < workers) {
+            int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
+            const float* p = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine_e, sr) : mine_e;
+            p0[q] = p[w * warp_stride];
+            if (EPI == EPI_SWIGLU) p1[q] = p[w * warp_stride + 8 * MP];
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < RG; ++q) {
+          if (q0 + q < workers) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
         }
       }
-      int n = n0 + j;
-      if (n >= a.N) continue;
+      if (!live) continue;
       if (EPI == EPI_SWIGLU) {
         if (a.bias) { v0 += a.bias[n]; v1 += a.bias[n + 8]; }
         ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((v0 / (1.0f + expf(-v0))) * v1);
       } else {
         if (a.bias) v0 += a.bias[n];
-        size_t o = (size_t)m * a.ldo + n;
         if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
-        else if (EPI == EPI_ACC) ((float*)a.out)[o] += v0;
+        else if (EPI == EPI_ACC) ((float*)a.out)[o] = old + v0;
+        else ((float*)a.out)[o] = v0;
+      }
+    }
+  }
+  if (a.splits > 1) cg::this_cluster().sync();           // nobody leaves while its slabs are being read
+}
+
+// ---------------------------------------------------------------- the single-shot kernel
+// The decode step's products: M <= 16 rows, every (slab, K slice) has a warp of its own, a slice is
+// at most LEAN_CH whole chunks, N is a multiple of 16.  One pass, no loops over slabs or rounds:
+// the same sums in the same order as gemm_skinny_kernel, in a third of the instructions (a warp's
+// serial instruction stream is what a product of a few microseconds waits for).
+#define LEAN_CH 10
+
+template <int OFF>
+__device__ __forceinline__ uint4 ldg_stream_at(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4+%5];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "n"(OFF));
+  return v;
+}
+
+template <int U, int N>
+struct LeanLoad {
+  static __device__ __forceinline__ void run(const bf16* p0, const bf16* p1, uint4* w0, uint4* w1, int n_chunks) {
+    if (U < 8 || U < n_chunks) {                       // the first 8 chunks are there (n_chunks >= 8), the rest are tested
+      w0[U] = ldg_stream_at<U * KCHUNK * 2>(p0);
+      w1[U] = ldg_stream_at<U * KCHUNK * 2>(p1);
+    }
+    LeanLoad<U + 1, N>::run(p0, p1, w0, w1, n_chunks);
+  }
+};
+template <int N>
+struct LeanLoad<N, N> {
+  static __device__ __forceinline__ void run(const bf16*, const bf16*, uint4*, uint4*, int) {}
+};
+
+template <int MT, int EPI, bool NORM>
+__global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * EPI);
+  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr int MP = MT * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int split = a.splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
+  const int wn = warp >> a.log2_warps_k, wk = warp & (a.warps_k - 1);
+  const int k_cta = split * a.k_per_cta;
+  const int n_chunks = a.chunks_per_warp;              // 8..LEAN_CH, the same for every warp
+  const int tile = blockIdx.y * (SK_WARPS >> a.log2_warps_k) + wn;
+  const bool active = tile < a.n_tiles;
+  const int n0 = tile * SK_ROWS;
+  bf16* xs = (bf16*)smem;
+  const int nv = a.K >> 2;
+  float4* piece = (float4*)(smem + a.xf_offset) + (size_t)warp * nv;     // NORM: the warp's float32 row
+  const unsigned piece_s = (unsigned)__cvta_generic_to_shared(piece);
+
+  auto request_row = [&](int r) {                      // NORM: float32 row r into the warp's piece
+    const float* xrow = a.xf + (size_t)r * a.lda;
+    for (int i = lane; i < nv; i += 32) sk_cp_async16(piece_s + 16u * i, xrow + 4 * i);
+  };
+  auto request_x = [&]() {
+    if (NORM) {
+      if (warp < a.M) request_row(warp);
+    } else {
+      const int vec_per_row = a.k_per_cta >> 3;
+      const unsigned xs_s = (unsigned)__cvta_generic_to_shared(xs);
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        const int r = warp + 8 * t;
+        bf16* dst = xs + (size_t)r * a.xs_stride;
+        if (r < a.M) {
+          const bf16* src = a.x + (size_t)r * a.lda + k_cta;
+          const unsigned dst_s = xs_s + 2u * (unsigned)(r * a.xs_stride);
+          for (int vv = lane; vv < vec_per_row; vv += 32) sk_cp_async16(dst_s + 16u * vv, src + vv * 8);
+        } else {
+          for (int vv = lane; vv < vec_per_row; vv += 32) *(uint4*)(dst + vv * 8) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  };
+
+  // ---- requests: the norm's weights and W never wait for the kernel before this one; x is asked
+  // for first when the launch is an ordinary one (so that it does not queue behind W), after the
+  // wait when the kernel runs as a programmatic dependent
+  if (NORM) {
+    const unsigned gs = (unsigned)__cvta_generic_to_shared(smem + a.gamma_offset);
+    for (int i = threadIdx.x; i < nv; i += SK_THREADS) sk_cp_async16(gs + 16u * i, a.norm_w + 4 * i);
+  }
+  if (!a.pdl) request_x();
+  uint4 w0[LEAN_CH], w1[LEAN_CH];
+  if (active) {
+    const int k0 = k_cta + wk * a.k_per_warp + c * 8;
+    const bf16* p0 = a.W + (size_t)(n0 + g) * a.ldw + k0;
+    LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
+  }
+  pdl_launch_dependents();
+  if (a.pdl) {
+    pdl_wait();
+    request_x();
+  }
+  FELLM_TRACE_WAITED();
+
+  sk_cp_async_wait_all();
+  if (NORM) {
+    // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39): a warp per row, whole rows
+    const float4* gamma_s = (const float4*)(smem + a.gamma_offset);
+    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      const int r = warp + 8 * t;
+      bf16* row = xs + (size_t)r * a.xs_stride;
+      if (r < a.M) {
+        if (t > 0) { __syncwarp(); request_row(r); sk_cp_async_wait_all(); __syncwarp(); }
+        if (nv == 256) norm_row_fast<8>(piece, gamma_s, row, lane, a.K, a.eps);
+        else if (nv == 512) norm_row_fast<16>(piece, gamma_s, row, lane, a.K, a.eps);
+        else {
+          float ss = 0.f;
+          for (int i = lane; i < nv; i += 32) {
+            const float4 v = piece[i];
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+          }
+          ss = warp_sum(ss);
+          const float sc = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+          for (int i = lane; i < nv; i += 32) {
+            const float4 v = piece[i], gw = gamma_s[i];
+            __nv_bfloat162 q0 = __floats2bfloat162_rn((v.x * sc) * gw.x, (v.y * sc) * gw.y);
+            __nv_bfloat162 q1 = __floats2bfloat162_rn((v.z * sc) * gw.z, (v.w * sc) * gw.w);
+            uint2 val; val.x = *(unsigned*)&q0; val.y = *(unsigned*)&q1;
+            *(uint2*)(row + 4 * i) = val;
+          }
+        }
+      } else {
+        for (int k = lane * 4; k < a.K; k += 128) *(uint2*)(row + k) = make_uint2(0, 0);
+      }
+    }
+  }
+  __syncthreads();
+  FELLM_TRACE_MARK(0);
+
+  // ---- the warp's slice of its slab
+  float acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+  float* slots = (float*)(smem + (size_t)MP * a.xs_stride * sizeof(bf16));      // [warp][16][MP]
+  if (active) {
+    const bf16* xw = xs + (size_t)g * a.xs_stride + wk * a.k_per_warp + c * 8;
+#pragma unroll
+    for (int u = 0; u < LEAN_CH; ++u) {
+      if (u < 8 || u < n_chunks) {
+        unsigned fa[4] = {w0[u].x, w1[u].x, w0[u].y, w1[u].y};
+        unsigned fb[4] = {w0[u].z, w1[u].z, w0[u].w, w1[u].w};
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          uint4 b = *(const uint4*)(xw + u * KCHUNK + (size_t)t * 8 * a.xs_stride);
+          mma16816(acc[t], fa, b.x, b.y);
+          mma16816(acc[t], fb, b.z, b.w);
+        }
+      }
+    }
+    float* p = slots + (size_t)warp * SK_ROWS * MP;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      *(float2*)(p + g * MP + t * 8 + 2 * c) = make_float2(acc[t][0], acc[t][1]);
+      *(float2*)(p + (g + 8) * MP + t * 8 + 2 * c) = make_float2(acc[t][2], acc[t][3]);
+    }
+  }
+  FELLM_TRACE_MARK(1);
+  if (a.splits > 1) cg::this_cluster().sync(); else __syncthreads();
+  FELLM_TRACE_MARK(2);
+
+  // ---- sum the partial slabs over the cluster's ranks and the CTA's K warps, in that order; every
+  // (rank, K warp) finishes a share of the slab's outputs
+  if (active) {
+    const int workers = a.splits << a.log2_warps_k, me = (split << a.log2_warps_k) + wk;
+    const float* mine = slots + (size_t)(wn << a.log2_warps_k) * SK_ROWS * MP;      // K warp 0 of this slab
+    const int units = (EPI == EPI_SWIGLU ? 8 : SK_ROWS) * a.M;
+    for (int i = me * 32 + lane; i < units; i += workers * 32) {
+      int m, j;
+      if (EPI == EPI_SWIGLU) { m = i >> 3; j = i & 7; } else { m = i >> 4; j = i & 15; }
+      const int n = n0 + j;
+      const size_t o = (size_t)m * a.ldo + n;
+      float old = 0.f;
+      if (EPI == EPI_ACC) old = ((float*)a.out)[o];                  // asked for before the partial sums
+      const float* mine_e = mine + j * MP + m;
+      constexpr int RG = 8;
+      float v0 = 0.f, v1 = 0.f;
+      for (int q0 = 0; q0 < workers; q0 += RG) {
+        float p0[RG], p1[RG];
+#pragma unroll
+        for (int q = 0; q < RG; ++q) {
+          const int idx = q0 + q;
+          p0[q] = 0.f; p1[q] = 0.f;
+          if (idx < workers) {
+            const int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
+            const float* pp = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine_e, sr) : mine_e;
+            p0[q] = pp[w * (SK_ROWS * MP)];
+            if (EPI == EPI_SWIGLU) p1[q] = pp[w * (SK_ROWS * MP) + 8 * MP];
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < RG; ++q) {
+          if (q0 + q < workers) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
+        }
+      }
+      if (EPI == EPI_SWIGLU) {
+        if (a.bias) { v0 += a.bias[n]; v1 += a.bias[n + 8]; }
+        ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((v0 / (1.0f + expf(-v0))) * v1);
+      } else {
+        if (a.bias) v0 += a.bias[n];
+        if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
+        else if (EPI == EPI_ACC) ((float*)a.out)[o] = old + v0;
         else ((float*)a.out)[o] = v0;
       }
     }
@@ -281,14 +615,39 @@ static inline size_t smem_bytes(int mt, int k_per_cta, bool direct, int tiles_pe
 }
 
 template <int MT, int EPI>
-static int launch(const SkinnyArgs& a, int ctas_y, cudaStream_t stream) {
+static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   size_t smem = smem_bytes(MT, a.k_per_cta, a.splits == 1 && a.warps_k == 1, a.tiles_per_warp);
+  a.gamma_offset = (int)smem;                              // the norm's weights, behind x and the partial slabs
+  if (a.xf && a.K <= SK_GAMMA_MAX) smem += (size_t)a.K * sizeof(float);
+  a.xf_offset = (int)smem;                                 // a float32 row piece per warp
+  if (a.xf) smem += (size_t)SK_WARPS * (a.K < SK_XF ? a.K : SK_XF) * sizeof(float);
   auto kern = gemm_skinny_kernel<MT, EPI>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+}
+
+template <int MT, int EPI, bool NORM>
+static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
+  size_t smem = smem_bytes(MT, a.k_per_cta, false, 1);
+  a.gamma_offset = (int)smem;
+  if (NORM) smem += (size_t)a.K * sizeof(float);
+  a.xf_offset = (int)smem;
+  if (NORM) smem += (size_t)SK_WARPS * a.K * sizeof(float);
+  auto kern = gemm_lean_kernel<MT, EPI, NORM>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+}
+
+template <int EPI>
+static int dispatch_lean(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
+  if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true>(a, ctas_y, s) : launch_lean<1, EPI, false>(a, ctas_y, s);
+  return a.xf ? launch_lean<2, EPI, true>(a, ctas_y, s) : launch_lean<2, EPI, false>(a, ctas_y, s);
 }
 
 template <int EPI>
@@ -327,10 +686,12 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   int warps_k = slices < SK_WARPS ? slices : SK_WARPS, splits = slices / warps_k;
   bool plan_a = (long long)n_tiles * slices <= resident_warps + resident_warps / 4;
   int ctas_y = 1, tiles_per_warp = 1, k_per_cta = 0;
+  static int cps = 0;
+  if (!cps) { const char* e = getenv("FELLM_B200_SKINNY_CPS"); cps = (e && e[0] == '1') ? 1 : 2; }
   if (plan_a) {
     k_per_cta = round_k(ceil_div(K, slices)) * warps_k;
     ctas_y = ceil_div(n_tiles, SK_WARPS / warps_k);
-    if (ctas_y > (148 * 2) / splits) ctas_y = (148 * 2) / splits;
+    if (ctas_y > (148 * cps) / splits) ctas_y = (148 * cps) / splits;
     tiles_per_warp = ceil_div(n_tiles, ctas_y * (SK_WARPS / warps_k));
     if (smem_bytes(mt, k_per_cta, slices == 1, tiles_per_warp) > 200 * 1024) plan_a = false;
   }
@@ -358,6 +719,24 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo; a.splits = splits;
   a.warps_k = warps_k; a.k_per_cta = k_per_cta; a.xs_stride = x_stride(k_per_cta);
   a.n_tiles = n_tiles; a.tiles_per_warp = tiles_per_warp;
+  a.log2_warps_k = 0;
+  while ((1 << a.log2_warps_k) < warps_k) ++a.log2_warps_k;
+  a.k_per_warp = k_per_cta / warps_k;
+  a.pdl = pdl_enabled(1) ? 1 : 0;
+  // the single-shot kernel: plan A with a slab per warp, whole chunks, whole slabs, whole-row norm
+  a.chunks_per_warp = a.k_per_warp / KCHUNK;
+  const bool lean = plan_a && M <= 16 && tiles_per_warp == 1 && slices > 1 && N % SK_ROWS == 0 &&
+                    K == slices * a.k_per_warp && a.chunks_per_warp >= 8 && a.chunks_per_warp <= LEAN_CH &&
+                    (!xf || (splits == 1 && K <= 4096));
+  if (lean) {
+    switch (epi) {
+      case EPI_STORE: return dispatch_lean<EPI_STORE>(a, ctas_y, stream);
+      case EPI_ACC: return dispatch_lean<EPI_ACC>(a, ctas_y, stream);
+      case EPI_SWIGLU: return dispatch_lean<EPI_SWIGLU>(a, ctas_y, stream);
+      case EPI_F32: return dispatch_lean<EPI_F32>(a, ctas_y, stream);
+      default: return FELLM_ERR_ARG;
+    }
+  }
   switch (epi) {
     case EPI_STORE: return dispatch_mt<EPI_STORE>(a, ctas_y, stream);
     case EPI_ACC: return dispatch_mt<EPI_ACC>(a, ctas_y, stream);

@@ -41,6 +41,7 @@ template <int EPI>
 __global__ void __launch_bounds__(TTHREADS)
 gemm_tiled_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, const float* __restrict__ bias,
                   void* __restrict__ out, int M, int N, int K, int lda, int ldw, int ldo) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_TILED);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* sA = (uint4*)smem_raw;                            // [stage][128 rows * 4 chunks]
   uint4* sB = sA + TSTAGES * TBM * 4;

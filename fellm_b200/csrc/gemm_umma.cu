@@ -161,6 +161,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, 
 template <int EPI>
 __global__ void __launch_bounds__(UM_THREADS)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * UM_STAGES + 4];    // full[], empty[], acc_full[2], acc_empty[2]
   __shared__ unsigned tmem_base_s;
@@ -186,7 +187,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem_base = tmem_base_s;
   pdl_launch_dependents();
-  pdl_wait();                        // A is the output of the kernel before this one
+  pdl_wait(); FELLM_TRACE_WAITED();                        // A is the output of the kernel before this one
 
   if (warp == 0) {
     if (lane == 0) {

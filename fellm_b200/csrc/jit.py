@@ -80,8 +80,24 @@ def _choose_build_dir() -> Path:
     raise KernelError(f"no writable folder for built kernels (tried {', '.join(map(str, cands))})")
 
 
+def tracing() -> bool:
+    """FELLM_B200_TRACE=1 builds every module with the kernel timeline compiled in (separate
+    libraries, tagged by the define)."""
+    return os.environ.get("FELLM_B200_TRACE", "") == "1"
+
+
 def _defines_key(defines: Optional[dict]) -> Tuple:
-    return tuple(sorted((str(k), str(v)) for k, v in (defines or {}).items()))
+    d = dict(defines or {})
+    if tracing():
+        d["FELLM_TRACE"] = 1
+    for item in filter(None, os.environ.get("FELLM_B200_DEFINES", "").split(",")):      # experiments: NAME=VALUE,...
+        k, _, v = item.partition("=")
+        d[k] = v or "1"
+    return tuple(sorted((str(k), str(v)) for k, v in d.items()))
+
+
+def loaded_libraries():
+    return list(_loaded.values())
 
 
 def _source_hash(name: str, dkey: Tuple) -> str:

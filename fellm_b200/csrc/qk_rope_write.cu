@@ -20,8 +20,9 @@ __global__ void qk_rope_write_kernel(const TA* __restrict__ qkv, const float* __
                                      TC* __restrict__ pool, int layer, int layers_in_group,
                                      int page_tokens, TA* __restrict__ q_out, int T, int H, int G, int hd,
                                      int write_kv, int* __restrict__ status) {
+  FELLM_TRACE_SCOPE(TRACE_QK_ROPE_WRITE);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   int lane = threadIdx.x & 31;
   int heads_total = H + 2 * G;
@@ -103,8 +104,9 @@ __global__ void qk_rope_write_vec_kernel(const bf16* __restrict__ qkv, const flo
                                          bf16* __restrict__ pool, int layer, int layers_in_group,
                                          int page_tokens, bf16* __restrict__ q_out, int T, int H, int G, int hd,
                                          int write_kv, int* __restrict__ status) {
+  FELLM_TRACE_SCOPE(TRACE_QK_ROPE_WRITE_VEC);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GL;
   const int l = threadIdx.x % GL;
   const int heads_total = H + 2 * G;

@@ -207,10 +207,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
               int* __restrict__ counts, const int* __restrict__ bias_tok, const float* __restrict__ bias_val,
               int* __restrict__ out_tokens, float* __restrict__ out_probs, int update_counts) {
+  FELLM_TRACE_SCOPE(TRACE_SAMPLE);
   __shared__ Shared s;
   int row = blockIdx.x;
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   RowParams p = params[row];
   Row r;
   r.logits = logits + (size_t)row * V;
@@ -353,6 +354,7 @@ sample_kernel(const float* __restrict__ logits, int V, const RowParams* __restri
 // counts[slot, token] += 1 for a list of (slot, token): primes a request's history with its prompt.
 __global__ void count_tokens_kernel(int* __restrict__ counts, int V, const int* __restrict__ slots,
                                     const int* __restrict__ tokens, int n) {
+  FELLM_TRACE_SCOPE(TRACE_COUNT_TOKENS);
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && tokens[i] >= 0 && tokens[i] < V) atomicAdd(&counts[(size_t)slots[i] * V + tokens[i]], 1);
 }
@@ -379,8 +381,9 @@ FELLM_API int fellm_count_tokens(int* counts, int V, const int* slots, const int
 #define ARGMAX_CHUNKS 64
 __global__ void __launch_bounds__(256)
 argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict__ pval, int* __restrict__ pidx) {
+  FELLM_TRACE_SCOPE(TRACE_ARGMAX_PARTIAL);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   int row = blockIdx.y, chunk = blockIdx.x;
   int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
   int lo = chunk * per, hi = min(V, lo + per);
@@ -407,8 +410,9 @@ argmax_partial_kernel(const float* __restrict__ logits, int V, float* __restrict
 }
 __global__ void __launch_bounds__(32)
 argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out_tokens) {
+  FELLM_TRACE_SCOPE(TRACE_ARGMAX_FINAL);
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   int row = blockIdx.x, lane = threadIdx.x;
   float best = -INFINITY; int bi = 0x7fffffff;
   for (int c = lane; c < ARGMAX_CHUNKS; c += 32) {

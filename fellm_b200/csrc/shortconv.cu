@@ -83,10 +83,11 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
                                  long long slot_stride, const int* __restrict__ item_slot,
                                  const int* __restrict__ item_start, const int* __restrict__ row_item,
                                  TA* __restrict__ y, int T, int n_items, int d, int Lc, int n_body_tiles) {
+  FELLM_TRACE_SCOPE(TRACE_SHORTCONV);
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   if (VEC && (int)blockIdx.y < n_body_tiles) {
-    pdl_wait();
+    pdl_wait(); FELLM_TRACE_WAITED();
     shortconv_body_vec((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, Lc);
     return;
   }
@@ -97,7 +98,7 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
   for (int t = 0; t < MAX_LC; ++t) wt[t] = t < Lc ? w[(size_t)c * Lc + t] : 0.f;      // weights: before the wait
   const float wlast = w[(size_t)c * Lc + (Lc - 1)];
   float bias = conv_bias ? conv_bias[c] : 0.f;
-  pdl_wait();
+  pdl_wait(); FELLM_TRACE_WAITED();
   const size_t ld = (size_t)3 * d;
 
   if ((int)blockIdx.y < n_body_tiles) {
