@@ -17,6 +17,10 @@
 // 1/sqrt(hd), online softmax with m, l and rescaling, out = acc / l).  FeLLM's kernels:
 // attention_fa2_prefill_paged (plugins/cuda_kernels/src/oxide_kernels.rs:4673, one warp per query
 // row), attention_fa2_decode_paged (5107, one block per head over all keys).
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 #ifndef HD
@@ -64,7 +68,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // addresses of [keys][ROWB] tiles).  Thread (g = lane/4, c = lane%4) owns rows g and g+8; a key at
 // tile index i (absolute index key0 + i) counts for row r iff lo[r] <= key0 + i <= hi[r].
 // m, l: running maximum (log2 domain) and this thread's share of the running sum per row.
-template <int NKT>
+template <int NKT, bool MASKED = true>
 __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigned k_s, unsigned v_s, int key0,
                                             const int (&lo)[2], const int (&hi)[2], float scale_log2,
                                             float (&o)[DN][4], float (&m)[2], float (&l)[2], int lane) {
@@ -93,7 +97,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (&qf)[KS][4], unsigne
     for (int e = 0; e < 4; ++e) {
       int key = key0 + n * 8 + 2 * c + (e & 1);
       int r = e >> 1;
-      float v = (key >= lo[r] && key <= hi[r]) ? s[n][e] * scale_log2 : -INFINITY;
+      float v = (!MASKED || (key >= lo[r] && key <= hi[r])) ? s[n][e] * scale_log2 : -INFINITY;
       s[n][e] = v;
       mx[r] = fmaxf(mx[r], v);
     }
@@ -285,6 +289,81 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
 #define DC_STAGES 3
 #define DC_MAX_PAGES 256
 
+// The warps of a decode CTA hold partial results (o, m, l) for the same 16-row block of heads over
+// different keys: they are combined through `merge` ([warp][16][HD + 2] floats of shared memory that
+// no warp reads as a key tile any more) into the CTA's result, which goes to `out` when the CTA is the
+// only one of its (row, kv head), else into the CTA's record of the scratch buffer.
+__device__ __forceinline__ void decode_warps_to_cta(const AttnArgs& a, float (&o)[DN][4], float (&m)[2], float (&l)[2],
+                                                    float* merge, int warp, int lane, int t, int g, int r0, int R,
+                                                    int split_index, int n_active) {
+  const int gq = lane >> 2, c = lane & 3;
+  const int SW = HD + 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    float* rec = merge + ((size_t)warp * 16 + gq + 8 * r) * SW;
+#pragma unroll
+    for (int d = 0; d < DN; ++d) { rec[d * 8 + 2 * c] = o[d][2 * r]; rec[d * 8 + 2 * c + 1] = o[d][2 * r + 1]; }
+    if (c == 0) { rec[HD] = m[r]; rec[HD + 1] = l[r]; }
+  }
+  __syncthreads();
+  const int rows_here = min(16, R - r0);
+  for (int i = threadIdx.x; i < rows_here * HD; i += DC_WARPS * 32) {
+    int row = i / HD, d = i - row * HD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) mx = fmaxf(mx, merge[((size_t)w * 16 + row) * SW + HD]);
+    float lt = 0.f, at = 0.f;
+#pragma unroll
+    for (int w = 0; w < DC_WARPS; ++w) {
+      const float* rec = merge + ((size_t)w * 16 + row) * SW;
+      float cw = rec[HD] == -INFINITY ? 0.f : exp2f(rec[HD] - mx);
+      lt += rec[HD + 1] * cw;
+      at += rec[d] * cw;
+    }
+    int h = g * R + r0 + row;
+    if (n_active == 1) {
+      a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
+    } else {
+      float* rec = a.scratch + (((size_t)t * a.H + h) * a.max_splits + split_index) * SW;
+      rec[d] = at;
+      if (d == 0) { rec[HD] = mx; rec[HD + 1] = lt; }
+    }
+  }
+  __syncthreads();
+}
+
+// The last CTA of a (row, kv head) to get here merges the ranges' records in order.
+__device__ __forceinline__ void decode_last_cta_merges(const AttnArgs& a, int* sm_last, int t, int g, int R, int n_active) {
+  if (n_active == 1) return;
+  const int SW = HD + 2;
+  __threadfence();                                      // every writer publishes its records ...
+  __syncthreads();                                      // ... before thread 0 counts this CTA in
+  if (threadIdx.x == 0) {
+    int old = atomicAdd(&a.counters[t * a.G + g], 1);
+    *sm_last = (old == n_active - 1);
+    if (*sm_last) a.counters[t * a.G + g] = 0;          // ready for the next launch
+  }
+  __syncthreads();
+  if (!*sm_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < R * HD; i += DC_WARPS * 32) {
+    int r = i / HD, d = i - r * HD;
+    int h = g * R + r;
+    const float* rec = a.scratch + ((size_t)t * a.H + h) * a.max_splits * SW;
+    float mx = -INFINITY;
+    for (int j = 0; j < n_active; ++j) mx = fmaxf(mx, rec[(size_t)j * SW + HD]);
+    float lt = 0.f, at = 0.f;
+    for (int j = 0; j < n_active; ++j) {
+      float cj = exp2f(rec[(size_t)j * SW + HD] - mx);
+      lt += rec[(size_t)j * SW + HD + 1] * cj;
+      at += rec[(size_t)j * SW + d] * cj;
+    }
+    a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
+  }
+}
+
 __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArgs a) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
   extern __shared__ __align__(128) unsigned char smem[];
@@ -292,7 +371,6 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
   __shared__ int sm_last;
   const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gq = lane >> 2, c = lane & 3;
   // positions, slots and block tables are written by copies before the step's kernels, not by a
   // kernel: they may be read before the wait
   const int pos = a.positions[t];
@@ -313,7 +391,6 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
   constexpr int TILE_B = DC_TK * ROWB;
   const unsigned ring = (unsigned)__cvta_generic_to_shared(smem) + warp * DC_STAGES * 2 * TILE_B;
   float* merge = (float*)smem;       // [warp][16][HD + 2], over the rings once every warp is done with them
-  const int SW = HD + 2;
   const int cta_step = DC_WARPS * DC_TK;
   const int n_tiles = (k1 - k0 - warp * DC_TK + cta_step - 1) / cta_step;          // may be <= 0
   const size_t page_elems = (size_t)a.page_tokens * HD;
@@ -361,70 +438,171 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
     }
     cp_async_wait<0>();
     __syncthreads();                                           // every warp has left its ring
-    // warp result -> shared memory
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-      float* rec = merge + ((size_t)warp * 16 + gq + 8 * r) * SW;
-#pragma unroll
-      for (int d = 0; d < DN; ++d) { rec[d * 8 + 2 * c] = o[d][2 * r]; rec[d * 8 + 2 * c + 1] = o[d][2 * r + 1]; }
-      if (c == 0) { rec[HD] = m[r]; rec[HD + 1] = l[r]; }
-    }
-    __syncthreads();
-    const int rows_here = min(16, R - r0);
-    for (int i = threadIdx.x; i < rows_here * HD; i += DC_WARPS * 32) {
-      int row = i / HD, d = i - row * HD;
-      float mx = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < DC_WARPS; ++w) mx = fmaxf(mx, merge[((size_t)w * 16 + row) * SW + HD]);
-      float lt = 0.f, at = 0.f;
-#pragma unroll
-      for (int w = 0; w < DC_WARPS; ++w) {
-        const float* rec = merge + ((size_t)w * 16 + row) * SW;
-        float cw = rec[HD] == -INFINITY ? 0.f : exp2f(rec[HD] - mx);
-        lt += rec[HD + 1] * cw;
-        at += rec[d] * cw;
-      }
-      int h = g * R + r0 + row;
-      if (n_active == 1) {
-        a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
-      } else {
-        float* rec = a.scratch + (((size_t)t * a.H + h) * a.max_splits + (s - s_lo)) * SW;
-        rec[d] = at;
-        if (d == 0) { rec[HD] = mx; rec[HD + 1] = lt; }
-      }
-    }
+    decode_warps_to_cta(a, o, m, l, merge, warp, lane, t, g, r0, R, s - s_lo, n_active);
     __syncthreads();
   }
-  if (n_active == 1) return;
-
-  // the last CTA of this (row, kv head) merges the ranges in order
-  __threadfence();                                      // every writer publishes its records ...
-  __syncthreads();                                      // ... before thread 0 counts this CTA in
-  if (threadIdx.x == 0) {
-    int old = atomicAdd(&a.counters[t * a.G + g], 1);
-    sm_last = (old == n_active - 1);
-    if (sm_last) a.counters[t * a.G + g] = 0;          // ready for the next launch
-  }
-  __syncthreads();
-  if (!sm_last) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < R * HD; i += DC_WARPS * 32) {
-    int r = i / HD, d = i - r * HD;
-    int h = g * R + r;
-    const float* rec = a.scratch + ((size_t)t * a.H + h) * a.max_splits * SW;
-    float mx = -INFINITY;
-    for (int j = 0; j < n_active; ++j) mx = fmaxf(mx, rec[(size_t)j * SW + HD]);
-    float lt = 0.f, at = 0.f;
-    for (int j = 0; j < n_active; ++j) {
-      float cj = exp2f(rec[(size_t)j * SW + HD] - mx);
-      lt += rec[(size_t)j * SW + HD + 1] * cj;
-      at += rec[(size_t)j * SW + d] * cj;
-    }
-    a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
-  }
+  decode_last_cta_merges(a, &sm_last, t, g, R, n_active);
 }
+
+// ------------------------------------------------------------------------------------ decode, TMA
+// Head size 64 and pages of 64 tokens: the [64 keys, 64 dims] tile of one kv head of one page is 8 KB
+// of contiguous cache, 128 bytes a row, so ONE cp.async.bulk.tensor with the 128-byte swizzle brings
+// it in the layout attend_tile() reads (16-byte chunk ^ (row & 7)).  A warp takes every fourth page
+// of the CTA's key range: one lane asks for the page's K and V tiles, the warp waits on its own
+// mbarrier, attends to the 64 keys, and asks for its next page.  No address arithmetic per 16 bytes:
+// a third of the instructions of the cp.async kernel, which stays for other head and page sizes.
+// Waits are bounded (a second): a warp that gives up sets *status = 301 and the CTA finishes with
+// what it has.
+#if HD == 64
+#define DT_PT 64
+#define DT_TILE_B (DT_PT * 128)
+#define DT_WAIT_NS 1000000000ull
+
+__device__ __forceinline__ void at_mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void at_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool at_mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool at_mbar_wait(unsigned bar, unsigned parity) {
+  if (at_mbar_try(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0));
+  for (unsigned i = 0; i < (1u << 26); ++i) {
+    if (at_mbar_try(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1));
+      if (t1 - t0 > DT_WAIT_NS) break;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ void at_tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+__global__ void __launch_bounds__(DC_WARPS * 32)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, int* status) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[DC_WARPS];
+  __shared__ int sm_pages[DC_MAX_PAGES];
+  __shared__ int sm_last;
+  const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // positions, slots and block tables are written by copies before the step's kernels, not by a
+  // kernel: they may be read before the wait
+  const int pos = a.positions[t];
+  const int kb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int s_lo = kb / a.split_len, s_hi = pos / a.split_len;
+  pdl_launch_dependents();
+  if (s < s_lo || s > s_hi) return;
+  const int n_active = s_hi - s_lo + 1;
+  const int k0 = max(kb, s * a.split_len), k1 = min(pos + 1, (s + 1) * a.split_len);
+  const int R = a.H / a.G;                              // <= 16 (the launcher checks)
+  const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
+  const int pg0 = k0 / DT_PT, n_pg = (k1 - 1) / DT_PT - pg0 + 1;
+  const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
+  if (pages_in_smem)
+    for (int i = threadIdx.x; i < n_pg; i += DC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
+  if (threadIdx.x < DC_WARPS) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  pdl_wait(); FELLM_TRACE_WAITED();
+  __syncthreads();
+  const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
+  float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
+  const unsigned tile_k = base + warp * 2 * DT_TILE_B, tile_v = tile_k + DT_TILE_B;
+  const unsigned bar = (unsigned)__cvta_generic_to_shared(&bars[warp]);
+  const int my_pages = (n_pg - warp + DC_WARPS - 1) / DC_WARPS;                              // may be <= 0
+  auto request = [&](int j) {                           // lane 0: K and V tile of this warp's j-th page
+    const int lp = pg0 + warp + j * DC_WARPS;
+    const int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
+    const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * DT_PT;          // < 2^31: the launcher checks
+    at_mbar_expect_tx(bar, 2 * DT_TILE_B);
+    at_tma_load_2d(tile_k, &pool_map, 0, row, bar);
+    at_tma_load_2d(tile_v, &pool_map, 0, row + a.G * DT_PT, bar);
+  };
+  if (lane == 0 && my_pages > 0) request(0);
+  unsigned qf[KS][4];
+  load_q(qf, [&](int i) -> const bf16* { return i < R ? a.q + ((size_t)t * a.H + g * R + i) * HD : nullptr; }, lane);
+  float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+  const int lo[2] = {k0, k0}, hi[2] = {k1 - 1, k1 - 1};
+  for (int j = 0; j < my_pages; ++j) {
+    const bool arrived = __all_sync(0xffffffffu, at_mbar_wait(bar, j & 1));
+    if (j == 0) FELLM_TRACE_MARK(0);
+    if (!arrived) {
+      if (lane == 0 && status) atomicExch(status, 301);
+      break;
+    }
+    const int key0 = (pg0 + warp + j * DC_WARPS) * DT_PT;
+    if (key0 + DT_PT > k1) {
+      // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
+      const int first = k1 - key0;
+      for (int i = first * CPR + lane; i < DT_PT * CPR; i += 32) st_shared_zero16(tile_v + tile_off(i / CPR, i % CPR));
+      __syncwarp();
+    }
+    if (key0 < k0 || key0 + DT_PT > k1)
+      attend_tile<DT_PT / 8, true>(qf, tile_k, tile_v, key0, lo, hi, a.scale_log2, o, m, l, lane);
+    else
+      attend_tile<DT_PT / 8, false>(qf, tile_k, tile_v, key0, lo, hi, a.scale_log2, o, m, l, lane);
+    __syncwarp();
+    if (j + 1 < my_pages) {
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // this warp's reads before the next copy's writes
+      if (lane == 0) request(j + 1);
+    }
+  }
+  FELLM_TRACE_MARK(1);
+  __syncthreads();                                         // every warp has left its tiles
+  decode_warps_to_cta(a, o, m, l, merge, warp, lane, t, g, 0, R, s - s_lo, n_active);
+  FELLM_TRACE_MARK(2);
+  decode_last_cta_merges(a, &sm_last, t, g, R, n_active);
+}
+
+// The cache pool as a 2-D tensor [rows of 64 dims]: the map is kept per (pool, rows).
+typedef CUresult (*AtEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int pool_map_for(const void* pool, long long rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static struct { const void* pool; long long rows; CUtensorMap map; } cache[8];
+  static int n_cached = 0, next = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_cached; ++i)
+    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return 0; }
+  static AtEncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return FELLM_ERR_ARG;
+    fn = (AtEncodeTiledFn)p;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  cuuint32_t box[2] = {HD, DT_PT};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  cache[next].pool = pool; cache[next].rows = rows; cache[next].map = m;
+  next = (next + 1) % 8;
+  if (n_cached < 8) ++n_cached;
+  *out = m;
+  return 0;
+}
+#endif
 
 static int fill_args(AttnArgs& a, const void* q, const void* pool, const int* block_table, int max_pages,
                      const int* positions, const int* row_slot, void* out, int T, int H, int G, int hd,
@@ -489,4 +667,37 @@ FELLM_API int fellm_attn_decode_mma(const void* q, const void* pool, const int* 
     if (ce != cudaSuccess) return (int)ce;
   }
   return launch_k(kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, a);
+}
+
+// The same through the TMA kernel: head size 64, pages of 64 tokens, at most 16 heads per kv head
+// (FELLM_ERR_SIZE otherwise: the caller falls back to fellm_attn_decode_mma).  n_pages: pages of the
+// pool; status: device int32 set to 301 if a wait ran out.
+FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n_pages, const int* block_table,
+                                    int max_pages, const int* positions, const int* row_slot, void* out,
+                                    float* scratch, int* counters, int T, int H, int G, int hd, int page_tokens,
+                                    int layer, int layers_in_group, float scale, int window, int split_len,
+                                    int max_splits, int* status, cudaStream_t stream) {
+#if HD == 64
+  if (T <= 0) return 0;
+  AttnArgs a;
+  int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
+                    layers_in_group, scale, window);
+  if (e) return e;
+  if (!scratch || !counters || split_len < 1 || max_splits < 1) return FELLM_ERR_ARG;
+  const long long rows = n_pages * layers_in_group * 2 * G * page_tokens;
+  if (page_tokens != DT_PT || H / G > 16 || (split_len % DT_PT) || rows >= (1ll << 31) || ((uintptr_t)pool & 15))
+    return FELLM_ERR_SIZE;
+  a.scratch = scratch; a.counters = counters; a.split_len = split_len; a.max_splits = max_splits;
+  CUtensorMap map;
+  e = pool_map_for(pool, rows, &map);
+  if (e) return e;
+  size_t tiles = (size_t)DC_WARPS * 2 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
+  size_t smem = (tiles > mrg ? tiles : mrg) + 1024;
+  auto kern = attention_decode_tma_kernel;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (ce != cudaSuccess) return (int)ce;
+  return launch_k(kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, map, a, status);
+#else
+  return FELLM_ERR_SIZE;
+#endif
 }

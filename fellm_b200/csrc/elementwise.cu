@@ -30,8 +30,8 @@ FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_i
   if (!tokens || !table || !out) return FELLM_ERR_ARG;
   int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_is_bf16)
-    return launch_k(embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
-  return launch_k(embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
+    return launch_k_class(2, embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
+  return launch_k_class(2, embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
 }
 
 // ---------------------------------------------------------------- RMSNorm

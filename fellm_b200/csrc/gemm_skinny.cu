@@ -423,8 +423,8 @@ struct LeanLoad<N, N> {
   static __device__ __forceinline__ void run(const bf16*, const bf16*, uint4*, uint4*, int) {}
 };
 
-template <int MT, int EPI, bool NORM>
-__global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) {
+template <int MT, int EPI, bool NORM, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kernel(SkinnyArgs a) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * EPI);
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int MP = MT * 8;
@@ -434,12 +434,12 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) 
   const int wn = warp >> a.log2_warps_k, wk = warp & (a.warps_k - 1);
   const int k_cta = split * a.k_per_cta;
   const int n_chunks = a.chunks_per_warp;              // 8..LEAN_CH, the same for every warp
-  const int tile = blockIdx.y * (SK_WARPS >> a.log2_warps_k) + wn;
+  const int tile = blockIdx.y * (WARPS >> a.log2_warps_k) + wn;
   const bool active = tile < a.n_tiles;
   const int n0 = tile * SK_ROWS;
   bf16* xs = (bf16*)smem;
   const int nv = a.K >> 2;
-  float4* piece = (float4*)(smem + a.xf_offset) + (size_t)warp * nv;     // NORM: the warp's float32 row
+  float4* piece = (float4*)(smem + a.xf_offset) + (size_t)(warp < MP ? warp : 0) * nv;     // NORM: the float32 row of warp < MP
   const unsigned piece_s = (unsigned)__cvta_generic_to_shared(piece);
 
   auto request_row = [&](int r) {                      // NORM: float32 row r into the warp's piece
@@ -448,13 +448,11 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) 
   };
   auto request_x = [&]() {
     if (NORM) {
-      if (warp < a.M) request_row(warp);
+      if (warp < a.M && warp < MP) request_row(warp);
     } else {
       const int vec_per_row = a.k_per_cta >> 3;
       const unsigned xs_s = (unsigned)__cvta_generic_to_shared(xs);
-#pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        const int r = warp + 8 * t;
+      for (int r = warp; r < MP; r += WARPS) {
         bf16* dst = xs + (size_t)r * a.xs_stride;
         if (r < a.M) {
           const bf16* src = a.x + (size_t)r * a.lda + k_cta;
@@ -472,7 +470,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) 
   // wait when the kernel runs as a programmatic dependent
   if (NORM) {
     const unsigned gs = (unsigned)__cvta_generic_to_shared(smem + a.gamma_offset);
-    for (int i = threadIdx.x; i < nv; i += SK_THREADS) sk_cp_async16(gs + 16u * i, a.norm_w + 4 * i);
+    for (int i = threadIdx.x; i < nv; i += WARPS * 32) sk_cp_async16(gs + 16u * i, a.norm_w + 4 * i);
   }
   if (!a.pdl) request_x();
   uint4 w0[LEAN_CH], w1[LEAN_CH];
@@ -493,12 +491,10 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_lean_kernel(SkinnyArgs a) 
     // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39): a warp per row, whole rows
     const float4* gamma_s = (const float4*)(smem + a.gamma_offset);
     __syncthreads();
-#pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      const int r = warp + 8 * t;
+    for (int r = warp; r < MP; r += WARPS) {
       bf16* row = xs + (size_t)r * a.xs_stride;
       if (r < a.M) {
-        if (t > 0) { __syncwarp(); request_row(r); sk_cp_async_wait_all(); __syncwarp(); }
+        if (r != warp) { __syncwarp(); request_row(r); sk_cp_async_wait_all(); __syncwarp(); }
         if (nv == 256) norm_row_fast<8>(piece, gamma_s, row, lane, a.K, a.eps);
         else if (nv == 512) norm_row_fast<16>(piece, gamma_s, row, lane, a.K, a.eps);
         else {
@@ -629,25 +625,29 @@ static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
 }
 
-template <int MT, int EPI, bool NORM>
+template <int MT, int EPI, bool NORM, int WARPS>
 static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
-  size_t smem = smem_bytes(MT, a.k_per_cta, false, 1);
+  size_t smem = (size_t)MT * 8 * x_stride(a.k_per_cta) * sizeof(bf16) + (size_t)WARPS * SK_ROWS * MT * 8 * sizeof(float);
   a.gamma_offset = (int)smem;
   if (NORM) smem += (size_t)a.K * sizeof(float);
   a.xf_offset = (int)smem;
-  if (NORM) smem += (size_t)SK_WARPS * a.K * sizeof(float);
-  auto kern = gemm_lean_kernel<MT, EPI, NORM>;
+  if (NORM) smem += (size_t)(WARPS < MT * 8 ? WARPS : MT * 8) * a.K * sizeof(float);
+  auto kern = gemm_lean_kernel<MT, EPI, NORM, WARPS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(WARPS * 32, 1, 1), smem, stream, a.splits, a);
 }
 
 template <int EPI>
-static int dispatch_lean(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
-  if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true>(a, ctas_y, s) : launch_lean<1, EPI, false>(a, ctas_y, s);
-  return a.xf ? launch_lean<2, EPI, true>(a, ctas_y, s) : launch_lean<2, EPI, false>(a, ctas_y, s);
+static int dispatch_lean(const SkinnyArgs& a, int ctas_y, int warps, cudaStream_t s) {
+  if (warps == 16) {
+    if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true, 16>(a, ctas_y, s) : launch_lean<1, EPI, false, 16>(a, ctas_y, s);
+    return a.xf ? launch_lean<2, EPI, true, 16>(a, ctas_y, s) : launch_lean<2, EPI, false, 16>(a, ctas_y, s);
+  }
+  if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true, 8>(a, ctas_y, s) : launch_lean<1, EPI, false, 8>(a, ctas_y, s);
+  return a.xf ? launch_lean<2, EPI, true, 8>(a, ctas_y, s) : launch_lean<2, EPI, false, 8>(a, ctas_y, s);
 }
 
 template <int EPI>
@@ -723,18 +723,37 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   while ((1 << a.log2_warps_k) < warps_k) ++a.log2_warps_k;
   a.k_per_warp = k_per_cta / warps_k;
   a.pdl = pdl_enabled(1) ? 1 : 0;
-  // the single-shot kernel: plan A with a slab per warp, whole chunks, whole slabs, whole-row norm
-  a.chunks_per_warp = a.k_per_warp / KCHUNK;
-  const bool lean = plan_a && M <= 16 && tiles_per_warp == 1 && slices > 1 && N % SK_ROWS == 0 &&
-                    K == slices * a.k_per_warp && a.chunks_per_warp >= 8 && a.chunks_per_warp <= LEAN_CH &&
-                    (!xf || (splits == 1 && K <= 4096));
-  if (lean) {
-    switch (epi) {
-      case EPI_STORE: return dispatch_lean<EPI_STORE>(a, ctas_y, stream);
-      case EPI_ACC: return dispatch_lean<EPI_ACC>(a, ctas_y, stream);
-      case EPI_SWIGLU: return dispatch_lean<EPI_SWIGLU>(a, ctas_y, stream);
-      case EPI_F32: return dispatch_lean<EPI_F32>(a, ctas_y, stream);
-      default: return FELLM_ERR_ARG;
+  // the single-shot kernel: a (slab, K slice) per warp, whole chunks, whole slabs, whole-row norm.
+  // CTAs of 8 warps, two to an SM; or of 16 warps, one to an SM, where that keeps the product in
+  // one wave of CTAs or saves a split of K over a cluster (x is then staged once per SM).
+  if (M <= 16 && slices > 1 && N % SK_ROWS == 0 && K % slices == 0 && (K / slices) % KCHUNK == 0 &&
+      K / slices >= 8 * KCHUNK && K / slices <= LEAN_CH * KCHUNK) {
+    auto shape = [&](int warps, int& wk, int& sp, int& ctas) {
+      wk = slices < warps ? slices : warps;
+      sp = slices / wk;
+      ctas = ceil_div(n_tiles, warps / wk);
+    };
+    int wk8, sp8, ct8, wk16, sp16, ct16;
+    shape(8, wk8, sp8, ct8);
+    shape(16, wk16, sp16, ct16);
+    const bool fits8 = sp8 <= 8 && ct8 * sp8 <= 148 * 2, fits16 = sp16 <= 8 && ct16 * sp16 <= 148;
+    int warps = 0;
+    if (fits16 && (sp16 < sp8 || !fits8 || ct8 * sp8 > 148)) warps = 16;
+    else if (fits8) warps = 8;
+    const int wk = warps == 16 ? wk16 : wk8, sp = warps == 16 ? sp16 : sp8, ct = warps == 16 ? ct16 : ct8;
+    if (warps && (!xf || (sp == 1 && K <= 4096))) {
+      a.splits = sp; a.warps_k = wk; a.k_per_warp = K / slices; a.k_per_cta = a.k_per_warp * wk;
+      a.xs_stride = x_stride(a.k_per_cta); a.tiles_per_warp = 1;
+      a.log2_warps_k = 0;
+      while ((1 << a.log2_warps_k) < wk) ++a.log2_warps_k;
+      a.chunks_per_warp = a.k_per_warp / KCHUNK;
+      switch (epi) {
+        case EPI_STORE: return dispatch_lean<EPI_STORE>(a, ct, warps, stream);
+        case EPI_ACC: return dispatch_lean<EPI_ACC>(a, ct, warps, stream);
+        case EPI_SWIGLU: return dispatch_lean<EPI_SWIGLU>(a, ct, warps, stream);
+        case EPI_F32: return dispatch_lean<EPI_F32>(a, ct, warps, stream);
+        default: return FELLM_ERR_ARG;
+      }
     }
   }
   switch (epi) {

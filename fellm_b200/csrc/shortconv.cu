@@ -172,11 +172,11 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   int n_body = all_single ? 0 : ceil_div(T, BODY_ROWS);    // every item has one token: heads only
   dim3 grid(ceil_div(d, threads), n_body + n_items);
   if (is_bf16 && d % 8 == 0 && n_body > 0)
-    return launch_k(shortconv_kernel<bf16, true>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+    return launch_k_class(2, shortconv_kernel<bf16, true>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
   if (is_bf16)
-    return launch_k(shortconv_kernel<bf16, false>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+    return launch_k_class(2, shortconv_kernel<bf16, false>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
-  return launch_k(shortconv_kernel<float, false>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
+  return launch_k_class(2, shortconv_kernel<float, false>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
                   slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body);
 }

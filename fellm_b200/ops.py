@@ -276,7 +276,8 @@ def check_umma_status(device):
         code = int(t.item())
         if code:
             t.zero_()
-            raise KernelError(f"the tcgen05 product gave up waiting on a barrier (role {code})")
+            what = "the TMA decode attention" if code == 301 else "the tcgen05 product"
+            raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
 
 def fast_gemm_takes(x, w) -> bool:
@@ -399,6 +400,9 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
 DECODE_TARGET_CTAS = 148 * 4
 
 
+USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
+
+
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     """(split_len, max_splits): key ranges of a multiple of 64 keys, enough of them to fill the
     machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
@@ -431,6 +435,15 @@ def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, wi
     scratch, counters = reserve_decode_scratch(q.device, T, H, G, hd, max_splits)
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    if USE_TMA_DECODE and hd == 64 and page_tokens == 64 and H // G <= 16 and pool.numel() // hd < 2 ** 31:
+        # pages of 64 tokens at head size 64: whole [64, 64] tiles by TMA
+        f = _fn("attention_mma", "fellm_attn_decode_tma",
+                [_c_p, _c_p, ctypes.c_longlong, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
+                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p], defines={"HD": hd})
+        _check(f(_p(q), _p(pool), pool.shape[0], _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
+                 _p(out), _p(scratch), _p(counters), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
+                 int(window or 0), split_len, max_splits, _p(umma_status(q.device)), _stream()), "attention_decode (TMA)")
+        return out
     f = _fn("attention_mma", "fellm_attn_decode_mma",
             [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_f, _c_int, _c_int, _c_int, _c_p], defines={"HD": hd})

@@ -319,10 +319,12 @@ def test_gemm_skinny_same_bits_every_run():
 
 @pytest.mark.parametrize("H,G,hd,page_tokens,window", [(16, 8, 64, 64, None), (6, 1, 48, 16, None), (4, 4, 128, 32, None),
                                                        (24, 8, 64, 64, None), (8, 1, 16, 16, 70), (5, 5, 80, 8, None),
-                                                       (2, 1, 256, 64, 300), (32, 8, 64, 16, None), (6, 1, 32, 64, None)])
+                                                       (2, 1, 256, 64, 300), (32, 8, 64, 16, None), (6, 1, 32, 64, None),
+                                                       (16, 1, 64, 64, 100), (34, 2, 64, 64, None), (8, 4, 64, 64, 700)])
 def test_attention_decode_split_kv(H, G, hd, page_tokens, window):
     """Rows of different lengths, each its own request, pages out of order, key ranges that end
-    inside pages: against the plain attention."""
+    inside pages (what lies behind the last key in its page is NaN): against the plain attention.
+    Head size 64 with pages of 64 tokens and up to 16 heads per kv head takes the TMA kernel."""
     torch.manual_seed(H + hd)
     lens = [1, 2, 63, 64, 65, 200, 777, 1500]
     T = len(lens)
@@ -341,6 +343,7 @@ def test_attention_decode_split_kv(H, G, hd, page_tokens, window):
             lo, hi = p * page_tokens, min(n, (p + 1) * page_tokens)
             pool[page, 1, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1).to(DEV)
             pool[page, 1, 1, :, :hi - lo] = v[lo:hi].transpose(0, 1).to(DEV)
+            pool[page, 1, :, :, hi - lo:] = float("nan")
     q = torch.randn(T, H, hd).bfloat16()
     got = ops.attention_decode(q.to(DEV), pool, table.to(DEV), i32([n - 1 for n in lens]), i32(list(range(1, T + 1))),
                                1, hd ** -0.5, window, max(lens))
