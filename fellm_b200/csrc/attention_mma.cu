@@ -448,14 +448,16 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
 // Head size 64 and pages of 64 tokens: the [64 keys, 64 dims] tile of one kv head of one page is 8 KB
 // of contiguous cache, 128 bytes a row, so ONE cp.async.bulk.tensor with the 128-byte swizzle brings
 // it in the layout attend_tile() reads (16-byte chunk ^ (row & 7)).  A warp takes every fourth page
-// of the CTA's key range: one lane asks for the page's K and V tiles, the warp waits on its own
-// mbarrier, attends to the 64 keys, and asks for its next page.  No address arithmetic per 16 bytes:
+// of the CTA's key range, in halves of 32 keys through two stages: one lane asks for a half page's
+// K and V tiles, the warp waits on the stage's mbarrier, attends to the 32 keys while the other
+// half is on its way, and asks for the half after that.  No address arithmetic per 16 bytes:
 // a third of the instructions of the cp.async kernel, which stays for other head and page sizes.
 // Waits are bounded (a second): a warp that gives up sets *status = 301 and the CTA finishes with
 // what it has.
 #if HD == 64
 #define DT_PT 64
-#define DT_TILE_B (DT_PT * 128)
+#define DT_HALF 32                     // keys per tile: half a page, so that a warp has two tiles in flight
+#define DT_TILE_B (DT_HALF * 128)
 #define DT_WAIT_NS 1000000000ull
 
 __device__ __forceinline__ void at_mbar_init(unsigned bar, unsigned count) {
@@ -493,7 +495,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, int* status) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[DC_WARPS];
+  __shared__ __align__(8) unsigned long long bars[DC_WARPS * 2];
   __shared__ int sm_pages[DC_MAX_PAGES];
   __shared__ int sm_last;
   const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
@@ -513,52 +515,60 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
   if (pages_in_smem)
     for (int i = threadIdx.x; i < n_pg; i += DC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
-  if (threadIdx.x < DC_WARPS) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
+  if (threadIdx.x < DC_WARPS * 2) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   pdl_wait(); FELLM_TRACE_WAITED();
   __syncthreads();
   const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
   float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
-  const unsigned tile_k = base + warp * 2 * DT_TILE_B, tile_v = tile_k + DT_TILE_B;
-  const unsigned bar = (unsigned)__cvta_generic_to_shared(&bars[warp]);
+  // a warp's two stages, each the K and the V tile of half a page (32 keys)
+  const unsigned stage0 = base + warp * 4 * DT_TILE_B;
+  const unsigned bar0 = (unsigned)__cvta_generic_to_shared(&bars[warp * 2]);
   const int my_pages = (n_pg - warp + DC_WARPS - 1) / DC_WARPS;                              // may be <= 0
-  auto request = [&](int j) {                           // lane 0: K and V tile of this warp's j-th page
-    const int lp = pg0 + warp + j * DC_WARPS;
+  const int n_tiles = my_pages > 0 ? my_pages * 2 : 0;
+  auto request = [&](int q) {                           // lane 0: K and V of the q-th half page of this warp
+    const int lp = pg0 + warp + (q >> 1) * DC_WARPS;
     const int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
-    const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * DT_PT;          // < 2^31: the launcher checks
+    const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * DT_PT + (q & 1) * DT_HALF;   // < 2^31: the launcher checks
+    const unsigned st = stage0 + (q & 1) * 2 * DT_TILE_B, bar = bar0 + (q & 1) * 8;
     at_mbar_expect_tx(bar, 2 * DT_TILE_B);
-    at_tma_load_2d(tile_k, &pool_map, 0, row, bar);
-    at_tma_load_2d(tile_v, &pool_map, 0, row + a.G * DT_PT, bar);
+    at_tma_load_2d(st, &pool_map, 0, row, bar);
+    at_tma_load_2d(st + DT_TILE_B, &pool_map, 0, row + a.G * DT_PT, bar);
   };
-  if (lane == 0 && my_pages > 0) request(0);
+  if (lane == 0) {
+    if (n_tiles > 0) request(0);
+    if (n_tiles > 1) request(1);
+  }
   unsigned qf[KS][4];
   load_q(qf, [&](int i) -> const bf16* { return i < R ? a.q + ((size_t)t * a.H + g * R + i) * HD : nullptr; }, lane);
   float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
   for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
   const int lo[2] = {k0, k0}, hi[2] = {k1 - 1, k1 - 1};
-  for (int j = 0; j < my_pages; ++j) {
-    const bool arrived = __all_sync(0xffffffffu, at_mbar_wait(bar, j & 1));
-    if (j == 0) FELLM_TRACE_MARK(0);
+  for (int q = 0; q < n_tiles; ++q) {
+    const unsigned st = stage0 + (q & 1) * 2 * DT_TILE_B, bar = bar0 + (q & 1) * 8;
+    const bool arrived = __all_sync(0xffffffffu, at_mbar_wait(bar, (q >> 1) & 1));
+    if (q == 0) FELLM_TRACE_MARK(0);
     if (!arrived) {
       if (lane == 0 && status) atomicExch(status, 301);
       break;
     }
-    const int key0 = (pg0 + warp + j * DC_WARPS) * DT_PT;
-    if (key0 + DT_PT > k1) {
-      // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
-      const int first = k1 - key0;
-      for (int i = first * CPR + lane; i < DT_PT * CPR; i += 32) st_shared_zero16(tile_v + tile_off(i / CPR, i % CPR));
-      __syncwarp();
+    const int key0 = (pg0 + warp + (q >> 1) * DC_WARPS) * DT_PT + (q & 1) * DT_HALF;
+    if (key0 < k1 && key0 + DT_HALF > k0) {              // else: a half page with no key of the range
+      if (key0 + DT_HALF > k1) {
+        // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
+        for (int i = (k1 - key0) * CPR + lane; i < DT_HALF * CPR; i += 32) st_shared_zero16(st + DT_TILE_B + tile_off(i / CPR, i % CPR));
+        __syncwarp();
+      }
+      if (key0 < k0 || key0 + DT_HALF > k1)
+        attend_tile<DT_HALF / 8, true>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      else
+        attend_tile<DT_HALF / 8, false>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
     }
-    if (key0 < k0 || key0 + DT_PT > k1)
-      attend_tile<DT_PT / 8, true>(qf, tile_k, tile_v, key0, lo, hi, a.scale_log2, o, m, l, lane);
-    else
-      attend_tile<DT_PT / 8, false>(qf, tile_k, tile_v, key0, lo, hi, a.scale_log2, o, m, l, lane);
     __syncwarp();
-    if (j + 1 < my_pages) {
+    if (q + 2 < n_tiles) {
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // this warp's reads before the next copy's writes
-      if (lane == 0) request(j + 1);
+      if (lane == 0) request(q + 2);
     }
   }
   FELLM_TRACE_MARK(1);
@@ -589,7 +599,7 @@ static int pool_map_for(const void* pool, long long rows, CUtensorMap* out) {
   }
   cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  cuuint32_t box[2] = {HD, DT_PT};
+  cuuint32_t box[2] = {HD, DT_HALF};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
@@ -691,7 +701,7 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   CUtensorMap map;
   e = pool_map_for(pool, rows, &map);
   if (e) return e;
-  size_t tiles = (size_t)DC_WARPS * 2 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
+  size_t tiles = (size_t)DC_WARPS * 4 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
   size_t smem = (tiles > mrg ? tiles : mrg) + 1024;
   auto kern = attention_decode_tma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -394,8 +394,9 @@ __global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1) gemm_skinny_kerne
 }
 
 // ---------------------------------------------------------------- the single-shot kernel
-// The decode step's products: M <= 16 rows, every (slab, K slice) has a warp of its own, a slice is
-// at most LEAN_CH whole chunks, N is a multiple of 16.  One pass, no loops over slabs or rounds:
+// The decode step's products: M <= 64 rows, every (slab, K slice) has a warp of its own, a slice is
+// at most LEAN_CH whole chunks, N is a multiple of 16, the CTA's K range of x fits shared memory.
+// One pass, no loops over slabs or rounds:
 // the same sums in the same order as gemm_skinny_kernel, in a third of the instructions (a warp's
 // serial instruction stream is what a product of a few microseconds waits for).
 #define LEAN_CH 10
@@ -521,31 +522,35 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   __syncthreads();
   FELLM_TRACE_MARK(0);
 
-  // ---- the warp's slice of its slab
-  float acc[MT][4];
-#pragma unroll
-  for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+  // ---- the warp's slice of its slab, four token tiles (32 rows of x) at a time
+  constexpr int TP = MT > 4 ? 4 : MT;
   float* slots = (float*)(smem + (size_t)MP * a.xs_stride * sizeof(bf16));      // [warp][16][MP]
   if (active) {
     const bf16* xw = xs + (size_t)g * a.xs_stride + wk * a.k_per_warp + c * 8;
-#pragma unroll
-    for (int u = 0; u < LEAN_CH; ++u) {
-      if (u < 8 || u < n_chunks) {
-        unsigned fa[4] = {w0[u].x, w1[u].x, w0[u].y, w1[u].y};
-        unsigned fb[4] = {w0[u].z, w1[u].z, w0[u].w, w1[u].w};
-#pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          uint4 b = *(const uint4*)(xw + u * KCHUNK + (size_t)t * 8 * a.xs_stride);
-          mma16816(acc[t], fa, b.x, b.y);
-          mma16816(acc[t], fb, b.z, b.w);
-        }
-      }
-    }
     float* p = slots + (size_t)warp * SK_ROWS * MP;
 #pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      *(float2*)(p + g * MP + t * 8 + 2 * c) = make_float2(acc[t][0], acc[t][1]);
-      *(float2*)(p + (g + 8) * MP + t * 8 + 2 * c) = make_float2(acc[t][2], acc[t][3]);
+    for (int pass = 0; pass < MT / TP; ++pass) {
+      float acc[TP][4];
+#pragma unroll
+      for (int t = 0; t < TP; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+#pragma unroll
+      for (int u = 0; u < LEAN_CH; ++u) {
+        if (u < 8 || u < n_chunks) {
+          unsigned fa[4] = {w0[u].x, w1[u].x, w0[u].y, w1[u].y};
+          unsigned fb[4] = {w0[u].z, w1[u].z, w0[u].w, w1[u].w};
+#pragma unroll
+          for (int t = 0; t < TP; ++t) {
+            uint4 b = *(const uint4*)(xw + u * KCHUNK + (size_t)(pass * TP + t) * 8 * a.xs_stride);
+            mma16816(acc[t], fa, b.x, b.y);
+            mma16816(acc[t], fb, b.z, b.w);
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < TP; ++t) {
+        *(float2*)(p + g * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][0], acc[t][1]);
+        *(float2*)(p + (g + 8) * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][2], acc[t][3]);
+      }
     }
   }
   FELLM_TRACE_MARK(1);
@@ -632,6 +637,7 @@ static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   if (NORM) smem += (size_t)a.K * sizeof(float);
   a.xf_offset = (int)smem;
   if (NORM) smem += (size_t)(WARPS < MT * 8 ? WARPS : MT * 8) * a.K * sizeof(float);
+  if (!NORM && MT <= 2 && a.xf) return FELLM_ERR_ARG;
   auto kern = gemm_lean_kernel<MT, EPI, NORM, WARPS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -640,14 +646,66 @@ static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(WARPS * 32, 1, 1), smem, stream, a.splits, a);
 }
 
+static size_t lean_smem(int mt, int warps, int k_per_cta, bool norm, int K) {
+  size_t smem = (size_t)mt * 8 * x_stride(k_per_cta) * sizeof(bf16) + (size_t)warps * SK_ROWS * mt * 8 * sizeof(float);
+  if (norm) smem += (size_t)K * sizeof(float) + (size_t)(warps < mt * 8 ? warps : mt * 8) * K * sizeof(float);
+  return smem;
+}
+
+template <int EPI, int WARPS>
+static int dispatch_lean_mt(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
+  if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true, WARPS>(a, ctas_y, s) : launch_lean<1, EPI, false, WARPS>(a, ctas_y, s);
+  if (a.M <= 16) return a.xf ? launch_lean<2, EPI, true, WARPS>(a, ctas_y, s) : launch_lean<2, EPI, false, WARPS>(a, ctas_y, s);
+  if (a.xf) return FELLM_ERR_SIZE;                       // the norm is fused for up to 16 rows
+  if (a.M <= 32) return launch_lean<4, EPI, false, WARPS>(a, ctas_y, s);
+  return launch_lean<8, EPI, false, WARPS>(a, ctas_y, s);
+}
+
 template <int EPI>
 static int dispatch_lean(const SkinnyArgs& a, int ctas_y, int warps, cudaStream_t s) {
-  if (warps == 16) {
-    if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true, 16>(a, ctas_y, s) : launch_lean<1, EPI, false, 16>(a, ctas_y, s);
-    return a.xf ? launch_lean<2, EPI, true, 16>(a, ctas_y, s) : launch_lean<2, EPI, false, 16>(a, ctas_y, s);
+  return warps == 16 ? dispatch_lean_mt<EPI, 16>(a, ctas_y, s) : dispatch_lean_mt<EPI, 8>(a, ctas_y, s);
+}
+
+// The single-shot kernel's shape for a product, if it takes it: a (slab, K slice) per warp, whole
+// chunks, whole slabs, whole-row norm.  CTAs of 8 warps (two to an SM where shared memory allows)
+// or of 16 warps (one to an SM); K slices go to the warps of a CTA as far as the CTA's part of x
+// fits shared memory, the rest over a cluster.  Among the shapes that run in one wave: fewest
+// cluster ranks, then most CTAs.
+struct LeanPlan { int warps, warps_k, splits, ctas_y, k_per_warp; };
+static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
+  if (M > 64 || (norm && M > 16) || N % SK_ROWS) return false;
+  const int in_flight = 2 * SK_U * KCHUNK;
+  int slices = 1;
+  while (slices < 64 && ceil_div(K, slices) > in_flight) slices *= 2;
+  if (slices < 2 || K % slices || (K / slices) % KCHUNK) return false;
+  const int kpw = K / slices;
+  if (kpw < 8 * KCHUNK || kpw > LEAN_CH * KCHUNK) return false;
+  const int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)), n_tiles = N / SK_ROWS;
+  bool found = false;
+  LeanPlan best = {};
+  long long best_key = 0;
+  for (int warps = 8; warps <= 16; warps *= 2) {
+    int wk = slices < warps ? slices : warps;
+    while (wk > 1 && lean_smem(mt, warps, kpw * wk, norm, K) > 200 * 1024) wk /= 2;
+    const size_t smem = lean_smem(mt, warps, kpw * wk, norm, K);
+    if (smem > 200 * 1024) continue;
+    const int sp = slices / wk, ct = ceil_div(n_tiles, warps / wk);
+    if (sp > 8 || (norm && (sp > 1 || K > 4096))) continue;
+    const int per_sm = (warps == 8 && smem <= 100 * 1024) ? 2 : 1;
+    if (ct * sp > 148 * per_sm) continue;
+    // order: fewest cluster ranks; then not two CTAs to an SM where one would do (x staged twice); then most CTAs
+    const int crowded = (per_sm == 2 && ct * sp > 148) ? 1 : 0;
+    const long long key = ((long long)sp << 40) | ((long long)crowded << 32) | (long long)(100000 - ct * sp);
+    if (!found || key < best_key) { best = LeanPlan{warps, wk, sp, ct, kpw}; best_key = key; found = true; }
   }
-  if (a.M <= 8) return a.xf ? launch_lean<1, EPI, true, 8>(a, ctas_y, s) : launch_lean<1, EPI, false, 8>(a, ctas_y, s);
-  return a.xf ? launch_lean<2, EPI, true, 8>(a, ctas_y, s) : launch_lean<2, EPI, false, 8>(a, ctas_y, s);
+  if (found) *out = best;
+  return found;
+}
+
+// Whether fellm_gemm_skinny would run this product on its single-shot kernel (1) or not (0).
+FELLM_API int fellm_gemm_skinny_single_shot(int M, int N, int K, int norm) {
+  LeanPlan p;
+  return plan_lean(M, N, K, norm != 0, &p) ? 1 : 0;
 }
 
 template <int EPI>
@@ -723,37 +781,19 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   while ((1 << a.log2_warps_k) < warps_k) ++a.log2_warps_k;
   a.k_per_warp = k_per_cta / warps_k;
   a.pdl = pdl_enabled(1) ? 1 : 0;
-  // the single-shot kernel: a (slab, K slice) per warp, whole chunks, whole slabs, whole-row norm.
-  // CTAs of 8 warps, two to an SM; or of 16 warps, one to an SM, where that keeps the product in
-  // one wave of CTAs or saves a split of K over a cluster (x is then staged once per SM).
-  if (M <= 16 && slices > 1 && N % SK_ROWS == 0 && K % slices == 0 && (K / slices) % KCHUNK == 0 &&
-      K / slices >= 8 * KCHUNK && K / slices <= LEAN_CH * KCHUNK) {
-    auto shape = [&](int warps, int& wk, int& sp, int& ctas) {
-      wk = slices < warps ? slices : warps;
-      sp = slices / wk;
-      ctas = ceil_div(n_tiles, warps / wk);
-    };
-    int wk8, sp8, ct8, wk16, sp16, ct16;
-    shape(8, wk8, sp8, ct8);
-    shape(16, wk16, sp16, ct16);
-    const bool fits8 = sp8 <= 8 && ct8 * sp8 <= 148 * 2, fits16 = sp16 <= 8 && ct16 * sp16 <= 148;
-    int warps = 0;
-    if (fits16 && (sp16 < sp8 || !fits8 || ct8 * sp8 > 148)) warps = 16;
-    else if (fits8) warps = 8;
-    const int wk = warps == 16 ? wk16 : wk8, sp = warps == 16 ? sp16 : sp8, ct = warps == 16 ? ct16 : ct8;
-    if (warps && (!xf || (sp == 1 && K <= 4096))) {
-      a.splits = sp; a.warps_k = wk; a.k_per_warp = K / slices; a.k_per_cta = a.k_per_warp * wk;
-      a.xs_stride = x_stride(a.k_per_cta); a.tiles_per_warp = 1;
-      a.log2_warps_k = 0;
-      while ((1 << a.log2_warps_k) < wk) ++a.log2_warps_k;
-      a.chunks_per_warp = a.k_per_warp / KCHUNK;
-      switch (epi) {
-        case EPI_STORE: return dispatch_lean<EPI_STORE>(a, ct, warps, stream);
-        case EPI_ACC: return dispatch_lean<EPI_ACC>(a, ct, warps, stream);
-        case EPI_SWIGLU: return dispatch_lean<EPI_SWIGLU>(a, ct, warps, stream);
-        case EPI_F32: return dispatch_lean<EPI_F32>(a, ct, warps, stream);
-        default: return FELLM_ERR_ARG;
-      }
+  LeanPlan lp;
+  if (plan_lean(M, N, K, xf != nullptr, &lp)) {
+    a.splits = lp.splits; a.warps_k = lp.warps_k; a.k_per_warp = lp.k_per_warp; a.k_per_cta = lp.k_per_warp * lp.warps_k;
+    a.xs_stride = x_stride(a.k_per_cta); a.tiles_per_warp = 1;
+    a.log2_warps_k = 0;
+    while ((1 << a.log2_warps_k) < lp.warps_k) ++a.log2_warps_k;
+    a.chunks_per_warp = a.k_per_warp / KCHUNK;
+    switch (epi) {
+      case EPI_STORE: return dispatch_lean<EPI_STORE>(a, lp.ctas_y, lp.warps, stream);
+      case EPI_ACC: return dispatch_lean<EPI_ACC>(a, lp.ctas_y, lp.warps, stream);
+      case EPI_SWIGLU: return dispatch_lean<EPI_SWIGLU>(a, lp.ctas_y, lp.warps, stream);
+      case EPI_F32: return dispatch_lean<EPI_F32>(a, lp.ctas_y, lp.warps, stream);
+      default: return FELLM_ERR_ARG;
     }
   }
   switch (epi) {

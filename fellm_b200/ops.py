@@ -295,6 +295,18 @@ def norm_fusable(x_f32, w, norm_w) -> bool:
             and x_f32.stride(1) == 1 and x_f32.stride(0) % 4 == 0 and w.stride(1) == 1)
 
 
+_single_shot_cache = {}
+
+
+def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
+    key = (M, N, K, norm)
+    hit = _single_shot_cache.get(key)
+    if hit is None:
+        f = _fn("gemm_skinny", "fellm_gemm_skinny_single_shot", [_c_int, _c_int, _c_int, _c_int])
+        hit = _single_shot_cache[key] = bool(f(M, N, K, int(norm)))
+    return hit
+
+
 def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False, norm=None):
     """out = x[M,K] @ w[N,K]^T (+bias) on tensor cores, bfloat16 in, float32 sums.
     accumulate: out (float32 [M,N]) += ; swiglu: w's rows are interleaved in blocks of 8 gate / 8 up
@@ -337,8 +349,12 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
         return out
     umma_ok = (USE_UMMA and norm is None and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
                and (epi != _EPI_SWIGLU or out.stride(0) % 8 == 0))
-    # few rows: the weight-streaming kernel; 17..32 rows: it too, except for very wide products
-    skinny = M <= 64 and (M <= 16 or not umma_ok or (M <= SKINNY_MAX_ROWS and N < 8192))
+    # few rows: the weight-streaming kernel; up to 64 rows: it too where its single-shot form takes the
+    # product (all of W requested at once by every SM), else up to 32 rows except for very wide products
+    # (measured at 64 rows: 14 us against 26 us for [1024, 4608], 8 against 9-11 for K = 1024, but 13
+    # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
+    skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
+                          or (M <= SKINNY_MAX_ROWS and N < 8192))
     if skinny:
         f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
         if norm is not None:

@@ -288,7 +288,7 @@ def test_gemm_bf16_store_acc_f32(M, N, K):
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
 def test_gemm_bf16_swiglu_epilogue(M, F, K):
     g = torch.Generator().manual_seed(F)
     x = torch.randn(M, K, generator=g).bfloat16()
@@ -456,10 +456,12 @@ def test_attention_prefill_finds_one_far_key(far, qpos):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 144, 144), (300, 1000, 1000), (2048, 1024, 4608),
-                                   (513, 3072, 1024), (1000, 200, 72)])
+                                   (513, 3072, 1024), (1000, 200, 72), (64, 1024, 4608), (64, 1024, 1024), (48, 3072, 1024),
+                                   (128, 2048, 1000), (33, 1000, 4608)])
 def test_gemm_umma_tcgen05(M, N, K):
     """The tcgen05 / TMEM / TMA product by itself: against float64, against the mma.sync product,
-    and its bounded waits must not have run out."""
+    and its bounded waits must not have run out.  (Products of up to 64 rows that the weight-streaming
+    kernel takes in one shot run there instead: the same checks hold.)"""
     x, w, want = _gemm_case(M, N, K, seed=5)
     xd, wd = x.to(DEV), w.to(DEV)
     got = ops.gemm_bf16(xd, wd, out_dtype=torch.float32)
@@ -467,13 +469,14 @@ def test_gemm_umma_tcgen05(M, N, K):
     assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4), (got.double().cpu() - want).abs().max()
     ref = torch.empty(M, N, device=DEV)
     ops.gemm_tiled(xd, wd, out=ref, epi=3)
-    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(got, ref, rtol=1e-4, atol=1e-4)            # the same products, summed in another order
     bias = torch.randn(N, device=DEV)
     res = torch.randn(M, N, device=DEV)
     out = res.clone()
     ops.gemm_bf16(xd, wd, bias, out=out, accumulate=True)
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want + bias.double().cpu(), rtol=1e-4, atol=1e-4)
     ops.check_umma_status(DEV)
+    assert torch.equal(ops.gemm_bf16(xd, wd, out_dtype=torch.float32), got)       # the same bits every run
 
 
 @pytest.mark.parametrize("M,N,K", [(33, 200, 328), (48, 1024, 1024), (64, 2048, 200), (64, 515, 144)])
