@@ -69,7 +69,12 @@ class Engine:
         if self.stepper.mega is not None:
             jit.compile_many(self.stepper.mega.kernel_modules())
         self._sampler: Optional[Sampler] = None
-        self._tok_host = torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True)
+        # sampled tokens (and the status word behind them) come back through a few pinned buffers in
+        # turn: a launch may be in flight while the one before it is read
+        self._tok_ring = [(torch.zeros(options.max_requests + 1, dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+                          for _ in range(4)]
+        self._tok_count = [0] * len(self._tok_ring)
+        self._launch_no = 0
         self._scheduler: Optional[Scheduler] = None
 
     # ---- constructors
@@ -138,19 +143,36 @@ class Engine:
     def start_request(self, slot: int, prompt, params: GenParams):
         self.sampler.start_request(slot, prompt, params)
 
-    def run(self, items: List[StepItem], sample_rows) -> List[int]:
-        """One step and one sampling launch; returns the sampled tokens on the host.  The tokens
-        and the kernels' status word come back in one synchronisation."""
-        logits = self.stepper.step(items)
+    def launch(self, items: List[StepItem], sample_rows, chain: bool = False) -> int:
+        """One step and one sampling launch, not waited for; returns a handle for collect().
+        chain: the items (one token each, in the order of the last launch's sample rows) take the
+        last launch's sampled tokens as they lie on the device.  The tokens and the kernels'
+        status word are copied to one of a few pinned host buffers behind the launch."""
+        logits = self.stepper.step(items, device_tokens=self.sampler.out_tokens if chain else None)
         n = len(sample_rows)
+        k = self._launch_no % len(self._tok_ring)
+        self._launch_no += 1
+        host, done = self._tok_ring[k]
         if n:
             toks = self.sampler.sample(logits, sample_rows)
-            self._tok_host[:n].copy_(toks, non_blocking=True)
-        self._tok_host[-1:].copy_(self.stepper.buffers.status, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        if int(self._tok_host[-1]):
+            host[:n].copy_(toks, non_blocking=True)
+        host[-1:].copy_(self.stepper.buffers.status, non_blocking=True)
+        done.record()
+        self._tok_count[k] = n
+        return k
+
+    def collect(self, handle: int) -> List[int]:
+        """Waits for a launch and returns its sampled tokens on the host."""
+        host, done = self._tok_ring[handle]
+        done.synchronize()
+        if int(host[-1]):
             self.stepper.check_status()
-        return self._tok_host[:n].tolist()
+        return host[:self._tok_count[handle]].tolist()
+
+    def run(self, items: List[StepItem], sample_rows) -> List[int]:
+        """launch() and collect() in one: the tokens and the status word come back in one
+        synchronisation."""
+        return self.collect(self.launch(items, sample_rows))
 
     # ---- generation
     def scheduler(self) -> Scheduler:

@@ -18,6 +18,13 @@ When pages run out (FeLLM: every sequence of the batch gets an Error event, 644-
   4. a request that could never fit (prompt + max_tokens beyond the context, or more pages than
      the pool has) is refused at enqueue with SchedulerError.
 No request fails because another one needed pages.
+
+One step ahead: while the requests that decode together stay the same, the next step is launched
+before the tokens of the last one have been read (its inputs are the sampled tokens where they
+lie on the device), so the host's work on a step overlaps the device's work on the next.  A
+request that ends on a stop token has then run one token too many; that token is dropped and the
+request's pages go back as usual (the launch that frees them for another request comes later in
+the stream).  Ends that the host can foresee (max_tokens, the end of the context) are not run ahead.
 """
 from __future__ import annotations
 
@@ -68,6 +75,15 @@ class PlanItem:
     decode: bool
 
 
+@dataclass
+class InFlight:
+    """A launched step whose tokens have not been read yet."""
+    handle: object
+    plan: List[PlanItem]
+    samplers: List[Request]
+    dropped: set = field(default_factory=set)     # ids of requests that ended while this step ran ahead
+
+
 def plan_batch(running: Sequence[Request], n_batch: int, n_ubatch: int) -> List[PlanItem]:
     """Decode-first, then prompt portions by priority and age, under n_batch tokens
     (scheduler.rs:88-152)."""
@@ -87,18 +103,22 @@ def plan_batch(running: Sequence[Request], n_batch: int, n_ubatch: int) -> List[
 
 
 class Scheduler:
-    """`backend` provides: .cache (CacheManager), .n_ctx, .run(items, sample_rows) -> host token
-    list for the rows that asked for a sample, .start_request(slot, prompt, params)."""
+    """`backend` provides: .cache (CacheManager), .n_ctx, .start_request(slot, prompt, params) and
+    .run(items, sample_rows) -> host token list for the rows that asked for a sample; or, to run
+    one step ahead, .launch(items, sample_rows, chain) -> handle and .collect(handle) -> host token
+    list (chain: the items' tokens are the last launch's samples, in order, still on the device)."""
 
-    def __init__(self, backend, n_batch: int, n_ubatch: int):
+    def __init__(self, backend, n_batch: int, n_ubatch: int, lookahead: bool = True):
         self.backend, self.cache = backend, backend.cache
         self.n_batch, self.n_ubatch = int(n_batch), int(n_ubatch)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.events: Deque[Event] = deque()
+        self.lookahead = bool(lookahead) and hasattr(backend, "launch")
+        self.inflight: Optional[InFlight] = None
         self._next_id, self._next_seq = 0, 0
         self.counters = {"requests": 0, "admitted": 0, "preempted": 0, "finished": 0, "steps": 0,
-                         "shrunk": 0, "tokens_run": 0, "admission_waits": 0}
+                         "shrunk": 0, "tokens_run": 0, "admission_waits": 0, "ran_ahead": 0, "dropped": 0}
 
     # ---- enqueue / cancel
     def enqueue_ids(self, ids: Sequence[int], params: Optional[GenParams] = None) -> int:
@@ -127,11 +147,13 @@ class Scheduler:
         for r in self.running:
             if r.id == rid:
                 self._finish(r, "cancelled")
+                if self.inflight is not None:
+                    self.inflight.dropped.add(rid)
                 return True
         return False
 
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self.inflight is None
 
     # ---- admission
     def _admit(self):
@@ -196,6 +218,18 @@ class Scheduler:
         return out
 
     def _iterate(self):
+        cur = self.inflight
+        self.inflight = None
+        if cur is None:
+            cur = self._launch()
+            if cur is None:
+                return
+        if self.lookahead:
+            self.inflight = self._launch_ahead(cur)
+        self._collect(cur)
+
+    def _launch(self) -> Optional[InFlight]:
+        """Plans a batch from what the host knows and launches it."""
         self._admit()
         plan = self._fit(plan_batch(self.running, self.n_batch, self.n_ubatch))
         if not plan:
@@ -203,7 +237,7 @@ class Scheduler:
                 # nothing runs and the head cannot be admitted: it can never fit
                 r = self.waiting.popleft()
                 self.events.append(Event("error", r.id, message="request cannot be placed in the cache"))
-            return
+            return None
         items, sample_rows, samplers = [], [], []
         for p in plan:
             r = p.req
@@ -218,7 +252,10 @@ class Scheduler:
                 sample_rows.append((self.cache.slot(r.id), r.params, r.draws))
                 samplers.append(r)
         try:
-            tokens = self.backend.run(items, sample_rows)
+            if self.lookahead:
+                handle = self.backend.launch(items, sample_rows, False)
+            else:
+                handle = self.backend.run(items, sample_rows)
         except Exception as e:                          # a failed launch ends the batch's requests
             for p in plan:
                 self._finish(p.req, "error", error=str(e))
@@ -230,23 +267,73 @@ class Scheduler:
                 p.req.pending = None
             else:
                 p.req.fed += p.n_tokens
+        return InFlight(handle, plan, samplers)
+
+    def _launch_ahead(self, cur: InFlight) -> Optional[InFlight]:
+        """The step after `cur`, launched before cur's tokens are read: only when it is the same
+        requests decoding one more token each, none of which the host can see ending, with nobody
+        waiting for admission and a page for everyone who needs one."""
+        if self.waiting or cur.dropped or len(cur.samplers) != len(cur.plan) or len(cur.plan) != len(self.running):
+            return None
+        n_ctx = self.backend.n_ctx
+        for r in cur.samplers:
+            if r.prefilling or r.pending is not None:
+                return None
+            # after cur: len(generated) + 1 tokens; the request goes on only if that is not its end
+            if len(r.generated) + 1 >= r.params.max_tokens or self.cache.length(r.id) + 1 >= n_ctx:
+                return None
+        if not self.cache.can_reserve([(r.id, 1) for r in cur.samplers]):
+            return None
+        items = [StepItem(r.id, [0], [0]) for r in cur.samplers]          # the tokens are on the device
+        sample_rows = [(self.cache.slot(r.id), r.params, r.draws + 1) for r in cur.samplers]
+        try:
+            handle = self.backend.launch(items, sample_rows, True)
+        except Exception:                                # decided again, with the tokens known, after the collect
+            return None
+        self.counters["steps"] += 1
+        self.counters["ran_ahead"] += 1
+        self.counters["tokens_run"] += len(items)
+        return InFlight(handle, [PlanItem(r, 1, True) for r in cur.samplers], list(cur.samplers))
+
+    def _collect(self, cur: InFlight):
+        """Reads a launched step's tokens and does the bookkeeping that follows from them."""
+        try:
+            tokens = self.backend.collect(cur.handle) if self.lookahead else cur.handle
+        except Exception as e:
+            ahead, self.inflight = self.inflight, None
+            for p in cur.plan:
+                if p.req in self.running:
+                    self._finish(p.req, "error", error=str(e))
+            if ahead is not None:
+                try:
+                    self.backend.collect(ahead.handle)
+                except Exception:
+                    pass
+            raise
+        ahead = self.inflight
         now = time.perf_counter()
-        for r, tok in zip(samplers, tokens):
+        for r, tok in zip(cur.samplers, tokens):
+            if r.id in cur.dropped:                      # ended on a stop token while this step ran ahead
+                self.counters["dropped"] += 1
+                continue
             tok = int(tok)
             r.draws += 1
             if r.t_first is None:
                 r.t_first = now
             r.generated.append(tok)
             self.events.append(Event("token", r.id, token=tok))
-            length = self.cache.length(r.id)
+            length = self.cache.length(r.id) - (1 if ahead is not None else 0)      # as it was after this step
             if tok in r.params.stop_token_ids:
                 self._finish(r, "stop")
             elif len(r.generated) >= r.params.max_tokens:
                 self._finish(r, "length")
             elif length + 1 >= self.backend.n_ctx:          # scheduler.rs:706-724: position+1 >= n_ctx
                 self._finish(r, "length")
-            else:
+            elif ahead is None:
                 r.pending = tok
+            # else: the token is already being run by the step ahead
+            if ahead is not None and r not in self.running:
+                ahead.dropped.add(r.id)
 
     def _finish(self, r: Request, reason: str, error: str = ""):
         if r in self.running:

@@ -26,16 +26,19 @@ class Sampler:
         size = ops.sample_params_size()
         if size != ROW_PARAMS.itemsize:
             raise KernelError(f"sampling parameter record is {size} bytes in the kernel, {ROW_PARAMS.itemsize} here")
-        self.params_host = torch.zeros(max_rows * size, dtype=torch.uint8, pin_memory=True)
-        self.params_np = self.params_host.numpy().view(ROW_PARAMS)
+        # a few pinned parameter buffers in turn: the host may fill the next launch's records while
+        # the copy of the last launch's still waits in the stream behind that launch's kernels
+        self._params_ring = []
+        for _ in range(4):
+            host = torch.zeros(max_rows * size, dtype=torch.uint8, pin_memory=True)
+            self._params_ring.append([host, host.numpy().view(ROW_PARAMS), torch.cuda.Event(), False])
+        self._params_no = 0
         self.params_dev = torch.zeros(max_rows * size, dtype=torch.uint8, device=device)
         self.out_tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=True)
         self.arg_val = torch.zeros(max_rows * 64, dtype=torch.float32, device=device)
         self.arg_idx = torch.zeros(max_rows * 64, dtype=torch.int32, device=device)
         self.counts: Optional[torch.Tensor] = None
-        self._copy_done = torch.cuda.Event()
-        self._copy_pending = False
 
     # ---- history for the penalties
     def _ensure_counts(self):
@@ -63,9 +66,11 @@ class Sampler:
             # plain argmax: no per-row parameters to ship, the row is reduced by 64 blocks at once
             ops.argmax_rows(logits, self.arg_val, self.arg_idx, self.out_tokens)
             return self.out_tokens[:n]
-        if self._copy_pending:
-            self._copy_done.synchronize()
-        rec = self.params_np
+        entry = self._params_ring[self._params_no % len(self._params_ring)]
+        self._params_no += 1
+        params_host, rec, copy_done, pending = entry
+        if pending:
+            copy_done.synchronize()
         bias_tok, bias_val = [], []
         need_counts = False
         for i, (slot, p, draw) in enumerate(rows):
@@ -78,9 +83,9 @@ class Sampler:
         if need_counts:
             self._ensure_counts()
         nbytes = n * ROW_PARAMS.itemsize
-        self.params_dev[:nbytes].copy_(self.params_host[:nbytes], non_blocking=True)
-        self._copy_done.record()
-        self._copy_pending = True
+        self.params_dev[:nbytes].copy_(params_host[:nbytes], non_blocking=True)
+        copy_done.record()
+        entry[3] = True
         bt = bv = None
         if bias_tok:
             bt = torch.tensor(bias_tok, dtype=torch.int32).to(self.device)

@@ -168,3 +168,94 @@ def test_cancel():
     assert s.cancel(a) and s.cancel(w) and not s.cancel(99)
     toks, done = run_all(s)
     assert done[a].finish_reason == "cancelled" and b.cache.free_pages() == b.cache.n_pages
+
+
+class AheadBackend(FakeBackend):
+    """The same fake with launch / collect: a launched step's tokens can be taken later, and a
+    chained launch reads its items' tokens from the launch before it."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.launched, self.last_out, self.open_handles = {}, [], 0
+
+    def launch(self, items, sample_rows, chain=False):
+        if chain:
+            assert len(items) == len(self.last_out) and all(len(it.tokens) == 1 for it in items)
+            items = [type(it)(it.req, [tok], it.want) for it, tok in zip(items, self.last_out)]
+        out = FakeBackend.run(self, items, sample_rows)
+        self.last_out = out
+        h = len(self.launched)
+        self.launched[h] = out
+        self.open_handles += 1
+        assert self.open_handles <= 2                      # one step ahead, never more
+        return h
+
+    def collect(self, handle):
+        self.open_handles -= 1
+        return self.launched[handle]
+
+
+def _scenario(backend_cls, lookahead, **bk):
+    import random
+    b = backend_cls(**bk)
+    s = Scheduler(b, n_batch=16, n_ubatch=8, lookahead=lookahead) if backend_cls is AheadBackend else Scheduler(b, 16, 8)
+    rng = random.Random(3)
+    ids, early = [], []
+    for i in range(9):
+        prompt = [rng.randrange(1, 90) for _ in range(rng.randrange(1, 14))]
+        stops = tuple(rng.sample(range(3, 100), 12)) if i % 2 else ()
+        ids.append(s.enqueue_ids(prompt, G(rng.randrange(1, 12), stop_token_ids=stops)))
+        if i % 3 == 2:
+            for _ in range(rng.randrange(1, 5)):
+                early += s.step()
+    toks, done = {}, {}
+    for _ in range(10_000):
+        evs = early + s.step()
+        early = []
+        for ev in evs:
+            if ev.kind == "token":
+                toks.setdefault(ev.req, []).append(ev.token)
+            elif ev.kind == "done":
+                done[ev.req] = ev.stats
+            else:
+                raise AssertionError(ev)
+        if s.idle():
+            break
+    b.cache.audit()
+    assert b.cache.free_pages() == b.cache.n_pages and b.cache.slots.free_count == bk.get("max_requests", 4)
+    return s, toks, {r: (d.finish_reason, d.predicted_tokens) for r, d in done.items()}
+
+
+def test_one_step_ahead_gives_the_same_tokens_and_reasons():
+    _, want_toks, want_done = _scenario(FakeBackend, False, page_tokens=4, max_tokens=64, max_requests=4, n_ctx=64)
+    s, toks, done = _scenario(AheadBackend, True, page_tokens=4, max_tokens=64, max_requests=4, n_ctx=64)
+    assert toks == want_toks and done == want_done
+    assert s.counters["ran_ahead"] > 0
+    s2, toks2, done2 = _scenario(AheadBackend, False, page_tokens=4, max_tokens=64, max_requests=4, n_ctx=64)
+    assert toks2 == want_toks and done2 == want_done and s2.counters["ran_ahead"] == 0
+
+
+def test_one_step_ahead_drops_the_token_after_a_stop_and_is_not_taken_before_a_foreseen_end():
+    b = AheadBackend()
+    s = Scheduler(b, 64, 64)
+    first = (sum([1, 2, 3]) * 31 + 3 * 7) % 97 + 3
+    second = ((sum([1, 2, 3]) + first) * 31 + 4 * 7) % 97 + 3
+    a = s.enqueue_ids([1, 2, 3], G(50, stop_token_ids=(second,)))
+    toks, done = run_all(s)
+    assert toks[a] == [first, second] and done[a].finish_reason == "stop"
+    assert s.counters["dropped"] == 1 and s.counters["ran_ahead"] == 2       # the step after `second` ran and was dropped
+    assert b.cache.free_pages() == b.cache.n_pages and s.idle()
+    # max_tokens is seen coming: the last step is not followed by one ahead
+    b = AheadBackend()
+    s = Scheduler(b, 64, 64)
+    a = s.enqueue_ids([4, 5], G(4))
+    toks, done = run_all(s)
+    assert len(toks[a]) == 4 and done[a].finish_reason == "length"
+    assert s.counters["steps"] == 4 and s.counters["dropped"] == 0 and s.counters["ran_ahead"] == 3
+
+
+def test_one_step_ahead_under_page_pressure_matches_the_plain_order():
+    kw = dict(page_tokens=4, max_tokens=24, max_requests=3, n_ctx=40)
+    _, want_toks, want_done = _scenario(FakeBackend, False, **kw)
+    s, toks, done = _scenario(AheadBackend, True, **kw)
+    assert toks == want_toks and done == want_done
