@@ -24,10 +24,6 @@ class EngineOptions:
     max_tokens: Optional[int] = None    # cache pool size in tokens; None = from memory
     kv_memory_fraction: float = 0.25    # fabric.rs:40-48 (share of free memory when max_tokens is None)
     cuda_graphs: bool = True
-    # bfloat16 decode steps of up to 16 requests as ONE persistent kernel (fellm_b200/engine/mega.py).
-    # Off by default: measured at the 350M shape, batch 8, it takes 0.88 ms a step against 0.65 ms for
-    # the per-kernel path replayed from a CUDA graph (profiles/decode_mega_stage_trace.md).
-    mega_decode: bool = False
     device: str = "cuda:0"
 
     def validate(self):

@@ -37,7 +37,8 @@ namespace cg = cooperative_groups;
 #define SK_XF 2048                   // floats of a row that a warp's float32 buffer takes at a time
 #define SK_GAMMA_MAX 2048            // norm weights of up to this many columns are parked in shared memory
 
-enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
+enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3, EPI_CONV = 4 };
+#define SK_MAX_LC 8
 
 __device__ __forceinline__ void mma16816(float* d, const unsigned* a, unsigned b0, unsigned b1) {
   asm volatile(
@@ -66,6 +67,9 @@ struct SkinnyArgs {
   const bf16* W; const float* bias; void* out;
   int M, N, K, lda, ldw, ldo, k_per_cta, xs_stride, splits, warps_k, n_tiles, tiles_per_warp, gamma_offset, xf_offset,
       log2_warps_k, k_per_warp, pdl, chunks_per_warp;
+  // EPI_CONV: the gated short convolution behind the input product of a ShortConv mixer
+  const float* conv_w; const float* conv_bias; float* conv_state; const int* row_slot;
+  long long conv_slot_stride; int conv_taps, red_offset;
 };
 
 template <int MT, int EPI>
@@ -426,7 +430,7 @@ struct LeanLoad<N, N> {
 
 template <int MT, int EPI, bool NORM, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kernel(SkinnyArgs a) {
-  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * EPI);
+  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * (EPI == EPI_CONV ? EPI_STORE : EPI));
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int MP = MT * 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -486,6 +490,21 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     request_x();
   }
   FELLM_TRACE_WAITED();
+
+  // EPI_CONV: thread (channel j of the CTA's 16, token m) asks for its taps and its state now; they
+  // are used after the product
+  float cv_hist[SK_MAX_LC - 1], cv_w[SK_MAX_LC], cv_bias = 0.f;
+  float* cv_state = nullptr;
+  const bool conv_thread = EPI == EPI_CONV && (int)threadIdx.x < SK_ROWS * a.M;
+  if (EPI == EPI_CONV && conv_thread) {
+    const int j = threadIdx.x & 15, m = threadIdx.x >> 4, ch = blockIdx.y * SK_ROWS + j, d = a.N / 3;
+    cv_state = a.conv_state + (size_t)a.row_slot[m] * a.conv_slot_stride + ch;
+#pragma unroll
+    for (int t = 0; t < SK_MAX_LC - 1; ++t) cv_hist[t] = t < a.conv_taps - 1 ? cv_state[(size_t)t * d] : 0.f;
+#pragma unroll
+    for (int t = 0; t < SK_MAX_LC; ++t) cv_w[t] = t < a.conv_taps ? a.conv_w[(size_t)ch * a.conv_taps + t] : 0.f;
+    if (a.conv_bias) cv_bias = a.conv_bias[ch];
+  }
 
   sk_cp_async_wait_all();
   if (NORM) {
@@ -594,11 +613,38 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
       if (EPI == EPI_SWIGLU) {
         if (a.bias) { v0 += a.bias[n]; v1 += a.bias[n + 8]; }
         ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((v0 / (1.0f + expf(-v0))) * v1);
+      } else if (EPI == EPI_CONV) {
+        // B, C or X of (channel j, token m), rounded as the stored product would be
+        if (a.bias) v0 += a.bias[n];
+        ((float*)(smem + a.red_offset))[(wn * SK_ROWS + j) * MP + m] = __bfloat162float(__float2bfloat16_rn(v0));
       } else {
         if (a.bias) v0 += a.bias[n];
         if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
         else if (EPI == EPI_ACC) ((float*)a.out)[o] = old + v0;
         else ((float*)a.out)[o] = v0;
+      }
+    }
+  }
+  if (EPI == EPI_CONV) {
+    // the CTA's three slabs are B, C and X of its 16 channels (the weight rows come in blocks of
+    // 16 B / 16 C / 16 X rows): bx = B*X; conv = bx*w[Lc-1] + sum_t state[t]*w[t]; y = C*(conv + bias);
+    // the state moves on by one (crates/backend-cpu/src/kernels/shortconv.rs:61-106).  Nobody else
+    // reads or writes these channels' state.
+    __syncthreads();
+    if (conv_thread) {
+      const int j = threadIdx.x & 15, m = threadIdx.x >> 4, d = a.N / 3, H = a.conv_taps - 1;
+      const float* red = (const float*)(smem + a.red_offset);
+      const float bx = red[j * MP + m] * red[(2 * SK_ROWS + j) * MP + m];
+      float wlast = 0.f;
+#pragma unroll
+      for (int t = 0; t < SK_MAX_LC; ++t) if (t == H) wlast = cv_w[t];
+      float conv = bx * wlast;
+#pragma unroll
+      for (int t = 0; t < SK_MAX_LC - 1; ++t) if (t < H) conv = fmaf(cv_hist[t], cv_w[t], conv);
+      ((bf16*)a.out)[(size_t)m * a.ldo + blockIdx.y * SK_ROWS + j] = __float2bfloat16_rn(red[(SK_ROWS + j) * MP + m] * (conv + cv_bias));
+#pragma unroll
+      for (int t = 0; t < SK_MAX_LC - 1; ++t) {
+        if (t < H) cv_state[(size_t)t * d] = (t + 1 < H) ? cv_hist[t + 1 < SK_MAX_LC - 1 ? t + 1 : t] : bx;
       }
     }
   }
@@ -615,6 +661,18 @@ static inline size_t smem_bytes(int mt, int k_per_cta, bool direct, int tiles_pe
   return sx + sp;
 }
 
+// Which products are launched as programmatic dependents (launch class 1) by epilogue kind: all but
+// the one with the convolution behind it.  A chain in which EVERY kernel starts early piles kernels
+// up on the SMs ahead of the one that has to finish first: measured on B200 at batch 8 (16 layers of
+// width 1024, one decode step replayed from a graph), 424 us with the convolution product in the
+// chain, 399 us with it launched the ordinary way, 414 us with the convolution as a kernel of its
+// own.  FELLM_B200_PDL_EPIS overrides the mask (bit = epilogue kind) for experiments.
+static int pdl_class_of(int epi) {
+  static int mask = -1;
+  if (mask < 0) { const char* e = getenv("FELLM_B200_PDL_EPIS"); mask = e ? atoi(e) : 15; }
+  return ((mask >> epi) & 1) ? 1 : 0;
+}
+
 template <int MT, int EPI>
 static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   size_t smem = smem_bytes(MT, a.k_per_cta, a.splits == 1 && a.warps_k == 1, a.tiles_per_warp);
@@ -627,7 +685,9 @@ static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
+  const int cls = pdl_class_of(EPI);
+  a.pdl = pdl_enabled(cls) ? 1 : 0;
+  return launch_k_class(cls, kern, dim3(a.splits, ctas_y, 1), dim3(SK_THREADS, 1, 1), smem, stream, a.splits, a);
 }
 
 template <int MT, int EPI, bool NORM, int WARPS>
@@ -638,12 +698,16 @@ static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   a.xf_offset = (int)smem;
   if (NORM) smem += (size_t)(WARPS < MT * 8 ? WARPS : MT * 8) * a.K * sizeof(float);
   if (!NORM && MT <= 2 && a.xf) return FELLM_ERR_ARG;
+  a.red_offset = (int)smem;
+  if (EPI == EPI_CONV) smem += (size_t)3 * SK_ROWS * MT * 8 * sizeof(float);
   auto kern = gemm_lean_kernel<MT, EPI, NORM, WARPS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_k_class(1, kern, dim3(a.splits, ctas_y, 1), dim3(WARPS * 32, 1, 1), smem, stream, a.splits, a);
+  const int cls = pdl_class_of(EPI);
+  a.pdl = pdl_enabled(cls) ? 1 : 0;
+  return launch_k_class(cls, kern, dim3(a.splits, ctas_y, 1), dim3(WARPS * 32, 1, 1), smem, stream, a.splits, a);
 }
 
 static size_t lean_smem(int mt, int warps, int k_per_cta, bool norm, int K) {
@@ -803,4 +867,35 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
     case EPI_F32: return dispatch_mt<EPI_F32>(a, ctas_y, stream);
     default: return FELLM_ERR_ARG;
   }
+}
+
+// The input product of a ShortConv mixer with the gated convolution behind it, for a decode step:
+// every row is one token of its own request.  W [3d, K]: rows in blocks of 16 channels, 16 B rows,
+// 16 C rows, 16 X rows (bias, if any, in the same order); y [M, d] = C * conv(B*X) in bfloat16;
+// state: this layer's slots, [Lc-1, d] float32 each, slot_stride floats apart, advanced by one
+// token; row_slot [M].  Takes M <= 16, K in 1024..1280 with K % 128 == 0 (four K slices of whole
+// chunks), d % 16 == 0, d <= 148*16; FELLM_ERR_SIZE otherwise (fellm_gemm_skinny_conv_takes asks).
+static bool conv_shape_ok(int M, int N, int K, int taps) {
+  return M >= 1 && M <= 16 && N % 48 == 0 && N / 48 <= 148 && K % (4 * KCHUNK) == 0 && K / 4 >= 8 * KCHUNK &&
+         K / 4 <= LEAN_CH * KCHUNK && taps >= 2 && taps <= SK_MAX_LC;
+}
+FELLM_API int fellm_gemm_skinny_conv_takes(int M, int N, int K, int taps) { return conv_shape_ok(M, N, K, taps) ? 1 : 0; }
+
+FELLM_API int fellm_gemm_skinny_conv(const void* x, const float* xf, const float* norm_w, float eps, const void* W,
+                                     const float* bias, const float* conv_w, const float* conv_bias, float* state,
+                                     long long slot_stride, const int* row_slot, int taps, void* y, int M, int N, int K,
+                                     int lda, int ldw, int ldo, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if ((!x && !xf) || !W || !y || !conv_w || !state || !row_slot || (xf && !norm_w)) return FELLM_ERR_ARG;
+  if (!conv_shape_ok(M, N, K, taps) || (ldw % 8) || (x && (lda % 8)) || (xf && (lda % 4)) || (xf && K > 4096)) return FELLM_ERR_SIZE;
+  SkinnyArgs a;
+  a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = y;
+  a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo;
+  a.splits = 1; a.warps_k = 4; a.log2_warps_k = 2; a.k_per_warp = K / 4; a.k_per_cta = K; a.xs_stride = x_stride(K);
+  a.n_tiles = N / SK_ROWS; a.tiles_per_warp = 1; a.chunks_per_warp = a.k_per_warp / KCHUNK; a.pdl = pdl_enabled(1) ? 1 : 0;
+  a.conv_w = conv_w; a.conv_bias = conv_bias; a.conv_state = state; a.row_slot = row_slot; a.conv_slot_stride = slot_stride;
+  a.conv_taps = taps;
+  const int ctas = N / 48;
+  if (M <= 8) return xf ? launch_lean<1, EPI_CONV, true, 12>(a, ctas, stream) : launch_lean<1, EPI_CONV, false, 12>(a, ctas, stream);
+  return xf ? launch_lean<2, EPI_CONV, true, 12>(a, ctas, stream) : launch_lean<2, EPI_CONV, false, 12>(a, ctas, stream);
 }

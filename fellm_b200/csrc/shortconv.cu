@@ -19,6 +19,13 @@
 #define MAX_LC 8
 #define BODY_ROWS 8
 
+// Column of (part p = 0 B / 1 C / 2 X, channel c) in a row of the input product's output: thirds
+// [B | C | X], or, `blocked`, blocks of 16 channels [B16 | C16 | X16] (the weight rows are then
+// ordered so that one CTA of the decode product holds B, C and X of its channels).
+__device__ __forceinline__ int sc_col(int p, int c, int d, int blocked) {
+  return blocked ? (c >> 4) * 48 + p * 16 + (c & 15) : p * d + c;
+}
+
 __device__ __forceinline__ void sc_unpack8(const uint4& v, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -30,13 +37,14 @@ __device__ __forceinline__ void sc_unpack8(const uint4& v, float* f) {
 // same order, as the scalar path.
 __device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __restrict__ w,
                                    const float* __restrict__ conv_bias, const int* __restrict__ item_start,
-                                   const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int Lc) {
+                                   const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int Lc, int blocked) {
   // the tile's threads (all blocks along x) are laid over [rows][groups of 8 channels]
   const int groups = d / 8, lin = blockIdx.x * blockDim.x + threadIdx.x;
   const int c0 = (lin % groups) * 8, row_in_tile = lin / groups;
   const int row_step = (gridDim.x * blockDim.x) / groups;   // >= 8: the grid has a thread per channel
   const int H = Lc - 1;
   const size_t ld = (size_t)3 * d;
+  const int cb = sc_col(0, c0, d, blocked), cc = sc_col(1, c0, d, blocked), cx = sc_col(2, c0, d, blocked);   // 8 channels stay in one block
   float wt[MAX_LC][8], bias[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
@@ -49,20 +57,20 @@ __device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __
     if (r >= T) break;
     int j = r - item_start[row_item[r]];
     if (j < H) continue;                         // head rows belong to the item's head thread
-    const bf16* row = bcx + (size_t)r * ld + c0;
+    const bf16* row = bcx + (size_t)r * ld;
     float b[8], x[8], cg[8], conv[8];
-    sc_unpack8(*(const uint4*)row, b);
-    sc_unpack8(*(const uint4*)(row + 2 * d), x);
-    sc_unpack8(*(const uint4*)(row + d), cg);
+    sc_unpack8(*(const uint4*)(row + cb), b);
+    sc_unpack8(*(const uint4*)(row + cx), x);
+    sc_unpack8(*(const uint4*)(row + cc), cg);
 #pragma unroll
     for (int e = 0; e < 8; ++e) conv[e] = (b[e] * x[e]) * w[(size_t)(c0 + e) * Lc + H];
 #pragma unroll
     for (int t = 0; t < MAX_LC - 1; ++t) {
       if (t < H) {
-        const bf16* pr = bcx + (size_t)(r - H + t) * ld + c0;
+        const bf16* pr = bcx + (size_t)(r - H + t) * ld;
         float pb[8], px[8];
-        sc_unpack8(*(const uint4*)pr, pb);
-        sc_unpack8(*(const uint4*)(pr + 2 * d), px);
+        sc_unpack8(*(const uint4*)(pr + cb), pb);
+        sc_unpack8(*(const uint4*)(pr + cx), px);
 #pragma unroll
         for (int e = 0; e < 8; ++e) conv[e] = fmaf(pb[e] * px[e], wt[t][e], conv[e]);
       }
@@ -82,13 +90,13 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
                                  const float* __restrict__ conv_bias, float* __restrict__ state,
                                  long long slot_stride, const int* __restrict__ item_slot,
                                  const int* __restrict__ item_start, const int* __restrict__ row_item,
-                                 TA* __restrict__ y, int T, int n_items, int d, int Lc, int n_body_tiles) {
+                                 TA* __restrict__ y, int T, int n_items, int d, int Lc, int n_body_tiles, int blocked) {
   FELLM_TRACE_SCOPE(TRACE_SHORTCONV);
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   if (VEC && (int)blockIdx.y < n_body_tiles) {
     pdl_wait(); FELLM_TRACE_WAITED();
-    shortconv_body_vec((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, Lc);
+    shortconv_body_vec((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, Lc, blocked);
     return;
   }
   if (c >= d) return;
@@ -100,6 +108,7 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
   float bias = conv_bias ? conv_bias[c] : 0.f;
   pdl_wait(); FELLM_TRACE_WAITED();
   const size_t ld = (size_t)3 * d;
+  const int cb = sc_col(0, c, d, blocked), cc = sc_col(1, c, d, blocked), cx = sc_col(2, c, d, blocked);
 
   if ((int)blockIdx.y < n_body_tiles) {
     int r0 = blockIdx.y * BODY_ROWS;
@@ -107,17 +116,17 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
       int j = r - item_start[row_item[r]];
       if (j < H) continue;                       // head rows belong to the item's head thread
       const TA* row = bcx + (size_t)r * ld;
-      float bx = to_f(row[c]) * to_f(row[2 * d + c]);
+      float bx = to_f(row[cb]) * to_f(row[cx]);
       float conv = bx * wlast;
 #pragma unroll
       for (int t = 0; t < MAX_LC - 1; ++t) {
         if (t < H) {
           const TA* pr = bcx + (size_t)(r - H + t) * ld;
-          float pbx = to_f(pr[c]) * to_f(pr[2 * d + c]);
+          float pbx = to_f(pr[cb]) * to_f(pr[cx]);
           conv = fmaf(pbx, wt[t], conv);
         }
       }
-      y[(size_t)r * d + c] = from_f<TA>(to_f(row[d + c]) * (conv + bias));
+      y[(size_t)r * d + c] = from_f<TA>(to_f(row[cc]) * (conv + bias));
     }
     return;
   }
@@ -132,12 +141,12 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
   int n_head = n < H ? n : H;
   for (int j = 0; j < n_head; ++j) {
     const TA* row = bcx + (size_t)(start + j) * ld;
-    float bx = to_f(row[c]) * to_f(row[2 * d + c]);
+    float bx = to_f(row[cb]) * to_f(row[cx]);
     float conv = bx * wlast;
 #pragma unroll
     for (int t = 0; t < MAX_LC - 1; ++t)
       if (t < H) conv = fmaf(hist[t], wt[t], conv);
-    y[(size_t)(start + j) * d + c] = from_f<TA>(to_f(row[d + c]) * (conv + bias));
+    y[(size_t)(start + j) * d + c] = from_f<TA>(to_f(row[cc]) * (conv + bias));
 #pragma unroll
     for (int t = 0; t < MAX_LC - 2; ++t) hist[t] = hist[t + 1];
     // append at index H-1 (the loop above shifted one too far for t >= H-1, fixed here)
@@ -150,7 +159,7 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
     for (int t = 0; t < MAX_LC - 1; ++t) {
       if (t < H) {
         const TA* pr = bcx + (size_t)(start + n - H + t) * ld;
-        hist[t] = to_f(pr[c]) * to_f(pr[2 * d + c]);
+        hist[t] = to_f(pr[cb]) * to_f(pr[cx]);
       }
     }
   }
@@ -159,13 +168,14 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
     if (t < H) st[(size_t)t * d + c] = hist[t];
 }
 
-// bcx [T, 3d] (B | C | X thirds), w [d, Lc] float32 (tap Lc-1 multiplies the current token),
+// bcx [T, 3d] (B | C | X thirds; or, blocked, [B16 | C16 | X16] per 16 channels), w [d, Lc] float32 (tap Lc-1 multiplies the current token),
 // conv_bias [d] or null, state: base of this layer's slots, slot_stride floats between slots.
 FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, const float* conv_bias,
                               float* state, long long slot_stride, const int* item_slot,
                               const int* item_start, const int* row_item, void* y, int T, int n_items,
-                              int d, int Lc, int all_single, cudaStream_t stream) {
+                              int d, int Lc, int all_single, int blocked, cudaStream_t stream) {
   if (T <= 0 || n_items <= 0) return 0;
+  if (blocked && (d % 16)) return FELLM_ERR_SIZE;
   if (Lc < 2 || Lc > MAX_LC) return FELLM_ERR_SIZE;
   if (!bcx || !w || !state || !y) return FELLM_ERR_ARG;
   int threads = d >= 128 ? 128 : 64;
@@ -173,10 +183,10 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   dim3 grid(ceil_div(d, threads), n_body + n_items);
   if (is_bf16 && d % 8 == 0 && n_body > 0)
     return launch_k_class(2, shortconv_kernel<bf16, true>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
-                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
+                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked);
   if (is_bf16)
     return launch_k_class(2, shortconv_kernel<bf16, false>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
-                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body);
+                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked);
   return launch_k_class(2, shortconv_kernel<float, false>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
-                  slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body);
+                  slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body, blocked);
 }

@@ -64,10 +64,7 @@ class Engine:
                                   device=self.device)
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
-                               device=self.device, cuda_graphs=options.cuda_graphs,
-                               mega_decode=options.mega_decode and options.dtype == "bfloat16")
-        if self.stepper.mega is not None:
-            jit.compile_many(self.stepper.mega.kernel_modules())
+                               device=self.device, cuda_graphs=options.cuda_graphs)
         self._sampler: Optional[Sampler] = None
         # sampled tokens (and the status word behind them) come back through a few pinned buffers in
         # turn: a launch may be in flight while the one before it is read

@@ -169,14 +169,8 @@ class Stepper:
     Index arrays and block tables live at fixed device addresses and are refreshed by copies before
     the replay."""
 
-    def __init__(self, model, cache, *, max_rows: int, max_items: int, device, cuda_graphs: bool = False,
-                 mega_decode: bool = False):
+    def __init__(self, model, cache, *, max_rows: int, max_items: int, device, cuda_graphs: bool = False):
         self.model, self.cache, self.device = model, cache, device
-        self.mega = None
-        if mega_decode:
-            from .mega import MegaDecoder
-            mega = MegaDecoder(model, cache, device)
-            self.mega = mega if mega.supported else None
         self.buffers = StepBuffers(max_rows, max_items, device)
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
@@ -309,9 +303,6 @@ class Stepper:
     def _run(self, ctx) -> torch.Tensor:
         from .. import ops
         views = self.cache.views(ctx.item_slot)
-        if self.mega is not None and self.mega.takes(ctx):
-            self.launches += 1
-            return self.mega.run(ctx, views)
         if not (self.cuda_graphs and ctx.all_single):
             before = ops.launch_count()
             logits = self.model.forward(ctx, views)

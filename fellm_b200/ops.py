@@ -155,10 +155,11 @@ def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
 MAX_CONV_TAPS = 8
 
 
-def shortconv(bcx, w, conv_bias, state, item_slot, item_start, row_item, n_items, all_single, out=None):
-    """bcx [T, 3d] (B | C | X), w float32 [d, Lc], state float32 [slots, Lc-1, d] (a view of one
-    layer's slots; slot stride may be larger than (Lc-1)*d).  Returns y [T, d] = C * conv(B*X) and
-    advances each item's state slot."""
+def shortconv(bcx, w, conv_bias, state, item_slot, item_start, row_item, n_items, all_single, out=None,
+              blocked=False):
+    """bcx [T, 3d] (B | C | X; blocked: [B16 | C16 | X16] per 16 channels, see block_bcx_rows), w
+    float32 [d, Lc], state float32 [slots, Lc-1, d] (a view of one layer's slots; slot stride may
+    be larger than (Lc-1)*d).  Returns y [T, d] = C * conv(B*X) and advances each item's state slot."""
     _dev(bcx, w, conv_bias, state, item_slot, item_start, row_item)
     T = bcx.shape[0]
     d, Lc = w.shape
@@ -173,10 +174,66 @@ def shortconv(bcx, w, conv_bias, state, item_slot, item_start, row_item, n_items
         out = torch.empty((T, d), dtype=bcx.dtype, device=bcx.device)
     f = _fn("shortconv", "fellm_shortconv",
             [_c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_p])
+             _c_int, _c_int, _c_p])
     _check(f(_p(bcx), _is_bf16(bcx), _p(w), _p(conv_bias), _p(state), state.stride(0), _p(item_slot),
-             _p(item_start), _p(row_item), _p(out), T, n_items, d, Lc, int(all_single), _stream()),
+             _p(item_start), _p(row_item), _p(out), T, n_items, d, Lc, int(all_single), int(blocked), _stream()),
            "shortconv")
+    return out
+
+
+def block_bcx_rows(w):
+    """Rows (or entries) [B | C | X] of a ShortConv input projection, d each, reordered into blocks
+    of 16 channels: 16 B rows, 16 C rows, 16 X rows.  d must be a multiple of 16."""
+    d = w.shape[0] // 3
+    assert w.shape[0] == 3 * d and d % 16 == 0
+    rest = w.shape[1:]
+    return w.reshape(3, d // 16, 16, *rest).transpose(0, 1).reshape(3 * d, *rest).contiguous()
+
+
+_conv_takes_cache = {}
+
+
+def conv_product_takes(M: int, N: int, K: int, taps: int) -> bool:
+    """Whether gemm_bf16_conv runs a product of these sizes (decode steps of up to 16 requests,
+    K of 1024..1280 in whole chunks)."""
+    key = (M, N, K, taps)
+    hit = _conv_takes_cache.get(key)
+    if hit is None:
+        f = _fn("gemm_skinny", "fellm_gemm_skinny_conv_takes", [_c_int, _c_int, _c_int, _c_int])
+        hit = _conv_takes_cache[key] = bool(f(M, N, K, taps))
+    return hit
+
+
+def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, norm=None, out=None):
+    """A decode step's ShortConv input product and gated convolution in one launch: every row of x
+    is one token of its own request (row_slot[i] = its state slot).  x bfloat16 [M, K], or with
+    norm=(weight, eps) the float32 residual rows to be RMS-normed on the way in; w_blocked [3d, K]
+    and bias in block_bcx_rows order.  Returns y bfloat16 [M, d]; the states move on by one token."""
+    _dev(x, w_blocked, bias, conv_w, conv_bias, state, row_slot)
+    M, K = x.shape
+    N = w_blocked.shape[0]
+    d, taps = conv_w.shape
+    assert N == 3 * d and w_blocked.dtype == torch.bfloat16 and w_blocked.stride(1) == 1 and x.stride(1) == 1
+    assert conv_w.dtype == torch.float32 and conv_w.is_contiguous()
+    assert state.dtype == torch.float32 and state.shape[1:] == (taps - 1, d) and state.stride(1) == d and state.stride(2) == 1
+    _i32(row_slot, "row_slot")
+    if out is None:
+        out = torch.empty((M, d), dtype=torch.bfloat16, device=x.device)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    f = _fn("gemm_skinny", "fellm_gemm_skinny_conv",
+            [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_p])
+    if norm is not None:
+        assert x.dtype == torch.float32 and norm[0].dtype == torch.float32
+        code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w_blocked), _p(bias), _p(conv_w), _p(conv_bias), _p(state),
+                 state.stride(0), _p(row_slot), taps, _p(out), M, N, K, x.stride(0), w_blocked.stride(0), out.stride(0),
+                 _stream())
+    else:
+        assert x.dtype == torch.bfloat16
+        code = f(_p(x), None, None, 0.0, _p(w_blocked), _p(bias), _p(conv_w), _p(conv_bias), _p(state),
+                 state.stride(0), _p(row_slot), taps, _p(out), M, N, K, x.stride(0), w_blocked.stride(0), out.stride(0),
+                 _stream())
+    _check(code, "gemm_skinny_conv")
     return out
 
 

@@ -6,10 +6,17 @@ here a request may bring a portion of any length, and the state after the portio
 state after the same tokens one by one."""
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from ..config.errors import ConfigError
 from .base import FixedState, Mixer, ParamDecl, register_part
-from .linear import linear, linear_modules
+from .linear import LazyNorm, linear, linear_modules
+
+
+import os
+
+FUSE_DECODE_CONV = os.environ.get("FELLM_B200_FUSE_CONV", "1") != "0"
 
 
 @register_part("mixer", "shortconv")
@@ -29,6 +36,19 @@ class ShortConv(Mixer):
                                "out_proj.bias": ParamDecl((d,), role="vector", init=("normal", 0.01))})
 
     takes_lazy_norm = True
+    blocked = False
+
+    def prepare(self):
+        """On the tensor-core path the input projection's rows are put in blocks of 16 channels (16
+        B rows, 16 C rows, 16 X rows), so that one CTA of a decode step's product holds B, C and X
+        of its channels and runs the convolution itself; the convolution kernel of the other steps
+        reads the same order."""
+        w = self.w["in_proj.weight"]
+        self.blocked = w.dtype == torch.bfloat16 and w.is_cuda and self.size % 16 == 0
+        if self.blocked:
+            self.w["in_proj.weight"] = ops.block_bcx_rows(w)
+            if "in_proj.bias" in self.w:
+                self.w["in_proj.bias"] = ops.block_bcx_rows(self.w["in_proj.bias"])
 
     def cache_need(self):
         return FixedState((self.taps - 1, self.size))
@@ -36,9 +56,19 @@ class ShortConv(Mixer):
     def forward(self, xn, ctx, cache, out, reads_only=False):
         if reads_only:
             raise ConfigError("a shortconv layer cannot run on another layer's state")
-        bcx = linear(xn, self.w["in_proj.weight"], self.w.get("in_proj.bias"))
-        y = ops.shortconv(bcx, self.w["conv.weight"], self.w.get("conv.bias"), cache.states,
-                          cache.item_slot, ctx.item_start, ctx.row_item, ctx.n_items, ctx.all_single)
+        w_in, b_in = self.w["in_proj.weight"], self.w.get("in_proj.bias")
+        if self.blocked and FUSE_DECODE_CONV and ctx.all_single and ops.conv_product_takes(ctx.n_rows, 3 * self.size, self.size, self.taps):
+            # a decode step: product and convolution in one launch
+            if isinstance(xn, LazyNorm) and xn.fusable_with(w_in):
+                x, norm = xn.x, (xn.norm.w["weight"], xn.norm.eps)
+            else:
+                x, norm = (xn.tensor() if isinstance(xn, LazyNorm) else xn), None
+            y = ops.gemm_bf16_conv(x, w_in, b_in, self.w["conv.weight"], self.w.get("conv.bias"), cache.states,
+                                   cache.item_slot, norm=norm)
+        else:
+            bcx = linear(xn, w_in, b_in)
+            y = ops.shortconv(bcx, self.w["conv.weight"], self.w.get("conv.bias"), cache.states, cache.item_slot,
+                              ctx.item_start, ctx.row_item, ctx.n_items, ctx.all_single, blocked=self.blocked)
         linear(y, self.w["out_proj.weight"], self.w.get("out_proj.bias"), out=out, accumulate=True)
         return out
 

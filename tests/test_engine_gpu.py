@@ -94,35 +94,37 @@ def test_step_refuses_what_it_cannot_place():
     eng.cache.audit()
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_fused_decode_step_equals_the_per_kernel_path(name):
-    """bfloat16 decode through the one-launch persistent kernel against the per-kernel path and
-    the plain implementation: several requests of different lengths decoded together, far enough
-    to cross pages."""
-    lens = [3, 17, 40]
-    n_dec = 45
-    toks = [tiny.tokens(name, n + n_dec, 70 + i) for i, n in enumerate(lens)]
-    outs = {}
-    for mode in ("fused", "kernels"):
-        eng = tiny.make_engine(name, "bfloat16", mega_decode=(mode == "fused"))
-        assert (eng.stepper.mega is not None) == (mode == "fused")
-        for i, n in enumerate(lens):
-            eng.add_request(i)
-            eng.step([StepItem(i, toks[i][:n], [])])
-        rows = []
-        for t in range(n_dec):
-            rows.append(eng.step([StepItem(i, [toks[i][lens[i] + t]], [0]) for i in range(len(lens))]).clone())
-        eng.check_status()
-        if mode == "fused":
-            assert eng.stepper.mega.launches == n_dec
-        outs[mode] = torch.stack(rows)                    # [n_dec, requests, vocab]
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decode_at_model_width_against_the_plain_implementation(graphs):
+    """A model of width 1024 with heads of 64 and pages of 64 tokens, bfloat16: the decode step then
+    runs the single-shot products, the convolution inside the input product and the TMA attention.
+    Several requests of different lengths decode together across a page's edge, directly and
+    replayed from a CUDA graph, against the plain implementation."""
+    lens = [3, 50, 61]
+    n_dec = 24
+    toks = [tiny.tokens("C", n + n_dec, 70 + i) for i, n in enumerate(lens)]
+    eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs)
     for i, n in enumerate(lens):
-        want = tiny.plain_logits(name, n + n_dec, 70 + i)[n:]
-        for mode in outs:
-            ok, err, tol = tiny.close(outs[mode][:, i], want, "bfloat16")
-            assert ok, (mode, i, err, tol)
-    ok, err, tol = tiny.close(outs["fused"].reshape(-1, outs["fused"].shape[-1]), outs["kernels"].reshape(-1, outs["kernels"].shape[-1]).cpu(), "bfloat16")
-    assert ok, (err, tol)
+        eng.add_request(i)
+        eng.step([StepItem(i, toks[i][:n], [])])
+    rows = []
+    for t in range(n_dec):
+        rows.append(eng.step([StepItem(i, [toks[i][lens[i] + t]], [0]) for i in range(len(lens))]).clone())
+    eng.check_status()
+    got = torch.stack(rows)                                 # [n_dec, requests, vocab]
+    if graphs:
+        assert len(eng.stepper.graphs) >= 1
+    for i, n in enumerate(lens):
+        want = tiny.plain_logits("C", n + n_dec, 70 + i)[n:]
+        ok, err, tol = tiny.close(got[:, i], want, "bfloat16")
+        assert ok, (i, err, tol)
+    # the same tokens fed as whole prompts give the same logits beyond rounding
+    eng2 = tiny.make_engine("C", "bfloat16", page_tokens=64)
+    for i, n in enumerate(lens):
+        eng2.add_request(i)
+        whole = eng2.step([StepItem(i, toks[i], list(range(n, n + n_dec)))])
+        ok, err, tol = tiny.close(got[:, i], whole, "bfloat16")
+        assert ok, (i, err, tol)
 
 
 def test_command_line_run_prints_tokens_and_timing_lines():

@@ -100,7 +100,8 @@ def conv_reference(bcx, w, bias, state):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("d,lc,use_bias", [(40, 2, False), (200, 3, True), (136, 5, False), (72, 8, True)])
+@pytest.mark.parametrize("d,lc,use_bias", [(40, 2, False), (200, 3, True), (136, 5, False), (72, 8, True), (1024, 3, False),
+                                           (144, 4, True)])
 def test_shortconv_portions_and_state(dtype, d, lc, use_bias):
     torch.manual_seed(d + lc)
     lens = [1, lc - 1, 1, 40, 2, 9]                       # shorter than the history, equal to it, longer
@@ -122,6 +123,13 @@ def test_shortconv_portions_and_state(dtype, d, lc, use_bias):
         assert torch.allclose(y[starts[i]:starts[i + 1]].float().cpu(), ref_y, **tol(dtype)), (i, n)
         assert torch.allclose(state[slots[i], 1].cpu(), ref_s, rtol=1e-6, atol=1e-6), (i, n)
     assert torch.equal(state[:, 0], before[:, 0]) and torch.equal(state[7], before[7])     # nothing else touched
+    if d % 16 == 0:
+        # the same columns in blocks of 16 channels (16 B, 16 C, 16 X): the same outputs and states, to the bit
+        st3 = before.clone()
+        bcx_blocked = ops.block_bcx_rows(bcx.t().contiguous()).t().contiguous()
+        y3 = ops.shortconv(bcx_blocked, w, bias, st3[:, 1], i32(slots), i32(starts), i32(row_item), len(lens), False,
+                           blocked=True)
+        assert torch.equal(y3, y) and torch.equal(st3, state)
     # portions one token at a time give bit-equal outputs and state (float32)
     if dtype == torch.float32:
         st2 = before.clone()
@@ -132,6 +140,39 @@ def test_shortconv_portions_and_state(dtype, d, lc, use_bias):
                 y2[r:r + 1] = ops.shortconv(bcx[r:r + 1].contiguous(), w, bias, st2[:, 1], i32([slots[i]]),
                                             i32([0, 1]), i32([0]), 1, True)
         assert torch.equal(y2, y) and torch.equal(st2, state)
+
+
+@pytest.mark.parametrize("M,d,K,lc,use_bias,use_norm", [(8, 1024, 1024, 3, False, True), (1, 1024, 1024, 3, True, True),
+                                                         (13, 2048, 1280, 4, True, False), (16, 48, 1152, 8, False, True),
+                                                         (5, 1024, 1024, 2, False, False)])
+def test_decode_conv_product_equals_product_then_convolution(M, d, K, lc, use_bias, use_norm):
+    """A decode step's ShortConv input product with the convolution in its epilogue: the same y and
+    the same states, to the bit, as the product and the convolution kernel one after the other."""
+    torch.manual_seed(M + d)
+    assert ops.conv_product_takes(M, 3 * d, K, lc) and not ops.conv_product_takes(17, 3 * d, K, lc)
+    assert not ops.conv_product_takes(M, 3 * d, 2048, lc)
+    w_in = ops.block_bcx_rows((torch.randn(3 * d, K, device=DEV) * 0.05).bfloat16())
+    b_in = ops.block_bcx_rows(torch.randn(3 * d, device=DEV)) if use_bias else None
+    conv_w = torch.randn(d, lc, device=DEV)
+    conv_b = torch.randn(d, device=DEV) if use_bias else None
+    state = torch.randn(20, 2, lc - 1, d, device=DEV)
+    slots = torch.randperm(20)[:M].tolist()
+    nw = torch.rand(K, device=DEV) + 0.5
+    x = torch.randn(M, K, device=DEV) * 2
+    if not use_norm:
+        x = x.bfloat16()
+    norm = (nw, 1e-5) if use_norm else None
+    st_a, st_b = state.clone(), state.clone()
+    for step in range(3):                                   # the state is carried from launch to launch
+        y = ops.gemm_bf16_conv(x, w_in, b_in, conv_w, conv_b, st_a[:, 1], i32(slots), norm=norm)
+        bcx = ops.gemm_bf16(x, w_in, b_in, norm=norm)
+        ref = ops.shortconv(bcx, conv_w, conv_b, st_b[:, 1], i32(slots), i32(list(range(M + 1))), i32(list(range(M))),
+                            M, True, blocked=True)
+        assert torch.equal(y, ref), (step, (y.float() - ref.float()).abs().max())
+        assert torch.equal(st_a, st_b), step
+        x = x * 0.9 + 0.1
+    untouched = [s for s in range(20) if s not in slots]
+    assert torch.equal(st_a[untouched], state[untouched]) and torch.equal(st_a[:, 0], state[:, 0])
 
 
 def test_shortconv_refuses_too_many_taps():

@@ -27,7 +27,17 @@ TINY_B = dict(
     tie_word_embeddings=False, max_position_embeddings=1024)
 SEED_B = 1
 
-CONFIGS = {"A": (TINY_A, SEED_A), "B": (TINY_B, SEED_B)}
+# Not tiny in width: the sizes at which the decode step takes its single-shot products, the
+# convolution in the input product's epilogue and the TMA decode attention (pages of 64 tokens).
+WIDE_C = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=384, hidden_size=1024, num_hidden_layers=3,
+    num_attention_heads=16, num_key_value_heads=8, head_dim=64,
+    layer_types=["conv", "full_attention", "conv"],
+    block_ff_dim=2048, block_auto_adjust_ff_dim=False, rope_theta=1000000.0, rope_pairing="split_half",
+    conv_L_cache=3, conv_bias=False, norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=512)
+SEED_C = 2
+
+CONFIGS = {"A": (TINY_A, SEED_A), "B": (TINY_B, SEED_B), "C": (WIDE_C, SEED_C)}
 _tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_tests_")
 
 
