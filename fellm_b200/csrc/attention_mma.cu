@@ -491,13 +491,53 @@ __device__ __forceinline__ void at_tma_load_2d(unsigned dst, const CUtensorMap* 
                ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
 
+// The step's own q, k, v taken straight from the QKV product's output [T, (H+2G)*64], so that the
+// per-head RMSNorm, the rotation and the write of k and v into the cache need no kernel of their
+// own (formulas: qk_rope_write.cu).  qkv null: q comes normed and rotated in AttnArgs::q.
+struct DecodeFuse {
+  const bf16* qkv; const float* q_w; const float* k_w; const float* inv_freq;
+  float eps; int pairing;
+};
+
+// One head of 64 elements by a warp, lane l holding elements 2l and 2l+1: RMSNorm (if w), rotation
+// by pos (if inv_freq) on pairs (2i, 2i+1) (pairing 0) or (i, i+32) (pairing 1).
+__device__ __forceinline__ float2 norm_rope_head64(const bf16* src, const float* w, float eps, const float* inv_freq,
+                                                   int pairing, int pos, int lane) {
+  float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(src + 2 * lane));
+  if (w) {
+    float ss = fmaf(v.x, v.x, v.y * v.y);
+    ss = warp_sum(ss);
+    const float sc = 1.0f / sqrtf(ss / 64.0f + eps);
+    v.x = (v.x * sc) * w[2 * lane];
+    v.y = (v.y * sc) * w[2 * lane + 1];
+  }
+  if (inv_freq) {
+    if (pairing == 0) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[lane], &sn, &cs);
+      const float x = v.x, y = v.y;
+      v.x = x * cs - y * sn; v.y = x * sn + y * cs;
+    } else {
+      const float ox = __shfl_xor_sync(0xffffffffu, v.x, 16), oy = __shfl_xor_sync(0xffffffffu, v.y, 16);
+      const int p0 = (2 * lane) & 31;
+      float s0, c0, s1, c1;
+      sincosf((float)pos * inv_freq[p0], &s0, &c0);
+      sincosf((float)pos * inv_freq[p0 + 1], &s1, &c1);
+      if (lane < 16) { v.x = v.x * c0 - ox * s0; v.y = v.y * c1 - oy * s1; }      // first of the pair: a*c - b*s
+      else { v.x = ox * s0 + v.x * c0; v.y = oy * s1 + v.y * c1; }                // second: a*s + b*c
+    }
+  }
+  return v;
+}
+
 __global__ void __launch_bounds__(DC_WARPS * 32)
-attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, int* status) {
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, DecodeFuse f, int* status) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bars[DC_WARPS * 2];
   __shared__ int sm_pages[DC_MAX_PAGES];
   __shared__ int sm_last;
+  __shared__ __align__(16) bf16 q_s[16 * HD];            // fused: the group's heads, normed and rotated
   const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // positions, slots and block tables are written by copies before the step's kernels, not by a
@@ -518,6 +558,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   if (threadIdx.x < DC_WARPS * 2) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   pdl_wait(); FELLM_TRACE_WAITED();
+  const bf16* qkv_row = f.qkv ? f.qkv + (size_t)t * (a.H + 2 * a.G) * HD : nullptr;
+  if (qkv_row) {
+    for (int i = warp; i < 16; i += DC_WARPS) {
+      float2 v = make_float2(0.f, 0.f);
+      if (i < R) v = norm_rope_head64(qkv_row + (size_t)(g * R + i) * HD, f.q_w, f.eps, f.inv_freq, f.pairing, pos, lane);
+      *(__nv_bfloat162*)(q_s + i * HD + 2 * lane) = __floats2bfloat162_rn(v.x, v.y);
+    }
+  }
   __syncthreads();
   const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
   float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
@@ -540,7 +588,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
     if (n_tiles > 1) request(1);
   }
   unsigned qf[KS][4];
-  load_q(qf, [&](int i) -> const bf16* { return i < R ? a.q + ((size_t)t * a.H + g * R + i) * HD : nullptr; }, lane);
+  load_q(qf, [&](int i) -> const bf16* {
+    if (i >= R) return nullptr;
+    return qkv_row ? q_s + i * HD : a.q + ((size_t)t * a.H + g * R + i) * HD;
+  }, lane);
   float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
   for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
@@ -554,6 +605,26 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
       break;
     }
     const int key0 = (pg0 + warp + (q >> 1) * DC_WARPS) * DT_PT + (q & 1) * DT_HALF;
+    if (qkv_row && s == s_hi && key0 <= pos && pos < key0 + DT_HALF) {
+      // fused: this tile holds the step's own position; its k (normed, rotated) and v go into the
+      // tile and into the cache page (no other CTA or warp reads this page's tile in this step)
+      const int lp = pos / DT_PT;
+      const int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
+      const float2 kv = norm_rope_head64(qkv_row + (size_t)(a.H + g) * HD, f.k_w, f.eps, f.inv_freq, f.pairing, pos, lane);
+      const __nv_bfloat162 kk = __floats2bfloat162_rn(kv.x, kv.y);
+      const __nv_bfloat162 vv = *(const __nv_bfloat162*)(qkv_row + (size_t)(a.H + a.G + g) * HD + 2 * lane);
+      const unsigned off = tile_off(pos - key0, (2 * lane) >> 3) + ((2 * lane) & 7) * 2;
+      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(st + off), "r"(*(const unsigned*)&kk) : "memory");
+      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(st + DT_TILE_B + off), "r"(*(const unsigned*)&vv) : "memory");
+      if (page >= 0) {
+        bf16* krow = const_cast<bf16*>(a.pool) + ((((size_t)page * a.layers_in_group + a.layer) * 2 * a.G + g) * DT_PT + (pos - lp * DT_PT)) * HD;
+        *(__nv_bfloat162*)(krow + 2 * lane) = kk;
+        *(__nv_bfloat162*)(krow + (size_t)a.G * DT_PT * HD + 2 * lane) = vv;
+      } else if (lane == 0 && status) {
+        atomicExch(status, 302);                          // no page mapped for the step's own position
+      }
+      __syncwarp();
+    }
     if (key0 < k1 && key0 + DT_HALF > k0) {              // else: a half page with no key of the range
       if (key0 + DT_HALF > k1) {
         // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
@@ -682,14 +753,19 @@ FELLM_API int fellm_attn_decode_mma(const void* q, const void* pool, const int* 
 // The same through the TMA kernel: head size 64, pages of 64 tokens, at most 16 heads per kv head
 // (FELLM_ERR_SIZE otherwise: the caller falls back to fellm_attn_decode_mma).  n_pages: pages of the
 // pool; status: device int32 set to 301 if a wait ran out.
+// qkv non-null: the QKV product's output [T, (H+2G)*64]; the kernel norms (q_w, k_w float32 [64] or null)
+// and rotates (inv_freq float32 [32] or null; pairing 0 adjacent / 1 split-half) q and k itself and
+// writes k and v into the cache; q is then not read.  status 302: a row's position has no page.
 FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n_pages, const int* block_table,
                                     int max_pages, const int* positions, const int* row_slot, void* out,
                                     float* scratch, int* counters, int T, int H, int G, int hd, int page_tokens,
                                     int layer, int layers_in_group, float scale, int window, int split_len,
-                                    int max_splits, int* status, cudaStream_t stream) {
+                                    int max_splits, int* status, const void* qkv, const float* q_w, const float* k_w,
+                                    float eps, const float* inv_freq, int pairing, cudaStream_t stream) {
 #if HD == 64
   if (T <= 0) return 0;
   AttnArgs a;
+  if (!q) q = qkv;
   int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
                     layers_in_group, scale, window);
   if (e) return e;
@@ -706,7 +782,9 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   auto kern = attention_decode_tma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
-  return launch_k(kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, map, a, status);
+  DecodeFuse f;
+  f.qkv = (const bf16*)qkv; f.q_w = q_w; f.k_w = k_w; f.inv_freq = inv_freq; f.eps = eps; f.pairing = pairing;
+  return launch_k(kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, map, a, f, status);
 #else
   return FELLM_ERR_SIZE;
 #endif

@@ -333,6 +333,8 @@ def check_umma_status(device):
         code = int(t.item())
         if code:
             t.zero_()
+            if code == 302:
+                raise KernelError("decode attention: a row's position has no cache page mapped")
             what = "the TMA decode attention" if code == 301 else "the tcgen05 product"
             raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
@@ -474,6 +476,7 @@ DECODE_TARGET_CTAS = 148 * 4
 
 
 USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
+FUSE_DECODE_ROPE = os.environ.get("FELLM_B200_FUSE_ROPE", "1") != "0"
 
 
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
@@ -499,23 +502,47 @@ def _mma_checks(q, pool, what):
     return T, H, G, hd, pool.shape[4]
 
 
-def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, window, max_len, out=None):
+def decode_fuses_rope(H: int, G: int, hd: int, page_tokens: int, pool) -> bool:
+    """Whether attention_decode can take the QKV product's output itself (fuse=...): the TMA kernel's sizes."""
+    return (USE_TMA_DECODE and FUSE_DECODE_ROPE and hd == 64 and page_tokens == 64 and G > 0 and H % G == 0
+            and H // G <= 16 and pool.numel() // hd < 2 ** 31)
+
+
+def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, window, max_len, out=None, fuse=None):
     """One query row per request (bfloat16): split-KV decode attention on tensor cores.
-    q [T, H, hd] -> [T, H*hd].  The kernel library is compiled for this head size."""
-    _dev(q, pool, block_table, positions, row_slot)
-    T, H, G, hd, page_tokens = _mma_checks(q, pool, "attention_decode")
+    q [T, H, hd] -> [T, H*hd].  The kernel library is compiled for this head size.
+    fuse=(qkv [T, (H+2G)*hd], q_w, k_w, eps, inv_freq, pairing) with q=None (see decode_fuses_rope):
+    the kernel norms and rotates q and k itself and writes k and v into the cache."""
+    if fuse is not None:
+        qkv = fuse[0]
+        G, hd, page_tokens = pool.shape[3], pool.shape[5], pool.shape[4]
+        T = qkv.shape[0]
+        H = qkv.shape[1] // hd - 2 * G
+        assert q is None and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and decode_fuses_rope(H, G, hd, page_tokens, pool)
+        _dev(qkv, pool, block_table, positions, row_slot, fuse[1], fuse[2], fuse[4])
+        assert pool.dtype == torch.bfloat16 and pool.is_contiguous()
+    else:
+        _dev(q, pool, block_table, positions, row_slot)
+        T, H, G, hd, page_tokens = _mma_checks(q, pool, "attention_decode")
     split_len, max_splits = decode_split(max_len, T, G)
-    scratch, counters = reserve_decode_scratch(q.device, T, H, G, hd, max_splits)
+    scratch, counters = reserve_decode_scratch(pool.device, T, H, G, hd, max_splits)
     if out is None:
-        out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
-    if USE_TMA_DECODE and hd == 64 and page_tokens == 64 and H // G <= 16 and pool.numel() // hd < 2 ** 31:
-        # pages of 64 tokens at head size 64: whole [64, 64] tiles by TMA
+        out = torch.empty((T, H * hd), dtype=torch.bfloat16, device=pool.device)
+    if fuse is not None or (USE_TMA_DECODE and hd == 64 and page_tokens == 64 and H // G <= 16 and pool.numel() // hd < 2 ** 31):
+        # pages of 64 tokens at head size 64: whole tiles by TMA
         f = _fn("attention_mma", "fellm_attn_decode_tma",
                 [_c_p, _c_p, ctypes.c_longlong, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
-                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p], defines={"HD": hd})
+                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_int,
+                 _c_p], defines={"HD": hd})
+        if fuse is not None:
+            qkv, q_w, k_w, eps, inv_freq, pairing = fuse
+            extra = (_p(qkv), _p(q_w), _p(k_w), float(eps), _p(inv_freq), PAIRINGS[pairing])
+        else:
+            extra = (None, None, None, 0.0, None, 0)
         _check(f(_p(q), _p(pool), pool.shape[0], _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
                  _p(out), _p(scratch), _p(counters), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
-                 int(window or 0), split_len, max_splits, _p(umma_status(q.device)), _stream()), "attention_decode (TMA)")
+                 int(window or 0), split_len, max_splits, _p(umma_status(pool.device)), *extra, _stream()),
+               "attention_decode (TMA)")
         return out
     f = _fn("attention_mma", "fellm_attn_decode_mma",
             [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,

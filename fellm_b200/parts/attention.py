@@ -62,6 +62,15 @@ class Attention(Mixer):
             raise ConfigError("attention: a layer built with shares_cache must run with cache_of, and only it")
         G = 0 if self.shares_cache else self.G
         qkv = linear(xn, self.w["qkv.weight"])
+        if (ctx.all_single and not self.shares_cache and qkv.dtype == torch.bfloat16
+                and ops.decode_fuses_rope(self.H, self.G, self.hd, cache.page_tokens, cache.pool)):
+            # a decode step: norm, rotation and the cache write happen inside the attention kernel
+            a = ops.attention_decode(None, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
+                                     self.scale, self.window, ctx.max_len,
+                                     fuse=(qkv, self.w.get("q_norm.weight"), self.w.get("k_norm.weight"), self.eps,
+                                           self.position.inv_freq, self.position.pairing))
+            linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
+            return out
         q = ops.qk_rope_write(qkv, self.w.get("q_norm.weight"), self.w.get("k_norm.weight"), self.eps,
                               self.position.inv_freq, self.position.pairing, ctx.positions, ctx.row_slot,
                               cache.block_table, cache.pool, cache.layer, cache.page_tokens, self.H, G,

@@ -399,6 +399,48 @@ def test_attention_decode_split_kv(H, G, hd, page_tokens, window):
     assert torch.equal(again.float().cpu().reshape(T, H, hd), got)
 
 
+@pytest.mark.parametrize("H,G,pairing,qk_norm,rope,window", [(16, 8, "split_half", True, True, None), (6, 2, "adjacent", True, True, None),
+                                                              (16, 1, "adjacent", False, True, 90), (4, 4, "split_half", True, False, None)])
+def test_attention_decode_takes_the_qkv_product_itself(H, G, pairing, qk_norm, rope, window):
+    """Head size 64, pages of 64 tokens: the decode kernel norms and rotates q and k and writes k and v
+    into the cache itself; against qk_rope_write followed by the same kernel, outputs and cache."""
+    hd, pt = 64, 64
+    torch.manual_seed(H * 7 + G)
+    lens = [1, 2, 33, 64, 65, 129, 700, 1500]                # the step's own position: first of a page, of a half, inside
+    T = len(lens)
+    n_pg = [-(-n // pt) for n in lens]
+    perm = torch.randperm(sum(n_pg), generator=torch.Generator().manual_seed(2)).tolist()
+    pool = torch.randn(sum(n_pg) + 1, 2, 2, G, pt, hd, device=DEV).bfloat16()
+    table = torch.full((T + 2, max(n_pg) + 1), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(lens):
+        for p in range(n_pg[r]):
+            table[r + 1, p] = perm[at] + 1; at += 1
+        last = int(table[r + 1, (n - 1) // pt])
+        pool[last, 1, :, :, (n - 1) % pt:] = float("nan")     # the step's own row and what lies behind it
+    qkv = torch.randn(T, (H + 2 * G) * hd, device=DEV).bfloat16()
+    qw, kw = (torch.rand(hd, device=DEV) + 0.5, torch.rand(hd, device=DEV) + 0.5) if qk_norm else (None, None)
+    inv = P.rope_inv_freq(10000.0, hd).to(DEV) if rope else None
+    pos, slots, tab = i32([n - 1 for n in lens]), i32(list(range(1, T + 1))), table.to(DEV)
+    assert ops.decode_fuses_rope(H, G, hd, pt, pool)
+    pool_a, pool_b = pool.clone(), pool.clone()
+    got = ops.attention_decode(None, pool_a, tab, pos, slots, 1, hd ** -0.5, window, max(lens),
+                               fuse=(qkv, qw, kw, 1e-6, inv, pairing))
+    ops.check_umma_status(DEV)
+    q = ops.qk_rope_write(qkv, qw, kw, 1e-6, inv, pairing, pos, slots, tab, pool_b, 1, pt, H, G, hd)
+    want = ops.attention_decode(q, pool_b, tab, pos, slots, 1, hd ** -0.5, window, max(lens))
+    assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2), (got.float() - want.float()).abs().max()
+    for r, n in enumerate(lens):
+        page, row = int(table[r + 1, (n - 1) // pt]), (n - 1) % pt
+        a, b = pool_a[page, 1, :, :, row].float(), pool_b[page, 1, :, :, row].float()
+        assert torch.equal(a[1], b[1]), r                                        # v: copied
+        assert torch.allclose(a[0], b[0], rtol=1e-2, atol=1e-2), (r, (a[0] - b[0]).abs().max())      # k: one bfloat16 rounding apart at most
+    keep = torch.ones_like(pool_a, dtype=torch.bool)
+    for r, n in enumerate(lens):
+        keep[int(table[r + 1, (n - 1) // pt]), 1, :, :, (n - 1) % pt] = False
+    assert torch.equal(torch.nan_to_num(pool_a[keep]), torch.nan_to_num(pool[keep]))       # nothing else written
+
+
 @pytest.mark.parametrize("far", [0, 63, 64, 1023, 1024, 2999])
 def test_attention_decode_finds_one_far_key(far):
     H, G, hd, pt, C = 16, 8, 64, 64, 3000
