@@ -404,6 +404,7 @@ __global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1) gemm_skinny_kerne
 // the same sums in the same order as gemm_skinny_kernel, in a third of the instructions (a warp's
 // serial instruction stream is what a product of a few microseconds waits for).
 #define LEAN_CH 10
+#define LEAN_TPW 8
 
 template <int OFF>
 __device__ __forceinline__ uint4 ldg_stream_at(const void* p) {
@@ -439,9 +440,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   const int wn = warp >> a.log2_warps_k, wk = warp & (a.warps_k - 1);
   const int k_cta = split * a.k_per_cta;
   const int n_chunks = a.chunks_per_warp;              // 8..LEAN_CH, the same for every warp
+  // the warp's slabs: tile, tile + tile_stride, ...: tiles_per_warp of them (some past the last slab)
   const int tile = blockIdx.y * (WARPS >> a.log2_warps_k) + wn;
-  const bool active = tile < a.n_tiles;
-  const int n0 = tile * SK_ROWS;
+  const int tile_stride = gridDim.y * (WARPS >> a.log2_warps_k);
+  const int tpw = a.tiles_per_warp;
   bf16* xs = (bf16*)smem;
   const int nv = a.K >> 2;
   float4* piece = (float4*)(smem + a.xf_offset) + (size_t)(warp < MP ? warp : 0) * nv;     // NORM: the float32 row of warp < MP
@@ -479,9 +481,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   }
   if (!a.pdl) request_x();
   uint4 w0[LEAN_CH], w1[LEAN_CH];
-  if (active) {
-    const int k0 = k_cta + wk * a.k_per_warp + c * 8;
-    const bf16* p0 = a.W + (size_t)(n0 + g) * a.ldw + k0;
+  const bf16* w_base = a.W + (size_t)g * a.ldw + k_cta + wk * a.k_per_warp + c * 8;
+  if (tile < a.n_tiles) {
+    const bf16* p0 = w_base + (size_t)tile * SK_ROWS * a.ldw;
     LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
   }
   pdl_launch_dependents();
@@ -541,12 +543,15 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   __syncthreads();
   FELLM_TRACE_MARK(0);
 
-  // ---- the warp's slice of its slab, four token tiles (32 rows of x) at a time
+  // ---- the warp's slice of each of its slabs, four token tiles (32 rows of x) at a time; the next
+  // slab's weights are asked for as soon as this one's are used up
   constexpr int TP = MT > 4 ? 4 : MT;
-  float* slots = (float*)(smem + (size_t)MP * a.xs_stride * sizeof(bf16));      // [warp][16][MP]
-  if (active) {
-    const bf16* xw = xs + (size_t)g * a.xs_stride + wk * a.k_per_warp + c * 8;
-    float* p = slots + (size_t)warp * SK_ROWS * MP;
+  float* slots = (float*)(smem + (size_t)MP * a.xs_stride * sizeof(bf16));      // [warp][slab of warp][16][MP]
+  const bf16* xw = xs + (size_t)g * a.xs_stride + wk * a.k_per_warp + c * 8;
+  for (int tl = 0; tl < tpw; ++tl) {
+    const int tile_l = tile + tl * tile_stride;
+    if (tile_l >= a.n_tiles) break;
+    float* p = slots + (size_t)(warp * tpw + tl) * SK_ROWS * MP;
 #pragma unroll
     for (int pass = 0; pass < MT / TP; ++pass) {
       float acc[TP][4];
@@ -571,16 +576,24 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
         *(float2*)(p + (g + 8) * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][2], acc[t][3]);
       }
     }
+    if (tl + 1 < tpw && tile_l + tile_stride < a.n_tiles) {
+      const bf16* p0 = w_base + (size_t)(tile_l + tile_stride) * SK_ROWS * a.ldw;
+      LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
+    }
   }
   FELLM_TRACE_MARK(1);
   if (a.splits > 1) cg::this_cluster().sync(); else __syncthreads();
   FELLM_TRACE_MARK(2);
 
   // ---- sum the partial slabs over the cluster's ranks and the CTA's K warps, in that order; every
-  // (rank, K warp) finishes a share of the slab's outputs
-  if (active) {
-    const int workers = a.splits << a.log2_warps_k, me = (split << a.log2_warps_k) + wk;
-    const float* mine = slots + (size_t)(wn << a.log2_warps_k) * SK_ROWS * MP;      // K warp 0 of this slab
+  // (rank, K warp) finishes a share of each slab's outputs
+  const int workers = a.splits << a.log2_warps_k, me = (split << a.log2_warps_k) + wk;
+  const int warp_stride = tpw * SK_ROWS * MP;
+  for (int tl = 0; tl < tpw; ++tl) {
+    const int tile_l = tile + tl * tile_stride;
+    if (tile_l >= a.n_tiles) break;
+    const int n0 = tile_l * SK_ROWS;
+    const float* mine = slots + (size_t)((wn << a.log2_warps_k) * tpw + tl) * SK_ROWS * MP;      // K warp 0 of this slab
     const int units = (EPI == EPI_SWIGLU ? 8 : SK_ROWS) * a.M;
     for (int i = me * 32 + lane; i < units; i += workers * 32) {
       int m, j;
@@ -601,8 +614,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
           if (idx < workers) {
             const int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
             const float* pp = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine_e, sr) : mine_e;
-            p0[q] = pp[w * (SK_ROWS * MP)];
-            if (EPI == EPI_SWIGLU) p1[q] = pp[w * (SK_ROWS * MP) + 8 * MP];
+            p0[q] = pp[w * warp_stride];
+            if (EPI == EPI_SWIGLU) p1[q] = pp[w * warp_stride + 8 * MP];
           }
         }
 #pragma unroll
@@ -692,7 +705,7 @@ static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
 
 template <int MT, int EPI, bool NORM, int WARPS>
 static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
-  size_t smem = (size_t)MT * 8 * x_stride(a.k_per_cta) * sizeof(bf16) + (size_t)WARPS * SK_ROWS * MT * 8 * sizeof(float);
+  size_t smem = (size_t)MT * 8 * x_stride(a.k_per_cta) * sizeof(bf16) + (size_t)WARPS * a.tiles_per_warp * SK_ROWS * MT * 8 * sizeof(float);
   a.gamma_offset = (int)smem;
   if (NORM) smem += (size_t)a.K * sizeof(float);
   a.xf_offset = (int)smem;
@@ -710,8 +723,8 @@ static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   return launch_k_class(cls, kern, dim3(a.splits, ctas_y, 1), dim3(WARPS * 32, 1, 1), smem, stream, a.splits, a);
 }
 
-static size_t lean_smem(int mt, int warps, int k_per_cta, bool norm, int K) {
-  size_t smem = (size_t)mt * 8 * x_stride(k_per_cta) * sizeof(bf16) + (size_t)warps * SK_ROWS * mt * 8 * sizeof(float);
+static size_t lean_smem(int mt, int warps, int k_per_cta, bool norm, int K, int tpw = 1) {
+  size_t smem = (size_t)mt * 8 * x_stride(k_per_cta) * sizeof(bf16) + (size_t)warps * tpw * SK_ROWS * mt * 8 * sizeof(float);
   if (norm) smem += (size_t)K * sizeof(float) + (size_t)(warps < mt * 8 ? warps : mt * 8) * K * sizeof(float);
   return smem;
 }
@@ -735,7 +748,7 @@ static int dispatch_lean(const SkinnyArgs& a, int ctas_y, int warps, cudaStream_
 // or of 16 warps (one to an SM); K slices go to the warps of a CTA as far as the CTA's part of x
 // fits shared memory, the rest over a cluster.  Among the shapes that run in one wave: fewest
 // cluster ranks, then most CTAs.
-struct LeanPlan { int warps, warps_k, splits, ctas_y, k_per_warp; };
+struct LeanPlan { int warps, warps_k, splits, ctas_y, k_per_warp, tiles_per_warp; };
 static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
   if (M > 64 || (norm && M > 16) || N % SK_ROWS) return false;
   const int in_flight = 2 * SK_U * KCHUNK;
@@ -751,16 +764,23 @@ static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
   for (int warps = 8; warps <= 16; warps *= 2) {
     int wk = slices < warps ? slices : warps;
     while (wk > 1 && lean_smem(mt, warps, kpw * wk, norm, K) > 200 * 1024) wk /= 2;
-    const size_t smem = lean_smem(mt, warps, kpw * wk, norm, K);
-    if (smem > 200 * 1024) continue;
-    const int sp = slices / wk, ct = ceil_div(n_tiles, warps / wk);
+    const int sp = slices / wk, warps_n = warps / wk;
     if (sp > 8 || (norm && (sp > 1 || K > 4096))) continue;
-    const int per_sm = (warps == 8 && smem <= 100 * 1024) ? 2 : 1;
-    if (ct * sp > 148 * per_sm) continue;
-    // order: fewest cluster ranks; then not two CTAs to an SM where one would do (x staged twice); then most CTAs
-    const int crowded = (per_sm == 2 && ct * sp > 148) ? 1 : 0;
-    const long long key = ((long long)sp << 40) | ((long long)crowded << 32) | (long long)(100000 - ct * sp);
-    if (!found || key < best_key) { best = LeanPlan{warps, wk, sp, ct, kpw}; best_key = key; found = true; }
+    // slabs a warp walks over: as few as let the CTAs run in one wave (a wide product of a larger
+    // model: up to LEAN_TPW, each slab's weights requested when the one before is used up)
+    for (int tpw = 1; tpw <= LEAN_TPW; ++tpw) {
+      const size_t smem = lean_smem(mt, warps, kpw * wk, norm, K, tpw);
+      if (smem > 200 * 1024) break;
+      const int ct = ceil_div(n_tiles, warps_n * tpw);
+      const int per_sm = (warps == 8 && smem <= 100 * 1024) ? 2 : 1;
+      if (ct * sp > 148 * per_sm) continue;
+      // order: fewest cluster ranks; fewest slabs a warp; not two CTAs to an SM where one would do
+      // (x staged twice); then most CTAs
+      const int crowded = (per_sm == 2 && ct * sp > 148) ? 1 : 0;
+      const long long key = ((long long)sp << 48) | ((long long)tpw << 40) | ((long long)crowded << 32) | (long long)(100000 - ct * sp);
+      if (!found || key < best_key) { best = LeanPlan{warps, wk, sp, ct, kpw, tpw}; best_key = key; found = true; }
+      break;
+    }
   }
   if (found) *out = best;
   return found;
@@ -806,7 +826,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   int slices = 1;
   while (slices < 64 && ceil_div(K, slices) > in_flight) slices *= 2;
   int warps_k = slices < SK_WARPS ? slices : SK_WARPS, splits = slices / warps_k;
-  bool plan_a = (long long)n_tiles * slices <= resident_warps + resident_warps / 4;
+  bool plan_a = (long long)n_tiles * slices <= (long long)resident_warps * 6;      // up to six slabs a warp, still cut over K
   int ctas_y = 1, tiles_per_warp = 1, k_per_cta = 0;
   static int cps = 0;
   if (!cps) { const char* e = getenv("FELLM_B200_SKINNY_CPS"); cps = (e && e[0] == '1') ? 1 : 2; }
@@ -848,7 +868,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   LeanPlan lp;
   if (plan_lean(M, N, K, xf != nullptr, &lp)) {
     a.splits = lp.splits; a.warps_k = lp.warps_k; a.k_per_warp = lp.k_per_warp; a.k_per_cta = lp.k_per_warp * lp.warps_k;
-    a.xs_stride = x_stride(a.k_per_cta); a.tiles_per_warp = 1;
+    a.xs_stride = x_stride(a.k_per_cta); a.tiles_per_warp = lp.tiles_per_warp;
     a.log2_warps_k = 0;
     while ((1 << a.log2_warps_k) < lp.warps_k) ++a.log2_warps_k;
     a.chunks_per_warp = a.k_per_warp / KCHUNK;

@@ -307,7 +307,9 @@ def _gemm_case(M, N, K, seed=0):
 
 # M <= 16 runs the weight-streaming kernel, 17..32 it or the tcgen05 product by width, larger M the tcgen05 product
 # (the decode-sized ones up to 16 rows take its single-shot form: a slab per warp, 8..10 chunks of K per warp)
-GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (13, 1024, 1024), (16, 2048, 2048), (9, 1536, 4608), (3, 515, 144), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
+# (wide products of a larger model: several slabs a warp, K = 8192 over a cluster of two)
+GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (13, 1024, 1024), (16, 2048, 2048), (9, 1536, 4608), (8, 6144, 2048),
+               (16, 2048, 8192), (40, 6144, 2048), (3, 515, 144), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
                (64, 2048, 200), (5, 65536, 64), (65, 144, 144), (128, 515, 320), (300, 1000, 1000), (2048, 256, 136)]
 
 
@@ -329,7 +331,7 @@ def test_gemm_bf16_store_acc_f32(M, N, K):
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
 def test_gemm_bf16_swiglu_epilogue(M, F, K):
     g = torch.Generator().manual_seed(F)
     x = torch.randn(M, K, generator=g).bfloat16()
@@ -456,7 +458,7 @@ def test_attention_decode_finds_one_far_key(far):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 1024), (8, 640, 144), (16, 200, 328), (3, 65536, 64), (8, 9216, 1024), (12, 3072, 1024),
-                                   (16, 4096, 2048), (5, 512, 1280), (7, 256, 4096)])
+                                   (16, 4096, 2048), (5, 512, 1280), (7, 256, 4096), (8, 6144, 2048)])
 def test_gemm_bf16_fused_rmsnorm_prologue(M, N, K):
     g = torch.Generator().manual_seed(N)
     x = torch.randn(M, K, generator=g) * 2
