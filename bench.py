@@ -131,11 +131,61 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     engine.check_status()
-    launches = engine.stepper.launches - l0 + (engine.stepper.steps_run - s0)       # + one sampling launch a step
+    launches = engine.stepper.launches - l0 + 2 * (engine.stepper.steps_run - s0)   # + the two argmax kernels a step
     mean_ctx = ctx0 + steps / 2
     for r in reqs:
         engine.release(r)
     return batch * steps / (ms / 1e3), ms / steps, launches, mean_ctx
+
+
+def run_timeline(engine, batch, context, out_path):
+    """One decode step's kernel timeline (FELLM_B200_TRACE=1): `batch` requests with `context` tokens
+    of random cache each (pages reserved, no prefill), a few steps so that the step's CUDA graph
+    exists, then one traced replay.  Writes a table of every launch and sums by kernel."""
+    import torch
+    from fellm_b200.engine import StepItem
+    from fellm_b200.engine.timeline import Timeline
+    reqs = [f"t{i}" for i in range(batch)]
+    for r in reqs:
+        engine.add_request(r)
+        engine.cache.reserve(r, context)
+        engine.cache.advance(r, context)
+    engine.cache.flush()
+    for g in engine.cache.paged:
+        g.pool.normal_(0, 1)
+    items = [StepItem(r, [5], [0]) for r in reqs]
+    for _ in range(4):
+        engine.step(items)
+    torch.cuda.synchronize()
+    graph = list(engine.stepper.graphs.values())[-1][0]
+    tl = Timeline()
+    for _ in range(3):
+        graph.replay()
+    tl.reset()
+    graph.replay()
+    launches = tl.launches()
+    tl.close()
+    total = launches[-1].end_us - launches[0].begin_us
+    agg, prev_end = {}, None
+    for l in launches:
+        a = agg.setdefault((l.name, l.blocks), [0, 0.0, 0.0, 0.0])
+        a[0] += 1
+        a[1] += l.end_us - l.waited_us
+        a[2] += l.waited_us - l.begin_us
+        if prev_end is not None:
+            a[3] += l.begin_us - prev_end
+        prev_end = l.end_us
+    lines = [f"batch {batch}, context {context}: {len(launches)} launches, {total:.1f} us from the first entry to the last exit",
+             "", "| kernel | CTAs | launches | run us (mean) | before its wait us (mean) | gap to the kernel before us (mean) | sum us |",
+             "|---|---|---|---|---|---|---|"]
+    for (name, blocks), a in sorted(agg.items(), key=lambda kv: -(kv[1][1] + kv[1][2] + kv[1][3])):
+        lines.append(f"| {name} | {blocks} | {a[0]} | {a[1] / a[0]:.2f} | {a[2] / a[0]:.2f} | {a[3] / a[0]:.2f} | {a[1] + a[2] + a[3]:.1f} |")
+    lines += ["", Timeline.table(launches), ""]
+    with open(out_path, "w") as f:
+        f.write("\n".join(lines))
+    for r in reqs:
+        engine.release(r)
+    return len(launches), total
 
 
 def run_e2e(engine, batch, steps, warmup, rng):
@@ -200,6 +250,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling a small case; not a bench value)")
+    ap.add_argument("--timeline", default=None, metavar="FILE",
+                    help="with FELLM_B200_TRACE=1: write the kernel timeline of one decode step (--batch requests, "
+                         "--context tokens each) to FILE and stop; not a bench value")
+    ap.add_argument("--context", type=int, default=PROMPT)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -231,6 +285,11 @@ def main():
     clocks = ClockSampler()
     clocks.start()
 
+    if args.timeline:
+        n, us = run_timeline(engine, args.batch, args.context, args.timeline)
+        print(json.dumps({"timeline": args.timeline, "batch": args.batch, "context": args.context, "launches": n, "us": round(us, 1)}))
+        clocks.stop()
+        return 0
     if args.only:
         if args.only == "decode":
             v, ms, _, _ = run_decode(engine, args.batch, steps, warmup, rng)
