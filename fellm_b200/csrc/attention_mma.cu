@@ -658,17 +658,136 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   decode_last_cta_merges(a, &sm_last, t, g, R, n_active);
 }
 
-// The cache pool as a 2-D tensor [rows of 64 dims]: the map is kept per (pool, rows).
+// ------------------------------------------------------------------------------------ prefill, TMA
+// The prefill kernel for head size 64, pages of 64 tokens and no window: a key tile IS a page, so
+// one thread brings K and V of a tile with two bulk tensor copies (three stages on mbarriers with
+// bounded waits) instead of 128 threads computing an address per 16 bytes, and tiles that every row
+// of a warp sees whole skip the masking.  Same sums in the same order as attention_prefill_kernel.
+#define PT_STAGES 3
+__global__ void __launch_bounds__(PF_WARPS * 32)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, int* status) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_PREFILL);
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[PT_STAGES];
+  __shared__ int sm_fail;
+  const int item = blockIdx.z, g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, c = lane & 3;
+  const int R = a.H / a.G;
+  const int tokb = max(1, (PF_WARPS * 16) / R);               // tokens per CTA
+  pdl_launch_dependents();
+  const int row_begin = a.item_start[item], n_rows = a.item_start[item + 1] - row_begin;
+  const int n_blocks = (n_rows + tokb - 1) / tokb;
+  if ((int)blockIdx.x >= (n_blocks + 1) / 2) return;
+  const int item_pos0 = a.positions[row_begin];
+  const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
+  if (threadIdx.x < PT_STAGES) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
+  if (threadIdx.x == 0) sm_fail = 0;
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  pdl_wait(); FELLM_TRACE_WAITED();
+  __syncthreads();
+  const unsigned s_base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  const unsigned bar0 = (unsigned)__cvta_generic_to_shared(&bars[0]);
+  constexpr int TILE_B = DT_PT * 128;                          // bytes of one K (or V) tile: a page
+  unsigned it_issue = 0, it_use = 0;                           // tiles requested / consumed so far, over both passes
+
+  // Causal work grows with the block's position: a CTA takes block bx and then its mirror
+  // n_blocks-1-bx, so that every CTA of an item has the same number of key tiles to go through.
+  for (int pass = 0; pass < 2; ++pass) {
+    const int blk = pass == 0 ? (int)blockIdx.x : n_blocks - 1 - (int)blockIdx.x;
+    if (pass == 1 && blk <= (int)blockIdx.x) break;
+    const int tok0 = blk * tokb;
+    const int n_tok = min(tokb, n_rows - tok0);
+    const int pos0 = item_pos0 + tok0;                         // position of the block's first token
+    int tok[2], hr[2], lo[2], hi[2];
+    bool valid[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      int rho = warp * 16 + gq + 8 * r;
+      tok[r] = rho / R; hr[r] = rho - tok[r] * R;
+      valid[r] = tok[r] < n_tok;
+      hi[r] = valid[r] ? pos0 + tok[r] : -1;
+      lo[r] = valid[r] ? 0 : 1 << 30;
+    }
+    unsigned qf[KS][4];
+    load_q(qf, [&](int i) -> const bf16* {
+      int rho = warp * 16 + i; int t = rho / R, h = rho - t * R;
+      return t < n_tok ? a.q + ((size_t)(row_begin + tok0 + t) * a.H + g * R + h) * HD : nullptr;
+    }, lane);
+    float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+    const int k_last = pos0 + n_tok - 1;
+    const int n_tiles = k_last / DT_PT + 1;                    // pages 0 .. that of the last token
+    auto issue = [&](int j) {                                  // thread 0: tile j of this pass = page j
+      const unsigned st = s_base + (it_issue % PT_STAGES) * 2 * TILE_B, bar = bar0 + (it_issue % PT_STAGES) * 8;
+      const int page = bt[j];
+      const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * DT_PT;      // < 2^31: the launcher checks
+      at_mbar_expect_tx(bar, 2 * TILE_B);
+      at_tma_load_2d(st, &pool_map, 0, row, bar);
+      at_tma_load_2d(st + TILE_B, &pool_map, 0, row + a.G * DT_PT, bar);
+      ++it_issue;
+    };
+    // every warp has left the stages of the pass before (the loop below ends on a barrier)
+    if (threadIdx.x == 0) {
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      for (int j = 0; j < PT_STAGES - 1 && j < n_tiles; ++j) issue(j);
+    }
+    // rows of this warp see a tile whole when it ends at or before the warp's first token
+    const bool warp_full = (warp * 16 + 15) < n_tok * R;
+    const int warp_first = pos0 + (warp * 16) / R, warp_hi = pos0 + min(n_tok - 1, (warp * 16 + 15) / R);
+    bool failed = false;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (threadIdx.x == 0 && j + PT_STAGES - 1 < n_tiles) {
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the reads of tile j-1 before the copy into its stage
+        issue(j + PT_STAGES - 1);
+      }
+      const unsigned st = s_base + (it_use % PT_STAGES) * 2 * TILE_B, bar = bar0 + (it_use % PT_STAGES) * 8;
+      if (!at_mbar_wait(bar, (it_use / PT_STAGES) & 1)) { sm_fail = 1; if (status) atomicExch(status, 301); }
+      ++it_use;
+      const int key0 = j * DT_PT;
+      if (key0 + DT_PT > k_last + 1) {
+        // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
+        for (int i = (k_last + 1 - key0) * CPR + threadIdx.x; i < DT_PT * CPR; i += PF_WARPS * 32)
+          st_shared_zero16(st + TILE_B + tile_off(i / CPR, i % CPR));
+        __syncthreads();
+      }
+      if (key0 <= warp_hi && warp * 16 < n_tok * R) {
+        if (warp_full && key0 + DT_PT - 1 <= warp_first)
+          attend_tile<DT_PT / 8, false>(qf, st, st + TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+        else
+          attend_tile<DT_PT / 8, true>(qf, st, st + TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      }
+      __syncthreads();                                         // the stage may be refilled; sm_fail is seen by all
+      if (sm_fail) { failed = true; break; }
+    }
+    if (failed) break;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      if (!valid[r]) continue;
+      float inv = 1.0f / l[r];
+      bf16* dst = a.out + ((size_t)(row_begin + tok0 + tok[r]) * a.H + g * R + hr[r]) * HD;
+#pragma unroll
+      for (int d = 0; d < DN; ++d)
+        *(unsigned*)(dst + d * 8 + 2 * c) = pack_bf16(o[d][2 * r] * inv, o[d][2 * r + 1] * inv);
+    }
+  }
+}
+
+// The cache pool as a 2-D tensor [rows of 64 dims]: the map is kept per (pool, rows, rows of a box).
 typedef CUresult (*AtEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static int pool_map_for(const void* pool, long long rows, CUtensorMap* out) {
+static int pool_map_for(const void* pool, long long rows, int box_rows, CUtensorMap* out) {
   static std::mutex mu;
-  static struct { const void* pool; long long rows; CUtensorMap map; } cache[8];
+  static struct { const void* pool; long long rows; int box_rows; CUtensorMap map; } cache[8];
   static int n_cached = 0, next = 0;
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < n_cached; ++i)
-    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return 0; }
+    if (cache[i].pool == pool && cache[i].rows == rows && cache[i].box_rows == box_rows) { *out = cache[i].map; return 0; }
   static AtEncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -679,14 +798,14 @@ static int pool_map_for(const void* pool, long long rows, CUtensorMap* out) {
   }
   cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-  cuuint32_t box[2] = {HD, DT_HALF};
+  cuuint32_t box[2] = {HD, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return 1000 + (int)r;
-  cache[next].pool = pool; cache[next].rows = rows; cache[next].map = m;
+  cache[next].pool = pool; cache[next].rows = rows; cache[next].box_rows = box_rows; cache[next].map = m;
   next = (next + 1) % 8;
   if (n_cached < 8) ++n_cached;
   *out = m;
@@ -784,7 +903,7 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
     return FELLM_ERR_SIZE;
   a.scratch = scratch; a.counters = counters; a.split_len = split_len; a.max_splits = max_splits;
   CUtensorMap map;
-  e = pool_map_for(pool, rows, &map);
+  e = pool_map_for(pool, rows, DT_HALF, &map);
   if (e) return e;
   size_t tiles = (size_t)DC_WARPS * 4 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
   size_t smem = (tiles > mrg ? tiles : mrg) + 1024;
@@ -799,6 +918,38 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   static int attn_class = -1;
   if (attn_class < 0) { const char* e = getenv("FELLM_B200_ATTN_PDL"); attn_class = (e && e[0] == '0') ? 0 : 1; }
   return launch_k_class(qkv ? attn_class : 0, kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, map, a, f, status);
+#else
+  return FELLM_ERR_SIZE;
+#endif
+}
+
+// The prefill kernel through TMA: head size 64, pages of 64 tokens, no window (FELLM_ERR_SIZE
+// otherwise: the caller falls back to fellm_attn_prefill_mma).  status: set to 301 if a wait ran out.
+FELLM_API int fellm_attn_prefill_tma(const void* q, const void* pool, long long n_pages, const int* block_table,
+                                     int max_pages, const int* positions, const int* row_slot, const int* item_start,
+                                     int n_items, int max_item_rows, void* out, int T, int H, int G, int hd,
+                                     int page_tokens, int layer, int layers_in_group, float scale, int window,
+                                     int* status, cudaStream_t stream) {
+#if HD == 64
+  if (T <= 0 || n_items <= 0) return 0;
+  AttnArgs a;
+  int e = fill_args(a, q, pool, block_table, max_pages, positions, row_slot, out, T, H, G, hd, page_tokens, layer,
+                    layers_in_group, scale, window);
+  if (e) return e;
+  if (!item_start) return FELLM_ERR_ARG;
+  const int R = H / G;
+  const long long rows = n_pages * layers_in_group * 2 * G * page_tokens;
+  if (R > PF_WARPS * 16 || page_tokens != DT_PT || window > 0 || rows >= (1ll << 31) || ((uintptr_t)pool & 15)) return FELLM_ERR_SIZE;
+  a.item_start = item_start; a.n_items = n_items;
+  int tokb = (PF_WARPS * 16) / R; if (tokb < 1) tokb = 1;
+  CUtensorMap map;
+  e = pool_map_for(pool, rows, DT_PT, &map);
+  if (e) return e;
+  size_t smem = (size_t)PT_STAGES * 2 * DT_PT * 128 + 1024;
+  auto kern = attention_prefill_tma_kernel;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (ce != cudaSuccess) return (int)ce;
+  return launch_k(kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, map, a, status);
 #else
   return FELLM_ERR_SIZE;
 #endif

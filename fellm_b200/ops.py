@@ -477,6 +477,7 @@ DECODE_TARGET_CTAS = 148 * 4
 
 USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
 FUSE_DECODE_ROPE = os.environ.get("FELLM_B200_FUSE_ROPE", "1") != "0"
+USE_TMA_PREFILL = os.environ.get("FELLM_B200_TMA_PREFILL", "1") != "0"
 
 
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
@@ -564,6 +565,15 @@ def attention_prefill(q, pool, block_table, positions, row_slot, item_start, n_i
     _i32(item_start, "item_start")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    if USE_TMA_PREFILL and hd == 64 and page_tokens == 64 and not window and pool.numel() // hd < 2 ** 31:
+        # a key tile is a page: K and V by bulk tensor copies
+        f = _fn("attention_mma", "fellm_attn_prefill_tma",
+                [_c_p, _c_p, ctypes.c_longlong, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int,
+                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p], defines={"HD": hd})
+        _check(f(_p(q), _p(pool), pool.shape[0], _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
+                 _p(item_start), n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
+                 float(scale), 0, _p(umma_status(q.device)), _stream()), "attention_prefill (TMA)")
+        return out
     f = _fn("attention_mma", "fellm_attn_prefill_mma",
             [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_f, _c_int, _c_p], defines={"HD": hd})

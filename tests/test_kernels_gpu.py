@@ -477,10 +477,13 @@ def test_gemm_bf16_fused_rmsnorm_prologue(M, N, K):
 
 @pytest.mark.parametrize("H,G,hd,page_tokens,window", [(16, 8, 64, 64, None), (6, 1, 48, 16, None), (4, 4, 128, 32, None),
                                                        (24, 8, 64, 16, None), (8, 1, 16, 16, 70), (5, 5, 80, 8, None),
-                                                       (2, 1, 256, 64, 300), (20, 1, 32, 16, None)])
+                                                       (2, 1, 256, 64, 300), (20, 1, 32, 16, None), (4, 4, 64, 64, None),
+                                                       (32, 1, 64, 64, None), (16, 8, 64, 64, 120)])
 def test_attention_prefill_mma(H, G, hd, page_tokens, window):
     """Items of mixed lengths in one launch (a portion that starts mid-sequence, a whole prompt, a
-    single decoded token, two tokens), pages out of order, against the plain attention."""
+    single decoded token, two tokens), pages out of order, NaN behind each item's last key in its
+    page, against the plain attention.  Head size 64 with pages of 64 tokens and no window takes
+    the TMA kernel."""
     torch.manual_seed(H * 3 + hd)
     ctx_before = [150, 0, 700, 33, 0]           # cached positions before this step's rows
     new = [97, 130, 1, 2, 64]                   # rows each item brings
@@ -500,6 +503,7 @@ def test_attention_prefill_mma(H, G, hd, page_tokens, window):
             lo, hi = p * page_tokens, min(total[r], (p + 1) * page_tokens)
             pool[page, 1, 0, :, :hi - lo] = k[lo:hi].transpose(0, 1).to(DEV)
             pool[page, 1, 1, :, :hi - lo] = v[lo:hi].transpose(0, 1).to(DEV)
+            pool[page, 1, :, :, hi - lo:] = float("nan")
     T = sum(new)
     q = torch.randn(T, H, hd).bfloat16()
     starts = [0]
