@@ -33,8 +33,10 @@ __device__ __forceinline__ void sc_unpack8(const uint4& v, float* f) {
 }
 
 // Body rows, bfloat16, d % 8 == 0: a thread takes 8 consecutive channels (16-byte loads) of a row;
-// the rows of a tile are independent of one another, so their loads overlap.  Same sums, in the
-// same order, as the scalar path.
+// the rows of a tile are independent of one another, so their loads overlap.  A row's data is asked
+// for before it is known whether the row is a body row (row -> item -> item start are two dependent
+// loads): rows before the batch's first are clamped, and a head row's result is dropped.  Same sums,
+// in the same order, as the scalar path.
 __device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __restrict__ w,
                                    const float* __restrict__ conv_bias, const int* __restrict__ item_start,
                                    const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int Lc, int blocked) {
@@ -45,36 +47,33 @@ __device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __
   const int H = Lc - 1;
   const size_t ld = (size_t)3 * d;
   const int cb = sc_col(0, c0, d, blocked), cc = sc_col(1, c0, d, blocked), cx = sc_col(2, c0, d, blocked);   // 8 channels stay in one block
-  float wt[MAX_LC][8], bias[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-#pragma unroll
-    for (int t = 0; t < MAX_LC; ++t) wt[t][e] = t < Lc ? w[(size_t)(c0 + e) * Lc + t] : 0.f;
-    bias[e] = conv_bias ? conv_bias[c0 + e] : 0.f;
-  }
+  const float* wc = w + (size_t)c0 * Lc;
   const int r0 = blockIdx.y * BODY_ROWS;
   for (int r = r0 + row_in_tile; r < r0 + BODY_ROWS; r += row_step) {
     if (r >= T) break;
-    int j = r - item_start[row_item[r]];
-    if (j < H) continue;                         // head rows belong to the item's head thread
+    const int item = row_item[r];
     const bf16* row = bcx + (size_t)r * ld;
-    float b[8], x[8], cg[8], conv[8];
-    sc_unpack8(*(const uint4*)(row + cb), b);
-    sc_unpack8(*(const uint4*)(row + cx), x);
-    sc_unpack8(*(const uint4*)(row + cc), cg);
+    const uint4 vb = *(const uint4*)(row + cb), vx = *(const uint4*)(row + cx), vc = *(const uint4*)(row + cc);
+    const int start = item_start[item];
+    float b[8], x[8], conv[8];
+    sc_unpack8(vb, b);
+    sc_unpack8(vx, x);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) conv[e] = (b[e] * x[e]) * w[(size_t)(c0 + e) * Lc + H];
+    for (int e = 0; e < 8; ++e) conv[e] = (b[e] * x[e]) * wc[e * Lc + H];
+    for (int t = 0; t < H; ++t) {
+      const int rp = r - H + t;
+      const bf16* pr = bcx + (size_t)(rp < 0 ? 0 : rp) * ld;
+      float pb[8], px[8];
+      sc_unpack8(*(const uint4*)(pr + cb), pb);
+      sc_unpack8(*(const uint4*)(pr + cx), px);
 #pragma unroll
-    for (int t = 0; t < MAX_LC - 1; ++t) {
-      if (t < H) {
-        const bf16* pr = bcx + (size_t)(r - H + t) * ld;
-        float pb[8], px[8];
-        sc_unpack8(*(const uint4*)(pr + cb), pb);
-        sc_unpack8(*(const uint4*)(pr + cx), px);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) conv[e] = fmaf(pb[e] * px[e], wt[t][e], conv[e]);
-      }
+      for (int e = 0; e < 8; ++e) conv[e] = fmaf(pb[e] * px[e], wc[e * Lc + t], conv[e]);
     }
+    if (r - start < H) continue;                 // head rows belong to the item's head thread
+    float cg[8], bias[8];
+    sc_unpack8(vc, cg);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) bias[e] = conv_bias ? conv_bias[c0 + e] : 0.f;
     uint4 o;
     __nv_bfloat162 p0 = __floats2bfloat162_rn(cg[0] * (conv[0] + bias[0]), cg[1] * (conv[1] + bias[1]));
     __nv_bfloat162 p1 = __floats2bfloat162_rn(cg[2] * (conv[2] + bias[2]), cg[3] * (conv[3] + bias[3]));

@@ -157,11 +157,15 @@ def _fill_decode(self, plan, wants, toks, lens) -> StepContext:
 StepBuffers.fill_decode = _fill_decode
 
 
+MAX_ROW_GRAPHS = 8          # captured graphs of steps that are not pure decode (each keeps its activations)
+
+
 class Stepper:
     """Owns the model, the cache manager and the step buffers; `step()` is the step function.
 
-    Steps in which every item brings one token (decode) are replayed from CUDA graphs when
-    `cuda_graphs` is on: FeLLM captures one decode step the same way
+    Steps are replayed from CUDA graphs when `cuda_graphs` is on (decode steps, and the shapes of
+    other steps that come again, e.g. prompts cut into equal portions: 121 direct launches of a
+    2,048-token portion cost the host as long as they cost the device): FeLLM captures one decode step the same way
     (crates/backend-cuda/src/graph.rs:39-160, crates/fellm-runtime/src/engine.rs:3195-3233).  A
     graph is keyed by the number of items, the number of wanted rows and the longest context
     rounded up to 1024 (the key-range split of decode attention follows it); the first step with a
@@ -178,6 +182,7 @@ class Stepper:
         self.graphs = {}
         self.graph_seen = {}
         self.graph_pool = None
+        self.row_graph_keys = []
         self.launches = 0                      # kernels of ours launched, replays included
         self._decode_plans = {}
 
@@ -303,15 +308,24 @@ class Stepper:
     def _run(self, ctx) -> torch.Tensor:
         from .. import ops
         views = self.cache.views(ctx.item_slot)
-        if not (self.cuda_graphs and ctx.all_single):
+        if not self.cuda_graphs:
             before = ops.launch_count()
             logits = self.model.forward(ctx, views)
             self.launches += ops.launch_count() - before
             return logits
-        key = (ctx.n_items, ctx.n_logit_rows, -(-ctx.max_len // 1024))
+        # what the launches of a step depend on besides the device arrays: the counts that size the
+        # grids and pick the kernels.  Decode steps: the longest context rounded up to 1024 (the
+        # key-range split of decode attention).  Other steps (portions of prompts, mixed batches)
+        # repeat their shape when prompts are cut into equal portions: a few of their graphs are kept.
+        if ctx.all_single:
+            key = (ctx.n_items, ctx.n_logit_rows, -(-ctx.max_len // 1024))
+        else:
+            key = ("rows", ctx.n_rows, ctx.n_items, ctx.n_logit_rows, ctx.max_item_rows, ctx.logits_all)
         entry = self.graphs.get(key)
         if entry is None:
             n_seen = self.graph_seen.get(key, 0)
+            if len(self.graph_seen) > 4096:                  # shapes seen once and never again
+                self.graph_seen = {k: v for k, v in self.graph_seen.items() if k in self.graphs}
             self.graph_seen[key] = n_seen + 1
             if n_seen == 0:
                 before = ops.launch_count()
@@ -326,6 +340,12 @@ class Stepper:
                 self.graph_pool = graph.pool()
             entry = (graph, logits, ops.launch_count() - before)
             self.graphs[key] = entry
+            if not ctx.all_single:
+                self.row_graph_keys.append(key)
+                if len(self.row_graph_keys) > MAX_ROW_GRAPHS:            # the oldest goes; its buffers return to the pool
+                    old = self.row_graph_keys.pop(0)
+                    self.graphs.pop(old, None)
+                    self.graph_seen.pop(old, None)
         graph, logits, n_launches = entry
         graph.replay()
         self.launches += n_launches

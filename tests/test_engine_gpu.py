@@ -127,6 +127,41 @@ def test_decode_at_model_width_against_the_plain_implementation(graphs):
         assert ok, (i, err, tol)
 
 
+@pytest.mark.parametrize("name,dtype", [("B", "bfloat16"), ("A", "float32"), ("C", "bfloat16")])
+def test_prompt_portions_of_a_shape_that_comes_again_are_replayed_from_a_graph(name, dtype):
+    """The same shape of step (one portion of 37 tokens, then one of 12 behind it, then both kinds
+    mixed with a decoding request) for several requests: the first goes directly, the second is
+    captured, the rest are replayed; every one against the plain implementation."""
+    pt = 64 if name == "C" else 16
+    eng = tiny.make_engine(name, dtype, cuda_graphs=True, page_tokens=pt)
+    n1, n2 = 37, 12
+    for i in range(5):
+        toks = tiny.tokens(name, n1 + n2, 40 + i)
+        want = tiny.plain_logits(name, n1 + n2, 40 + i)
+        eng.add_request(i)
+        a = eng.step([StepItem(i, toks[:n1], [0, n1 - 1])]).clone()
+        b = eng.step([StepItem(i, toks[n1:], list(range(n2)))]).clone()
+        eng.check_status()
+        for got, exp in ((a, want[[0, n1 - 1]]), (b, want[n1:])):
+            ok, err, tol = tiny.close(got, exp, dtype)
+            assert ok, (i, err, tol)
+        eng.release(i)
+    keys = [k for k in eng.stepper.graphs if k[0] == "rows"]
+    assert len(keys) == 2, keys
+    # more shapes than graphs are kept: the oldest are dropped, nothing breaks
+    from fellm_b200.engine import step as step_mod
+    for n in range(20, 20 + step_mod.MAX_ROW_GRAPHS + 3):
+        for rep in range(2):
+            toks = tiny.tokens(name, n, 90 + n)
+            eng.add_request("x")
+            got = eng.step([StepItem("x", toks, [n - 1])]).clone()
+            ok, err, tol = tiny.close(got, tiny.plain_logits(name, n, 90 + n)[[n - 1]], dtype)
+            assert ok, (n, rep, err, tol)
+            eng.release("x")
+    assert len([k for k in eng.stepper.graphs if k[0] == "rows"]) <= step_mod.MAX_ROW_GRAPHS
+    eng.cache.audit()
+
+
 def test_command_line_run_prints_tokens_and_timing_lines():
     import subprocess
     import sys
