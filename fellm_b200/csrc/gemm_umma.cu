@@ -102,8 +102,9 @@ struct UmmaArgs {
 };
 
 // One 32-column chunk of an output row: v[j] is C[m][n + j].
+// `res`: for EPI_ACC, the 32 values out already holds there, loaded while the MMAs ran (or null).
 template <int EPI>
-__device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, int n) {
+__device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, int n, const float4* res = nullptr) {
   if (EPI == EPI_SWIGLU) {
     // columns: 8 gate, 8 up, 8 gate, 8 up -> 16 features
     bf16* dst = (bf16*)a.out + (size_t)m * a.ldo + (n >> 1);
@@ -140,7 +141,7 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-      if (EPI == EPI_ACC) { float4 o = dst[j]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
+      if (EPI == EPI_ACC) { float4 o = res ? res[j] : dst[j]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
       dst[j] = r;
     }
   } else {
@@ -239,14 +240,30 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++use) {
       const unsigned acc = use & 1;
       const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * UM_BN;
+      const int m = m0 + q * 32 + lane;
+      // += residual: what out holds in this thread's two chunks is fetched while the MMAs of the
+      // tile still run (nothing else writes these elements during the launch)
+      constexpr int CHUNKS = UM_BN / 2 / 32;
+      float4 res[EPI == EPI_ACC ? CHUNKS : 1][8];
+      bool res_ok[CHUNKS];
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int n = n0 + half * (UM_BN / 2) + ch * 32;
+        res_ok[ch] = EPI == EPI_ACC && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
+        if (EPI == EPI_ACC && res_ok[ch]) {
+          const float4* src = (const float4*)((const float*)a.out + (size_t)m * a.ldo + n);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) res[ch][j] = src[j];
+        }
+      }
       if (!mbar_wait(accfull0 + 8 * acc, (use >> 1) & 1, a.status, 103)) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int m = m0 + q * 32 + lane;
-#pragma unroll 1
-      for (int c0 = half * (UM_BN / 2); c0 < (half + 1) * (UM_BN / 2); c0 += 32) {
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int c0 = half * (UM_BN / 2) + ch * 32;
         float v[32];
         tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * UM_BN + (unsigned)c0, v);      // whole warp, also for rows past M
-        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0);
+        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch] : nullptr);
       }
       // this warp has read its part of the accumulator: one of the eight arrivals that free it
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
