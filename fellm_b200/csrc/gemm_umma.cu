@@ -18,11 +18,9 @@
 #include "common.cuh"
 
 #define UM_BM 128
-#define UM_BN 128
 #define UM_BK 64                      // one 128-byte swizzle atom of bfloat16 per row
 #define UM_STAGES 5                   // 160 KB of stages in flight ahead of the MMA thread; one persistent CTA per SM
 #define UM_THREADS 320                // TMA warp, MMA warp, 8 epilogue warps
-#define UM_STAGE_BYTES ((UM_BM + UM_BN) * UM_BK * 2)
 #define UM_SPIN_LIMIT (1u << 26)
 #define UM_WAIT_NS 1000000000ull       // one second: far beyond any healthy wait, short enough to stay responsive
 
@@ -159,28 +157,30 @@ __device__ __forceinline__ void store_chunk(const UmmaArgs& a, float* v, int m, 
 // Persistent: a CTA walks over output tiles t = blockIdx.x, + gridDim.x, ... (tiles that follow one another share
 // their weight tile).  Two accumulators in tensor memory: while the epilogue warps read tile i out of one, the MMA
 // thread fills the other with tile i+1, and the TMA thread is already fetching operands further ahead.
-template <int EPI>
+template <int EPI, int BN>
 __global__ void __launch_bounds__(UM_THREADS)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
+  constexpr int STAGES = BN == 256 ? 4 : UM_STAGES;         // 48 KB or 32 KB a stage
+  constexpr int STAGE_BYTES = (UM_BM + BN) * UM_BK * 2;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[2 * UM_STAGES + 4];    // full[], empty[], acc_full[2], acc_empty[2]
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];    // full[], empty[], acc_full[2], acc_empty[2]
   __shared__ unsigned tmem_base_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the dynamic buffer is aligned by hand: swizzled TMA tiles want 1024 bytes
   unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[UM_STAGES]);
-  const unsigned accfull0 = smem_u32(&bars[2 * UM_STAGES]), accempty0 = smem_u32(&bars[2 * UM_STAGES + 2]);
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const unsigned accfull0 = smem_u32(&bars[2 * STAGES]), accempty0 = smem_u32(&bars[2 * STAGES + 2]);
   const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
-  const int m_tiles = (a.M + UM_BM - 1) / UM_BM, n_tiles = (a.N + UM_BN - 1) / UM_BN, total = m_tiles * n_tiles;
+  const int m_tiles = (a.M + UM_BM - 1) / UM_BM, n_tiles = (a.N + BN - 1) / BN, total = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < UM_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(accfull0 + 8 * b, 1); mbar_init(accempty0 + 8 * b, 8); }   // 8 epilogue warps
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 1) {                   // tensor memory: two 128x128 float32 accumulators = 256 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * UM_BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -195,12 +195,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       unsigned it = 0;               // k-blocks issued so far, over all tiles: stage = it % STAGES
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * UM_BN;
+        const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          int s = it % UM_STAGES;
-          if (it >= UM_STAGES && !mbar_wait(empty0 + 8 * s, (it / UM_STAGES - 1) & 1, a.status, 101)) { ok = false; break; }
-          unsigned dst = tiles + s * UM_STAGE_BYTES;
-          mbar_expect_tx(full0 + 8 * s, UM_STAGE_BYTES);
+          int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(empty0 + 8 * s, (it / STAGES - 1) & 1, a.status, 101)) { ok = false; break; }
+          unsigned dst = tiles + s * STAGE_BYTES;
+          mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
           tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
           tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
         }
@@ -208,22 +208,22 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const unsigned idesc = umma_idesc(UM_BM, UM_BN);
+      const unsigned idesc = umma_idesc(UM_BM, BN);
       unsigned it = 0, use = 0;      // use: tiles done so far; accumulator = use & 1
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++use) {
-        const unsigned acc = use & 1, d_tmem = tmem_base + acc * UM_BN;
+        const unsigned acc = use & 1, d_tmem = tmem_base + acc * BN;
         if (use >= 2) {              // the epilogue must have drained this accumulator's previous tile
           ok = mbar_wait(accempty0 + 8 * acc, ((use >> 1) - 1) & 1, a.status, 104);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          int s = it % UM_STAGES;
-          ok = mbar_wait(full0 + 8 * s, (it / UM_STAGES) & 1, a.status, 102);
+          int s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, a.status, 102);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-          unsigned sa = tiles + s * UM_STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
+          unsigned sa = tiles + s * STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
           unsigned long long da = umma_desc(sa), db = umma_desc(sb);
 #pragma unroll
           for (int k = 0; k < UM_BK / 16; ++k)          // 32 bytes further along K inside the swizzle atom
@@ -239,17 +239,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     unsigned use = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++use) {
       const unsigned acc = use & 1;
-      const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * UM_BN;
+      const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * BN;
       const int m = m0 + q * 32 + lane;
       // += residual: what out holds in this thread's two chunks is fetched while the MMAs of the
       // tile still run (nothing else writes these elements during the launch)
-      constexpr int CHUNKS = UM_BN / 2 / 32;
-      float4 res[EPI == EPI_ACC ? CHUNKS : 1][8];
+      constexpr int CHUNKS = BN / 2 / 32;
+      constexpr int PRE = CHUNKS < 2 ? CHUNKS : 2;               // chunks fetched ahead (64 registers)
+      float4 res[EPI == EPI_ACC ? PRE : 1][8];
       bool res_ok[CHUNKS];
 #pragma unroll
       for (int ch = 0; ch < CHUNKS; ++ch) {
-        const int n = n0 + half * (UM_BN / 2) + ch * 32;
-        res_ok[ch] = EPI == EPI_ACC && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
+        const int n = n0 + half * (BN / 2) + ch * 32;
+        res_ok[ch] = EPI == EPI_ACC && ch < PRE && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
         if (EPI == EPI_ACC && res_ok[ch]) {
           const float4* src = (const float4*)((const float*)a.out + (size_t)m * a.ldo + n);
 #pragma unroll
@@ -260,10 +261,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
       for (int ch = 0; ch < CHUNKS; ++ch) {
-        const int c0 = half * (UM_BN / 2) + ch * 32;
+        const int c0 = half * (BN / 2) + ch * 32;
         float v[32];
-        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * UM_BN + (unsigned)c0, v);      // whole warp, also for rows past M
-        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch] : nullptr);
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * BN + (unsigned)c0, v);      // whole warp, also for rows past M
+        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch < PRE ? ch : 0] : nullptr);
       }
       // this warp has read its part of the accumulator: one of the eight arrivals that free it
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -276,7 +277,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * UM_BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -294,13 +295,13 @@ static EncodeTiledFn encode_fn() {
   }
   return fn;
 }
-// rows x K bfloat16, row stride ld elements; box = 64 k x 128 rows, 128-byte swizzle, zeros outside
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld) {
+// rows x K bfloat16, row stride ld elements; box = 64 k x box_rows rows, 128-byte swizzle, zeros outside
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return FELLM_ERR_ARG;
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {UM_BK, UM_BM};
+  cuuint32_t box[2] = {UM_BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -308,10 +309,10 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld)
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-template <int EPI>
+template <int EPI, int BN>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, cudaStream_t stream) {
-  size_t smem = (size_t)UM_STAGES * UM_STAGE_BYTES + 1024;
-  auto kern = gemm_umma_kernel<EPI>;
+  size_t smem = (size_t)(BN == 256 ? 4 : UM_STAGES) * (UM_BM + BN) * UM_BK * 2 + 1024;
+  auto kern = gemm_umma_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   static int n_sm = 0;
@@ -320,7 +321,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& 
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
   }
-  int total = ceil_div(a.N, UM_BN) * ceil_div(a.M, UM_BM);
+  int total = ceil_div(a.N, BN) * ceil_div(a.M, UM_BM);
   return launch_k(kern, dim3(total < n_sm ? total : n_sm, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
 }
 
@@ -332,17 +333,23 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
   // TMA: 16-byte aligned bases and row strides
   if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
   if (epi == EPI_SWIGLU && ((N % 16) || (ldo % 8))) return FELLM_ERR_SIZE;
+  // 128 x 256 tiles (a quarter fewer operand bytes a FLOP) where they fill the SMs as well as 128 x 128 ones
+  const int m_tiles = ceil_div(M, UM_BM);
+  const int waves128 = ceil_div(ceil_div(N, 128) * m_tiles, 148), waves256 = ceil_div(ceil_div(N, 256) * m_tiles, 148);
+  static int wide_ok = -1;
+  if (wide_ok < 0) { const char* ev = getenv("FELLM_B200_UMMA_WIDE"); wide_ok = (ev && ev[0] == '0') ? 0 : 1; }
+  const bool wide = wide_ok && N >= 512 && 2 * waves256 <= waves128;
   CUtensorMap ma, mw;
-  int e = make_map(&ma, A, M, K, lda);
+  int e = make_map(&ma, A, M, K, lda, UM_BM);
   if (e) return e;
-  e = make_map(&mw, W, N, K, ldw);
+  e = make_map(&mw, W, N, K, ldw, wide ? 256 : 128);
   if (e) return e;
   UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
   switch (epi) {
-    case EPI_STORE: return launch<EPI_STORE>(ma, mw, a, stream);
-    case EPI_ACC: return launch<EPI_ACC>(ma, mw, a, stream);
-    case EPI_SWIGLU: return launch<EPI_SWIGLU>(ma, mw, a, stream);
-    case EPI_F32: return launch<EPI_F32>(ma, mw, a, stream);
+    case EPI_STORE: return wide ? launch<EPI_STORE, 256>(ma, mw, a, stream) : launch<EPI_STORE, 128>(ma, mw, a, stream);
+    case EPI_ACC: return wide ? launch<EPI_ACC, 256>(ma, mw, a, stream) : launch<EPI_ACC, 128>(ma, mw, a, stream);
+    case EPI_SWIGLU: return wide ? launch<EPI_SWIGLU, 256>(ma, mw, a, stream) : launch<EPI_SWIGLU, 128>(ma, mw, a, stream);
+    case EPI_F32: return wide ? launch<EPI_F32, 256>(ma, mw, a, stream) : launch<EPI_F32, 128>(ma, mw, a, stream);
     default: return FELLM_ERR_ARG;
   }
 }

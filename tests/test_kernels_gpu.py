@@ -307,9 +307,10 @@ def _gemm_case(M, N, K, seed=0):
 
 # M <= 16 runs the weight-streaming kernel, 17..32 it or the tcgen05 product by width, larger M the tcgen05 product
 # (the decode-sized ones up to 16 rows take its single-shot form: a slab per warp, 8..10 chunks of K per warp)
-# (wide products of a larger model: several slabs a warp, K = 8192 over a cluster of two)
+# (wide products of a larger model: several slabs a warp, K = 8192 over a cluster of two; many rows and a wide N:
+# the tcgen05 product in 128 x 256 tiles, also with a ragged last tile)
 GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (13, 1024, 1024), (16, 2048, 2048), (9, 1536, 4608), (8, 6144, 2048),
-               (16, 2048, 8192), (40, 6144, 2048), (3, 515, 144), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
+               (16, 2048, 8192), (40, 6144, 2048), (3, 515, 144), (2048, 2048, 1024), (2048, 2000, 136), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
                (64, 2048, 200), (5, 65536, 64), (65, 144, 144), (128, 515, 320), (300, 1000, 1000), (2048, 256, 136)]
 
 
@@ -331,7 +332,7 @@ def test_gemm_bf16_store_acc_f32(M, N, K):
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (2048, 4608, 1024), (1900, 1000, 200), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
 def test_gemm_bf16_swiglu_epilogue(M, F, K):
     g = torch.Generator().manual_seed(F)
     x = torch.randn(M, K, generator=g).bfloat16()
