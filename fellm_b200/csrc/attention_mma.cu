@@ -170,7 +170,7 @@ struct AttnArgs {
 
 __device__ __forceinline__ const bf16* key_row(const AttnArgs& a, const int* bt, int g, int key) {
   int lp = key / a.page_tokens;
-  int page = bt[lp];
+  int page = max(bt[lp], 0);                 // an unmapped entry (-1) must never become an address: page 0 is read instead
   return a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * ((size_t)a.page_tokens * HD)
          + (size_t)(key - lp * a.page_tokens) * HD;
 }
@@ -403,7 +403,7 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
         int key = key0 + row;
         if (key < k1) {
           int lp = key / a.page_tokens;
-          int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
+          int page = max(pages_in_smem ? sm_pages[lp - pg0] : bt[lp], 0);      // never an address below the pool
           const bf16* kp = a.pool + ((((size_t)page * a.layers_in_group + a.layer) * 2) * a.G + g) * page_elems
                            + (size_t)(key - lp * a.page_tokens) * HD + ch * 8;
           cp_async16(ks + tile_off(row, ch), kp);

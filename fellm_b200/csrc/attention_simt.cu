@@ -45,7 +45,7 @@ paged_attention_simt_kernel(const TA* __restrict__ q, const TC* __restrict__ poo
     float s = -INFINITY;
     const TC* vrow = nullptr;
     if (kj <= pos) {
-      int page = bt[kj / page_tokens];
+      int page = max(bt[kj / page_tokens], 0);      // an unmapped entry (-1) must never become an address
       size_t base = ((((size_t)page * layers_in_group + layer) * 2) * G + g) * page_tokens + (kj % page_tokens);
       const TC* krow = pool + base * hd;
       vrow = pool + (base + (size_t)G * page_tokens) * hd;

@@ -121,7 +121,7 @@ def _fill_decode(self, plan, wants, toks, lens) -> StepContext:
     o_tok, o_pos, o_ri, o_rs = 0, n, 2 * n, 3 * n
     o_is, o_slot, o_len, o_lr = 4 * n, 5 * n + 1, 6 * n + 1, 7 * n + 1
     total = o_lr + W
-    sig = (id(plan), wants)
+    sig = (plan["serial"], wants)
     if plan["ring"][k] != sig or self.ring_sig[k] != sig:
         h[o_ri:o_ri + n] = plan["arange"][:n]
         h[o_rs:o_rs + n] = plan["slots"]
@@ -185,6 +185,7 @@ class Stepper:
         self.row_graph_keys = []
         self.launches = 0                      # kernels of ours launched, replays included
         self._decode_plans = {}
+        self._plan_serial = 0
 
     def step(self, items: List[StepItem], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs exactly the given tokens as one batch and returns float32 logits
@@ -260,21 +261,24 @@ class Stepper:
         None when the general path has to look at the step (unknown request, page or context
         limits, windows to trim)."""
         cache = self.cache
-        key = tuple(it.req for it in items)
-        plan = self._decode_plans.get(key)
+        reqs = tuple(it.req for it in items)
         n = len(items)
-        lens_d = cache.req_len
+        lens_d, slot_d = cache.req_len, cache.req_slot
         try:
-            lens = np.fromiter((lens_d[r] for r in key), dtype=np.int64, count=n)
+            lens = np.fromiter((lens_d[r] for r in reqs), dtype=np.int64, count=n)
+            # a request's name may come again later in another slot: the slots are part of the key
+            key = (reqs, tuple(slot_d[r] for r in reqs))
         except KeyError:
             return None
+        plan = self._decode_plans.get(key)
         if plan is None:
-            if len(set(key)) != n:
+            if len(set(reqs)) != n:
                 return None
             if len(self._decode_plans) > 64:
                 self._decode_plans.clear()
-            slots = np.array([cache.slot(r) for r in key], dtype=np.int64)
-            plan = {"slots": slots, "arange": np.arange(n + 1), "ring": [None] * len(self.buffers.ring)}
+            self._plan_serial += 1                         # never reused, unlike id(): names what a staging buffer holds
+            plan = {"slots": np.array(key[1], dtype=np.int64), "arange": np.arange(n + 1),
+                    "ring": [None] * len(self.buffers.ring), "serial": self._plan_serial}
             self._decode_plans[key] = plan
         wants = tuple(bool(it.want) for it in items)
         if int(lens.max()) + 1 > cache.n_ctx:
@@ -289,10 +293,10 @@ class Stepper:
             toks = None
         pt = cache.page_tokens
         if (lens % pt == 0).any():                          # somebody starts a page
-            asks = [(r, 1) for r in key]
+            asks = [(r, 1) for r in reqs]
             if not cache.can_reserve(asks):
                 raise CacheError("out of cache pages for this step")
-            for r, l in zip(key, lens):
+            for r, l in zip(reqs, lens):
                 if l % pt == 0:
                     cache.reserve(r, 1)
         ctx = self.buffers.fill_decode(plan, wants, toks, lens)
@@ -300,7 +304,7 @@ class Stepper:
             ctx.tokens.copy_(device_tokens[:n])
         cache.flush()
         logits = self._run(ctx)
-        for r in key:
+        for r in reqs:
             lens_d[r] += 1
         self.steps_run += 1
         return logits

@@ -65,6 +65,33 @@ def test_greedy_generation_through_the_entry_point(name, dtype):
     assert eng.cache.free_pages() == eng.cache.n_pages
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_scheduler_one_step_ahead_gives_the_same_tokens_and_drops_what_follows_a_stop(graphs):
+    """Batched generation with the scheduler running one step ahead (tokens fed back on the device)
+    against the same with every step read before the next is launched: same tokens, same reasons;
+    a stop token ends its request although the step after it has already run."""
+    from fellm_b200.engine.scheduler import Scheduler
+    name = "B"
+    prompts = [tiny.tokens(name, n, 80 + i) for i, n in enumerate((9, 21, 14))]
+    eng = tiny.make_engine(name, "float32", cuda_graphs=graphs)
+    plain_sched = Scheduler(eng, eng.options.n_batch, eng.options.n_ubatch, lookahead=False)
+    eng._scheduler = plain_sched
+    want, _ = eng.generate_batch(prompts, GenParams.greedy(20))
+    assert plain_sched.counters["ran_ahead"] == 0
+    eng._scheduler = Scheduler(eng, eng.options.n_batch, eng.options.n_ubatch, lookahead=True)
+    got, stats = eng.generate_batch(prompts, GenParams.greedy(20))
+    assert got == want and eng._scheduler.counters["ran_ahead"] > 10
+    # stop at each request's 6th token
+    stops = [GenParams.greedy(20, stop_token_ids=(w[5],)) for w in want]
+    got2, stats2 = eng.generate_batch(prompts, stops)
+    for g, w, st in zip(got2, want, stats2):
+        cut = w.index(w[5]) + 1
+        assert g == w[:cut] and st.finish_reason == "stop" and st.predicted_tokens == cut
+    assert eng._scheduler.counters["dropped"] >= 1
+    eng.cache.audit()
+    assert eng.cache.free_pages() == eng.cache.n_pages
+
+
 def test_scheduler_preempts_on_a_small_pool_and_tokens_stay():
     name = "B"
     prompts = [tiny.tokens(name, n, 60 + i) for i, n in enumerate((40, 33, 25, 47))]
@@ -78,6 +105,36 @@ def test_scheduler_preempts_on_a_small_pool_and_tokens_stay():
     assert all(s.finish_reason == "length" and s.predicted_tokens == 24 for s in stats)
     small.cache.audit()
     assert small.cache.free_pages() == small.cache.n_pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_request_name_that_comes_again_in_another_slot(dtype):
+    """Requests a, b, c decode together, are released, and the same names come again in other slots
+    (the slot list is last in, first out): the decode step must follow the slots, not the names."""
+    name = "A"
+    eng = tiny.make_engine(name, dtype)
+    lens = {"a": 5, "b": 19, "c": 11}
+    for round_ in range(2):
+        order = ["a", "b", "c"] if round_ == 0 else ["c", "a", "b"]
+        for r in order:
+            eng.add_request(r)
+        slots = {r: eng.cache.slot(r) for r in lens}
+        toks = {r: tiny.tokens(name, n + 4, 30 + i + 10 * round_) for i, (r, n) in enumerate(lens.items())}
+        for r, n in lens.items():
+            eng.step([StepItem(r, toks[r][:n], [])])
+        for t in range(4):
+            got = eng.step([StepItem(r, [toks[r][lens[r] + t]], [0]) for r in ("a", "b", "c")])
+            for i, (r, n) in enumerate(lens.items()):
+                want = tiny.plain_logits(name, n + 4, 30 + i + 10 * round_)[n + t]
+                ok, err, tol = tiny.close(got[i], want, dtype)
+                assert ok, (round_, r, t, err, tol)
+        eng.check_status()
+        if round_ == 0:
+            first_slots = slots
+        else:
+            assert slots != first_slots                   # the names did move
+        for r in ("a", "b", "c"):
+            eng.release(r)
 
 
 def test_step_refuses_what_it_cannot_place():
