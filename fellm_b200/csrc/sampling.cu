@@ -359,15 +359,6 @@ __global__ void count_tokens_kernel(int* __restrict__ counts, int V, const int* 
   if (i < n && tokens[i] >= 0 && tokens[i] < V) atomicAdd(&counts[(size_t)slots[i] * V + tokens[i]], 1);
 }
 
-FELLM_API int fellm_sample(const float* logits, int rows, int V, const void* params, int* counts,
-                           const int* bias_tok, const float* bias_val, int* out_tokens, float* out_probs,
-                           int update_counts, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  if (!logits || !params || !out_tokens || V < 1) return FELLM_ERR_ARG;
-  return launch_k(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1, logits, V, (const RowParams*)params,
-                  counts, bias_tok, bias_val, out_tokens, out_probs, update_counts);
-}
-
 FELLM_API int fellm_count_tokens(int* counts, int V, const int* slots, const int* tokens, int n,
                                  cudaStream_t stream) {
   if (n <= 0) return 0;
@@ -438,3 +429,421 @@ FELLM_API int fellm_argmax_rows(const float* logits, int rows, int V, float* pva
 }
 
 FELLM_API int fellm_sample_params_size() { return (int)sizeof(RowParams); }
+
+// ------------------------------------------------------------------------------------------------
+// The same sampler with a CLUSTER of eight CTAs per row.  One block per row leaves a row of 65,536
+// logits to one SM: a dozen passes over the row cost 0.35 ms, as much as the whole decode step
+// before it.  Here every CTA keeps an eighth of the row in shared memory (penalties, bias and
+// temperature applied once), histograms and sums are combined over the cluster through
+// distributed shared memory in rank order (so every CTA computes the same numbers, and the same
+// numbers every run), and the draw walks only the one warp that holds the target.
+// Same cuts, same tie rule (lower id first), same fixed-point weights as sample_kernel above.
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+#define SC_CL 8
+#define SC_THREADS 512
+#define SC_WARPS (SC_THREADS / 32)
+
+struct CShared {
+  u64 hist[2][256];              // this CTA's histogram of the pass, two in turn
+  u64 ghist[256];                // the cluster's
+  float xf[2]; u64 xu[2][2]; int xi[2];          // this CTA's share of a cluster-wide reduction, two in turn
+  float wf[SC_WARPS]; u64 wu[SC_WARPS][2]; int wi[SC_WARPS];
+  u64 warp_ties[SC_WARPS], warp_w[SC_WARPS];
+  unsigned prefix; int found; u64 remaining, bin_total;
+  float bf; u64 bu[2]; int bi;
+};
+
+struct ClCtx {
+  CShared* s; int pp; int rank;
+};
+
+__device__ __forceinline__ u64 shfl_down_u64(u64 v, int d) {
+  unsigned lo = __shfl_down_sync(0xffffffffu, (unsigned)v, d), hi = __shfl_down_sync(0xffffffffu, (unsigned)(v >> 32), d);
+  return ((u64)hi << 32) | lo;
+}
+__device__ __forceinline__ u64 shfl_xor_u64(u64 v, int d) {
+  unsigned lo = __shfl_xor_sync(0xffffffffu, (unsigned)v, d), hi = __shfl_xor_sync(0xffffffffu, (unsigned)(v >> 32), d);
+  return ((u64)hi << 32) | lo;
+}
+__device__ __forceinline__ u64 warp_sum_u64(u64 v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += shfl_xor_u64(v, o);
+  return v;
+}
+
+// Cluster-wide maximum / ordered sum / minimum: every thread of every CTA of the cluster calls these.
+__device__ float cl_max(ClCtx& c, float v) {
+  CShared* s = c.s;
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) s->wf[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = -INFINITY;
+    for (int w = 0; w < SC_WARPS; ++w) t = fmaxf(t, s->wf[w]);
+    s->xf[c.pp] = t;
+  }
+  cg::this_cluster().sync();
+  if (threadIdx.x == 0) {
+    float t = -INFINITY;
+    for (int r = 0; r < SC_CL; ++r) t = fmaxf(t, *cg::this_cluster().map_shared_rank(&s->xf[c.pp], r));
+    s->bf = t;
+  }
+  __syncthreads();
+  c.pp ^= 1;
+  return s->bf;
+}
+__device__ float cl_sum(ClCtx& c, float v) {
+  CShared* s = c.s;
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) s->wf[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < SC_WARPS; ++w) t += s->wf[w];
+    s->xf[c.pp] = t;
+  }
+  cg::this_cluster().sync();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int r = 0; r < SC_CL; ++r) t += *cg::this_cluster().map_shared_rank(&s->xf[c.pp], r);
+    s->bf = t;
+  }
+  __syncthreads();
+  c.pp ^= 1;
+  return s->bf;
+}
+__device__ int cl_min_int(ClCtx& c, int v) {
+  CShared* s = c.s;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) s->wi[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0x7fffffff;
+    for (int w = 0; w < SC_WARPS; ++w) t = min(t, s->wi[w]);
+    s->xi[c.pp] = t;
+  }
+  cg::this_cluster().sync();
+  if (threadIdx.x == 0) {
+    int t = 0x7fffffff;
+    for (int r = 0; r < SC_CL; ++r) t = min(t, *cg::this_cluster().map_shared_rank(&s->xi[c.pp], r));
+    s->bi = t;
+  }
+  __syncthreads();
+  c.pp ^= 1;
+  return s->bi;
+}
+// Per-warp u64 values (already in s->warp_ties / s->warp_w style arrays `mine`): returns the sum of
+// all warps of the CTAs before this one (*before) and of the whole cluster (*total).
+__device__ void cl_prefix_u64(ClCtx& c, const u64* mine, u64* before, u64* total) {
+  CShared* s = c.s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    u64 t = 0;
+    for (int w = 0; w < SC_WARPS; ++w) t += mine[w];
+    s->xu[c.pp][0] = t;
+  }
+  cg::this_cluster().sync();
+  if (threadIdx.x == 0) {
+    u64 b = 0, t = 0;
+    for (int r = 0; r < SC_CL; ++r) {
+      u64 x = *cg::this_cluster().map_shared_rank(&s->xu[c.pp][0], r);
+      if (r < c.rank) b += x;
+      t += x;
+    }
+    s->bu[0] = b; s->bu[1] = t;
+  }
+  __syncthreads();
+  c.pp ^= 1;
+  *before = s->bu[0]; *total = s->bu[1];
+}
+
+// One histogram entry from every lane of a warp (all 32 call it).  When the whole warp hits one bin
+// (the top bytes of a row of logits are nearly all the same) one lane adds the warp's sum.
+__device__ __forceinline__ void hist_add(u64* hist, unsigned bin, u64 w, bool active) {
+  const unsigned am = __ballot_sync(0xffffffffu, active);
+  if (am == 0xffffffffu) {
+    const unsigned b0 = __shfl_sync(0xffffffffu, bin, 0);
+    if (__all_sync(0xffffffffu, bin == b0)) {
+      const u64 t = warp_sum_u64(w);
+      if ((threadIdx.x & 31) == 0) atomicAdd(&hist[b0], t);
+      return;
+    }
+  }
+  if (active) atomicAdd(&hist[bin], w);
+}
+
+// The cut whose kept weight first reaches `target` (see radix_cut), over the cluster's row.
+// vals: this CTA's slice in shared memory (n_local of them); the warp walks [w0, w1).
+__device__ Cut radix_cut_cl(ClCtx& c, const float* vals, int w0, int w1, u64 target, const Weigher& wg, Cut outer,
+                            float minp_thr, const Weigher& pg) {
+  CShared* s = c.s;
+  const int lane = threadIdx.x & 31;
+  unsigned prefix = 0;
+  u64 remaining = target, bin_total = 0;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    u64* hist = s->hist[c.pp];
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      const int i = i0 + lane;
+      bool active = i < w1;
+      float x = active ? vals[i] : 0.f;
+      unsigned k = key_of(x);
+      active = active && k > outer.kt && !(minp_thr > 0.f && pg.prob(x) < minp_thr) &&
+               (pass == 0 || (k >> (shift + 8)) == (prefix >> (shift + 8)));
+      hist_add(hist, (k >> shift) & 255, active ? wg.w(x) : 0ull, active);
+    }
+    if (c.rank == 0 && threadIdx.x == 0 && outer.q > 0) {          // the ties of the outer cut, once
+      unsigned k = outer.kt;
+      float x = val_of(k);
+      bool ok = !(minp_thr > 0.f && pg.prob(x) < minp_thr);
+      if (ok && (pass == 0 || (k >> (shift + 8)) == (prefix >> (shift + 8)))) atomicAdd(&hist[(k >> shift) & 255], outer.q * wg.w(x));
+    }
+    __syncthreads();
+    cg::this_cluster().sync();
+    if (threadIdx.x < 256) {
+      u64 t = 0;
+      for (int r = 0; r < SC_CL; ++r) t += *cg::this_cluster().map_shared_rank(&hist[threadIdx.x], r);
+      s->ghist[threadIdx.x] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      // lane l holds bins 8l .. 8l+7; from the top bin down, the first bin at which the running sum reaches `remaining`
+      u64 tl = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tl += s->ghist[8 * lane + j];
+      u64 incl = tl;                                               // sum over lanes >= this one
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) { u64 t = shfl_down_u64(incl, d); if (lane + d < 32) incl += t; }
+      const unsigned crossing = __ballot_sync(0xffffffffu, incl >= remaining);
+      if (crossing == 0) {
+        if (lane == 0) s->found = 0;
+      } else {
+        const int l = 31 - __clz(crossing);
+        if (lane == l) {
+          u64 cum = incl - tl;
+          int d = 8 * lane + 7;
+          for (; d > 8 * lane; --d) {
+            u64 h = s->ghist[d];
+            if (cum + h >= remaining) break;
+            cum += h;
+          }
+          s->found = 1; s->remaining = remaining - cum; s->prefix = prefix | ((unsigned)d << shift); s->bin_total = s->ghist[d];
+        }
+      }
+    }
+    __syncthreads();
+    const int found = s->found;
+    if (found) { remaining = s->remaining; prefix = s->prefix; bin_total = s->bin_total; }
+    c.pp ^= 1;
+    __syncthreads();
+    if (!found) return outer;
+  }
+  Cut cut;
+  cut.kt = prefix;
+  u64 wt = wg.w(val_of(cut.kt));
+  if (wt == 0) wt = 1;
+  u64 n_ties = bin_total / wt;
+  cut.q = (remaining + wt - 1) / wt;
+  if (cut.q > n_ties) cut.q = n_ties;
+  if (cut.kt == outer.kt && cut.q > outer.q) cut.q = outer.q;
+  return cut;
+}
+
+__global__ void __cluster_dims__(SC_CL, 1, 1) __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int V, int slice, const RowParams* __restrict__ params,
+                      int* __restrict__ counts, const int* __restrict__ bias_tok, const float* __restrict__ bias_val,
+                      int* __restrict__ out_tokens, float* __restrict__ out_probs, int update_counts) {
+  FELLM_TRACE_SCOPE(TRACE_SAMPLE);
+  extern __shared__ __align__(16) float vals[];          // this CTA's slice: adjusted logits (/ temperature)
+  __shared__ CShared s;
+  ClCtx c; c.s = &s; c.pp = 0; c.rank = (int)cg::this_cluster().block_rank();
+  const int row = blockIdx.x / SC_CL;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_launch_dependents();
+  pdl_wait(); FELLM_TRACE_WAITED();
+  const RowParams p = params[row];
+  Row r;
+  r.logits = logits + (size_t)row * V;
+  const bool pen = counts && ((p.rep_pen > 1.0f && isfinite(p.rep_pen)) || p.freq_pen != 0.f || p.pres_pen != 0.f);
+  int* my_counts = counts ? counts + (size_t)p.slot * V : nullptr;
+  r.counts = pen ? my_counts : nullptr;
+  r.bias_tok = bias_tok; r.bias_val = bias_val; r.bias_begin = p.bias_begin; r.bias_end = p.bias_end;
+  r.rep_pen = p.rep_pen; r.freq_pen = p.freq_pen; r.pres_pen = p.pres_pen; r.V = V;
+  float* probs = out_probs ? out_probs + (size_t)row * V : nullptr;
+  const bool greedy = p.temperature <= 0.f || p.top_k == 1;
+  r.inv_temp = greedy ? 1.0f : 1.0f / fmaxf(p.temperature, 1.1920929e-07f);
+
+  // ids of this CTA: [v0, v0 + n_local); warp w walks the local range [w0, w1), lane-strided
+  const int v0 = c.rank * slice, n_local = max(0, min(V, v0 + slice) - v0);
+  for (int i = threadIdx.x; i < n_local; i += SC_THREADS) vals[i] = r.adjusted(v0 + i) * r.inv_temp;
+  __syncthreads();
+  const int per_warp = (slice + SC_WARPS - 1) / SC_WARPS;
+  const int w0 = min(n_local, warp * per_warp), w1 = min(n_local, w0 + per_warp);
+
+  if (greedy) {
+    // first maximum of the adjusted logits (sampling.rs:588-604)
+    float best = -INFINITY;
+    for (int i = w0 + lane; i < w1; i += 32) best = fmaxf(best, vals[i]);
+    const float m = cl_max(c, best);
+    int bi = 0x7fffffff;
+    for (int i = w0 + lane; i < w1; i += 32) if (vals[i] == m) bi = min(bi, v0 + i);
+    int tok = cl_min_int(c, bi);
+    if (!(m > -INFINITY) || tok == 0x7fffffff) tok = 0;  // all -inf / NaN: token 0, as the reference's loop
+    if (c.rank == 0 && threadIdx.x == 0) {
+      out_tokens[row] = tok;
+      if (update_counts && my_counts) my_counts[tok] += 1;
+    }
+    if (probs) for (int i = threadIdx.x; i < n_local; i += SC_THREADS) probs[v0 + i] = (v0 + i) == tok ? 1.f : 0.f;
+    cg::this_cluster().sync();                           // nobody leaves while its shared memory may be read
+    return;
+  }
+
+  // top-k cut
+  Cut all; all.kt = 0u; all.q = 0;                       // key 0 is NaN only: everything is above it
+  Weigher unit; unit.mode = 0; unit.m = 0; unit.sum1 = 1; unit.sum2 = 1; unit.use_sum2 = false;
+  Cut cut = all;
+  if (p.top_k > 0 && p.top_k < V) cut = radix_cut_cl(c, vals, w0, w1, (u64)p.top_k, unit, all, 0.f, unit);
+
+  // softmax over the kept tokens
+  float part = -INFINITY;
+  for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; unsigned k = key_of(x); if (k >= cut.kt && k > 0u) part = fmaxf(part, x); }
+  const float m = cl_max(c, part);
+  part = 0.f;
+  for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; if (key_of(x) > cut.kt) part += expf(x - m); }
+  const float sum1 = cl_sum(c, part) + (cut.q ? (float)cut.q * expf(val_of(cut.kt) - m) : 0.f);
+  Weigher pg; pg.mode = 1; pg.m = m; pg.sum1 = sum1; pg.sum2 = 1.f; pg.use_sum2 = false;
+
+  // min-p: drop p < p_max * min_p, renormalise
+  float minp_thr = 0.f;
+  if (p.min_p > 0.f && p.min_p < 1.f) {
+    minp_thr = pg.prob(m) * p.min_p;
+    part = 0.f;
+    for (int i = w0 + lane; i < w1; i += 32) {
+      float x = vals[i];
+      if (key_of(x) > cut.kt) { float q = pg.prob(x); if (q >= minp_thr) part += q; }
+    }
+    float tq = cut.q ? pg.prob(val_of(cut.kt)) : 0.f;
+    float sum2 = cl_sum(c, part) + ((cut.q && tq >= minp_thr) ? (float)cut.q * tq : 0.f);
+    if (sum2 > 0.f) { pg.sum2 = sum2; pg.use_sum2 = true; }
+  }
+  Weigher base = pg;                                     // p before the min-p renormalisation:
+  base.use_sum2 = false;                                 // what the min-p threshold is compared with
+
+  // top-p cut: shortest prefix whose mass reaches top_p
+  float sum3 = 1.f; bool use_sum3 = false;
+  if (p.top_p < 1.f && p.top_p > 0.f) {
+    cut = radix_cut_cl(c, vals, w0, w1, __float2ull_ru(p.top_p * FIX_ONE), pg, cut, minp_thr, base);
+    part = 0.f;
+    for (int i = w0 + lane; i < w1; i += 32) {
+      float x = vals[i];
+      if (key_of(x) > cut.kt) { float q = pg.prob(x); if (!(minp_thr > 0.f && base.prob(x) < minp_thr)) part += q; }
+    }
+    float tq = cut.q ? pg.prob(val_of(cut.kt)) : 0.f;
+    bool tie_ok = cut.q && !(minp_thr > 0.f && base.prob(val_of(cut.kt)) < minp_thr);
+    sum3 = cl_sum(c, part) + (tie_ok ? (float)cut.q * tq : 0.f);
+    use_sum3 = sum3 > 0.f;
+  }
+
+  // draw in token-id order.  Ties of the cut are kept lowest id first: their ranks come first.
+  u64 bits = splitmix64(p.seed);
+  float u = (float)(bits >> 40) * (1.0f / 16777216.0f);
+  const u64 target = __float2ull_rd(u * FIX_ONE);
+  auto is_ok = [&](float x, unsigned k) { return k > 0u && k >= cut.kt && !(minp_thr > 0.f && base.prob(x) < minp_thr); };
+  {
+    u64 n_t = 0;
+    for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; unsigned k = key_of(x); if (k == cut.kt && is_ok(x, k)) ++n_t; }
+    n_t = warp_sum_u64(n_t);
+    if (lane == 0) s.warp_ties[warp] = n_t;
+  }
+  u64 ties_before, ties_total;
+  cl_prefix_u64(c, s.warp_ties, &ties_before, &ties_total);
+  for (int w = 0; w < warp; ++w) ties_before += s.warp_ties[w];
+  // One element of this warp's range: is it kept, and with which weight.  `tie_run`: kept ties before
+  // the row of 32; returns the weight (0 if not kept) and adds the row's ties to tie_run.
+  auto weigh = [&](int i0, u64& tie_run, float* pf_out, bool* member_out) -> u64 {
+    const int i = i0 + lane;
+    float x = 0.f; unsigned k = 0; bool ok = false;
+    if (i < w1) { x = vals[i]; k = key_of(x); ok = is_ok(x, k); }
+    const bool tie = ok && k == cut.kt;
+    const unsigned tm = __ballot_sync(0xffffffffu, tie);
+    const u64 tie_rank = tie_run + __popc(tm & ((1u << lane) - 1));
+    const bool member = ok && (k > cut.kt || tie_rank < cut.q);
+    float pf = 0.f;
+    if (member) { pf = pg.prob(x); if (use_sum3) pf = pf / sum3; }
+    tie_run += __popc(tm);
+    *pf_out = pf; *member_out = member;
+    return member ? __float2ull_rd(pf * FIX_ONE) : 0ull;
+  };
+  // pass 1: the warp's total weight, the processed distribution if asked for, the last kept id
+  int last = -1;
+  {
+    u64 tie_run = ties_before, lane_sum = 0;
+    for (int i0 = w0; i0 < w1; i0 += 32) {
+      float pf; bool member;
+      lane_sum += weigh(i0, tie_run, &pf, &member);
+      if (probs && i0 + lane < w1) probs[v0 + i0 + lane] = pf;
+      if (member) last = v0 + i0 + lane;
+    }
+    lane_sum = warp_sum_u64(lane_sum);
+    if (lane == 0) s.warp_w[warp] = lane_sum;
+  }
+  u64 w_before, w_total;
+  cl_prefix_u64(c, s.warp_w, &w_before, &w_total);
+  for (int w = 0; w < warp; ++w) w_before += s.warp_w[w];
+  // the last kept id, for a target that the rounded weights never reach
+  const int neg_last = cl_min_int(c, last < 0 ? 0x7fffffff : -last);
+  if (w_total > target) {
+    // pass 2, by the one warp whose range holds the target: the first id whose running weight passes it
+    if (w_before <= target && target < w_before + s.warp_w[warp]) {
+      u64 tie_run = ties_before, cum = w_before;
+      int tok = -1;
+      for (int i0 = w0; i0 < w1 && tok < 0; i0 += 32) {
+        float pf; bool member;
+        u64 incl = weigh(i0, tie_run, &pf, &member);
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) { u64 t = shfl_up_u64(incl, d); if (lane >= d) incl += t; }
+        const unsigned over = __ballot_sync(0xffffffffu, member && cum + incl > target);
+        if (over) tok = v0 + i0 + (__ffs(over) - 1);
+        cum += ((u64)__shfl_sync(0xffffffffu, (unsigned)(incl >> 32), 31) << 32) | __shfl_sync(0xffffffffu, (unsigned)incl, 31);
+      }
+      if (lane == 0 && tok >= 0) {
+        out_tokens[row] = tok;
+        if (update_counts && my_counts) my_counts[tok] += 1;
+      }
+    }
+  } else if (c.rank == 0 && threadIdx.x == 0) {
+    int tok = neg_last == 0x7fffffff ? 0 : -neg_last;
+    out_tokens[row] = tok;
+    if (update_counts && my_counts) my_counts[tok] += 1;
+  }
+  cg::this_cluster().sync();                             // nobody leaves while its shared memory may be read
+}
+
+FELLM_API int fellm_sample(const float* logits, int rows, int V, const void* params, int* counts,
+                           const int* bias_tok, const float* bias_val, int* out_tokens, float* out_probs,
+                           int update_counts, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (!logits || !params || !out_tokens || V < 1) return FELLM_ERR_ARG;
+  // a cluster of eight CTAs a row where an eighth of the row fits a CTA's shared memory
+  int slice = ((V + SC_CL - 1) / SC_CL + 31) / 32 * 32;
+  size_t smem = (size_t)slice * sizeof(float);
+  static int use_cluster = -1;
+  if (use_cluster < 0) { const char* e = getenv("FELLM_B200_SAMPLE_CLUSTER"); use_cluster = (e && e[0] == '0') ? 0 : 1; }
+  if (use_cluster && smem <= 160 * 1024) {
+    if (smem > 32 * 1024) {
+      cudaError_t ce = cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (ce != cudaSuccess) return (int)ce;
+    }
+    sample_cluster_kernel<<<dim3(rows * SC_CL), dim3(SC_THREADS), smem, stream>>>(logits, V, slice, (const RowParams*)params, counts, bias_tok,
+                                                                                 bias_val, out_tokens, out_probs, update_counts);
+    return launch_status();
+  }
+  return launch_k(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, stream, 1, logits, V, (const RowParams*)params,
+                  counts, bias_tok, bias_val, out_tokens, out_probs, update_counts);
+}
+
