@@ -448,11 +448,11 @@ namespace cg = cooperative_groups;
 struct CShared {
   u64 hist[2][256];              // this CTA's histogram of the pass, two in turn
   u64 ghist[256];                // the cluster's
-  float xf[2]; u64 xu[2][2]; int xi[2];          // this CTA's share of a cluster-wide reduction, two in turn
+  float xf[2]; float xf2[2][2]; u64 xu[2][2]; int xi[2];          // this CTA's share of a cluster-wide reduction, two in turn
   float wf[SC_WARPS]; u64 wu[SC_WARPS][2]; int wi[SC_WARPS];
   u64 warp_ties[SC_WARPS], warp_w[SC_WARPS];
   unsigned prefix; int found; u64 remaining, bin_total;
-  float bf; u64 bu[2]; int bi;
+  float bf, bf2; u64 bu[2]; int bi;
 };
 
 struct ClCtx {
@@ -562,17 +562,33 @@ __device__ void cl_prefix_u64(ClCtx& c, const u64* mine, u64* before, u64* total
 
 // One histogram entry from every lane of a warp (all 32 call it).  When the whole warp hits one bin
 // (the top bytes of a row of logits are nearly all the same) one lane adds the warp's sum.
-__device__ __forceinline__ void hist_add(u64* hist, unsigned bin, u64 w, bool active) {
+__device__ __forceinline__ void hist_add(u64* hist, unsigned bin, u64 w, bool active, bool unit) {
   const unsigned am = __ballot_sync(0xffffffffu, active);
-  if (am == 0xffffffffu) {
-    const unsigned b0 = __shfl_sync(0xffffffffu, bin, 0);
-    if (__all_sync(0xffffffffu, bin == b0)) {
-      const u64 t = warp_sum_u64(w);
-      if ((threadIdx.x & 31) == 0) atomicAdd(&hist[b0], t);
-      return;
+  if (unit) {
+    // weights of 1 (top-k): the lanes of a bin are counted by one of them (a row of logits has two or
+    // three distinct top bytes: 32 atomics on as many addresses would take turns)
+    if (active) {
+      const unsigned peers = __match_any_sync(am, bin);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (u64)__popc(peers));
     }
+    return;
   }
-  if (active) atomicAdd(&hist[bin], w);
+  if (__popc(am) < 8) {                                  // few lanes: they take their turns
+    if (active) atomicAdd(&hist[bin], w);
+    return;
+  }
+  // probability weights (top-p), many lanes: bin by bin (a row has few distinct ones), the warp sums
+  // the bin's weights and one lane adds them
+  unsigned left = am;
+  while (left) {
+    const int src = __ffs(left) - 1;
+    const unsigned b = __shfl_sync(0xffffffffu, bin, src);
+    const bool mine = active && bin == b;
+    const unsigned grp = __ballot_sync(0xffffffffu, mine);
+    const u64 t = warp_sum_u64(mine ? w : 0ull);
+    if ((int)(threadIdx.x & 31) == src) atomicAdd(&hist[b], t);
+    left &= ~grp;
+  }
 }
 
 // The cut whose kept weight first reaches `target` (see radix_cut), over the cluster's row.
@@ -595,7 +611,7 @@ __device__ Cut radix_cut_cl(ClCtx& c, const float* vals, int w0, int w1, u64 tar
       unsigned k = key_of(x);
       active = active && k > outer.kt && !(minp_thr > 0.f && pg.prob(x) < minp_thr) &&
                (pass == 0 || (k >> (shift + 8)) == (prefix >> (shift + 8)));
-      hist_add(hist, (k >> shift) & 255, active ? wg.w(x) : 0ull, active);
+      hist_add(hist, (k >> shift) & 255, active ? wg.w(x) : 0ull, active, wg.mode == 0);
     }
     if (c.rank == 0 && threadIdx.x == 0 && outer.q > 0) {          // the ties of the outer cut, once
       unsigned k = outer.kt;
@@ -709,13 +725,45 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int slice, const 
   Cut cut = all;
   if (p.top_k > 0 && p.top_k < V) cut = radix_cut_cl(c, vals, w0, w1, (u64)p.top_k, unit, all, 0.f, unit);
 
-  // softmax over the kept tokens
+  // softmax over the kept tokens: every CTA's maximum and its sum relative to it go round in one
+  // exchange; the cluster's maximum and sum follow in rank order
   float part = -INFINITY;
   for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; unsigned k = key_of(x); if (k >= cut.kt && k > 0u) part = fmaxf(part, x); }
-  const float m = cl_max(c, part);
-  part = 0.f;
-  for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; if (key_of(x) > cut.kt) part += expf(x - m); }
-  const float sum1 = cl_sum(c, part) + (cut.q ? (float)cut.q * expf(val_of(cut.kt) - m) : 0.f);
+  float m, sum1;
+  {
+    part = warp_max(part);
+    if (lane == 0) s.wf[warp] = part;
+    __syncthreads();
+    float m_cta = -INFINITY;
+    for (int w = 0; w < SC_WARPS; ++w) m_cta = fmaxf(m_cta, s.wf[w]);
+    __syncthreads();
+    float ps = 0.f;
+    for (int i = w0 + lane; i < w1; i += 32) { float x = vals[i]; if (key_of(x) > cut.kt) ps += expf(x - m_cta); }
+    ps = warp_sum(ps);
+    if (lane == 0) s.wf[warp] = ps;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < SC_WARPS; ++w) t += s.wf[w];
+      s.xf2[c.pp][0] = m_cta; s.xf2[c.pp][1] = t;
+    }
+    cg::this_cluster().sync();
+    if (threadIdx.x == 0) {
+      float mm = -INFINITY, ms[SC_CL], ss[SC_CL];
+      for (int r = 0; r < SC_CL; ++r) {
+        const float* q = cg::this_cluster().map_shared_rank(&s.xf2[c.pp][0], r);
+        ms[r] = q[0]; ss[r] = q[1];
+        mm = fmaxf(mm, ms[r]);
+      }
+      float t = 0.f;
+      for (int r = 0; r < SC_CL; ++r) if (ss[r] != 0.f) t += ss[r] * expf(ms[r] - mm);
+      s.bf = mm; s.bf2 = t;
+    }
+    __syncthreads();
+    c.pp ^= 1;
+    m = s.bf;
+    sum1 = s.bf2 + (cut.q ? (float)cut.q * expf(val_of(cut.kt) - m) : 0.f);
+  }
   Weigher pg; pg.mode = 1; pg.m = m; pg.sum1 = sum1; pg.sum2 = 1.f; pg.use_sum2 = false;
 
   // min-p: drop p < p_max * min_p, renormalise
@@ -792,11 +840,37 @@ sample_cluster_kernel(const float* __restrict__ logits, int V, int slice, const 
     lane_sum = warp_sum_u64(lane_sum);
     if (lane == 0) s.warp_w[warp] = lane_sum;
   }
+  // the weights before this CTA and in all, and (same exchange) the last kept id, for a target that
+  // the rounded weights never reach
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+  if (lane == 0) s.wi[warp] = last;
   u64 w_before, w_total;
-  cl_prefix_u64(c, s.warp_w, &w_before, &w_total);
+  int neg_last;
+  {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      u64 t = 0; int l = -1;
+      for (int w = 0; w < SC_WARPS; ++w) { t += s.warp_w[w]; l = max(l, s.wi[w]); }
+      s.xu[c.pp][0] = t; s.xi[c.pp] = l;
+    }
+    cg::this_cluster().sync();
+    if (threadIdx.x == 0) {
+      u64 b = 0, t = 0; int l = -1;
+      for (int r = 0; r < SC_CL; ++r) {
+        u64 x = *cg::this_cluster().map_shared_rank(&s.xu[c.pp][0], r);
+        l = max(l, *cg::this_cluster().map_shared_rank(&s.xi[c.pp], r));
+        if (r < c.rank) b += x;
+        t += x;
+      }
+      s.bu[0] = b; s.bu[1] = t; s.bi = l;
+    }
+    __syncthreads();
+    c.pp ^= 1;
+    w_before = s.bu[0]; w_total = s.bu[1];
+    neg_last = s.bi < 0 ? 0x7fffffff : -s.bi;
+  }
   for (int w = 0; w < warp; ++w) w_before += s.warp_w[w];
-  // the last kept id, for a target that the rounded weights never reach
-  const int neg_last = cl_min_int(c, last < 0 ? 0x7fffffff : -last);
   if (w_total > target) {
     // pass 2, by the one warp whose range holds the target: the first id whose running weight passes it
     if (w_before <= target && target < w_before + s.warp_w[warp]) {
