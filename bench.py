@@ -211,7 +211,8 @@ def run_e2e(engine, batch, steps, warmup, rng):
     for r in list(sched.running):
         sched.cancel(r.id)
     sched.step()
-    h2d = (5 * batch + 3 * batch + 1) * 4 + batch * 48          # step index arrays + sampling records
+    h2d = (7 * batch + 1 + batch) * 4                             # the step's index arrays: tokens, positions, row->item, row->slot,
+                                                                  # item starts (+1), item slots, item lengths, wanted rows (greedy rows ship no sampling records)
     d2h = (batch + 1) * 4                                         # sampled ids + status word
     return n / dt, h2d, d2h
 

@@ -44,6 +44,38 @@ class Launch:
     ctas: list = field(default_factory=list)     # with detail=True: (begin, waited, end, marks...) of every CTA
 
 
+def group_records(records, detail: bool = False) -> List[Launch]:
+    """records: one [tag, entry, after wait, exit, mark0..3] (nanoseconds of the global timer; tag =
+    kernel id | CTAs of the launch << 16) per CTA, in any order.  CTAs of one launch share a tag and
+    lie together in time: a launch is closed when as many records as it has CTAs have come, so two
+    launches of the same kernel and grid that overlap (programmatic dependents) still come apart."""
+    if not records:
+        return []
+    records = sorted(records, key=lambda r: r[1])
+    t0 = int(records[0][1])
+    out: List[Launch] = []
+    open_groups = {}                     # tag -> [records still expected, Launch]
+    for tag, begin, waited, end, *marks in records:
+        ident, blocks = tag & 0xFFFF, tag >> 16
+        b, w, e = (begin - t0) / 1e3, ((waited or begin) - t0) / 1e3, ((end or begin) - t0) / 1e3
+        mk = tuple((m - t0) / 1e3 if m else 0.0 for m in marks)
+        g = open_groups.get(tag)
+        if g is None:
+            g = [blocks, Launch(kernel_name(ident), blocks, b, w, e, mk)]
+            open_groups[tag] = g
+            out.append(g[1])
+        else:
+            g[1].waited_us = min(g[1].waited_us, w)
+            g[1].end_us = max(g[1].end_us, e)
+            g[1].marks_us = tuple(max(x, y) for x, y in zip(g[1].marks_us, mk))
+        if detail:
+            g[1].ctas.append((b, w, e) + mk)
+        g[0] -= 1
+        if g[0] == 0:
+            del open_groups[tag]
+    return out
+
+
 class Timeline:
     def __init__(self, device="cuda:0", capacity: int = 1 << 17):
         if not jit.tracing():
@@ -80,33 +112,7 @@ class Timeline:
     def launches(self, detail: bool = False) -> List[Launch]:
         torch.cuda.synchronize()
         n = min(int(self.count.item()), self.capacity)
-        rec = self.records[:n].cpu()
-        if n == 0:
-            return []
-        order = torch.argsort(rec[:, 1], stable=True)
-        rec = rec[order]
-        t0 = int(rec[0, 1])
-        out: List[Launch] = []
-        open_groups = {}                     # tag -> [records still expected, Launch]
-        for tag, begin, waited, end, *marks in rec.tolist():
-            ident, blocks = tag & 0xFFFF, tag >> 16
-            b, w, e = (begin - t0) / 1e3, ((waited or begin) - t0) / 1e3, ((end or begin) - t0) / 1e3
-            mk = tuple((m - t0) / 1e3 if m else 0.0 for m in marks)
-            g = open_groups.get(tag)
-            if g is None:
-                g = [blocks, Launch(kernel_name(ident), blocks, b, w, e, mk)]
-                open_groups[tag] = g
-                out.append(g[1])
-            else:
-                g[1].waited_us = min(g[1].waited_us, w)
-                g[1].end_us = max(g[1].end_us, e)
-                g[1].marks_us = tuple(max(x, y) for x, y in zip(g[1].marks_us, mk))
-            if detail:
-                g[1].ctas.append((b, w, e) + mk)
-            g[0] -= 1
-            if g[0] == 0:
-                del open_groups[tag]
-        return out
+        return group_records(self.records[:n].cpu().tolist(), detail)
 
     @staticmethod
     def table(launches: List[Launch]) -> str:
