@@ -18,7 +18,9 @@ _fns = {}
 
 
 def _fn(module: str, name: str, argtypes, defines=None):
-    key = (module, name, jit._defines_key(defines))
+    # (the cache key is made without the jit's own key: that one reads the environment, and this
+    # function runs once per kernel launch)
+    key = (module, name, tuple(defines.items()) if defines else None)
     f = _fns.get(key)
     if f is None:
         lib = jit.load_module(module, defines)
@@ -32,7 +34,15 @@ def _fn(module: str, name: str, argtypes, defines=None):
     return f
 
 
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream          # the handle without building a Stream object
+except AttributeError:                                         # pragma: no cover
+    _raw_stream = None
+
+
 def _stream() -> int:
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
