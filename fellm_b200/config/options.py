@@ -19,6 +19,7 @@ class EngineOptions:
     n_ctx: int = 8192
     n_batch: int = 2048
     n_ubatch: int = 512
+    ctx_past_model: bool = False    # replay of given tokens: n_ctx is taken as given, not clamped to the model's maximum
     page_tokens: int = 64
     max_requests: int = 64          # state slots and block-table rows
     max_tokens: Optional[int] = None    # cache pool size in tokens; None = from memory

@@ -53,6 +53,8 @@ class Engine:
             bind_tensors(self.model, tensors, self.device)
         # context: FeLLM clamps n_ctx to the model's maximum, 0 = the maximum (engine.rs:190-197)
         n_ctx = spec.max_position if options.n_ctx == 0 else min(options.n_ctx, spec.max_position)
+        if options.ctx_past_model and options.n_ctx > 0:
+            n_ctx = options.n_ctx          # positions past max_position_embeddings rotate like any other: nothing is learned per position
         self.n_ctx = n_ctx
         cache_dtype = torch.bfloat16 if options.dtype == "bfloat16" else torch.float32
         needs = self.model.cache_needs()

@@ -131,3 +131,18 @@ def test_float32_does_not_depend_on_the_cut(name):
     b = collect(steps, run_trace(tiny.model_folder(name), "float32", 192, steps, vocab(name), page_tokens=16))["w"]
     for p in range(n):
         assert torch.equal(a[p], b[p]), f"position {p} differs by {(a[p] - b[p]).abs().max().item():.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_request_longer_than_max_position_embeddings_in_one_step(dtype):
+    """Replay holds a request as long as the pool lets it (configuration A says 512 positions), and a
+    step takes a whole prompt of more tokens than a scheduler iteration would."""
+    name, n = "A", 4400
+    toks = tiny.tokens(name, n, 21)
+    cut = n - 3
+    places = [0, 63, 64, 511, 512, 513, 2047, 2048, 4095, 4096, cut - 1]
+    steps = [{"entries": [{"id": "long", "tokens": toks[:cut], "want": places}]}]
+    steps += [{"entries": [{"id": "long", "tokens": [toks[t]], "want": [0]}]} for t in range(cut, n)]
+    steps[-1]["end"] = ["long"]
+    res = run_trace(tiny.model_folder(name), dtype, 4416, steps, vocab(name))
+    check(name, dtype, steps, res, {"long": (n, 21)})
