@@ -482,9 +482,13 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
     return _decode_scratch[device]
 
 
-DECODE_TARGET_CTAS = 148 * 4
+# CTAs the split of decode attention aims at: one wave of the TMA kernel (three CTAs of 68 KB to an
+# SM).  Measured on B200, 16 layers of width 1024, context 2048 (4000): batch 8 379 (411) us a step
+# with 444, 387 (438) with 592, 399 (417) with 300; batch 32 764 with 444, 822 with 592.
+DECODE_TARGET_CTAS = int(os.environ.get("FELLM_B200_DECODE_TARGET", 148 * 3))
 
 
+SPLIT_WHOLE_ROUNDS = os.environ.get("FELLM_B200_SPLIT_ROUNDS", "1") != "0"
 USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
 FUSE_DECODE_ROPE = os.environ.get("FELLM_B200_FUSE_ROPE", "1") != "0"
 USE_TMA_PREFILL = os.environ.get("FELLM_B200_TMA_PREFILL", "1") != "0"
@@ -495,8 +499,13 @@ def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
     while contexts grow."""
     bucket = -(-max(max_len, 1) // 1024) * 1024
-    want = max(1, (target or DECODE_TARGET_CTAS) // max(rows * kv_heads, 1))
+    items = max(rows * kv_heads, 1)
+    want = max(1, (target or DECODE_TARGET_CTAS) // items)
+    if items > (target or DECODE_TARGET_CTAS):
+        want = 2            # more than a wave even unsplit: halves, so that the last wave is a short one
     split_len = max(64, -(-(-(-bucket // want)) // 64) * 64)
+    if split_len > 256 and SPLIT_WHOLE_ROUNDS:
+        split_len = -(-split_len // 256) * 256      # whole rounds of the kernel's four warps, a page each
     return split_len, -(-bucket // split_len)
 
 
