@@ -32,59 +32,95 @@ __device__ __forceinline__ void sc_unpack8(const uint4& v, float* f) {
   for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
 
-// Body rows, bfloat16, d % 8 == 0: a thread takes 8 consecutive channels (16-byte loads) of a row;
-// the rows of a tile are independent of one another, so their loads overlap.  A row's data is asked
-// for before it is known whether the row is a body row (row -> item -> item start are two dependent
-// loads): rows before the batch's first are clamped, and a head row's result is dropped.  Same sums,
-// in the same order, as the scalar path.
+// Body rows, bfloat16, d % 8 == 0: a thread takes 8 consecutive channels (16-byte loads) of
+// BODY_ROWS consecutive rows.  Its taps stay in registers and so do the products B*X of the Lc-1
+// rows before the one it is at, so that a row costs three loads (B, X, C) and is read once, plus
+// the Lc-1 rows before the tile.  Rows are asked for four at a time, before it is known whether
+// they are body rows (row -> item -> item start are two dependent loads): rows before the batch's
+// first are clamped, and a head row's result is dropped.  Same sums, in the same order, as the
+// scalar path.  LC = taps (2..5; other counts take the scalar path).
+template <int LC>
 __device__ void shortconv_body_vec(const bf16* __restrict__ bcx, const float* __restrict__ w,
                                    const float* __restrict__ conv_bias, const int* __restrict__ item_start,
-                                   const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int Lc, int blocked) {
-  // the tile's threads (all blocks along x) are laid over [rows][groups of 8 channels]
+                                   const int* __restrict__ row_item, bf16* __restrict__ y, int T, int d, int blocked) {
+  constexpr int H = LC - 1, RB = 4;
+  // the threads of a grid row (all blocks along x) are laid over [tiles][groups of 8 channels]
   const int groups = d / 8, lin = blockIdx.x * blockDim.x + threadIdx.x;
-  const int c0 = (lin % groups) * 8, row_in_tile = lin / groups;
-  const int row_step = (gridDim.x * blockDim.x) / groups;   // >= 8: the grid has a thread per channel
-  const int H = Lc - 1;
+  const int tiles_per_y = (gridDim.x * blockDim.x) / groups;      // >= 8: a grid row has a thread per channel
+  const int tile_in_y = lin / groups;
+  if (tile_in_y >= tiles_per_y) return;
+  const int c0 = (lin - tile_in_y * groups) * 8;
+  const int r0 = (blockIdx.y * tiles_per_y + tile_in_y) * BODY_ROWS;
+  if (r0 >= T) return;
   const size_t ld = (size_t)3 * d;
   const int cb = sc_col(0, c0, d, blocked), cc = sc_col(1, c0, d, blocked), cx = sc_col(2, c0, d, blocked);   // 8 channels stay in one block
-  const float* wc = w + (size_t)c0 * Lc;
-  const int r0 = blockIdx.y * BODY_ROWS;
-  for (int r = r0 + row_in_tile; r < r0 + BODY_ROWS; r += row_step) {
-    if (r >= T) break;
-    const int item = row_item[r];
-    const bf16* row = bcx + (size_t)r * ld;
-    const uint4 vb = *(const uint4*)(row + cb), vx = *(const uint4*)(row + cx), vc = *(const uint4*)(row + cc);
-    const int start = item_start[item];
-    float b[8], x[8], conv[8];
-    sc_unpack8(vb, b);
-    sc_unpack8(vx, x);
+  float wt[LC][8], bias[8], win[H > 0 ? H : 1][8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) conv[e] = (b[e] * x[e]) * wc[e * Lc + H];
-    for (int t = 0; t < H; ++t) {
-      const int rp = r - H + t;
-      const bf16* pr = bcx + (size_t)(rp < 0 ? 0 : rp) * ld;
-      float pb[8], px[8];
-      sc_unpack8(*(const uint4*)(pr + cb), pb);
-      sc_unpack8(*(const uint4*)(pr + cx), px);
+  for (int e = 0; e < 8; ++e) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) conv[e] = fmaf(pb[e] * px[e], wc[e * Lc + t], conv[e]);
+    for (int t = 0; t < LC; ++t) wt[t][e] = w[(size_t)(c0 + e) * LC + t];
+    bias[e] = conv_bias ? conv_bias[c0 + e] : 0.f;
+  }
+#pragma unroll
+  for (int t = 0; t < H; ++t) {                              // B*X of the rows before the tile, oldest first
+    const int rp = r0 - H + t;
+    const bf16* pr = bcx + (size_t)(rp < 0 ? 0 : rp) * ld;
+    float pb[8], px[8];
+    sc_unpack8(*(const uint4*)(pr + cb), pb);
+    sc_unpack8(*(const uint4*)(pr + cx), px);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) win[t][e] = pb[e] * px[e];
+  }
+  for (int rb = r0; rb < r0 + BODY_ROWS && rb < T; rb += RB) {
+    uint4 vb[RB], vx[RB], vc[RB];
+    int first[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      const int r = rb + i < T ? rb + i : T - 1;
+      const bf16* row = bcx + (size_t)r * ld;
+      vb[i] = *(const uint4*)(row + cb); vx[i] = *(const uint4*)(row + cx); vc[i] = *(const uint4*)(row + cc);
+      first[i] = row_item[r];
     }
-    if (r - start < H) continue;                 // head rows belong to the item's head thread
-    float cg[8], bias[8];
-    sc_unpack8(vc, cg);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) bias[e] = conv_bias ? conv_bias[c0 + e] : 0.f;
-    uint4 o;
-    __nv_bfloat162 p0 = __floats2bfloat162_rn(cg[0] * (conv[0] + bias[0]), cg[1] * (conv[1] + bias[1]));
-    __nv_bfloat162 p1 = __floats2bfloat162_rn(cg[2] * (conv[2] + bias[2]), cg[3] * (conv[3] + bias[3]));
-    __nv_bfloat162 p2 = __floats2bfloat162_rn(cg[4] * (conv[4] + bias[4]), cg[5] * (conv[5] + bias[5]));
-    __nv_bfloat162 p3 = __floats2bfloat162_rn(cg[6] * (conv[6] + bias[6]), cg[7] * (conv[7] + bias[7]));
-    o.x = *(unsigned*)&p0; o.y = *(unsigned*)&p1; o.z = *(unsigned*)&p2; o.w = *(unsigned*)&p3;
-    *(uint4*)(y + (size_t)r * d + c0) = o;
+    for (int i = 0; i < RB; ++i) first[i] = item_start[first[i]];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      const int r = rb + i;
+      if (r >= T) break;
+      float b[8], x[8], bx[8], conv[8];
+      sc_unpack8(vb[i], b);
+      sc_unpack8(vx[i], x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { bx[e] = b[e] * x[e]; conv[e] = bx[e] * wt[H][e]; }
+#pragma unroll
+      for (int t = 0; t < H; ++t) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) conv[e] = fmaf(win[t][e], wt[t][e], conv[e]);
+      }
+#pragma unroll
+      for (int t = 0; t + 1 < H; ++t) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[t][e] = win[t + 1][e];
+      }
+      if (H > 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[H - 1][e] = bx[e];
+      }
+      if (r - first[i] < H) continue;             // head rows belong to the item's head thread
+      float cg[8];
+      sc_unpack8(vc[i], cg);
+      uint4 o;
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(cg[0] * (conv[0] + bias[0]), cg[1] * (conv[1] + bias[1]));
+      __nv_bfloat162 p1 = __floats2bfloat162_rn(cg[2] * (conv[2] + bias[2]), cg[3] * (conv[3] + bias[3]));
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(cg[4] * (conv[4] + bias[4]), cg[5] * (conv[5] + bias[5]));
+      __nv_bfloat162 p3 = __floats2bfloat162_rn(cg[6] * (conv[6] + bias[6]), cg[7] * (conv[7] + bias[7]));
+      o.x = *(unsigned*)&p0; o.y = *(unsigned*)&p1; o.z = *(unsigned*)&p2; o.w = *(unsigned*)&p3;
+      *(uint4*)(y + (size_t)r * d + c0) = o;
+    }
   }
 }
 
-template <typename TA, bool VEC>
+template <typename TA, int VLC>
 __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __restrict__ w,
                                  const float* __restrict__ conv_bias, float* __restrict__ state,
                                  long long slot_stride, const int* __restrict__ item_slot,
@@ -93,9 +129,9 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
   FELLM_TRACE_SCOPE(TRACE_SHORTCONV);
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
-  if (VEC && (int)blockIdx.y < n_body_tiles) {
+  if (VLC > 0 && (int)blockIdx.y < n_body_tiles) {
     pdl_wait(); FELLM_TRACE_WAITED();
-    shortconv_body_vec((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, Lc, blocked);
+    shortconv_body_vec<(VLC > 0 ? VLC : 2)>((const bf16*)bcx, w, conv_bias, item_start, row_item, (bf16*)y, T, d, blocked);
     return;
   }
   if (c >= d) return;
@@ -179,13 +215,27 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   if (!bcx || !w || !state || !y) return FELLM_ERR_ARG;
   int threads = d >= 128 ? 128 : 64;
   int n_body = all_single ? 0 : ceil_div(T, BODY_ROWS);    // every item has one token: heads only
-  dim3 grid(ceil_div(d, threads), n_body + n_items);
-  if (is_bf16 && d % 8 == 0 && n_body > 0)
-    return launch_k_class(2, shortconv_kernel<bf16, true>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
-                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked);
+  const int gx = ceil_div(d, threads);
+  if (is_bf16 && d % 8 == 0 && n_body > 0 && Lc <= 5) {
+    // vectorised body: a thread takes 8 channels of a tile of BODY_ROWS rows; a grid row holds
+    // (gx * threads) / (d / 8) >= 8 such tiles
+    const int tiles_per_y = (gx * threads) / (d / 8);
+    n_body = ceil_div(n_body, tiles_per_y);
+    dim3 grid(gx, n_body + n_items);
+#define SC_VEC(LC_) launch_k_class(2, shortconv_kernel<bf16, LC_>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state, \
+                    slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked)
+    switch (Lc) {
+      case 2: return SC_VEC(2);
+      case 3: return SC_VEC(3);
+      case 4: return SC_VEC(4);
+      default: return SC_VEC(5);
+    }
+#undef SC_VEC
+  }
+  dim3 grid(gx, n_body + n_items);
   if (is_bf16)
-    return launch_k_class(2, shortconv_kernel<bf16, false>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+    return launch_k_class(2, shortconv_kernel<bf16, 0>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked);
-  return launch_k_class(2, shortconv_kernel<float, false>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
+  return launch_k_class(2, shortconv_kernel<float, 0>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
                   slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body, blocked);
 }
