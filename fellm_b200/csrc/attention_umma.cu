@@ -1,0 +1,415 @@
+// Causal attention of prompt portions over the paged cache on the Blackwell tensor path: head size
+// 64, pages of 64 tokens, no window.  A CTA takes 128 rows (token, head of one kv head's group) and
+// walks over the pages of keys up to its last token:
+//   S = Q K^T      tcgen05.mma 128x64x16 (kind::f16), Q and the K page K-major in shared memory
+//                  (128-byte swizzle; the page comes by one bulk tensor copy), S in tensor memory;
+//   softmax        four warps, a row a thread: tcgen05.ld of the row's 64 scores, running maximum and
+//                  sum in registers with no shuffles, P rounded to bfloat16 into shared memory;
+//   O_tile = P V   tcgen05.mma with the V page as the MN-major operand, into tensor memory;
+//   o = o*corr + O_tile in registers.
+// Roles in a CTA of 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
+// owner of the tensor-memory allocation (two score tiles and the P V tile), warps 2-5 = softmax.
+// Every wait on an mbarrier is bounded (a second, or until another role has given up): a role that
+// gives up records 311..316 in `status`, and every role falls through to the common exit, where
+// tensor memory is freed.
+// The same sums as attention_prefill_kernel (attention_mma.cu) up to the order within a tile's row.
+//
+// FeLLM counterpart: attention_fa2_prefill_paged (plugins/cuda_kernels/src/oxide_kernels.rs:4673,
+// one warp per query row).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+#define AU_HD 64
+#define AU_PT 64                       // keys per tile: a page
+#define AU_ROWS 128
+#define AU_STAGES 4
+#define AU_THREADS 192
+#define AU_TILE_B (AU_PT * 128)        // bytes of one K (or V) page tile
+#define AU_WAIT_NS 1000000000ull
+#define AU_SPIN_LIMIT (1u << 26)
+
+struct AuArgs {
+  const bf16* q; const int* block_table; const int* positions; const int* row_slot; const int* item_start;
+  bf16* out; int* status;
+  int max_pages, H, G, layer, layers_in_group;
+  float scale_log2;
+};
+
+__device__ __forceinline__ unsigned au_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void au_mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void au_mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void au_mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool au_mbar_try(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long au_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait: false if the phase has not completed after AU_WAIT_NS (then *status = code and *fail
+// is set) or if another role has set *fail meanwhile.
+__device__ __forceinline__ bool au_wait(unsigned bar, unsigned parity, volatile int* fail, int* status, int code) {
+  if (au_mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = au_now();
+  for (unsigned i = 0; i < AU_SPIN_LIMIT; ++i) {
+    if (au_mbar_try(bar, parity)) return true;
+    if ((i & 63) == 63) {
+      if (*fail) return false;
+      if (au_now() - t0 > AU_WAIT_NS) break;
+    }
+  }
+  *fail = 1;
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void au_tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Operand tile with rows of 128 bytes under the 128-byte swizzle, groups of 8 rows 1024 bytes apart:
+// K-major (the rows are M or N, the 128 bytes run along K) or MN-major (the rows are K, the 128
+// bytes are 64 elements of N); the instruction descriptor says which.
+__device__ __forceinline__ unsigned long long au_desc(unsigned smem_addr, bool mn_major = false) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);          // start address
+  if (mn_major) d |= (unsigned long long)(8192 >> 4) << 16;       // leading byte offset: the next 64 elements of MN (there are none here)
+  d |= (unsigned long long)(1024 >> 4) << 32;                     // stride byte offset: the next group of 8 rows
+  d |= 1ull << 46;                                                // descriptor version (sm_100)
+  d |= 2ull << 61;                                                // SWIZZLE_128B
+  return d;
+}
+// kind::f16: D float32, A and B bfloat16; b_mn: B is MN-major (bit 16); N >> 3 at bit 17, M >> 4 at bit 24.
+__device__ __forceinline__ unsigned au_idesc(int m, int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ void au_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void au_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void au_tmem_ld32_issue(unsigned taddr, float* v) {
+  unsigned* r = reinterpret_cast<unsigned*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void au_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void au_tmem_ld32(unsigned taddr, float* v) {
+  au_tmem_ld32_issue(taddr, v);
+  au_tmem_ld_wait();
+}
+__device__ __forceinline__ void au_st_shared16(unsigned addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// byte offset of 16-byte chunk `chunk` of row `row` in a tile of 128-byte rows under the 128-byte swizzle
+__device__ __forceinline__ unsigned au_off(int row, int chunk) { return (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+__device__ __forceinline__ float au_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Tensor memory columns: two score tiles (the MMA thread fills one while the softmax warps read the
+// other) and the tile of P V.
+#define AU_COL_S 0
+#define AU_COL_O 128
+#define AU_TMEM_COLS 256
+
+__global__ void __launch_bounds__(AU_THREADS, 2)
+attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_ATTENTION_PREFILL);
+  extern __shared__ unsigned char smem_raw[];
+  // full[STAGES], empty[STAGES], q_ready, s_full[2], p_full, o_full
+  __shared__ __align__(8) unsigned long long bars[2 * AU_STAGES + 5];
+  __shared__ unsigned tmem_base_s;
+  __shared__ int sm_fail;
+  const int item = blockIdx.z, g = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = a.H / a.G;                                     // divides 128 (the launcher checks)
+  const int tokb = AU_ROWS / R;                                // tokens a CTA
+  pdl_launch_dependents();
+  const int row_begin = a.item_start[item], n_rows = a.item_start[item + 1] - row_begin;
+  const int n_blocks = (n_rows + tokb - 1) / tokb;
+  if ((int)blockIdx.x >= n_blocks) return;                     // before any barrier or allocation
+  const int blk = n_blocks - 1 - (int)blockIdx.x;              // the blocks with the most keys start first
+  const int tok0 = blk * tokb, n_tok = min(tokb, n_rows - tok0);
+  const int pos0 = a.positions[row_begin] + tok0;              // position of the block's first token
+  const int k_last = pos0 + n_tok - 1;
+  const int n_tiles = k_last / AU_PT + 1;                      // pages 0 .. that of the last token
+  const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
+
+  const unsigned base = (au_smem(smem_raw) + 1023u) & ~1023u;  // the swizzle is by address
+  const unsigned q_s = base, p_s = base + AU_ROWS * 128, stage0 = base + 2 * AU_ROWS * 128;
+  const unsigned full0 = au_smem(&bars[0]), empty0 = au_smem(&bars[AU_STAGES]);
+  const unsigned q_ready = au_smem(&bars[2 * AU_STAGES]), s_full0 = q_ready + 8, p_full = q_ready + 24, o_full = q_ready + 32;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AU_STAGES; ++s) { au_mbar_init(full0 + 8 * s, 1); au_mbar_init(empty0 + 8 * s, 1); }
+    au_mbar_init(q_ready, 4); au_mbar_init(s_full0, 1); au_mbar_init(s_full0 + 8, 1); au_mbar_init(p_full, 4); au_mbar_init(o_full, 1);
+    sm_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(au_smem(&tmem_base_s)), "r"(AU_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+  volatile int* fail = &sm_fail;
+  pdl_wait(); FELLM_TRACE_WAITED();                            // q and the cache rows of this step come from the kernel before
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % AU_STAGES;
+        if (j >= AU_STAGES && !au_wait(empty0 + 8 * s, (j / AU_STAGES - 1) & 1, fail, a.status, 311)) break;
+        const int page = max(bt[j], 0);                        // an unmapped entry (-1) must never become an address
+        const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * AU_PT;      // < 2^31: the launcher checks
+        const unsigned dst = stage0 + s * 2 * AU_TILE_B;
+        au_mbar_expect_tx(full0 + 8 * s, 2 * AU_TILE_B);
+        au_tma_load_2d(dst, &pool_map, 0, row, full0 + 8 * s);
+        au_tma_load_2d(dst + AU_TILE_B, &pool_map, 0, row + a.G * AU_PT, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc_s = au_idesc(AU_ROWS, AU_PT, false), idesc_o = au_idesc(AU_ROWS, AU_HD, true);
+      const unsigned long long dq = au_desc(q_s), dp = au_desc(p_s);
+      auto scores = [&](int j) -> bool {                       // S_j = Q K_j^T into score tile j & 1
+        const int s = j % AU_STAGES;
+        if (!au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 312)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned long long dk = au_desc(stage0 + s * 2 * AU_TILE_B);
+#pragma unroll
+        for (int k = 0; k < AU_HD / 16; ++k)                   // 32 bytes further along the head inside the swizzle atom
+          au_mma(tmem_base + AU_COL_S + (j & 1) * AU_PT, dq + (unsigned long long)(k * 2), dk + (unsigned long long)(k * 2), idesc_s, k ? 1u : 0u);
+        au_commit(s_full0 + 8 * (j & 1));
+        return true;
+      };
+      bool ok = au_wait(q_ready, 0, fail, a.status, 313);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        ok = scores(0);
+        if (ok && n_tiles > 1) ok = scores(1);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % AU_STAGES;
+        // P_j lies in shared memory; S_j and the P V tile of j-1 have been read
+        ok = au_wait(p_full, j & 1, fail, a.status, 314);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned long long dv = au_desc(stage0 + s * 2 * AU_TILE_B + AU_TILE_B, true);
+#pragma unroll
+        for (int k = 0; k < AU_PT / 16; ++k)                   // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+          au_mma(tmem_base + AU_COL_O, dp + (unsigned long long)(k * 2), dv + (unsigned long long)(k * 128), idesc_o, k ? 1u : 0u);
+        au_commit(o_full);
+        au_commit(empty0 + 8 * s);                             // the page's stage is free once these MMAs have read it
+        if (j + 2 < n_tiles) ok = scores(j + 2);               // into the score tile that S_j has left
+      }
+    }
+  } else {
+    // softmax warps: TMEM lanes 32*(warp%4) .. +32 = the CTA's rows, a row a thread
+    const int qd = warp & 3, row = qd * 32 + lane;
+    const int tok = row / R, head = row - tok * R;
+    const bool valid = tok < n_tok;
+    const int pos = pos0 + tok;
+    const size_t out_row = ((size_t)(row_begin + tok0 + tok) * a.H + g * R + head) * AU_HD;
+    {
+      const uint4* src = (const uint4*)(a.q + out_row);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) au_st_shared16(q_s + au_off(row, ch), valid ? src[ch] : make_uint4(0, 0, 0, 0));
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // these writes before the MMA's reads
+    __syncwarp();
+    if (lane == 0) au_mbar_arrive(q_ready);
+    const unsigned t_row = tmem_base + ((unsigned)(qd * 32) << 16);
+    const float scale = a.scale_log2;
+    // o lags one tile behind: P V of tile j is added (after o has been scaled by tile j's correction)
+    // while tile j+1's scores are already exponentiated, so that the MMA's latency is not waited for
+    float o[AU_HD], m = -INFINITY, l = 0.f, corr_prev = 0.f;
+#pragma unroll
+    for (int d = 0; d < AU_HD; ++d) o[d] = 0.f;
+    auto add_pv = [&](int j) -> bool {                         // o = o * (correction of tile j) + P_j V_j
+      if (!au_wait(o_full, j & 1, fail, a.status, 317)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        float ot[32];
+        au_tmem_ld32(t_row + AU_COL_O + 32 * hlf, ot);
+#pragma unroll
+        for (int d = 0; d < 32; ++d) o[32 * hlf + d] = fmaf(o[32 * hlf + d], corr_prev, ot[d]);
+      }
+      return true;
+    };
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int key0 = j * AU_PT, s = j % AU_STAGES;
+      if (key0 + AU_PT > k_last + 1) {
+        // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
+        ok = au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 315);
+        if (!ok) break;
+        const unsigned v_s = stage0 + s * 2 * AU_TILE_B + AU_TILE_B;
+        for (int i = (k_last + 1 - key0) * 8 + (int)threadIdx.x - 64; i < AU_PT * 8; i += 128)
+          au_st_shared16(v_s + au_off(i >> 3, i & 7), make_uint4(0, 0, 0, 0));
+      }
+      ok = au_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, fail, a.status, 316);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      float sc[AU_PT];
+      au_tmem_ld32_issue(t_row + AU_COL_S + (j & 1) * AU_PT, sc);
+      au_tmem_ld32_issue(t_row + AU_COL_S + (j & 1) * AU_PT + 32, sc + 32);
+      au_tmem_ld_wait();
+      if (key0 + AU_PT - 1 > pos) {
+#pragma unroll
+        for (int c = 0; c < AU_PT; ++c) sc[c] = (key0 + c <= pos) ? sc[c] : -INFINITY;
+      }
+      float r4[4] = {sc[0], sc[1], sc[2], sc[3]};               // four chains, not one of 63 dependent steps
+#pragma unroll
+      for (int c = 4; c < AU_PT; c += 4) {
+        r4[0] = fmaxf(r4[0], sc[c]); r4[1] = fmaxf(r4[1], sc[c + 1]); r4[2] = fmaxf(r4[2], sc[c + 2]); r4[3] = fmaxf(r4[3], sc[c + 3]);
+      }
+      const float raw = fmaxf(fmaxf(r4[0], r4[1]), fmaxf(r4[2], r4[3]));
+      // key 0 counts for every row, so the maximum is finite from the first tile on (rows past the
+      // block's tokens are all zeros and are never stored); the scale is positive
+      const float mx = fmaxf(m, raw * scale);
+      const float corr = (m == -INFINITY) ? 0.f : au_ex2(m - mx);
+      m = mx;
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned pk[AU_PT / 2];
+#pragma unroll
+      for (int c = 0; c < AU_PT; c += 4) {
+        const float p0 = au_ex2(fmaf(sc[c], scale, -mx)), p1 = au_ex2(fmaf(sc[c + 1], scale, -mx));
+        const float p2 = au_ex2(fmaf(sc[c + 2], scale, -mx)), p3 = au_ex2(fmaf(sc[c + 3], scale, -mx));
+        s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
+        __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
+        pk[c >> 1] = *(unsigned*)&pa; pk[(c >> 1) + 1] = *(unsigned*)&pb;
+      }
+      l = l * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+      if (j > 0) {                                             // also: the MMA has read P of the tile before
+        ok = add_pv(j - 1);
+        if (!ok) break;
+      }
+      corr_prev = corr;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        au_st_shared16(p_s + au_off(row, ch), make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]));
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // P (and the zeroed V rows) before the MMA's reads
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) au_mbar_arrive(p_full);
+    }
+    if (ok) ok = add_pv(n_tiles - 1);
+    if (ok && valid) {
+      const float inv = 1.0f / l;
+      uint4* dst = (uint4*)(a.out + out_row);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(o[8 * ch] * inv, o[8 * ch + 1] * inv), p1 = __floats2bfloat162_rn(o[8 * ch + 2] * inv, o[8 * ch + 3] * inv);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(o[8 * ch + 4] * inv, o[8 * ch + 5] * inv), p3 = __floats2bfloat162_rn(o[8 * ch + 6] * inv, o[8 * ch + 7] * inv);
+        dst[ch] = make_uint4(*(unsigned*)&p0, *(unsigned*)&p1, *(unsigned*)&p2, *(unsigned*)&p3);
+      }
+    }
+  }
+  // common exit: every role comes here, also after a wait that gave up
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(AU_TMEM_COLS) : "memory");
+  }
+}
+
+// The cache pool as a 2-D tensor [rows of 64 dims], a page of one kv head (64 rows) a box: the map is
+// kept per (pool, rows).
+typedef CUresult (*AuEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int au_pool_map(const void* pool, long long rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static struct { const void* pool; long long rows; CUtensorMap map; } cache[8];
+  static int n_cached = 0, next = 0;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_cached; ++i)
+    if (cache[i].pool == pool && cache[i].rows == rows) { *out = cache[i].map; return 0; }
+  static AuEncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return FELLM_ERR_ARG;
+    fn = (AuEncodeTiledFn)p;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)AU_HD, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)AU_HD * 2};
+  cuuint32_t box[2] = {AU_HD, AU_PT};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 1000 + (int)r;
+  cache[next].pool = pool; cache[next].rows = rows; cache[next].map = m;
+  next = (next + 1) % 8;
+  if (n_cached < 8) ++n_cached;
+  *out = m;
+  return 0;
+}
+
+// Whether fellm_attn_prefill_umma takes these sizes (1) or not (0).
+FELLM_API int fellm_attn_prefill_umma_takes(int H, int G, int hd, int page_tokens, int window) {
+  if (G < 1 || H % G) return 0;
+  const int R = H / G;
+  return (hd == AU_HD && page_tokens == AU_PT && window <= 0 && R <= AU_ROWS && AU_ROWS % R == 0) ? 1 : 0;
+}
+
+// q [T, H, 64] bfloat16 (normed, rotated), out [T, H*64]; pool [n_pages, layers_in_group, 2, G, 64, 64];
+// rows of item i are item_start[i]..item_start[i+1], its positions are consecutive from
+// positions[item_start[i]]; max_item_rows: the longest item of the step.  status: device int32 that a
+// role sets (311..317) if a wait ran out.  FELLM_ERR_SIZE for sizes it does not take.
+FELLM_API int fellm_attn_prefill_umma(const void* q, const void* pool, long long n_pages, const int* block_table,
+                                      int max_pages, const int* positions, const int* row_slot, const int* item_start,
+                                      int n_items, int max_item_rows, void* out, int T, int H, int G, int hd,
+                                      int page_tokens, int layer, int layers_in_group, float scale, int window,
+                                      int* status, cudaStream_t stream) {
+  if (T <= 0 || n_items <= 0) return 0;
+  if (!q || !pool || !block_table || !positions || !row_slot || !item_start || !out) return FELLM_ERR_ARG;
+  if (!fellm_attn_prefill_umma_takes(H, G, hd, page_tokens, window)) return FELLM_ERR_SIZE;
+  const long long rows = n_pages * layers_in_group * 2 * G * page_tokens;
+  if (rows >= (1ll << 31) || ((uintptr_t)pool & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return FELLM_ERR_SIZE;
+  AuArgs a;
+  a.q = (const bf16*)q; a.block_table = block_table; a.positions = positions; a.row_slot = row_slot; a.item_start = item_start;
+  a.out = (bf16*)out; a.status = status; a.max_pages = max_pages; a.H = H; a.G = G; a.layer = layer;
+  a.layers_in_group = layers_in_group; a.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap map;
+  int e = au_pool_map(pool, rows, &map);
+  if (e) return e;
+  const int tokb = AU_ROWS / (H / G);
+  size_t smem = (size_t)2 * AU_ROWS * 128 + (size_t)AU_STAGES * 2 * AU_TILE_B + 1024;
+  auto kern = attention_prefill_umma_kernel;
+  cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (ce != cudaSuccess) return (int)ce;
+  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb), G, n_items), dim3(AU_THREADS), smem, stream, 1, map, a);
+}

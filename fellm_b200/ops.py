@@ -345,7 +345,8 @@ def check_umma_status(device):
             t.zero_()
             if code == 302:
                 raise KernelError("decode attention: a row's position has no cache page mapped")
-            what = "the TMA decode attention" if code == 301 else "the tcgen05 product"
+            what = ("the TMA decode attention" if code == 301 else
+                    "the tcgen05 prefill attention" if 311 <= code <= 317 else "the tcgen05 product")
             raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
 
@@ -492,6 +493,8 @@ SPLIT_WHOLE_ROUNDS = os.environ.get("FELLM_B200_SPLIT_ROUNDS", "1") != "0"
 USE_TMA_DECODE = os.environ.get("FELLM_B200_TMA_DECODE", "1") != "0"
 FUSE_DECODE_ROPE = os.environ.get("FELLM_B200_FUSE_ROPE", "1") != "0"
 USE_TMA_PREFILL = os.environ.get("FELLM_B200_TMA_PREFILL", "1") != "0"
+USE_UMMA_PREFILL = os.environ.get("FELLM_B200_UMMA_ATTN", "1") != "0"
+UMMA_PREFILL_MIN_ROWS = int(os.environ.get("FELLM_B200_UMMA_ATTN_MIN_ROWS", 1))    # (token, head) rows of the longest item
 
 
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
@@ -584,6 +587,16 @@ def attention_prefill(q, pool, block_table, positions, row_slot, item_start, n_i
     _i32(item_start, "item_start")
     if out is None:
         out = torch.empty((T, H * hd), dtype=q.dtype, device=q.device)
+    if (USE_UMMA_PREFILL and hd == 64 and page_tokens == 64 and not window and pool.numel() // hd < 2 ** 31
+            and 128 % (H // G) == 0 and max_item_rows * (H // G) >= UMMA_PREFILL_MIN_ROWS):
+        # tcgen05: 128 (token, head) rows a CTA, S and P V in tensor memory
+        f = _fn("attention_umma", "fellm_attn_prefill_umma",
+                [_c_p, _c_p, ctypes.c_longlong, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int,
+                 _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p])
+        _check(f(_p(q), _p(pool), pool.shape[0], _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
+                 _p(item_start), n_items, max_item_rows, _p(out), T, H, G, hd, page_tokens, layer, pool.shape[1],
+                 float(scale), 0, _p(umma_status(q.device)), _stream()), "attention_prefill (tcgen05)")
+        return out
     if USE_TMA_PREFILL and hd == 64 and page_tokens == 64 and not window and pool.numel() // hd < 2 ** 31:
         # a key tile is a page: K and V by bulk tensor copies
         f = _fn("attention_mma", "fellm_attn_prefill_tma",
@@ -606,6 +619,8 @@ def attention_modules(dtype: str, head_dim: int):
     mods = [("attention_simt", None)]
     if dtype == "bfloat16":
         mods.append(("attention_mma", {"HD": head_dim}))
+        if head_dim == 64 and USE_UMMA_PREFILL:
+            mods.append(("attention_umma", None))
     return mods
 
 

@@ -479,12 +479,19 @@ def test_gemm_bf16_fused_rmsnorm_prologue(M, N, K):
 @pytest.mark.parametrize("H,G,hd,page_tokens,window", [(16, 8, 64, 64, None), (6, 1, 48, 16, None), (4, 4, 128, 32, None),
                                                        (24, 8, 64, 16, None), (8, 1, 16, 16, 70), (5, 5, 80, 8, None),
                                                        (2, 1, 256, 64, 300), (20, 1, 32, 16, None), (4, 4, 64, 64, None),
-                                                       (32, 1, 64, 64, None), (16, 8, 64, 64, 120)])
-def test_attention_prefill_mma(H, G, hd, page_tokens, window):
+                                                       (32, 1, 64, 64, None), (16, 8, 64, 64, 120), (12, 4, 64, 64, None),
+                                                       (16, 1, 64, 64, None)])
+@pytest.mark.parametrize("tcgen05", [True, False])
+def test_attention_prefill_mma(H, G, hd, page_tokens, window, tcgen05, monkeypatch):
     """Items of mixed lengths in one launch (a portion that starts mid-sequence, a whole prompt, a
     single decoded token, two tokens), pages out of order, NaN behind each item's last key in its
     page, against the plain attention.  Head size 64 with pages of 64 tokens and no window takes
-    the TMA kernel."""
+    the tcgen05 kernel where the heads of a kv head divide its 128 rows, else (or with it switched
+    off) the TMA kernel on mma.sync."""
+    takes = hd == 64 and page_tokens == 64 and not window
+    if not tcgen05 and not takes:
+        pytest.skip("the same kernel either way")
+    monkeypatch.setattr(ops, "USE_UMMA_PREFILL", tcgen05)
     torch.manual_seed(H * 3 + hd)
     ctx_before = [150, 0, 700, 33, 0]           # cached positions before this step's rows
     new = [97, 130, 1, 2, 64]                   # rows each item brings
@@ -526,8 +533,10 @@ def test_attention_prefill_mma(H, G, hd, page_tokens, window):
 
 
 @pytest.mark.parametrize("far,qpos", [(0, 999), (63, 999), (64, 999), (935, 999), (936, 1000), (999, 999)])
-def test_attention_prefill_finds_one_far_key(far, qpos):
+@pytest.mark.parametrize("tcgen05", [True, False])
+def test_attention_prefill_finds_one_far_key(far, qpos, tcgen05, monkeypatch):
     """One key stands out among a thousand; the query block straddles it or lies far behind it."""
+    monkeypatch.setattr(ops, "USE_UMMA_PREFILL", tcgen05)
     H, G, hd, pt, C = 4, 2, 64, 64, 1001
     keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
     d = torch.randn(hd); d = d / d.norm()
