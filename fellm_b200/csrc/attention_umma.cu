@@ -3,16 +3,20 @@
 // walks over the pages of keys up to its last token:
 //   S = Q K^T      tcgen05.mma 128x64x16 (kind::f16), Q and the K page K-major in shared memory
 //                  (128-byte swizzle; the page comes by one bulk tensor copy), S in tensor memory;
-//   softmax        four warps, a row a thread: tcgen05.ld of the row's 64 scores, running maximum and
-//                  sum in registers with no shuffles, P rounded to bfloat16 into shared memory;
+//   softmax        a row a thread: tcgen05.ld of the row's 64 scores, running maximum and sum in
+//                  registers with no shuffles, P rounded to bfloat16 into shared memory;
 //   O_tile = P V   tcgen05.mma with the V page as the MN-major operand, into tensor memory;
-//   o = o*corr + O_tile in registers.
-// Roles in a CTA of 192 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
-// owner of the tensor-memory allocation (two score tiles and the P V tile), warps 2-5 = softmax.
+//   o = o*corr + O_tile in registers, one tile late, so that the MMA's latency is not waited for.
+// Two groups of four softmax warps take the even and the odd pages, each with its own running
+// maximum, sum and o, score tile, P tile and P V tile; they are merged through shared memory at the
+// end.  The exponentials bound this kernel (16 a clock an SM): the longest block of a causal prompt
+// sets its duration, and two groups halve that block's chain.
+// Roles in a CTA of 320 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
+// owner of the tensor-memory allocation, warps 2-5 and 6-9 = the softmax groups.
 // Every wait on an mbarrier is bounded (a second, or until another role has given up): a role that
-// gives up records 311..316 in `status`, and every role falls through to the common exit, where
+// gives up records 311..317 in `status`, and every role falls through to the common exit, where
 // tensor memory is freed.
-// The same sums as attention_prefill_kernel (attention_mma.cu) up to the order within a tile's row.
+// The same sums as attention_prefill_kernel (attention_mma.cu) up to the order within a row.
 //
 // FeLLM counterpart: attention_fa2_prefill_paged (plugins/cuda_kernels/src/oxide_kernels.rs:4673,
 // one warp per query row).
@@ -26,7 +30,7 @@
 #define AU_PT 64                       // keys per tile: a page
 #define AU_ROWS 128
 #define AU_STAGES 4
-#define AU_THREADS 192
+#define AU_THREADS 320
 #define AU_TILE_B (AU_PT * 128)        // bytes of one K (or V) page tile
 #define AU_WAIT_NS 1000000000ull
 #define AU_SPIN_LIMIT (1u << 26)
@@ -131,29 +135,30 @@ __device__ __forceinline__ float au_ex2(float x) {
   return y;
 }
 
-// Tensor memory columns: two score tiles (the MMA thread fills one while the softmax warps read the
-// other) and the tile of P V.
+// Tensor memory columns: a score tile and a P V tile for each softmax group.
 #define AU_COL_S 0
 #define AU_COL_O 128
 #define AU_TMEM_COLS 256
+#define AU_MERGE_STRIDE (AU_HD + 2)    // floats of a row's record in the merge buffer: o, m, l
 
-__global__ void __launch_bounds__(AU_THREADS, 2)
+__global__ void __launch_bounds__(AU_THREADS, 1)
 attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuArgs a) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_PREFILL);
   extern __shared__ unsigned char smem_raw[];
-  // full[STAGES], empty[STAGES], q_ready, s_full[2], p_full, o_full
-  __shared__ __align__(8) unsigned long long bars[2 * AU_STAGES + 5];
+  // full[STAGES], empty[STAGES], q_ready, s_full[2], p_full[2], o_full[2]
+  __shared__ __align__(8) unsigned long long bars[2 * AU_STAGES + 7];
   __shared__ unsigned tmem_base_s;
   __shared__ int sm_fail;
-  const int item = blockIdx.z, g = blockIdx.y;
+  const int item = blockIdx.z;
+  const int g = blockIdx.x % a.G, rank = blockIdx.x / a.G;     // CTAs in launch order: the longest blocks of every kv head first
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = a.H / a.G;                                     // divides 128 (the launcher checks)
   const int tokb = AU_ROWS / R;                                // tokens a CTA
   pdl_launch_dependents();
   const int row_begin = a.item_start[item], n_rows = a.item_start[item + 1] - row_begin;
   const int n_blocks = (n_rows + tokb - 1) / tokb;
-  if ((int)blockIdx.x >= n_blocks) return;                     // before any barrier or allocation
-  const int blk = n_blocks - 1 - (int)blockIdx.x;              // the blocks with the most keys start first
+  if (rank >= n_blocks) return;                                // before any barrier or allocation
+  const int blk = n_blocks - 1 - rank;
   const int tok0 = blk * tokb, n_tok = min(tokb, n_rows - tok0);
   const int pos0 = a.positions[row_begin] + tok0;              // position of the block's first token
   const int k_last = pos0 + n_tok - 1;
@@ -161,12 +166,15 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
   const int* bt = a.block_table + (size_t)a.row_slot[row_begin] * a.max_pages;
 
   const unsigned base = (au_smem(smem_raw) + 1023u) & ~1023u;  // the swizzle is by address
-  const unsigned q_s = base, p_s = base + AU_ROWS * 128, stage0 = base + 2 * AU_ROWS * 128;
+  unsigned char* base_ptr = smem_raw + (base - au_smem(smem_raw));
+  const unsigned q_s = base, p_s0 = base + AU_ROWS * 128, stage0 = base + 3 * AU_ROWS * 128;
+  float* merge = (float*)(base_ptr + 3 * AU_ROWS * 128);       // over the stages, once every MMA is done
   const unsigned full0 = au_smem(&bars[0]), empty0 = au_smem(&bars[AU_STAGES]);
-  const unsigned q_ready = au_smem(&bars[2 * AU_STAGES]), s_full0 = q_ready + 8, p_full = q_ready + 24, o_full = q_ready + 32;
+  const unsigned q_ready = au_smem(&bars[2 * AU_STAGES]), s_full0 = q_ready + 8, p_full0 = q_ready + 24, o_full0 = q_ready + 40;
   if (threadIdx.x == 0) {
     for (int s = 0; s < AU_STAGES; ++s) { au_mbar_init(full0 + 8 * s, 1); au_mbar_init(empty0 + 8 * s, 1); }
-    au_mbar_init(q_ready, 4); au_mbar_init(s_full0, 1); au_mbar_init(s_full0 + 8, 1); au_mbar_init(p_full, 4); au_mbar_init(o_full, 1);
+    au_mbar_init(q_ready, 4);
+    for (int b = 0; b < 2; ++b) { au_mbar_init(s_full0 + 8 * b, 1); au_mbar_init(p_full0 + 8 * b, 4); au_mbar_init(o_full0 + 8 * b, 1); }
     sm_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -196,9 +204,10 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // tile j belongs to softmax group j & 1: its score tile, P tile, P V tile and barriers
       const unsigned idesc_s = au_idesc(AU_ROWS, AU_PT, false), idesc_o = au_idesc(AU_ROWS, AU_HD, true);
-      const unsigned long long dq = au_desc(q_s), dp = au_desc(p_s);
-      auto scores = [&](int j) -> bool {                       // S_j = Q K_j^T into score tile j & 1
+      const unsigned long long dq = au_desc(q_s);
+      auto scores = [&](int j) -> bool {                       // S_j = Q K_j^T
         const int s = j % AU_STAGES;
         if (!au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 312)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -216,71 +225,75 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
         if (ok && n_tiles > 1) ok = scores(1);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % AU_STAGES;
-        // P_j lies in shared memory; S_j and the P V tile of j-1 have been read
-        ok = au_wait(p_full, j & 1, fail, a.status, 314);
+        const int s = j % AU_STAGES, grp = j & 1;
+        // P_j lies in shared memory; S_j and the group's P V tile before this one have been read
+        ok = au_wait(p_full0 + 8 * grp, (j >> 1) & 1, fail, a.status, 314);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned long long dp = au_desc(p_s0 + grp * AU_ROWS * 128);
         const unsigned long long dv = au_desc(stage0 + s * 2 * AU_TILE_B + AU_TILE_B, true);
 #pragma unroll
         for (int k = 0; k < AU_PT / 16; ++k)                   // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-          au_mma(tmem_base + AU_COL_O, dp + (unsigned long long)(k * 2), dv + (unsigned long long)(k * 128), idesc_o, k ? 1u : 0u);
-        au_commit(o_full);
+          au_mma(tmem_base + AU_COL_O + grp * AU_HD, dp + (unsigned long long)(k * 2), dv + (unsigned long long)(k * 128), idesc_o, k ? 1u : 0u);
+        au_commit(o_full0 + 8 * grp);
         au_commit(empty0 + 8 * s);                             // the page's stage is free once these MMAs have read it
         if (j + 2 < n_tiles) ok = scores(j + 2);               // into the score tile that S_j has left
       }
     }
   } else {
-    // softmax warps: TMEM lanes 32*(warp%4) .. +32 = the CTA's rows, a row a thread
-    const int qd = warp & 3, row = qd * 32 + lane;
+    // softmax warps: TMEM lanes 32*(warp%4) .. +32 = the CTA's rows, a row a thread; group = which pages
+    const int grp = (warp - 2) >> 2, qd = warp & 3, row = qd * 32 + lane;
     const int tok = row / R, head = row - tok * R;
     const bool valid = tok < n_tok;
     const int pos = pos0 + tok;
     const size_t out_row = ((size_t)(row_begin + tok0 + tok) * a.H + g * R + head) * AU_HD;
-    {
+    if (grp == 0) {
       const uint4* src = (const uint4*)(a.q + out_row);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) au_st_shared16(q_s + au_off(row, ch), valid ? src[ch] : make_uint4(0, 0, 0, 0));
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // these writes before the MMA's reads
+      __syncwarp();
+      if (lane == 0) au_mbar_arrive(q_ready);
     }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // these writes before the MMA's reads
-    __syncwarp();
-    if (lane == 0) au_mbar_arrive(q_ready);
     const unsigned t_row = tmem_base + ((unsigned)(qd * 32) << 16);
+    const unsigned p_s = p_s0 + grp * AU_ROWS * 128;
+    const unsigned s_full = s_full0 + 8 * grp, p_full = p_full0 + 8 * grp, o_full = o_full0 + 8 * grp;
     const float scale = a.scale_log2;
-    // o lags one tile behind: P V of tile j is added (after o has been scaled by tile j's correction)
-    // while tile j+1's scores are already exponentiated, so that the MMA's latency is not waited for
+    // o lags one tile behind: P V of a tile is added (after o has been scaled by that tile's correction)
+    // while the group's next scores are already exponentiated, so that the MMA's latency is not waited for
     float o[AU_HD], m = -INFINITY, l = 0.f, corr_prev = 0.f;
 #pragma unroll
     for (int d = 0; d < AU_HD; ++d) o[d] = 0.f;
-    auto add_pv = [&](int j) -> bool {                         // o = o * (correction of tile j) + P_j V_j
-      if (!au_wait(o_full, j & 1, fail, a.status, 317)) return false;
+    auto add_pv = [&](int i) -> bool {                         // i: the group's i-th tile.  o = o * (its correction) + P V
+      if (!au_wait(o_full, i & 1, fail, a.status, 317)) return false;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 #pragma unroll
       for (int hlf = 0; hlf < 2; ++hlf) {
         float ot[32];
-        au_tmem_ld32(t_row + AU_COL_O + 32 * hlf, ot);
+        au_tmem_ld32(t_row + AU_COL_O + grp * AU_HD + 32 * hlf, ot);
 #pragma unroll
         for (int d = 0; d < 32; ++d) o[32 * hlf + d] = fmaf(o[32 * hlf + d], corr_prev, ot[d]);
       }
       return true;
     };
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int key0 = j * AU_PT, s = j % AU_STAGES;
+    int n_mine = 0;
+    for (int j = grp; j < n_tiles; j += 2, ++n_mine) {
+      const int key0 = j * AU_PT, s = j % AU_STAGES, i = j >> 1;
       if (key0 + AU_PT > k_last + 1) {
         // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
         ok = au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 315);
         if (!ok) break;
         const unsigned v_s = stage0 + s * 2 * AU_TILE_B + AU_TILE_B;
-        for (int i = (k_last + 1 - key0) * 8 + (int)threadIdx.x - 64; i < AU_PT * 8; i += 128)
-          au_st_shared16(v_s + au_off(i >> 3, i & 7), make_uint4(0, 0, 0, 0));
+        for (int e = (k_last + 1 - key0) * 8 + row; e < AU_PT * 8; e += AU_ROWS)
+          au_st_shared16(v_s + au_off(e >> 3, e & 7), make_uint4(0, 0, 0, 0));
       }
-      ok = au_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, fail, a.status, 316);
+      ok = au_wait(s_full, i & 1, fail, a.status, 316);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       float sc[AU_PT];
-      au_tmem_ld32_issue(t_row + AU_COL_S + (j & 1) * AU_PT, sc);
-      au_tmem_ld32_issue(t_row + AU_COL_S + (j & 1) * AU_PT + 32, sc + 32);
+      au_tmem_ld32_issue(t_row + AU_COL_S + grp * AU_PT, sc);
+      au_tmem_ld32_issue(t_row + AU_COL_S + grp * AU_PT + 32, sc + 32);
       au_tmem_ld_wait();
       if (key0 + AU_PT - 1 > pos) {
 #pragma unroll
@@ -292,24 +305,26 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
         r4[0] = fmaxf(r4[0], sc[c]); r4[1] = fmaxf(r4[1], sc[c + 1]); r4[2] = fmaxf(r4[2], sc[c + 2]); r4[3] = fmaxf(r4[3], sc[c + 3]);
       }
       const float raw = fmaxf(fmaxf(r4[0], r4[1]), fmaxf(r4[2], r4[3]));
-      // key 0 counts for every row, so the maximum is finite from the first tile on (rows past the
-      // block's tokens are all zeros and are never stored); the scale is positive
+      // A tile may hold no key that a row sees (the odd group's first page lies behind the rows of a
+      // block's first 64 positions): then nothing changes and P is zero.  The scale is positive.
       const float mx = fmaxf(m, raw * scale);
+      const bool none = mx == -INFINITY;
       const float corr = (m == -INFINITY) ? 0.f : au_ex2(m - mx);
       m = mx;
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned pk[AU_PT / 2];
 #pragma unroll
       for (int c = 0; c < AU_PT; c += 4) {
-        const float p0 = au_ex2(fmaf(sc[c], scale, -mx)), p1 = au_ex2(fmaf(sc[c + 1], scale, -mx));
-        const float p2 = au_ex2(fmaf(sc[c + 2], scale, -mx)), p3 = au_ex2(fmaf(sc[c + 3], scale, -mx));
+        float p0 = au_ex2(fmaf(sc[c], scale, -mx)), p1 = au_ex2(fmaf(sc[c + 1], scale, -mx));
+        float p2 = au_ex2(fmaf(sc[c + 2], scale, -mx)), p3 = au_ex2(fmaf(sc[c + 3], scale, -mx));
+        if (none) { p0 = p1 = p2 = p3 = 0.f; }                  // -inf - -inf is not a number
         s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
         __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
         pk[c >> 1] = *(unsigned*)&pa; pk[(c >> 1) + 1] = *(unsigned*)&pb;
       }
       l = l * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-      if (j > 0) {                                             // also: the MMA has read P of the tile before
-        ok = add_pv(j - 1);
+      if (i > 0) {                                             // also: the MMA has read the group's P of the tile before
+        ok = add_pv(i - 1);
         if (!ok) break;
       }
       corr_prev = corr;
@@ -321,15 +336,33 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
       __syncwarp();
       if (lane == 0) au_mbar_arrive(p_full);
     }
-    if (ok) ok = add_pv(n_tiles - 1);
-    if (ok && valid) {
-      const float inv = 1.0f / l;
+    if (ok && n_mine > 0) ok = add_pv(n_mine - 1);
+    // Both groups are through their last P V tile: every MMA and every copy of this CTA is done, and
+    // the stages are free for the odd group's records.  (A group that gave up still comes to the
+    // barriers; the result is then not stored.)
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (grp == 1) {
+      float* rec = merge + (size_t)row * AU_MERGE_STRIDE;
+#pragma unroll
+      for (int d = 0; d < AU_HD; ++d) rec[d] = o[d];
+      rec[AU_HD] = m; rec[AU_HD + 1] = l;
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    if (grp == 0 && ok && !*fail && valid) {
+      const float* rec = merge + (size_t)row * AU_MERGE_STRIDE;
+      const float m1 = rec[AU_HD], l1 = rec[AU_HD + 1];
+      const float mm = fmaxf(m, m1);                            // the even group has page 0: m is finite
+      const float c0 = au_ex2(m - mm), c1 = (m1 == -INFINITY) ? 0.f : au_ex2(m1 - mm);
+      const float inv = 1.0f / (l * c0 + l1 * c1);
       uint4* dst = (uint4*)(a.out + out_row);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(o[8 * ch] * inv, o[8 * ch + 1] * inv), p1 = __floats2bfloat162_rn(o[8 * ch + 2] * inv, o[8 * ch + 3] * inv);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(o[8 * ch + 4] * inv, o[8 * ch + 5] * inv), p3 = __floats2bfloat162_rn(o[8 * ch + 6] * inv, o[8 * ch + 7] * inv);
-        dst[ch] = make_uint4(*(unsigned*)&p0, *(unsigned*)&p1, *(unsigned*)&p2, *(unsigned*)&p3);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (o[8 * ch + e] * c0 + rec[8 * ch + e] * c1) * inv;
+        __nv_bfloat162 q0 = __floats2bfloat162_rn(v[0], v[1]), q1 = __floats2bfloat162_rn(v[2], v[3]);
+        __nv_bfloat162 q2 = __floats2bfloat162_rn(v[4], v[5]), q3 = __floats2bfloat162_rn(v[6], v[7]);
+        dst[ch] = make_uint4(*(unsigned*)&q0, *(unsigned*)&q1, *(unsigned*)&q2, *(unsigned*)&q3);
       }
     }
   }
@@ -407,9 +440,9 @@ FELLM_API int fellm_attn_prefill_umma(const void* q, const void* pool, long long
   int e = au_pool_map(pool, rows, &map);
   if (e) return e;
   const int tokb = AU_ROWS / (H / G);
-  size_t smem = (size_t)2 * AU_ROWS * 128 + (size_t)AU_STAGES * 2 * AU_TILE_B + 1024;
+  size_t smem = (size_t)3 * AU_ROWS * 128 + (size_t)AU_STAGES * 2 * AU_TILE_B + 1024;     // Q, two P tiles, the stages
   auto kern = attention_prefill_umma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
-  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb), G, n_items), dim3(AU_THREADS), smem, stream, 1, map, a);
+  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb) * G, 1, n_items), dim3(AU_THREADS), smem, stream, 1, map, a);
 }
