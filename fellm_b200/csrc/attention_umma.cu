@@ -3,14 +3,17 @@
 // walks over the pages of keys up to its last token:
 //   S = Q K^T      tcgen05.mma 128x64x16 (kind::f16), Q and the K page K-major in shared memory
 //                  (128-byte swizzle; the page comes by one bulk tensor copy), S in tensor memory;
-//   softmax        a row a thread: tcgen05.ld of the row's 64 scores, running maximum and sum in
-//                  registers with no shuffles, P rounded to bfloat16 into shared memory;
-//   O_tile = P V   tcgen05.mma with the V page as the MN-major operand, into tensor memory;
-//   o = o*corr + O_tile in registers, one tile late, so that the MMA's latency is not waited for.
-// Two groups of four softmax warps take the even and the odd pages, each with its own running
-// maximum, sum and o, score tile, P tile and P V tile; they are merged through shared memory at the
-// end.  The exponentials bound this kernel (16 a clock an SM): the longest block of a causal prompt
-// sets its duration, and two groups halve that block's chain.
+//   softmax        a row a thread: tcgen05.ld of the row's 64 scores, maximum and sum in registers
+//                  with no shuffles, P rounded to bfloat16 into shared memory;
+//   O += P V       tcgen05.mma with the V page as the MN-major operand, accumulated in tensor memory.
+// The accumulator is scaled by 2^-m with m a row's REFERENCE maximum, which moves only when a tile's
+// maximum exceeds it by 2^8: only then is the accumulator read, scaled and written back.
+// Two groups of four softmax warps take the even and the odd pages, each with its own reference,
+// sum and accumulator, two score tiles (the MMA thread runs two tiles a group ahead) and two P tiles
+// (a group need not wait for the MMA that reads the P it has just written); every score tile and P
+// tile has barriers of its own, so that no waiter can fall a phase behind.  The groups are merged
+// through shared memory at the end.  The exponentials (16 a clock an SM) and the many small MMAs
+// bound this kernel; the longest block of a causal prompt sets its duration.
 // Roles in a CTA of 320 threads: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
 // owner of the tensor-memory allocation, warps 2-5 and 6-9 = the softmax groups.
 // Every wait on an mbarrier is bounded (a second, or until another role has given up): a role that
@@ -29,8 +32,11 @@
 #define AU_HD 64
 #define AU_PT 64                       // keys per tile: a page
 #define AU_ROWS 128
-#define AU_STAGES 4
-#define AU_THREADS 320
+#define AU_STAGES 6                    // pages in flight: the scores run two tiles a group ahead of the softmax
+#ifndef AU_GROUPS
+#define AU_GROUPS 2                    // softmax groups of four warps; group g takes pages g, g + AU_GROUPS, ...
+#endif
+#define AU_THREADS (64 + 128 * AU_GROUPS)
 #define AU_TILE_B (AU_PT * 128)        // bytes of one K (or V) page tile
 #define AU_WAIT_NS 1000000000ull
 #define AU_SPIN_LIMIT (1u << 26)
@@ -123,6 +129,18 @@ __device__ __forceinline__ void au_tmem_ld32(unsigned taddr, float* v) {
   au_tmem_ld32_issue(taddr, v);
   au_tmem_ld_wait();
 }
+__device__ __forceinline__ void au_tmem_st32(unsigned taddr, const float* v) {
+  const unsigned* r = reinterpret_cast<const unsigned*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+         "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+         "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void au_tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void au_st_shared16(unsigned addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -135,18 +153,22 @@ __device__ __forceinline__ float au_ex2(float x) {
   return y;
 }
 
-// Tensor memory columns: a score tile and a P V tile for each softmax group.
+// Tensor memory columns: two score tiles (one being read while the MMA thread fills the other) and an
+// accumulator of P V for each softmax group.
 #define AU_COL_S 0
-#define AU_COL_O 128
-#define AU_TMEM_COLS 256
+#define AU_COL_O (2 * AU_GROUPS * AU_PT)
+#define AU_TMEM_COLS 512
+static_assert(3 * AU_GROUPS * 64 <= AU_TMEM_COLS, "tensor memory: 192 columns a group");
 #define AU_MERGE_STRIDE (AU_HD + 2)    // floats of a row's record in the merge buffer: o, m, l
+#define AU_RESCALE_AT 8.0f             // a row's reference maximum moves when a tile's maximum is 2^8 above it
 
 __global__ void __launch_bounds__(AU_THREADS, 1)
 attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuArgs a) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_PREFILL);
   extern __shared__ unsigned char smem_raw[];
-  // full[STAGES], empty[STAGES], q_ready, s_full[2], p_full[2], o_full[2]
-  __shared__ __align__(8) unsigned long long bars[2 * AU_STAGES + 7];
+  // full[STAGES], empty[STAGES], q_ready, s_full[GROUPS][2], p_full[GROUPS][2], o_full[GROUPS][2]: a barrier
+  // for each of a group's two score tiles and two P tiles, so that no waiter is ever a phase behind
+  __shared__ __align__(8) unsigned long long bars[2 * AU_STAGES + 1 + 6 * AU_GROUPS];
   __shared__ unsigned tmem_base_s;
   __shared__ int sm_fail;
   const int item = blockIdx.z;
@@ -167,14 +189,18 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
 
   const unsigned base = (au_smem(smem_raw) + 1023u) & ~1023u;  // the swizzle is by address
   unsigned char* base_ptr = smem_raw + (base - au_smem(smem_raw));
-  const unsigned q_s = base, p_s0 = base + AU_ROWS * 128, stage0 = base + 3 * AU_ROWS * 128;
-  float* merge = (float*)(base_ptr + 3 * AU_ROWS * 128);       // over the stages, once every MMA is done
+  const unsigned q_s = base, p_s0 = base + AU_ROWS * 128, stage0 = base + (1 + 2 * AU_GROUPS) * AU_ROWS * 128;
+  float* merge = (float*)(base_ptr + AU_ROWS * 128);           // over the P tiles and the stages, once every MMA is done
   const unsigned full0 = au_smem(&bars[0]), empty0 = au_smem(&bars[AU_STAGES]);
-  const unsigned q_ready = au_smem(&bars[2 * AU_STAGES]), s_full0 = q_ready + 8, p_full0 = q_ready + 24, o_full0 = q_ready + 40;
+  const unsigned q_ready = au_smem(&bars[2 * AU_STAGES]), s_full0 = q_ready + 8, p_full0 = s_full0 + 16 * AU_GROUPS,
+                 o_full0 = p_full0 + 16 * AU_GROUPS;
   if (threadIdx.x == 0) {
     for (int s = 0; s < AU_STAGES; ++s) { au_mbar_init(full0 + 8 * s, 1); au_mbar_init(empty0 + 8 * s, 1); }
     au_mbar_init(q_ready, 4);
-    for (int b = 0; b < 2; ++b) { au_mbar_init(s_full0 + 8 * b, 1); au_mbar_init(p_full0 + 8 * b, 4); au_mbar_init(o_full0 + 8 * b, 1); }
+    for (int b = 0; b < AU_GROUPS; ++b) {
+      au_mbar_init(s_full0 + 16 * b, 1); au_mbar_init(s_full0 + 16 * b + 8, 1); au_mbar_init(p_full0 + 16 * b, 4); au_mbar_init(p_full0 + 16 * b + 8, 4);
+      au_mbar_init(o_full0 + 16 * b, 1); au_mbar_init(o_full0 + 16 * b + 8, 1);
+    }
     sm_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -204,40 +230,38 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // tile j belongs to softmax group j & 1: its score tile, P tile, P V tile and barriers
+      // tile j belongs to softmax group j % GROUPS: its score tile, P tile, accumulator and barriers
       const unsigned idesc_s = au_idesc(AU_ROWS, AU_PT, false), idesc_o = au_idesc(AU_ROWS, AU_HD, true);
       const unsigned long long dq = au_desc(q_s);
-      auto scores = [&](int j) -> bool {                       // S_j = Q K_j^T
-        const int s = j % AU_STAGES;
+      auto scores = [&](int j) -> bool {                       // S_j = Q K_j^T into the group's score tile (j / GROUPS) & 1
+        const int s = j % AU_STAGES, grp = j % AU_GROUPS, sb = (j / AU_GROUPS) & 1;
         if (!au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 312)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const unsigned long long dk = au_desc(stage0 + s * 2 * AU_TILE_B);
 #pragma unroll
         for (int k = 0; k < AU_HD / 16; ++k)                   // 32 bytes further along the head inside the swizzle atom
-          au_mma(tmem_base + AU_COL_S + (j & 1) * AU_PT, dq + (unsigned long long)(k * 2), dk + (unsigned long long)(k * 2), idesc_s, k ? 1u : 0u);
-        au_commit(s_full0 + 8 * (j & 1));
+          au_mma(tmem_base + AU_COL_S + (2 * grp + sb) * AU_PT, dq + (unsigned long long)(k * 2), dk + (unsigned long long)(k * 2), idesc_s, k ? 1u : 0u);
+        au_commit(s_full0 + 16 * grp + 8 * sb);
         return true;
       };
       bool ok = au_wait(q_ready, 0, fail, a.status, 313);
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        ok = scores(0);
-        if (ok && n_tiles > 1) ok = scores(1);
-      }
+      if (ok) asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      for (int j = 0; j < 2 * AU_GROUPS && j < n_tiles && ok; ++j) ok = scores(j);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % AU_STAGES, grp = j & 1;
-        // P_j lies in shared memory; S_j and the group's P V tile before this one have been read
-        ok = au_wait(p_full0 + 8 * grp, (j >> 1) & 1, fail, a.status, 314);
+        const int s = j % AU_STAGES, grp = j % AU_GROUPS, i = j / AU_GROUPS;
+        // P_j lies in shared memory, S_j has been read, and the accumulator is scaled to P_j's reference
+        ok = au_wait(p_full0 + 16 * grp + 8 * (i & 1), (i >> 1) & 1, fail, a.status, 314);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        const unsigned long long dp = au_desc(p_s0 + grp * AU_ROWS * 128);
+        const unsigned long long dp = au_desc(p_s0 + (2 * grp + (i & 1)) * AU_ROWS * 128);
         const unsigned long long dv = au_desc(stage0 + s * 2 * AU_TILE_B + AU_TILE_B, true);
 #pragma unroll
         for (int k = 0; k < AU_PT / 16; ++k)                   // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-          au_mma(tmem_base + AU_COL_O + grp * AU_HD, dp + (unsigned long long)(k * 2), dv + (unsigned long long)(k * 128), idesc_o, k ? 1u : 0u);
-        au_commit(o_full0 + 8 * grp);
+          au_mma(tmem_base + AU_COL_O + grp * AU_HD, dp + (unsigned long long)(k * 2), dv + (unsigned long long)(k * 128), idesc_o,
+                 (i | k) ? 1u : 0u);                           // the group's first tile starts its accumulator
+        au_commit(o_full0 + 16 * grp + 8 * (i & 1));
         au_commit(empty0 + 8 * s);                             // the page's stage is free once these MMAs have read it
-        if (j + 2 < n_tiles) ok = scores(j + 2);               // into the score tile that S_j has left
+        if (j + 2 * AU_GROUPS < n_tiles) ok = scores(j + 2 * AU_GROUPS);   // into the score tile that S_j has left
       }
     }
   } else {
@@ -256,30 +280,17 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
       if (lane == 0) au_mbar_arrive(q_ready);
     }
     const unsigned t_row = tmem_base + ((unsigned)(qd * 32) << 16);
-    const unsigned p_s = p_s0 + grp * AU_ROWS * 128;
-    const unsigned s_full = s_full0 + 8 * grp, p_full = p_full0 + 8 * grp, o_full = o_full0 + 8 * grp;
+    const unsigned t_acc = t_row + AU_COL_O + grp * AU_HD;
+    const unsigned s_full = s_full0 + 16 * grp, p_full = p_full0 + 16 * grp, o_full = o_full0 + 16 * grp;
     const float scale = a.scale_log2;
-    // o lags one tile behind: P V of a tile is added (after o has been scaled by that tile's correction)
-    // while the group's next scores are already exponentiated, so that the MMA's latency is not waited for
-    float o[AU_HD], m = -INFINITY, l = 0.f, corr_prev = 0.f;
-#pragma unroll
-    for (int d = 0; d < AU_HD; ++d) o[d] = 0.f;
-    auto add_pv = [&](int i) -> bool {                         // i: the group's i-th tile.  o = o * (its correction) + P V
-      if (!au_wait(o_full, i & 1, fail, a.status, 317)) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        float ot[32];
-        au_tmem_ld32(t_row + AU_COL_O + grp * AU_HD + 32 * hlf, ot);
-#pragma unroll
-        for (int d = 0; d < 32; ++d) o[32 * hlf + d] = fmaf(o[32 * hlf + d], corr_prev, ot[d]);
-      }
-      return true;
-    };
+    // The accumulator of P V stays in tensor memory, scaled by 2^-m where m is the row's REFERENCE
+    // maximum; m only moves when a tile's maximum exceeds it by AU_RESCALE_AT (P then stays below 2^8,
+    // well inside bfloat16 and float32), and only then is the accumulator read, scaled and written back.
+    float m = -INFINITY, l = 0.f;
     bool ok = true;
     int n_mine = 0;
-    for (int j = grp; j < n_tiles; j += 2, ++n_mine) {
-      const int key0 = j * AU_PT, s = j % AU_STAGES, i = j >> 1;
+    for (int j = grp; j < n_tiles; j += AU_GROUPS, ++n_mine) {
+      const int key0 = j * AU_PT, s = j % AU_STAGES, i = n_mine;
       if (key0 + AU_PT > k_last + 1) {
         // rows past the last key hold whatever the page held before: zero the V rows, so that 0 * V is 0
         ok = au_wait(full0 + 8 * s, (j / AU_STAGES) & 1, fail, a.status, 315);
@@ -288,12 +299,12 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
         for (int e = (k_last + 1 - key0) * 8 + row; e < AU_PT * 8; e += AU_ROWS)
           au_st_shared16(v_s + au_off(e >> 3, e & 7), make_uint4(0, 0, 0, 0));
       }
-      ok = au_wait(s_full, i & 1, fail, a.status, 316);
+      ok = au_wait(s_full + 8 * (i & 1), (i >> 1) & 1, fail, a.status, 316);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       float sc[AU_PT];
-      au_tmem_ld32_issue(t_row + AU_COL_S + grp * AU_PT, sc);
-      au_tmem_ld32_issue(t_row + AU_COL_S + grp * AU_PT + 32, sc + 32);
+      au_tmem_ld32_issue(t_row + AU_COL_S + (2 * grp + (i & 1)) * AU_PT, sc);
+      au_tmem_ld32_issue(t_row + AU_COL_S + (2 * grp + (i & 1)) * AU_PT + 32, sc + 32);
       au_tmem_ld_wait();
       if (key0 + AU_PT - 1 > pos) {
 #pragma unroll
@@ -304,64 +315,106 @@ attention_prefill_umma_kernel(const __grid_constant__ CUtensorMap pool_map, AuAr
       for (int c = 4; c < AU_PT; c += 4) {
         r4[0] = fmaxf(r4[0], sc[c]); r4[1] = fmaxf(r4[1], sc[c + 1]); r4[2] = fmaxf(r4[2], sc[c + 2]); r4[3] = fmaxf(r4[3], sc[c + 3]);
       }
-      const float raw = fmaxf(fmaxf(r4[0], r4[1]), fmaxf(r4[2], r4[3]));
-      // A tile may hold no key that a row sees (the odd group's first page lies behind the rows of a
-      // block's first 64 positions): then nothing changes and P is zero.  The scale is positive.
-      const float mx = fmaxf(m, raw * scale);
-      const bool none = mx == -INFINITY;
-      const float corr = (m == -INFINITY) ? 0.f : au_ex2(m - mx);
-      m = mx;
+      const float tile_max = fmaxf(fmaxf(r4[0], r4[1]), fmaxf(r4[2], r4[3])) * scale;      // the scale is positive
+      // A tile may hold no key that a row sees (a later group's first page lies behind the rows of a
+      // block's first positions): its maximum is -inf, nothing moves and P is zero.
+      const bool move = tile_max > m + AU_RESCALE_AT || (m == -INFINITY && tile_max > -INFINITY);
+      float corr = 1.f;
+      if (move) {
+        corr = (m == -INFINITY) ? 0.f : au_ex2(m - tile_max);
+        m = tile_max;
+        l *= corr;
+      }
+      const bool none = m == -INFINITY;
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
       unsigned pk[AU_PT / 2];
 #pragma unroll
       for (int c = 0; c < AU_PT; c += 4) {
-        float p0 = au_ex2(fmaf(sc[c], scale, -mx)), p1 = au_ex2(fmaf(sc[c + 1], scale, -mx));
-        float p2 = au_ex2(fmaf(sc[c + 2], scale, -mx)), p3 = au_ex2(fmaf(sc[c + 3], scale, -mx));
+        float p0 = au_ex2(fmaf(sc[c], scale, -m)), p1 = au_ex2(fmaf(sc[c + 1], scale, -m));
+        float p2 = au_ex2(fmaf(sc[c + 2], scale, -m)), p3 = au_ex2(fmaf(sc[c + 3], scale, -m));
         if (none) { p0 = p1 = p2 = p3 = 0.f; }                  // -inf - -inf is not a number
         s4[0] += p0; s4[1] += p1; s4[2] += p2; s4[3] += p3;
         __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
         pk[c >> 1] = *(unsigned*)&pa; pk[(c >> 1) + 1] = *(unsigned*)&pb;
       }
-      l = l * corr + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
-      if (i > 0) {                                             // also: the MMA has read the group's P of the tile before
-        ok = add_pv(i - 1);
+      l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      // two P tiles a group: this one is free once the MMA of the group's tile before the last has read it
+      if (i > 1) {
+        ok = au_wait(o_full + 8 * (i & 1), ((i - 2) >> 1) & 1, fail, a.status, 317);
         if (!ok) break;
       }
-      corr_prev = corr;
+      if (i > 0 && __any_sync(0xffffffffu, move)) {
+        // some row of the warp moved its reference: scale the warp's rows of the accumulator, once the
+        // MMA of the tile before has added into it
+        ok = au_wait(o_full + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, fail, a.status, 317);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          float ot[32];
+          au_tmem_ld32(t_acc + 32 * hlf, ot);
+#pragma unroll
+          for (int d = 0; d < 32; ++d) ot[d] *= corr;
+          au_tmem_st32(t_acc + 32 * hlf, ot);
+        }
+        au_tmem_st_wait();
+      }
+      const unsigned p_s = p_s0 + (2 * grp + (i & 1)) * AU_ROWS * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch)
         au_st_shared16(p_s + au_off(row, ch), make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]));
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // P (and the zeroed V rows) before the MMA's reads
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) au_mbar_arrive(p_full);
+      if (lane == 0) au_mbar_arrive(p_full + 8 * (i & 1));
     }
-    if (ok && n_mine > 0) ok = add_pv(n_mine - 1);
-    // Both groups are through their last P V tile: every MMA and every copy of this CTA is done, and
-    // the stages are free for the odd group's records.  (A group that gave up still comes to the
-    // barriers; the result is then not stored.)
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
-    if (grp == 1) {
-      float* rec = merge + (size_t)row * AU_MERGE_STRIDE;
+    float o[AU_HD];
+    if (ok && n_mine > 0) {
+      ok = au_wait(o_full + 8 * ((n_mine - 1) & 1), ((n_mine - 1) >> 1) & 1, fail, a.status, 317);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        au_tmem_ld32_issue(t_acc, o);
+        au_tmem_ld32_issue(t_acc + 32, o + 32);
+        au_tmem_ld_wait();
+      }
+    }
+    if (n_mine == 0 || !ok) {
+#pragma unroll
+      for (int d = 0; d < AU_HD; ++d) o[d] = 0.f;
+    }
+    // Every group is through its last tile: every MMA and every copy of this CTA is done, and the P
+    // tiles and stages are free for the later groups' records.  (A group that gave up still comes to
+    // the barriers; the result is then not stored.)
+    asm volatile("bar.sync 1, %0;\n" ::"n"(128 * AU_GROUPS) : "memory");
+    if (grp > 0) {
+      float* rec = merge + ((size_t)(grp - 1) * AU_ROWS + row) * AU_MERGE_STRIDE;
 #pragma unroll
       for (int d = 0; d < AU_HD; ++d) rec[d] = o[d];
       rec[AU_HD] = m; rec[AU_HD + 1] = l;
     }
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+    asm volatile("bar.sync 1, %0;\n" ::"n"(128 * AU_GROUPS) : "memory");
     if (grp == 0 && ok && !*fail && valid) {
-      const float* rec = merge + (size_t)row * AU_MERGE_STRIDE;
-      const float m1 = rec[AU_HD], l1 = rec[AU_HD + 1];
-      const float mm = fmaxf(m, m1);                            // the even group has page 0: m is finite
-      const float c0 = au_ex2(m - mm), c1 = (m1 == -INFINITY) ? 0.f : au_ex2(m1 - mm);
-      const float inv = 1.0f / (l * c0 + l1 * c1);
+      float mm = m;                                            // group 0 has page 0: m is finite
+#pragma unroll
+      for (int q = 0; q < AU_GROUPS - 1; ++q) mm = fmaxf(mm, merge[((size_t)q * AU_ROWS + row) * AU_MERGE_STRIDE + AU_HD]);
+      const float c0 = au_ex2(m - mm);
+      float lt = l * c0;
+#pragma unroll
+      for (int d = 0; d < AU_HD; ++d) o[d] *= c0;
+#pragma unroll
+      for (int q = 0; q < AU_GROUPS - 1; ++q) {
+        const float* rec = merge + ((size_t)q * AU_ROWS + row) * AU_MERGE_STRIDE;
+        const float mq = rec[AU_HD], cq = (mq == -INFINITY) ? 0.f : au_ex2(mq - mm);
+        lt = fmaf(rec[AU_HD + 1], cq, lt);
+#pragma unroll
+        for (int d = 0; d < AU_HD; ++d) o[d] = fmaf(rec[d], cq, o[d]);
+      }
+      const float inv = 1.0f / lt;
       uint4* dst = (uint4*)(a.out + out_row);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = (o[8 * ch + e] * c0 + rec[8 * ch + e] * c1) * inv;
-        __nv_bfloat162 q0 = __floats2bfloat162_rn(v[0], v[1]), q1 = __floats2bfloat162_rn(v[2], v[3]);
-        __nv_bfloat162 q2 = __floats2bfloat162_rn(v[4], v[5]), q3 = __floats2bfloat162_rn(v[6], v[7]);
+        __nv_bfloat162 q0 = __floats2bfloat162_rn(o[8 * ch] * inv, o[8 * ch + 1] * inv), q1 = __floats2bfloat162_rn(o[8 * ch + 2] * inv, o[8 * ch + 3] * inv);
+        __nv_bfloat162 q2 = __floats2bfloat162_rn(o[8 * ch + 4] * inv, o[8 * ch + 5] * inv), q3 = __floats2bfloat162_rn(o[8 * ch + 6] * inv, o[8 * ch + 7] * inv);
         dst[ch] = make_uint4(*(unsigned*)&q0, *(unsigned*)&q1, *(unsigned*)&q2, *(unsigned*)&q3);
       }
     }
@@ -440,7 +493,7 @@ FELLM_API int fellm_attn_prefill_umma(const void* q, const void* pool, long long
   int e = au_pool_map(pool, rows, &map);
   if (e) return e;
   const int tokb = AU_ROWS / (H / G);
-  size_t smem = (size_t)3 * AU_ROWS * 128 + (size_t)AU_STAGES * 2 * AU_TILE_B + 1024;     // Q, two P tiles, the stages
+  size_t smem = (size_t)(1 + 2 * AU_GROUPS) * AU_ROWS * 128 + (size_t)AU_STAGES * 2 * AU_TILE_B + 1024;     // Q, the P tiles, the stages
   auto kern = attention_prefill_umma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
