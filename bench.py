@@ -3,14 +3,23 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-One JSON line on stdout.  `value`: decoded tokens a second at batch 8, contexts growing from the
-2,048-token prompts (K = 2048 steps reach 4,096), timed on the device with CUDA events around K
-decode steps that include greedy sampling and feed the sampled tokens back on the device.
+One JSON line on stdout.  `value`: decoded tokens a second at batch 8 over the LAST K decode steps
+before the contexts (2,048-token prompts, grown by decoding) reach 4,096: K = 2048 times the whole
+growth from 2,048 to 4,096, a smaller K the steps that end at 4,096, the steps before them running
+untimed; `metric` and `config` name the contexts the timed steps covered.  Timed on the device with
+CUDA events around K decode steps that include greedy sampling and feed the sampled tokens back on
+the device.
 `e2e`: the same through the Python entry point's scheduler (host tokens in from pinned memory and
 out every step).  `prefill`: one 2,048-token prompt in one step.  `roofline`: bytes the decode step
 has to read (every weight once, the live requests' cache and conv state) / its time, against the
 measured copy bandwidth.  `points`: decode at batch 1 and 64.  The engine works on one GPU:
 --gpus N > 1 prints a line that says so and exits with 2.
+
+    python bench.py --shape 700m --workload mixed        # prompts of 128..4096 ids in portions of 512 beside decode tokens
+    python bench.py --shape 1.2b --workload concurrent   # 64 requests x 2,048-id prompts x 512 steps at temperature 0.8
+
+print one line each for the two other workloads of the benchmark (through the scheduler, host
+tokens in and out); `--workloads` adds both lines to the headline line under "workloads".
 """
 import argparse
 import json
@@ -32,6 +41,15 @@ LFM2_350M = dict(   # the 350M shape of the benchmark: 16 layers, attention at 2
     tie_word_embeddings=True, max_position_embeddings=128000)
 SEED = 2
 PROMPT, CONTEXT_END, PREFILL_TOKENS = 2048, 4096, 2048
+# the other shapes of the benchmark: same layers and vocabulary, (hidden, heads, block_ff_dim, seed)
+SHAPES = {"350m": (1024, 16, 6656, 2), "700m": (1536, 24, 10752, 3), "1.2b": (2048, 32, 12288, 4)}
+
+
+def shape_config(name):
+    hidden, heads, ff, seed = SHAPES[name]
+    cfg = dict(LFM2_350M)
+    cfg.update(hidden_size=hidden, num_attention_heads=heads, block_ff_dim=ff)
+    return cfg, seed
 
 
 def peaks():
@@ -94,9 +112,10 @@ def flops_per_token(cfg, n_layers_attn, context):
     return 2 * mm, 2 * V * d, 4 * H * hd * n_layers_attn        # matmul flops/token, head flops/row, attention flops per (token, key)
 
 
-def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT):
-    """Prefills `batch` requests of `prompt` random ids, then times `steps` decode steps on the
-    device.  Returns (tokens/s, ms/step, launches in the timed region, mean context)."""
+def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CONTEXT_END):
+    """Prefills `batch` requests of `prompt` random ids, decodes untimed until `steps` steps are left
+    before the contexts reach `context_end` (at least `warmup` steps), then times those on the device.
+    Returns (tokens/s, ms/step, launches in the timed region, mean context, first and last context)."""
     import torch
     from fellm_b200.engine import GenParams, StepItem
     vocab = engine.spec.vocab_size
@@ -113,11 +132,12 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT):
     engine.check_status()
     tokens = first.clone()
     items = [StepItem(r, [0], [0]) for r in reqs]
+    step = engine.stepper.step                      # the step function itself: its logits are read by the sampler at once
     def one():
         nonlocal tokens
-        logits = engine.step(items, device_tokens=tokens)
+        logits = step(items, device_tokens=tokens)
         tokens = engine.sampler.sample(logits, rows)
-    for _ in range(warmup):
+    for _ in range(max(warmup, context_end - prompt - steps)):
         one()
     torch.cuda.synchronize()
     l0 = engine.stepper.launches
@@ -132,10 +152,10 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT):
     ms = e0.elapsed_time(e1)
     engine.check_status()
     launches = engine.stepper.launches - l0 + 2 * (engine.stepper.steps_run - s0)   # + the two argmax kernels a step
-    mean_ctx = ctx0 + steps / 2
+    mean_ctx = ctx0 + (steps + 1) / 2                # a step at cache length c reads c + 1 positions
     for r in reqs:
         engine.release(r)
-    return batch * steps / (ms / 1e3), ms / steps, launches, mean_ctx
+    return batch * steps / (ms / 1e3), ms / steps, launches, mean_ctx, ctx0 + 1, ctx0 + steps
 
 
 def run_timeline(engine, batch, context, out_path):
@@ -195,11 +215,12 @@ def run_e2e(engine, batch, steps, warmup, rng):
     from fellm_b200.engine import GenParams
     sched = engine.scheduler()
     vocab = engine.spec.vocab_size
+    ahead = max(warmup, CONTEXT_END - PROMPT - steps)            # untimed steps: the timed ones end at CONTEXT_END
     for _ in range(batch):
-        sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(warmup + steps + 8))
+        sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(ahead + steps + 8))
     while any(r.prefilling for r in list(sched.running) + list(sched.waiting)) or sched.waiting:
         sched.step()
-    for _ in range(warmup):
+    for _ in range(ahead):
         sched.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -240,6 +261,125 @@ def run_prefill(engine, tokens, reps, rng):
     return times[len(times) // 2]
 
 
+def run_mixed_workload(engine, rng, n_requests, max_new):
+    """Prompts of 128..4,096 random ids through the scheduler (n_ubatch 512: prompt portions of up to
+    512 tokens beside the decode tokens of the requests already generating), greedy, max_new tokens
+    each.  The figures are FeLLM's (crates/fellm-cli/src/main.rs:953-967, crates/fellm-runtime/src/
+    engine.rs:230-264): prompt eval = prompt tokens / time to the first token, eval = generated
+    tokens / time after it, here as means over the requests, beside the batch's own totals."""
+    import torch
+    from fellm_b200.engine import GenParams
+    sched = engine.scheduler()
+    vocab = engine.spec.vocab_size
+    lens = [int(n) for n in rng.integers(128, 4097, n_requests)]
+    base = dict(sched.counters)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for n in lens:
+        sched.enqueue_ids(rng.integers(0, vocab, n).tolist(), GenParams.greedy(max_new))
+    stats, n_tok = [], 0
+    while not sched.idle():
+        for ev in sched.step():
+            if ev.kind == "token":
+                n_tok += 1
+            elif ev.kind == "done":
+                stats.append(ev.stats)
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    c = {k: sched.counters[k] - base.get(k, 0) for k in sched.counters}
+    return {"requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": n_tok, "wall_s": round(wall, 3),
+            "tokens_per_s": round((sum(lens) + n_tok) / wall, 1),
+            "prompt_eval_tok_s_mean": round(sum(s.prompt_tok_per_sec() for s in stats) / len(stats), 1),
+            "eval_tok_s_mean": round(sum(s.generation_tok_per_sec() for s in stats) / len(stats), 1),
+            "steps": c["steps"], "rows_per_step_mean": round(c["tokens_run"] / max(c["steps"], 1), 1),
+            "mixed_step_share": round(c["mixed_steps"] / max(c["steps"], 1), 3), "preempted": c["preempted"],
+            "n_ubatch": sched.n_ubatch, "n_batch": sched.n_batch}
+
+
+def run_concurrent_workload(engine, rng, n_requests, prompt, steps, temperature, hbm):
+    """n_requests prompts of `prompt` random ids admitted together, `steps` tokens each, sampled at
+    `temperature` over the whole vocabulary (no top-k, no penalties) by the sampling kernel inside the
+    loop; through the scheduler, host tokens out every step.  Decode figures cover the steps in which
+    every request decodes."""
+    import torch
+    from fellm_b200.engine import GenParams
+    sched = engine.scheduler()
+    vocab = engine.spec.vocab_size
+    params = GenParams(max_tokens=steps, temperature=temperature, top_k=0, top_p=1.0, min_p=0.0, seed=7,
+                       repetition_penalty=1.0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(n_requests):
+        sched.enqueue_ids(rng.integers(0, vocab, prompt).tolist(), params)
+    n_tok, t_decode, tok_at_decode, ctx_sum, dec_steps = 0, None, 0, 0.0, 0
+    distinct = set()
+    while not sched.idle():
+        all_decode = (not sched.waiting and len(sched.running) == n_requests
+                      and not any(r.prefilling for r in sched.running))
+        if all_decode and t_decode is None:
+            torch.cuda.synchronize()
+            t_decode, tok_at_decode = time.perf_counter(), n_tok
+        if all_decode:
+            ctx_sum += sum(engine.cache.length(r.id) for r in sched.running) / n_requests + 1
+            dec_steps += 1
+        for ev in sched.step():
+            if ev.kind == "token":
+                n_tok += 1
+                distinct.add(ev.token)
+            elif ev.kind == "error":
+                raise RuntimeError(ev.message)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    prefill_s, decode_s = t_decode - t0, t1 - t_decode
+    mean_ctx = ctx_sum / max(dec_steps, 1)
+    wbytes = model_bytes(engine)
+    state_bytes = sum(g.bytes_per_request() for g in engine.cache.fixed)
+    step_bytes = wbytes + n_requests * (mean_ctx * engine.cache.bytes_per_token() + 2 * state_bytes)
+    ms_step = decode_s / max(dec_steps, 1) * 1e3
+    return {"requests": n_requests, "prompt_len": prompt, "decode_steps": dec_steps, "temperature": temperature,
+            "prompt_eval_tok_s": round(n_requests * prompt / prefill_s, 1),
+            "decode_tok_s": round((n_tok - tok_at_decode) / decode_s, 1), "ms_per_step": round(ms_step, 4),
+            "context_mean": round(mean_ctx, 1), "distinct_tokens": len(distinct),
+            "roofline_frac": round(step_bytes / (ms_step / 1e3) / 1e9 / hbm, 4), "weights_mb": wbytes // 1000000}
+
+
+def workload_engine(shape, workload, layers=None):
+    from fellm_b200.config import EngineOptions
+    from fellm_b200.engine import Engine
+    cfg, seed = shape_config(shape)
+    if layers and layers < cfg["num_hidden_layers"]:
+        cfg["num_hidden_layers"] = layers
+        cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < layers]
+    if workload == "mixed":
+        opts = EngineOptions(dtype="bfloat16", n_ctx=8192, n_batch=2048, n_ubatch=512, page_tokens=64, max_requests=16,
+                             max_tokens=16 * 4480, cuda_graphs=True)
+    else:
+        opts = EngineOptions(dtype="bfloat16", n_ctx=4096, n_batch=4096, n_ubatch=2048, page_tokens=64, max_requests=64,
+                             max_tokens=64 * 2624, cuda_graphs=True)
+    return Engine.random(cfg, seed, opts)
+
+
+def run_workload(shape, workload, hbm, layers=None):
+    import numpy as np
+    import torch
+    engine = workload_engine(shape, workload, layers)
+    rng = np.random.default_rng(SHAPES[shape][3])
+    c = engine.config
+    if workload == "mixed":
+        run_mixed_workload(engine, np.random.default_rng(0), 4, 8)          # kernels loaded, graphs of the common shapes captured
+        out = run_mixed_workload(engine, rng, 32, 128)
+    else:
+        run_concurrent_workload(engine, np.random.default_rng(0), 64, 128, 8, 0.8, hbm)
+        out = run_concurrent_workload(engine, rng, 64, 2048, 512, 0.8, hbm)
+    out.update(shape=shape, workload=workload, hidden=c.hidden_size, heads=c.num_attention_heads, ff=c.ff_dim,
+               layers=c.num_hidden_layers, dtype="bf16")
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -249,6 +389,11 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="350m")
+    ap.add_argument("--workload", choices=["mixed", "concurrent"], default=None,
+                    help="run one of the other workloads of the benchmark at --shape and print its line")
+    ap.add_argument("--workloads", action="store_true",
+                    help="after the headline measurement, run 700m/mixed and 1.2b/concurrent and add them under 'workloads'")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling a small case; not a bench value)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
@@ -269,20 +414,28 @@ def main():
     from fellm_b200.config import EngineOptions
     from fellm_b200.engine import Engine
 
+    hbm, tf_burst, tf_sus, src = peaks()
+    if args.workload:
+        clocks = ClockSampler()
+        clocks.start()
+        out = run_workload(args.shape, args.workload, hbm, args.layers)
+        out["clocks"] = clocks.stop()
+        print(json.dumps(out))
+        return 0
+
     warmup = max(args.warmup, 3)
-    cfg = dict(LFM2_350M)
+    cfg, seed = shape_config(args.shape)
     full_layers = cfg["num_hidden_layers"]
     if args.layers and args.layers < full_layers:
         cfg["num_hidden_layers"] = args.layers
         cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < args.layers]
     steps = args.steps
-    ctx_end = PROMPT + warmup + steps + 16
+    ctx_end = PROMPT + max(warmup, CONTEXT_END - PROMPT - steps) + steps + 16
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
     opts = EngineOptions(dtype="bfloat16", n_ctx=max(ctx_end, CONTEXT_END + 64), n_batch=4096, n_ubatch=2048, page_tokens=64,
                          max_requests=max_batch, max_tokens=max_batch * (max(ctx_end, CONTEXT_END) + 64), cuda_graphs=True)
-    engine = Engine.random(cfg, SEED, opts)
-    rng = np.random.default_rng(SEED)
-    hbm, tf_burst, tf_sus, src = peaks()
+    engine = Engine.random(cfg, seed, opts)
+    rng = np.random.default_rng(seed)
     clocks = ClockSampler()
     clocks.start()
 
@@ -293,14 +446,15 @@ def main():
         return 0
     if args.only:
         if args.only == "decode":
-            v, ms, _, _ = run_decode(engine, args.batch, steps, warmup, rng)
-            print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg["num_hidden_layers"], "tokens_per_s": round(v, 1), "ms_per_step": round(ms, 4)}))
+            v, ms, _, _, c0, c1 = run_decode(engine, args.batch, steps, warmup, rng, context_end=args.context + warmup + steps)
+            print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg["num_hidden_layers"], "tokens_per_s": round(v, 1),
+                              "ms_per_step": round(ms, 4), "contexts": [c0, c1]}))
         else:
             ms = run_prefill(engine, PREFILL_TOKENS, max(1, min(steps, 5)), rng)
             print(json.dumps({"only": "prefill", "layers": cfg["num_hidden_layers"], "tokens": PREFILL_TOKENS, "ms": round(ms, 4)}))
         clocks.stop()
         return 0
-    value, ms_step, launches, mean_ctx = run_decode(engine, args.batch, steps, warmup, rng)
+    value, ms_step, launches, mean_ctx, ctx_first, ctx_last = run_decode(engine, args.batch, steps, warmup, rng)
     prefill_ms = run_prefill(engine, PREFILL_TOKENS, 5, rng)
     e2e, h2d, d2h = run_e2e(engine, args.batch, min(steps, 512), warmup, rng)
     points = {}
@@ -318,27 +472,33 @@ def main():
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     mm, head, att = flops_per_token(c, n_attn, PREFILL_TOKENS)
     pf_flops = mm * PREFILL_TOKENS + head * 1 + att * PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2
+    label = {"350m": "LFM2-350M", "700m": "LFM2-700M", "1.2b": "LFM2-1.2B"}[args.shape]
     out = {
-        "metric": "decode tok/s at batch 8 (LFM2-350M shape, contexts 2048 growing to 4096)",
+        "metric": f"decode tok/s at batch {args.batch} ({label} shape, {PROMPT}-token prompts, timed steps at contexts "
+                  f"{ctx_first}..{ctx_last})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded uniform-random token ids, random weights N(0,0.02) seed 2",
-        "config": {"model": "LFM2-350M shape", "layers": c.num_hidden_layers, "layers_of_config": full_layers,
+        "dtype": "bf16", "data": f"synthetic: seeded uniform-random token ids, random weights N(0,0.02) seed {seed}",
+        "config": {"model": f"{label} shape", "layers": c.num_hidden_layers, "layers_of_config": full_layers,
                    "attention_layers": n_attn, "hidden": c.hidden_size, "heads": c.num_attention_heads,
                    "kv_heads": c.num_key_value_heads, "head_dim": c.head_dim, "ff": c.ff_dim, "vocab": c.vocab_size,
-                   "conv_L_cache": c.conv_L_cache, "global_batch": args.batch, "seq_len": CONTEXT_END,
-                   "prompt_len": PROMPT, "page_tokens": opts.page_tokens, "parallelism": "single GPU",
-                   "l2": "weights (%d MB) exceed L2, no flush" % (wbytes // 1000000), "sampling": "greedy on device",
-                   "peaks": src},
+                   "conv_L_cache": c.conv_L_cache, "global_batch": args.batch, "seq_len": ctx_last,
+                   "context_first": ctx_first, "prompt_len": PROMPT, "page_tokens": opts.page_tokens,
+                   "parallelism": "single GPU", "l2": "weights (%d MB) exceed L2, no flush" % (wbytes // 1000000),
+                   "sampling": "greedy on device"},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
         "prefill": {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 4), "frac": round(pf_flops / (prefill_ms / 1e3) / (tf_burst * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm, "unit": "GB/s",
-                     "frac": round(achieved / hbm, 4)},
+                     "frac": round(achieved / hbm, 4), "peaks": src, "context_mean": round(mean_ctx, 1)},
         "points": points,
         "clocks": clk,
     }
+    if args.workloads:
+        del engine
+        torch.cuda.empty_cache()
+        out["workloads"] = {"700m_mixed": run_workload("700m", "mixed", hbm), "1.2b_concurrent": run_workload("1.2b", "concurrent", hbm)}
     print(json.dumps(out))
     return 0
 

@@ -178,7 +178,10 @@ class _StateGroup:
 class CacheManager:
     def __init__(self, needs, *, page_tokens: int, max_tokens: int, max_requests: int, n_ctx: int,
                  dtype: torch.dtype, device):
-        """needs[n]: the cache need of schedule entry n (PagedKV, FixedState or None).
+        """needs[n]: the cache need of schedule entry n: PagedKV, FixedState, None, or a list of
+        them for a mixer that keeps several things (pages and a state; two states of different
+        shapes, as FeLLM's GatedDeltaNet keeps a convolution history and a matrix,
+        crates/fellm-model/src/graph.rs:792-806).  An entry's view is then a list in the same order.
         max_tokens: positions the page pool of each group holds (rounded up to whole pages)."""
         self.page_tokens, self.n_slots, self.n_ctx = int(page_tokens), int(max_requests), int(n_ctx)
         self.device = device
@@ -188,23 +191,31 @@ class CacheManager:
         self._entry_view: Dict[int, object] = {}
         n_pages = -(-int(max_tokens) // self.page_tokens)
         width = -(-self.n_ctx // self.page_tokens)
-        by_need: Dict[object, List[int]] = {}
+        by_need: Dict[object, List[tuple]] = {}          # need -> [(entry, index among the entry's needs)]
         for n, need in enumerate(needs):
-            if need is not None:
-                by_need.setdefault(need, []).append(n)
-        for need, entries in by_need.items():
+            for k, one in enumerate(need if isinstance(need, (list, tuple)) else [need]):
+                if one is None:
+                    continue
+                if not isinstance(one, (PagedKV, FixedState)):
+                    raise CacheError(f"schedule entry {n}: unknown cache need {one!r}")
+                by_need.setdefault(one, []).append((n, k))
+        placed: Dict[tuple, object] = {}
+        for need, users in by_need.items():
             if isinstance(need, PagedKV):
-                g = _PagedGroup(need, entries, n_pages, self.n_slots, width, self.page_tokens, dtype, device)
+                g = _PagedGroup(need, users, n_pages, self.n_slots, width, self.page_tokens, dtype, device)
                 self.paged.append(g)
-                for li, n in enumerate(entries):
-                    self._entry_view[n] = PagedView(g.pool, g.table_dev, li, self.page_tokens, need.window)
-            elif isinstance(need, FixedState):
-                g = _StateGroup(need, entries, self.n_slots, device)
-                self.fixed.append(g)
-                for li, n in enumerate(entries):
-                    self._entry_view[n] = StateView(g.states[:, li])
+                for li, user in enumerate(users):
+                    placed[user] = PagedView(g.pool, g.table_dev, li, self.page_tokens, need.window)
             else:
-                raise CacheError(f"schedule entry {n}: unknown cache need {need!r}")
+                g = _StateGroup(need, users, self.n_slots, device)
+                self.fixed.append(g)
+                for li, user in enumerate(users):
+                    placed[user] = StateView(g.states[:, li])
+        for n, need in enumerate(needs):
+            if isinstance(need, (list, tuple)):
+                self._entry_view[n] = [placed.get((n, k)) for k in range(len(need))]
+            elif need is not None:
+                self._entry_view[n] = placed[(n, 0)]
         self.n_entries = len(needs)
         self._views_key, self._views = None, None
         self.has_windows = any(g.need.window is not None for g in self.paged)
@@ -221,6 +232,21 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         return sum(g.bytes_per_token() for g in self.paged)
+
+    @staticmethod
+    def tokens_for_budget(needs, element_size: int, budget: int, page_tokens: int, cap: int) -> int:
+        """Positions a pool of `budget` bytes holds, every paged group getting the same number of
+        them: FeLLM's pages = budget / page_bytes (crates/fellm-runtime/src/kv_fabric/fabric.rs:
+        59-61), in whole pages, at least one and at most `cap` positions."""
+        per_token = 0
+        for need in needs:
+            for one in (need if isinstance(need, (list, tuple)) else [need]):
+                if isinstance(one, PagedKV):
+                    per_token += 2 * one.kv_heads * one.head_dim * element_size
+        if per_token == 0:
+            return page_tokens
+        tokens = max(min(budget // per_token, cap), page_tokens)
+        return tokens - tokens % page_tokens
 
     # ---- requests
     def has(self, req) -> bool:
@@ -301,11 +327,11 @@ class CacheManager:
         if key is not None and self._views_key == key:
             return self._views
         out = []
+        def of_step(v):
+            return StateView(v.states, item_slot) if isinstance(v, StateView) else v
         for n in range(self.n_entries):
             v = self._entry_view.get(n)
-            if isinstance(v, StateView):
-                v = StateView(v.states, item_slot)
-            out.append(v)
+            out.append([of_step(one) for one in v] if isinstance(v, list) else of_step(v))
         if key is not None:
             self._views_key, self._views = key, out
         return out

@@ -24,6 +24,7 @@ class EngineOptions:
     max_requests: int = 64          # state slots and block-table rows
     max_tokens: Optional[int] = None    # cache pool size in tokens; None = from memory
     kv_memory_fraction: float = 0.25    # fabric.rs:40-48 (share of free memory when max_tokens is None)
+    kv_device_budget: int = 0           # bytes of cache pages when max_tokens is None; 0 = from free memory (FeLLM's --kv-device-budget)
     cuda_graphs: bool = True
     device: str = "cuda:0"
 
@@ -37,6 +38,8 @@ class EngineOptions:
         for k in ("n_batch", "n_ubatch", "max_requests"):
             if getattr(self, k) < 1:
                 raise ConfigError(f"{k} must be >= 1")
+        if self.kv_device_budget < 0:
+            raise ConfigError("kv_device_budget must be >= 0 bytes")
         if self.n_ctx < 0:
             raise ConfigError("n_ctx must be >= 0")
         return self

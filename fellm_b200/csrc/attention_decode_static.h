@@ -27,6 +27,12 @@
  * that overlap on the GPU (different streams, no ordering between them) race on the arrays: order
  * them.
  *
+ * Key ranges: row t reads the keys 0..positions[t] (the last `window` of them if window > 0) in
+ * ranges of `split_len` keys, one CTA per (range, kv head, row); the grid has `max_splits` ranges.
+ * Choose max_splits >= ceil((largest position + 1) / split_len), so that every range has a CTA of
+ * its own.  With fewer, the last range takes all the keys behind it: the result is the same, the
+ * launch slower.  More ranges than a row needs cost nothing but scratch.
+ *
  * Arguments as fellm_attn_decode_mma, without the scratch and counters; the library is compiled for
  * one head size (-DHD=...) and refuses any other.  Returns 0, a positive cudaError_t, or a negative
  * code (FELLM_ERR_SIZE -1, FELLM_ERR_ARG -2, FELLM_STATIC_TOO_LARGE -3).

@@ -375,11 +375,14 @@ __global__ void __launch_bounds__(DC_WARPS * 32) attention_decode_kernel(AttnArg
   // kernel: they may be read before the wait
   const int pos = a.positions[t];
   const int kb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-  const int s_lo = kb / a.split_len, s_hi = pos / a.split_len;
+  // a launch with fewer key ranges than the longest row has (max_splits * split_len <= pos): the
+  // last range takes every key behind it, so that the result stays right (only slower)
+  const int s_end = (int)gridDim.x - 1;
+  const int s_lo = min(kb / a.split_len, s_end), s_hi = min(pos / a.split_len, s_end);
   pdl_launch_dependents();
   if (s < s_lo || s > s_hi) return;
   const int n_active = s_hi - s_lo + 1;
-  const int k0 = max(kb, s * a.split_len), k1 = min(pos + 1, (s + 1) * a.split_len);
+  const int k0 = max(kb, s * a.split_len), k1 = s == s_end ? pos + 1 : min(pos + 1, (s + 1) * a.split_len);
   const int R = a.H / a.G;
   const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
   const int pg0 = k0 / a.page_tokens, n_pg = (k1 - 1) / a.page_tokens - pg0 + 1;
@@ -544,11 +547,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   // kernel: they may be read before the wait
   const int pos = a.positions[t];
   const int kb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-  const int s_lo = kb / a.split_len, s_hi = pos / a.split_len;
+  // a launch with fewer key ranges than the longest row has (max_splits * split_len <= pos): the
+  // last range takes every key behind it, so that the result stays right (only slower)
+  const int s_end = (int)gridDim.x - 1;
+  const int s_lo = min(kb / a.split_len, s_end), s_hi = min(pos / a.split_len, s_end);
   pdl_launch_dependents();
   if (s < s_lo || s > s_hi) return;
   const int n_active = s_hi - s_lo + 1;
-  const int k0 = max(kb, s * a.split_len), k1 = min(pos + 1, (s + 1) * a.split_len);
+  const int k0 = max(kb, s * a.split_len), k1 = s == s_end ? pos + 1 : min(pos + 1, (s + 1) * a.split_len);
   const int R = a.H / a.G;                              // <= 16 (the launcher checks)
   const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
   const int pg0 = k0 / DT_PT, n_pg = (k1 - 1) / DT_PT - pg0 + 1;

@@ -135,3 +135,16 @@ static inline int launch_status() {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// SMs of the current device (asked once per device; the planners size grids and waves by it).
+static inline int fellm_sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = 148;   // B200
+    cached[dev] = n;
+  }
+  return cached[dev];
+}

@@ -162,7 +162,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 FELLM_API int fellm_silu_mul(const void* gu, void* out, int is_bf16, int rows, int F, cudaStream_t stream) {
   if (rows <= 0) return 0;
   size_t n = (size_t)rows * F;
-  int blocks = (int)((n + 255) / 256); if (blocks > 148 * 16) blocks = 148 * 16;
+  int blocks = (int)((n + 255) / 256); if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
   if (is_bf16) return launch_k(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, rows, F);
   return launch_k(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (const float*)gu, (float*)out, rows, F);
 }

@@ -751,6 +751,7 @@ static int dispatch_lean(const SkinnyArgs& a, int ctas_y, int warps, cudaStream_
 struct LeanPlan { int warps, warps_k, splits, ctas_y, k_per_warp, tiles_per_warp; };
 static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
   if (M > 64 || (norm && M > 16) || N % SK_ROWS) return false;
+  const int n_sm = fellm_sm_count();
   const int in_flight = 2 * SK_U * KCHUNK;
   int slices = 1;
   while (slices < 64 && ceil_div(K, slices) > in_flight) slices *= 2;
@@ -773,10 +774,10 @@ static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
       if (smem > 200 * 1024) break;
       const int ct = ceil_div(n_tiles, warps_n * tpw);
       const int per_sm = (warps == 8 && smem <= 100 * 1024) ? 2 : 1;
-      if (ct * sp > 148 * per_sm) continue;
+      if (ct * sp > n_sm * per_sm) continue;
       // order: fewest cluster ranks; fewest slabs a warp; not two CTAs to an SM where one would do
       // (x staged twice); then most CTAs
-      const int crowded = (per_sm == 2 && ct * sp > 148) ? 1 : 0;
+      const int crowded = (per_sm == 2 && ct * sp > n_sm) ? 1 : 0;
       const long long key = ((long long)sp << 48) | ((long long)tpw << 40) | ((long long)crowded << 32) | (long long)(100000 - ct * sp);
       if (!found || key < best_key) { best = LeanPlan{warps, wk, sp, ct, kpw, tpw}; best_key = key; found = true; }
       break;
@@ -815,7 +816,8 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   if (epi == EPI_SWIGLU && (N % 16)) return FELLM_ERR_SIZE;
   int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   const size_t smem_cap = 100 * 1024;                     // two CTAs per SM
-  const int resident_warps = 148 * 2 * SK_WARPS;
+  const int n_sm = fellm_sm_count();
+  const int resident_warps = n_sm * 2 * SK_WARPS;
   const int in_flight = 2 * SK_U * KCHUNK;                // k a warp holds in flight: two rounds
   int n_tiles = ceil_div(N, SK_ROWS);
   auto round_k = [&](int k) { return ceil_div(k, KCHUNK) * KCHUNK; };
@@ -833,7 +835,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
   if (plan_a) {
     k_per_cta = round_k(ceil_div(K, slices)) * warps_k;
     ctas_y = ceil_div(n_tiles, SK_WARPS / warps_k);
-    if (ctas_y > (148 * cps) / splits) ctas_y = (148 * cps) / splits;
+    if (ctas_y > (n_sm * cps) / splits) ctas_y = (n_sm * cps) / splits;
     tiles_per_warp = ceil_div(n_tiles, ctas_y * (SK_WARPS / warps_k));
     if (smem_bytes(mt, k_per_cta, slices == 1, tiles_per_warp) > 200 * 1024) plan_a = false;
   }
@@ -847,7 +849,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
       for (splits = 1; splits <= 8; splits *= 2) {
         k_per_cta = round_k(ceil_div(K, splits));
         ctas_y = ceil_div(n_tiles, SK_WARPS);
-        if (ctas_y > (148 * 2) / splits) ctas_y = (148 * 2) / splits;
+        if (ctas_y > (n_sm * 2) / splits) ctas_y = (n_sm * 2) / splits;
         if (ctas_y < 1) ctas_y = 1;
         tiles_per_warp = ceil_div(n_tiles, ctas_y * SK_WARPS);
         if (smem_bytes(mt, k_per_cta, splits == 1, tiles_per_warp) <= cap) { found = true; break; }
@@ -894,9 +896,9 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
 // 16 C rows, 16 X rows (bias, if any, in the same order); y [M, d] = C * conv(B*X) in bfloat16;
 // state: this layer's slots, [Lc-1, d] float32 each, slot_stride floats apart, advanced by one
 // token; row_slot [M].  Takes M <= 16, K in 1024..1280 with K % 128 == 0 (four K slices of whole
-// chunks), d % 16 == 0, d <= 148*16; FELLM_ERR_SIZE otherwise (fellm_gemm_skinny_conv_takes asks).
+// chunks), d % 16 == 0, d <= 16 * the SM count; FELLM_ERR_SIZE otherwise (fellm_gemm_skinny_conv_takes asks).
 static bool conv_shape_ok(int M, int N, int K, int taps) {
-  return M >= 1 && M <= 16 && N % 48 == 0 && N / 48 <= 148 && K % (4 * KCHUNK) == 0 && K / 4 >= 8 * KCHUNK &&
+  return M >= 1 && M <= 16 && N % 48 == 0 && N / 48 <= fellm_sm_count() && K % (4 * KCHUNK) == 0 && K / 4 >= 8 * KCHUNK &&
          K / 4 <= LEAN_CH * KCHUNK && taps >= 2 && taps <= SK_MAX_LC;
 }
 FELLM_API int fellm_gemm_skinny_conv_takes(int M, int N, int K, int taps) { return conv_shape_ok(M, N, K, taps) ? 1 : 0; }

@@ -315,12 +315,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& 
   auto kern = gemm_umma_kernel<EPI, BN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  static int n_sm = 0;
-  if (!n_sm) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
-  }
+  const int n_sm = fellm_sm_count();
   int total = ceil_div(a.N, BN) * ceil_div(a.M, UM_BM);
   return launch_k(kern, dim3(total < n_sm ? total : n_sm, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
 }
@@ -335,7 +330,8 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
   if (epi == EPI_SWIGLU && ((N % 16) || (ldo % 8))) return FELLM_ERR_SIZE;
   // 128 x 256 tiles (a quarter fewer operand bytes a FLOP) where they fill the SMs as well as 128 x 128 ones
   const int m_tiles = ceil_div(M, UM_BM);
-  const int waves128 = ceil_div(ceil_div(N, 128) * m_tiles, 148), waves256 = ceil_div(ceil_div(N, 256) * m_tiles, 148);
+  const int n_sm = fellm_sm_count();
+  const int waves128 = ceil_div(ceil_div(N, 128) * m_tiles, n_sm), waves256 = ceil_div(ceil_div(N, 256) * m_tiles, n_sm);
   static int wide_ok = -1;
   if (wide_ok < 0) { const char* ev = getenv("FELLM_B200_UMMA_WIDE"); wide_ok = (ev && ev[0] == '0') ? 0 : 1; }
   const bool wide = wide_ok && N >= 512 && 2 * waves256 <= waves128;

@@ -4,7 +4,9 @@
 // FeLLM does this as separate ops: rmsnorm_group (oxide_kernels.rs:165), rope_batch (323),
 // kv_write_batch (4227) twice; formulas in crates/backend-cpu/src/kernels/norm.rs:6-39 and
 // rope.rs:28-62.  Angle = float32(position) * inv_freq[i]; a' = a*c - b*s, b' = a*s + b*c on
-// pairs (2i, 2i+1) (pairing 0, "adjacent") or (i, i+hd/2) (pairing 1, "split_half").
+// pairs (2i, 2i+1) (pairing 0, "adjacent") or (i, i+rot_dim/2) (pairing 1, "split_half") of the
+// first rot_dim <= hd elements of a head (rope.rs:37-44: rope_dim <= head_dim); the elements
+// behind rot_dim are normed and not rotated.  inv_freq has rot_dim/2 entries.
 //
 // Cache pool layout (one pool per cache group, shared by the group's layers):
 //   [page][layer in group][k=0 / v=1][kv head][token in page][hd]
@@ -19,7 +21,7 @@ __global__ void qk_rope_write_kernel(const TA* __restrict__ qkv, const float* __
                                      const int* __restrict__ block_table, int max_pages,
                                      TC* __restrict__ pool, int layer, int layers_in_group,
                                      int page_tokens, TA* __restrict__ q_out, int T, int H, int G, int hd,
-                                     int write_kv, int* __restrict__ status) {
+                                     int rot_dim, int write_kv, int* __restrict__ status) {
   FELLM_TRACE_SCOPE(TRACE_QK_ROPE_WRITE);
   pdl_launch_dependents();
   pdl_wait(); FELLM_TRACE_WAITED();
@@ -50,13 +52,19 @@ __global__ void qk_rope_write_kernel(const TA* __restrict__ qkv, const float* __
     return;
   }
   const float* nw = is_q ? q_w : k_w;
-  int half = hd >> 1;
+  int half = rot_dim >> 1;
   float scale = 1.f;
   if (nw) {
     float ss = 0.f;
     for (int e = lane; e < hd; e += 32) { float v = to_f(src[e]); ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     scale = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  for (int e = rot_dim + lane; e < hd; e += 32) {      // behind the rotated part: normed, not rotated
+    float a = to_f(src[e]);
+    if (nw) a = (a * scale) * nw[e];
+    if (is_q) q_out[((size_t)row * H + head) * hd + e] = from_f<TA>(a);
+    else dst_c[e] = from_f<TC>(a);
   }
   for (int p = lane; p < half; p += 32) {
     int i0 = pairing == 0 ? 2 * p : p;
@@ -192,16 +200,18 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
                                   float eps, const float* inv_freq, int pairing, const int* positions,
                                   const int* row_slot, const int* block_table, int max_pages, void* pool,
                                   int cache_bf16, int layer, int layers_in_group, int page_tokens,
-                                  void* q_out, int T, int H, int G, int hd, int write_kv, int* status,
-                                  cudaStream_t stream) {
+                                  void* q_out, int T, int H, int G, int hd, int rot_dim, int write_kv,
+                                  int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd < 2 || (hd & 1)) return FELLM_ERR_SIZE;
+  if (!inv_freq) rot_dim = 0;
+  if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1)) return FELLM_ERR_SIZE;
   if (!qkv || !q_out || !positions || !row_slot || (write_kv && (!pool || !block_table))) return FELLM_ERR_ARG;
   if (act_bf16 != cache_bf16) return FELLM_ERR_ARG;
   long long warps = (long long)T * (H + 2 * G);
   int threads = 128;
   long long blocks = (warps * 32 + threads - 1) / threads;
-  if (act_bf16 && hd % 16 == 0 && hd <= 256) {
+  if (act_bf16 && hd % 16 == 0 && hd <= 256 && (rot_dim == hd || rot_dim == 0)) {
     int lanes = hd / 16, gl = 1;
     while (gl < lanes) gl <<= 1;
     long long nthreads = warps * gl;
@@ -221,8 +231,8 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
   if (act_bf16)
     return launch_k_class(2, qk_rope_write_kernel<bf16, bf16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
                     (const bf16*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
-                    (bf16*)pool, layer, layers_in_group, page_tokens, (bf16*)q_out, T, H, G, hd, write_kv, status);
+                    (bf16*)pool, layer, layers_in_group, page_tokens, (bf16*)q_out, T, H, G, hd, rot_dim, write_kv, status);
   return launch_k_class(2, qk_rope_write_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
                   (const float*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
-                  (float*)pool, layer, layers_in_group, page_tokens, (float*)q_out, T, H, G, hd, write_kv, status);
+                  (float*)pool, layer, layers_in_group, page_tokens, (float*)q_out, T, H, G, hd, rot_dim, write_kv, status);
 }

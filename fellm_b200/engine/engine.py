@@ -65,6 +65,8 @@ class Engine:
                                   max_requests=options.max_requests, n_ctx=n_ctx, dtype=cache_dtype,
                                   device=self.device)
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
+        for part in self.model.all_parts():
+            part.reserve(self.device, options.max_requests, n_ctx)
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
                                device=self.device, cuda_graphs=options.cuda_graphs)
         self._sampler: Optional[Sampler] = None
@@ -99,23 +101,19 @@ class Engine:
         return cls(arch, config, options, tensors=tensors)
 
     def _tokens_from_memory(self, needs, cache_dtype) -> int:
-        """FeLLM: usable = free - reserves; budget = usable * kv_memory_fraction; pages =
-        budget / page_bytes (crates/fellm-runtime/src/kv_fabric/fabric.rs:40-61)."""
-        from ..parts.base import PagedKV
+        """FeLLM: usable = free - reserves; budget = usable * kv_memory_fraction, or the explicit
+        device budget; pages = budget / page_bytes (crates/fellm-runtime/src/kv_fabric/fabric.rs:40-61)."""
         esize = 2 if cache_dtype == torch.bfloat16 else 4
-        per_token = {}
-        for need in needs:
-            if isinstance(need, PagedKV):
-                per_token[need] = per_token.get(need, 0) + 2 * need.kv_heads * need.head_dim * esize
-        total = sum(per_token.values())
-        if total == 0:
-            return self.options.page_tokens
-        free, _ = torch.cuda.mem_get_info(self.device)
-        budget = int(max(free - (2 << 30), 0) * self.options.kv_memory_fraction)
-        tokens = budget // total
-        cap = self.options.max_requests * self.n_ctx
-        tokens = max(min(tokens, cap), self.options.page_tokens)
-        return tokens - tokens % self.options.page_tokens
+        pt = self.options.page_tokens
+        cap = self.options.max_requests * (-(-self.n_ctx // pt) * pt)
+        if self.options.kv_device_budget > 0:
+            budget = self.options.kv_device_budget
+            if CacheManager.tokens_for_budget(needs, esize, budget, 1, cap) < pt:
+                raise ConfigError(f"kv_device_budget of {budget} bytes does not hold one page of {pt} tokens")
+        else:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(max(free - (2 << 30), 0) * self.options.kv_memory_fraction)
+        return CacheManager.tokens_for_budget(needs, esize, budget, pt, cap)
 
     @property
     def sampler(self) -> Sampler:
@@ -133,7 +131,10 @@ class Engine:
         self.cache.release(req)
 
     def step(self, items: List[StepItem], device_tokens=None) -> torch.Tensor:
-        return self.stepper.step(items, device_tokens)
+        """The step function (Stepper.step).  The logits are the caller's own: with CUDA graphs on,
+        the step's graph keeps writing into its own output, so a copy is handed out."""
+        logits = self.stepper.step(items, device_tokens)
+        return logits.clone() if self.stepper.cuda_graphs else logits
 
     def check_status(self):
         self.stepper.check_status()
@@ -194,11 +195,9 @@ class Engine:
         out = {r: [] for r in rids}
         stats = {}
         while len(stats) < len(rids):
-            ev = sched.poll_event()
+            ev = sched.poll_event(rids)          # other callers' events stay queued for them
             if ev is None:
                 break
-            if ev.req not in out:
-                continue
             if ev.kind == "token":
                 out[ev.req].append(ev.token)
             elif ev.kind == "done":
@@ -222,11 +221,9 @@ class TokenStream:
 
     def __next__(self) -> int:
         while not self._done:
-            ev = self.sched.poll_event()
+            ev = self.sched.poll_event(self.rid)     # other streams' events stay queued for them
             if ev is None:
                 break
-            if ev.req != self.rid:
-                continue
             if ev.kind == "token":
                 return ev.token
             self.stats, self._done = ev.stats, True

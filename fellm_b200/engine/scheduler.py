@@ -118,7 +118,8 @@ class Scheduler:
         self.inflight: Optional[InFlight] = None
         self._next_id, self._next_seq = 0, 0
         self.counters = {"requests": 0, "admitted": 0, "preempted": 0, "finished": 0, "steps": 0,
-                         "shrunk": 0, "tokens_run": 0, "admission_waits": 0, "ran_ahead": 0, "dropped": 0}
+                         "shrunk": 0, "tokens_run": 0, "admission_waits": 0, "ran_ahead": 0, "dropped": 0,
+                         "mixed_steps": 0}
 
     # ---- enqueue / cancel
     def enqueue_ids(self, ids: Sequence[int], params: Optional[GenParams] = None) -> int:
@@ -262,6 +263,8 @@ class Scheduler:
             raise
         self.counters["steps"] += 1
         self.counters["tokens_run"] += sum(p.n_tokens for p in plan)
+        if any(p.decode for p in plan) and not all(p.decode for p in plan):
+            self.counters["mixed_steps"] += 1             # prompt portions beside decode tokens
         for p in plan:
             if p.decode:
                 p.req.pending = None
@@ -351,10 +354,27 @@ class Scheduler:
         else:
             self.events.append(Event("done", r.id, stats=stats))
 
-    def poll_event(self) -> Optional[Event]:
-        """The next event, running iterations until there is one; None when all work is done."""
-        while not self.events:
+    def poll_event(self, reqs=None) -> Optional[Event]:
+        """The next event, running iterations until there is one; None when all work is done.
+
+        reqs: a request id or a collection of ids: the next event of THOSE requests; events of
+        other requests stay queued, in order, for whoever asks for them (two token streams, or a
+        stream beside generate_batch, each read their own and lose nothing)."""
+        if reqs is None:
+            while not self.events:
+                if self.idle():
+                    return None
+                self._iterate()
+            return self.events.popleft()
+        mine = {reqs} if isinstance(reqs, int) else set(reqs)
+        scanned = 0
+        while True:
+            for i in range(scanned, len(self.events)):
+                if self.events[i].req in mine:
+                    ev = self.events[i]
+                    del self.events[i]
+                    return ev
+            scanned = len(self.events)
             if self.idle():
                 return None
             self._iterate()
-        return self.events.popleft()

@@ -158,6 +158,7 @@ StepBuffers.fill_decode = _fill_decode
 
 
 MAX_ROW_GRAPHS = 8          # captured graphs of steps that are not pure decode (each keeps its activations)
+MAX_DECODE_GRAPHS = 48      # captured decode steps (each keeps its logits [wanted, vocab]); the least recently used goes
 
 
 class Stepper:
@@ -183,6 +184,7 @@ class Stepper:
         self.graph_seen = {}
         self.graph_pool = None
         self.row_graph_keys = []
+        self.decode_graph_keys = []            # least recently used first
         self.launches = 0                      # kernels of ours launched, replays included
         self._decode_plans = {}
         self._plan_serial = 0
@@ -191,6 +193,9 @@ class Stepper:
         """Runs exactly the given tokens as one batch and returns float32 logits
         [sum(len(want)), vocab] on the device, in the order of the items and of each `want`.
         Nothing is changed when the step cannot be placed (unknown request, no pages).
+        With cuda_graphs on, the tensor returned belongs to the step's graph and is written again
+        by the next step of the same shape: read it, or copy it, before the next call
+        (Engine.step hands out a copy).
 
         device_tokens: int32 [rows] on the device to use instead of the items' token ids (which
         are then placeholders): lets a decode loop feed sampled tokens back without the host."""
@@ -350,6 +355,15 @@ class Stepper:
                     old = self.row_graph_keys.pop(0)
                     self.graphs.pop(old, None)
                     self.graph_seen.pop(old, None)
+            else:
+                self.decode_graph_keys.append(key)
+                if len(self.decode_graph_keys) > MAX_DECODE_GRAPHS:
+                    old = self.decode_graph_keys.pop(0)
+                    self.graphs.pop(old, None)
+                    self.graph_seen.pop(old, None)
+        elif ctx.all_single and self.decode_graph_keys[-1] != key:
+            self.decode_graph_keys.remove(key)
+            self.decode_graph_keys.append(key)
         graph, logits, n_launches = entry
         graph.replay()
         self.launches += n_launches

@@ -1,1 +1,1 @@
-from .model import Block, Model, build_model
+from .model import ARRANGEMENTS, Block, Model, build_model, normed, register_arrangement

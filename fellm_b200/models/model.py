@@ -25,26 +25,53 @@ def _normed(x, norm, consumer, act_dtype):
     return norm.forward(x, act_dtype)
 
 
+ARRANGEMENTS = {}
+
+
+def register_arrangement(name: str):
+    """Decorator: `fn(block, x, ctx, cache, act_dtype, reads_only)` wires a block's parts for
+    LayerSpec.arrangement == name.  x is the float32 residual stream [T, d] and is updated in
+    place (mixers and feed-forwards ADD into the tensor they are given as `out`); `block` has
+    .norm1, .mixer, .norm2, .ffn (None where the spec names none)."""
+    def deco(fn):
+        ARRANGEMENTS[name] = fn
+        return fn
+    return deco
+
+
+def normed(x, norm, consumer, act_dtype):
+    """The consumer's input: normed now, or left to the consumer's first product."""
+    return _normed(x, norm, consumer, act_dtype)
+
+
+@register_arrangement("prenorm")
+def _prenorm(block, x, ctx, cache, act_dtype, reads_only):
+    """x += mixer(norm1(x)); x += ffn(norm2(x))   (crates/fellm-model/src/graph.rs:1650-1777)."""
+    block.mixer.forward(_normed(x, block.norm1, block.mixer, act_dtype), ctx, cache, x, reads_only=reads_only)
+    if block.ffn is not None:
+        block.ffn.forward(_normed(x, block.norm2, block.ffn, act_dtype), ctx, x)
+
+
 class Block:
-    """One layer's parts and their arrangement."""
+    """One layer's parts; how they are wired is looked up by the spec's arrangement name."""
 
     def __init__(self, spec, dtype: str):
-        if spec.arrangement != "prenorm":
-            raise ConfigError(f"unknown block arrangement {spec.arrangement!r}")
+        if spec.arrangement not in ARRANGEMENTS:
+            raise ConfigError(f"unknown block arrangement {spec.arrangement!r}; registered: "
+                              f"{', '.join(sorted(ARRANGEMENTS))}")
         self.spec = spec
-        self.norm1 = build_part("norm", spec.norm1, dtype)
+        self.arrange = ARRANGEMENTS[spec.arrangement]
+        self.norm1 = build_part("norm", spec.norm1, dtype) if spec.norm1 is not None else None
         self.mixer = build_part("mixer", spec.mixer, dtype)
-        self.norm2 = build_part("norm", spec.norm2, dtype)
-        self.ffn = build_part("feed_forward", spec.ffn, dtype)
+        self.norm2 = build_part("norm", spec.norm2, dtype) if spec.norm2 is not None else None
+        self.ffn = build_part("feed_forward", spec.ffn, dtype) if spec.ffn is not None else None
 
     def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def forward(self, x, ctx, cache, act_dtype, reads_only=False):
-        """x: float32 residual stream [T, d], updated in place:
-        x += mixer(norm1(x)); x += ffn(norm2(x))."""
-        self.mixer.forward(_normed(x, self.norm1, self.mixer, act_dtype), ctx, cache, x, reads_only=reads_only)
-        self.ffn.forward(_normed(x, self.norm2, self.ffn, act_dtype), ctx, x)
+        """x: float32 residual stream [T, d], updated in place."""
+        self.arrange(self, x, ctx, cache, act_dtype, reads_only)
         return x
 
 
@@ -75,6 +102,15 @@ class Model:
                     raise ConfigError(f"two parts claim the tensor {name}")
                 table[name] = (part, local, decl)
         return table
+
+    def tied_aliases(self) -> Dict[str, str]:
+        """{name a file may also carry: name of the tensor it must equal}.  A tied head owns no
+        tensor, but files written from a state dict often store the head all the same, as a copy of
+        the embedding matrix (FeLLM reads `output.weight` when it is there and ties otherwise,
+        crates/fellm-model/src/graph.rs:29-34); such a copy is accepted if it is one."""
+        if getattr(self.head, "tied", False):
+            return {self.head.spec.tensor_name("weight"): self.embedding.spec.tensor_name("weight")}
+        return {}
 
     def bind(self, tensors: Dict[str, torch.Tensor]):
         """tensors: {file name: tensor already on the device, in its kept dtype}."""

@@ -253,10 +253,11 @@ PAIRINGS = {"adjacent": 0, "split_half": 1}
 
 
 def qk_rope_write(qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, pool, layer,
-                  page_tokens, H, G, hd, write_kv=True, status=None, q_out=None):
+                  page_tokens, H, G, hd, write_kv=True, status=None, q_out=None, rot_dim=None):
     """qkv [T, (H+2G)*hd] -> q_out [T, H, hd] (per-head RMSNorm, rotary), and k (normed, rotated)
     and v written to pool[page, layer, 0/1, g, slot, :].  q_w/k_w None: no QK norm; inv_freq None:
-    no rotation.  pool: [pages, layers, 2, G, page_tokens, hd]; block_table [slots, width] is indexed
+    no rotation; rot_dim (default hd): the first rot_dim elements of a head are rotated, with
+    inv_freq [rot_dim/2].  pool: [pages, layers, 2, G, page_tokens, hd]; block_table [slots, width] is indexed
     by row_slot[t], the slot of the request row t belongs to."""
     _dev(qkv, q_w, k_w, inv_freq, positions, row_slot, block_table, pool)
     T = qkv.shape[0]
@@ -270,14 +271,20 @@ def qk_rope_write(qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, bl
     _i32(positions, "positions"), _i32(row_slot, "row_slot")
     if q_out is None:
         q_out = torch.empty((T, H, hd), dtype=qkv.dtype, device=qkv.device)
+    rot_dim = hd if rot_dim is None else int(rot_dim)
+    if inv_freq is not None:
+        if rot_dim % 2 or not 2 <= rot_dim <= hd:
+            raise KernelError(f"rotary dimension {rot_dim} must be even and within the head size {hd}")
+        if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2:
+            raise KernelError(f"inv_freq must hold {rot_dim // 2} float32 values, got {inv_freq.numel()}")
     f = _fn("qk_rope_write", "fellm_qk_rope_write",
             [_c_p, _c_int, _c_p, _c_p, _c_f, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int, _c_int,
-             _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+             _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
     _check(f(_p(qkv), _is_bf16(qkv), _p(q_w), _p(k_w), float(eps), _p(inv_freq), PAIRINGS[pairing],
              _p(positions), _p(row_slot), _p(block_table) if write_kv else None,
              block_table.shape[1] if write_kv else 0, _p(pool) if write_kv else None,
              _is_bf16(pool) if write_kv else _is_bf16(qkv), layer, pool.shape[1] if write_kv else 1,
-             page_tokens, _p(q_out), T, H, G, hd, int(write_kv), _p(status), _stream()), "qk_rope_write")
+             page_tokens, _p(q_out), T, H, G, hd, rot_dim, int(write_kv), _p(status), _stream()), "qk_rope_write")
     return q_out
 
 
@@ -311,10 +318,6 @@ SKINNY_MAX_ROWS = 32      # measured on B200 (350M shapes): above 32 rows the tc
 _GEMM_ARGS = [_c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
 _SKINNY_ARGS = [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p]
 NORM_FUSE_MAX_ROWS = 16
-
-
-def has_fast_gemm() -> bool:
-    return True
 
 
 def fast_gemm_modules():
@@ -465,28 +468,62 @@ def interleave_gate_up(gate, up):
 # ------------------------------------------------------------------------------ attention dispatch
 
 _decode_scratch = {}
+_decode_scratch_retired = []      # replaced buffers stay alive: a CUDA graph captured earlier still names them
 
 
-def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_dim: int, max_splits: int):
+def decode_scratch_need(max_rows: int, heads: int, kv_heads: int, head_dim: int, n_ctx: int):
+    """(floats, counters) the split-KV decode kernel can ask for with up to max_rows rows and
+    contexts up to n_ctx: the largest over every row count of what attention_decode reserves."""
+    floats = 0
+    for rows in range(1, max(max_rows, 1) + 1):
+        for bucket in range(1024, max(n_ctx, 1) + 1024, 1024):       # the split is chosen per 1024 of context
+            _, max_splits = decode_split(bucket, rows, kv_heads)
+            floats = max(floats, rows * heads * max_splits * (head_dim + 2))
+    return floats, max(max_rows, 1) * kv_heads
+
+
+def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_dim: int, max_splits: int, *,
+                           floats: int = 0, counters: int = 0):
     """Scratch of the split-KV decode kernel: partial results of every (row, head, key range) and
-    one counter per (row, kv head).  Allocated before any CUDA graph is captured, grown never
-    during one."""
-    need = max(rows * heads * max_splits * (head_dim + 2), 1 << 21)     # at least 8 MB: growth is rare
+    one counter per (row, kv head).  An engine sizes it once, before its first step, for the
+    largest step it can run (floats=, counters= from decode_scratch_need); a later call that needs
+    more (kernels called by hand at other sizes) gets a new buffer, never during a graph capture,
+    and the old one is kept alive for the graphs that were captured with it."""
+    need = max(rows * heads * max_splits * (head_dim + 2), floats, 1 << 21)     # at least 8 MB: growth is rare
+    need_c = max(rows * kv_heads, counters, 1 << 16)
+    device = torch.device(device)
     cur = _decode_scratch.get(device)
-    if cur is None or cur[0].numel() < need or cur[1].numel() < rows * kv_heads:
+    if cur is None or cur[0].numel() < need or cur[1].numel() < need_c:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("decode attention scratch must be reserved before graph capture")
+        if cur is not None:
+            _decode_scratch_retired.append(cur)
         scratch = torch.empty(max(need, cur[0].numel() if cur else 0), dtype=torch.float32, device=device)
-        counters = torch.zeros(max(rows * kv_heads, 1 << 16, cur[1].numel() if cur else 0), dtype=torch.int32,
-                               device=device)
-        _decode_scratch[device] = (scratch, counters)
+        counters_t = torch.zeros(max(need_c, cur[1].numel() if cur else 0), dtype=torch.int32, device=device)
+        _decode_scratch[device] = (scratch, counters_t)
     return _decode_scratch[device]
 
 
 # CTAs the split of decode attention aims at: one wave of the TMA kernel (three CTAs of 68 KB to an
 # SM).  Measured on B200, 16 layers of width 1024, context 2048 (4000): batch 8 379 (411) us a step
 # with 444, 387 (438) with 592, 399 (417) with 300; batch 32 764 with 444, 822 with 592.
-DECODE_TARGET_CTAS = int(os.environ.get("FELLM_B200_DECODE_TARGET", 148 * 3))
+DECODE_TARGET_CTAS = int(os.environ.get("FELLM_B200_DECODE_TARGET", 0))     # 0: three CTAs for every SM of the device
+_sm_count = {}
+
+
+def sm_count(device=None) -> int:
+    """SMs of the device (of a B200, 148, where no GPU is present: the planners are checked on CPU too)."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    n = _sm_count.get(idx)
+    if n is None:
+        n = _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
+def decode_target_ctas() -> int:
+    return DECODE_TARGET_CTAS or 3 * sm_count()
 
 
 SPLIT_WHOLE_ROUNDS = os.environ.get("FELLM_B200_SPLIT_ROUNDS", "1") != "0"
@@ -503,8 +540,9 @@ def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     while contexts grow."""
     bucket = -(-max(max_len, 1) // 1024) * 1024
     items = max(rows * kv_heads, 1)
-    want = max(1, (target or DECODE_TARGET_CTAS) // items)
-    if items > (target or DECODE_TARGET_CTAS):
+    target = target or decode_target_ctas()
+    want = max(1, target // items)
+    if items > target:
         want = 2            # more than a wave even unsplit: halves, so that the last wave is a short one
     split_len = max(64, -(-(-(-bucket // want)) // 64) * 64)
     if split_len > 256 and SPLIT_WHOLE_ROUNDS:

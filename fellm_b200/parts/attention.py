@@ -31,6 +31,14 @@ class Attention(Mixer):
         self.window = None if window is None else int(window)
         self.shares_cache = bool(shares_cache)
         self.position = build_part("position", position, dtype)
+        # what the kernels need of a position part: inv_freq (float32 [rot_dim/2], or None for no
+        # rotation), pairing, rot_dim <= head_dim (the rotated leading elements of a head)
+        self.rot_dim = self.hd if self.position.inv_freq is None else int(getattr(self.position, "rot_dim", self.hd))
+        if self.rot_dim % 2 or not 2 <= self.rot_dim <= self.hd:
+            raise ConfigError(f"attention: rotary dimension {self.rot_dim} must be even and within head_dim {self.hd}")
+        if self.position.inv_freq is not None and self.position.inv_freq.numel() != self.rot_dim // 2:
+            raise ConfigError(f"attention: the position part gives {self.position.inv_freq.numel()} frequencies "
+                              f"for a rotary dimension of {self.rot_dim}")
         self.scale = 1.0 / math.sqrt(self.hd)              # fixed in code, graph.rs:2379
         d, H, G, hd = self.size, self.H, self.G, self.hd
         self.decls = {"q_proj.weight": ParamDecl((H * hd, d)), "out_proj.weight": ParamDecl((d, H * hd))}
@@ -57,12 +65,17 @@ class Attention(Mixer):
             self.w["qkv.weight"] = torch.cat([q, k, v], dim=0).contiguous()      # [(H+2G)*hd, d]
         self.position.to(q.device)
 
+    def reserve(self, device, max_rows, n_ctx):
+        if self.w["qkv.weight"].dtype == torch.bfloat16:
+            floats, counters = ops.decode_scratch_need(max_rows, self.H, self.G, self.hd, n_ctx)
+            ops.reserve_decode_scratch(device, 1, self.H, self.G, self.hd, 1, floats=floats, counters=counters)
+
     def forward(self, xn, ctx, cache, out, reads_only=False):
         if reads_only != self.shares_cache:
             raise ConfigError("attention: a layer built with shares_cache must run with cache_of, and only it")
         G = 0 if self.shares_cache else self.G
         qkv = linear(xn, self.w["qkv.weight"])
-        if (ctx.all_single and not self.shares_cache and qkv.dtype == torch.bfloat16
+        if (ctx.all_single and not self.shares_cache and qkv.dtype == torch.bfloat16 and self.rot_dim == self.hd
                 and ops.decode_fuses_rope(self.H, self.G, self.hd, cache.page_tokens, cache.pool)):
             # a decode step: norm, rotation and the cache write happen inside the attention kernel
             a = ops.attention_decode(None, cache.pool, cache.block_table, ctx.positions, ctx.row_slot, cache.layer,
@@ -74,7 +87,7 @@ class Attention(Mixer):
         q = ops.qk_rope_write(qkv, self.w.get("q_norm.weight"), self.w.get("k_norm.weight"), self.eps,
                               self.position.inv_freq, self.position.pairing, ctx.positions, ctx.row_slot,
                               cache.block_table, cache.pool, cache.layer, cache.page_tokens, self.H, G,
-                              self.hd, write_kv=not self.shares_cache, status=ctx.status)
+                              self.hd, write_kv=not self.shares_cache, status=ctx.status, rot_dim=self.rot_dim)
         a = ops.paged_attention(q, cache, ctx, self.scale, self.window)
         linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
         return out

@@ -74,6 +74,11 @@ class Part:
     def prepare(self):
         """Called once after bind(): repack or fuse weights for the kernels."""
 
+    def reserve(self, device, max_rows: int, n_ctx: int):
+        """Called once by the engine, after bind() and before the first step: allocate here what
+        the part's kernels need besides inputs and outputs, sized for steps of up to max_rows rows
+        and contexts of up to n_ctx (so that nothing grows under a captured CUDA graph)."""
+
     def kernel_modules(self, dtype: str):
         """[(module name, defines)] of the CUDA modules this part launches in `dtype`, so that
         they can be compiled before the first step."""
@@ -95,13 +100,15 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """PagedKV, FixedState or None."""
+        """What the mixer keeps between steps: PagedKV, FixedState, None, or a list of those when
+        it keeps several things (pages and a state, or two states of different shapes); `cache` in
+        forward() is then a list of views in the same order."""
         return None
 
     def forward(self, xn: torch.Tensor, ctx, cache, out: torch.Tensor, reads_only: bool = False):
         """xn: [T, d] normed input in the engine's dtype; `out`: float32 [T, d] residual stream,
         to which the mixer ADDS its result in place.  `cache` is this run's view of its cache
-        group (PagedView / StateView / None).  `reads_only`: the cache belongs to an earlier run;
+        group (PagedView / StateView / None; a list of views when cache_need() returned a list).  `reads_only`: the cache belongs to an earlier run;
         read it, write nothing."""
         raise NotImplementedError
 

@@ -37,12 +37,15 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block.  `arrangement` names how the parts are wired:
-    'prenorm': h = x + mixer(norm1(x)); out = h + ffn(norm2(h))   (graph.rs:1650-1777)."""
-    norm1: PartSpec
+    """One block.  `arrangement` names how the parts are wired, a key of
+    fellm_b200.models.model.ARRANGEMENTS (`register_arrangement` adds one):
+    'prenorm': h = x + mixer(norm1(x)); out = h + ffn(norm2(h))   (graph.rs:1650-1777).
+    norm1, norm2 and ffn may be None where an arrangement has no use for them (a layer without a
+    feed-forward, a block with one norm)."""
+    norm1: Optional[PartSpec]
     mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    norm2: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
     arrangement: str = "prenorm"
 
 

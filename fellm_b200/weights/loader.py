@@ -42,9 +42,13 @@ def _convert(t: torch.Tensor, decl, engine_dtype: str, device) -> torch.Tensor:
 def check_and_collect(model, available: Dict[str, tuple]):
     """available: {name: shape}.  Returns the problems as three lists."""
     table = model.param_table()
+    aliases = model.tied_aliases()
     missing = [n for n in table if n not in available]
-    unexpected = [n for n in available if n not in table]
+    unexpected = [n for n in available if n not in table and n not in aliases]
     wrong = []
+    for alias, owner in aliases.items():
+        if alias in available and owner in available and tuple(available[alias]) != tuple(available[owner]):
+            wrong.append(f"{alias}: file has {list(available[alias])}, but it is tied to {owner} {list(available[owner])}")
     for name, (_, _, decl) in table.items():
         if name in available:
             shape = tuple(available[name])
@@ -66,6 +70,14 @@ def _raise_if_any(where, missing, unexpected, wrong):
     raise WeightError("\n".join(parts))
 
 
+def _check_aliases(where, model, names, get):
+    """A tensor the model ties to another one may be in the file too, but only as a copy."""
+    for alias, owner in model.tied_aliases().items():
+        if alias in names and not torch.equal(get(alias), get(owner)):
+            raise WeightError(f"{where}: the model ties {alias} to {owner}, but the file's {alias} holds other "
+                              "values; set tie_word_embeddings to false to use it")
+
+
 def load_into(model, folder, device) -> None:
     """Reads <folder>/model.safetensors and binds every parameter of `model`."""
     path = Path(folder) / "model.safetensors"
@@ -73,6 +85,7 @@ def load_into(model, folder, device) -> None:
     try:
         missing, unexpected, wrong = check_and_collect(model, {n: f.shape(n) for n in f.names()})
         _raise_if_any(str(path), missing, unexpected, wrong)
+        _check_aliases(str(path), model, set(f.names()), f.tensor)
         tensors = {}
         for name, (_, _, decl) in model.param_table().items():
             tensors[name] = _convert(f.tensor(name), decl, model.dtype, device)
@@ -85,5 +98,6 @@ def bind_tensors(model, tensors: Dict[str, torch.Tensor], device) -> None:
     """Binds from tensors in memory (the random-weights mode without a file)."""
     missing, unexpected, wrong = check_and_collect(model, {n: tuple(t.shape) for n, t in tensors.items()})
     _raise_if_any("the given tensors", missing, unexpected, wrong)
+    _check_aliases("the given tensors", model, set(tensors), tensors.__getitem__)
     table = model.param_table()
     model.bind({n: _convert(tensors[n], table[n][2], model.dtype, device) for n in table})

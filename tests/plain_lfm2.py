@@ -104,8 +104,12 @@ def rope_inv_freq(theta: float, rope_dim: int):
 
 def rope_apply(x, positions, inv_freq, pairing: str):
     """x [T, heads, hd]; angle = float32(pos) * inv_freq; a' = a*c - b*s, b' = a*s + b*c on
-    pairs (2i, 2i+1) ('adjacent') or (i, i+hd/2) ('split_half')
+    pairs (2i, 2i+1) ('adjacent') or (i, i+rope_dim/2) ('split_half') of the first
+    rope_dim = 2*len(inv_freq) <= hd elements of each head; the rest stays as it is
     (crates/backend-cpu/src/kernels/rope.rs:28-62)."""
+    rope_dim = 2 * inv_freq.numel()
+    if rope_dim < x.shape[-1]:
+        return torch.cat([rope_apply(x[..., :rope_dim], positions, inv_freq, pairing), x[..., rope_dim:]], dim=-1)
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]      # [T, hd/2]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     half = x.shape[-1] // 2

@@ -51,3 +51,43 @@ def test_errors_become_exit_code_one(tmp_path, capsys):
     assert cli.main(["inspect", "--model", str(tmp_path)]) == 1
     assert "no config.json" in capsys.readouterr().err
     assert cli.main(["run", "--prompt", "1"]) == 1      # neither a folder nor --random
+
+
+def test_every_parsed_option_reaches_the_engine_options(tmp_path, monkeypatch):
+    """An option that is parsed is used: --kv-device-budget becomes EngineOptions.kv_device_budget
+    (bytes of cache pages, crates/fellm-cli/src/main.rs:42-200), --log sets the logger's level."""
+    import logging
+    seen = {}
+
+    class FakeEngine:
+        @staticmethod
+        def open(folder, opts):
+            seen["opts"] = opts
+            raise ConfigError("stop here")
+
+    import fellm_b200.engine as engine_mod
+    monkeypatch.setattr(engine_mod, "Engine", FakeEngine)
+    rc = cli.main(["--log", "debug", "run", "some_folder", "--prompt", "1", "--kv-device-budget", "1048576",
+                   "--kv-memory-fraction", "0.5", "-c", "1024", "--page-tokens", "16"])
+    assert rc == 1
+    o = seen["opts"]
+    assert (o.kv_device_budget, o.kv_memory_fraction, o.n_ctx, o.page_tokens) == (1048576, 0.5, 1024, 16)
+    assert logging.getLogger("fellm_b200").level == logging.DEBUG
+    f = tmp_path / "fellm.toml"
+    f.write_text('log = "warn"\n[run]\nkv_device_budget = 4096\n')
+    assert cli.main(["--config", str(f), "bench", "some_folder", "--requests", "3"]) == 1
+    assert seen["opts"].kv_device_budget == 4096 and logging.getLogger("fellm_b200").level == logging.WARNING
+
+
+def test_cache_size_from_a_byte_budget():
+    """pages = budget / page_bytes (crates/fellm-runtime/src/kv_fabric/fabric.rs:59-61), in whole pages."""
+    from fellm_b200.cache import CacheManager
+    from fellm_b200.parts.base import FixedState, PagedKV
+    needs = [FixedState((2, 64)), PagedKV(2, 16, None), None, PagedKV(2, 16, None), [PagedKV(1, 32, 100), FixedState((4,))]]
+    per_token = (2 * 2 * 16 * 2) * 2 + 2 * 1 * 32 * 2          # bfloat16: two layers of 2x16, one of 1x32
+    f = CacheManager.tokens_for_budget
+    assert f(needs, 2, per_token * 1000, 16, 10 ** 9) == 992    # whole pages of 16
+    assert f(needs, 2, per_token * 1000, 16, 640) == 640        # capped
+    assert f(needs, 2, 10, 16, 640) == 16                       # never less than one page
+    assert f(needs, 4, per_token * 1000, 64, 10 ** 9) == 448    # float32 cache: half the tokens
+    assert f([FixedState((3,)), None], 2, 10 ** 6, 64, 10 ** 9) == 64

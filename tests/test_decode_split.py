@@ -17,8 +17,8 @@ def test_split_properties(max_len, rows, kv_heads):
     assert max_splits >= 1 and max_splits * split_len >= bucket >= max_len
     assert (max_splits - 1) * split_len < bucket          # no range without a key of the bucket
     items = rows * kv_heads
-    if items <= ops.DECODE_TARGET_CTAS:
-        assert items * max_splits <= max(ops.DECODE_TARGET_CTAS, items)      # one wave
+    if items <= ops.decode_target_ctas():
+        assert items * max_splits <= max(ops.decode_target_ctas(), items)      # one wave
     elif bucket >= 128:
         assert max_splits == 2                            # more than a wave even unsplit: halves
 
@@ -33,3 +33,16 @@ def test_one_choice_for_a_bucket_of_contexts():
 
 def test_bench_shape():
     assert ops.decode_split(2049, 8, 8) == (512, 6)       # batch 8, 8 kv heads: 6 ranges of 8 pages for up to 3072 keys
+
+
+def test_scratch_sized_once_covers_every_step_an_engine_can_run():
+    """An engine reserves the split kernel's scratch before its first step, so that no captured
+    graph outlives a buffer: the size must cover every row count and every context bucket."""
+    import random
+    for max_rows, H, G, hd, n_ctx in [(8, 4, 2, 16, 512), (64, 16, 8, 64, 8192), (200, 32, 4, 128, 5000), (3, 6, 1, 48, 1024)]:
+        floats, counters = ops.decode_scratch_need(max_rows, H, G, hd, n_ctx)
+        rng = random.Random(max_rows)
+        for _ in range(300):
+            rows, max_len = rng.randrange(1, max_rows + 1), rng.randrange(1, n_ctx + 1)
+            _, max_splits = ops.decode_split(max_len, rows, G)
+            assert rows * H * max_splits * (hd + 2) <= floats and rows * G <= counters

@@ -102,6 +102,9 @@ def test_scheduler_preempts_on_a_small_pool_and_tokens_stay():
     sched = small.scheduler()
     assert sched.counters["preempted"] > 0 or sched.counters["shrunk"] > 0
     assert got == alone
+    cfg, w = tiny.plain_model(name)
+    assert got[0] == plain_lfm2.greedy(cfg, w, prompts[0], 24)       # and both are the plain implementation's tokens
+    assert got[3][:6] == plain_lfm2.greedy(cfg, w, prompts[3], 6)
     assert all(s.finish_reason == "length" and s.predicted_tokens == 24 for s in stats)
     small.cache.audit()
     assert small.cache.free_pages() == small.cache.n_pages
@@ -205,6 +208,23 @@ def test_prompt_portions_of_a_shape_that_comes_again_are_replayed_from_a_graph(n
         eng.release(i)
     keys = [k for k in eng.stepper.graphs if k[0] == "rows"]
     assert len(keys) == 2, keys
+    # both kinds beside a decoding request: each mixed shape four times (direct, captured, replayed twice)
+    dec_toks, dec_want = tiny.tokens(name, 30, 77), tiny.plain_logits(name, 30, 77)
+    eng.add_request("dec")
+    eng.step([StepItem("dec", dec_toks[:20], [])])
+    for j in range(4):
+        toks, want = tiny.tokens(name, n1 + n2, 60 + j), tiny.plain_logits(name, n1 + n2, 60 + j)
+        eng.add_request(f"m{j}")
+        a = eng.step([StepItem("dec", [dec_toks[20 + 2 * j]], [0]), StepItem(f"m{j}", toks[:n1], [n1 - 1])])
+        b = eng.step([StepItem(f"m{j}", toks[n1:], [n2 - 1]), StepItem("dec", [dec_toks[21 + 2 * j]], [0])])
+        eng.check_status()
+        for got, exp in ((a[0:1], dec_want[[20 + 2 * j]]), (a[1:2], want[[n1 - 1]]), (b[0:1], want[[n1 + n2 - 1]]),
+                         (b[1:2], dec_want[[21 + 2 * j]])):
+            ok, err, tol = tiny.close(got, exp, dtype)
+            assert ok, (j, err, tol)
+        eng.release(f"m{j}")
+    eng.release("dec")
+    assert len([k for k in eng.stepper.graphs if k[0] == "rows"]) == 4
     # more shapes than graphs are kept: the oldest are dropped, nothing breaks
     from fellm_b200.engine import step as step_mod
     for n in range(20, 20 + step_mod.MAX_ROW_GRAPHS + 3):

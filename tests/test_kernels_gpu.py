@@ -585,3 +585,79 @@ def test_gemm_skinny_up_to_64_rows(M, N, K, monkeypatch):
     x, w, want = _gemm_case(M, N, K, seed=9)
     got = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
     assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4)
+
+
+def build_cache_pages(keys, values, page_tokens, dtype, first_live_page=0, n_layers=2, layer=1):
+    """Like build_cache, without a loop over positions: pages in reverse physical order, NaN in the
+    pages before `first_live_page`, which the block table marks as given back (-1)."""
+    C, G, hd = keys.shape
+    n_pg = -(-C // page_tokens)
+    pad = n_pg * page_tokens - C
+    kp = torch.cat([keys, torch.full((pad, G, hd), float("nan"))]).reshape(n_pg, page_tokens, G, hd).transpose(1, 2)
+    vp = torch.cat([values, torch.full((pad, G, hd), float("nan"))]).reshape(n_pg, page_tokens, G, hd).transpose(1, 2)
+    pool = torch.randn(n_pg + 2, n_layers, 2, G, page_tokens, hd).to(dtype)
+    phys = [n_pg - p for p in range(n_pg)]                       # logical page p lives in page n_pg - p
+    pool[phys, layer, 0] = kp.to(dtype)
+    pool[phys, layer, 1] = vp.to(dtype)
+    table = torch.full((3, n_pg + 2), -1, dtype=torch.int32)
+    table[1, :n_pg] = torch.tensor(phys, dtype=torch.int32)
+    if first_live_page:
+        pool[phys[:first_live_page], layer] = float("nan")
+        table[1, :first_live_page] = -1
+    return pool.to(DEV), table.to(DEV)
+
+
+@pytest.mark.parametrize("hd,pt", [(64, 64), (32, 16)])
+@pytest.mark.parametrize("window", [16, 17, 64, 100])
+def test_attention_decode_window_edge(hd, pt, window):
+    """The tensor-core decode kernels (TMA at head size 64 / pages of 64, cp.async otherwise): the key
+    just outside the window must not count, the one just inside must.  The window's first key lies
+    inside a page, on a page's first slot, in the request's first page, or in a later key range of
+    the split; the pages wholly behind the window are given back (-1 in the block table, NaN in the
+    pool) as the cache manager does."""
+    H, G, C = 4, 2, 1500
+    torch.manual_seed(window + hd)
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    d = torch.randn(hd); d = d / d.norm()
+    q = (d * 30.0).repeat(1, H, 1).to(DEV).bfloat16()
+    boundary = 10 * pt + window - 1                          # window starts on a page's first slot
+    for pos in (window - 1, window, window + 3, boundary, boundary + 1, boundary - 1, 1400, C - 1):
+        for edge, inside in ((pos - window, False), (pos - window + 1, True)):
+            if edge < 0:
+                continue
+            k2 = keys.clone(); k2[edge] = d * 30.0
+            for trimmed in (False, True):
+                dead = max(0, pos + 1 - window + 1) // pt if trimmed else 0
+                pool, table = build_cache_pages(k2[:pos + 1], values[:pos + 1], pt, torch.bfloat16, first_live_page=dead)
+                got = ops.attention_decode(q, pool, table, i32([pos]), i32([1]), 1, hd ** -0.5, window, C)
+                got = got.float().cpu().reshape(H, hd)
+                assert not torch.isnan(got).any(), (pos, edge, trimmed)
+                hit = torch.allclose(got[0], values[edge, 0].bfloat16().float(), atol=3e-2)
+                assert hit == inside, (window, pos, edge, inside, trimmed)
+    ops.check_umma_status(DEV)
+
+
+@pytest.mark.parametrize("hd,pt", [(64, 64), (32, 16), (48, 8)])
+@pytest.mark.parametrize("window", [16, 17, 64, 100])
+def test_attention_prefill_window_edge(hd, pt, window):
+    """The same for a prompt portion on tensor cores: rows of one portion whose windows start in
+    different pages (the first row's in an earlier page than the last row's)."""
+    H, G, C, n_new = 4, 2, 700, 70
+    torch.manual_seed(window + hd + 1)
+    keys, values = torch.randn(C, G, hd) * 0.1, torch.randn(C, G, hd)
+    d = torch.randn(hd); d = d / d.norm()
+    positions = list(range(C - n_new, C))
+    for row in (0, 1, 37, n_new - 1):
+        pos = positions[row]
+        for edge, inside in ((pos - window, False), (pos - window + 1, True)):
+            k2 = keys.clone(); k2[edge] = d * 30.0
+            q = torch.randn(n_new, H, hd) * 0.1
+            q[row] = d * 30.0
+            dead = max(0, positions[0] + 1 - window + 1) // pt          # behind the FIRST row's window
+            pool, table = build_cache_pages(k2, values, pt, torch.bfloat16, first_live_page=dead)
+            got = ops.attention_prefill(q.to(DEV).bfloat16(), pool, table, i32(positions), i32([1] * n_new), i32([0, n_new]),
+                                        1, n_new, 1, hd ** -0.5, window)
+            got = got.float().cpu().reshape(n_new, H, hd)
+            assert not torch.isnan(got).any(), (row, edge)
+            hit = torch.allclose(got[row, 0], values[edge, 0].bfloat16().float(), atol=3e-2)
+            assert hit == inside, (window, row, edge, inside)

@@ -13,8 +13,9 @@ from fellm_b200.cache import CacheManager
 from fellm_b200.config import EngineOptions, register_architecture
 from fellm_b200.engine import Engine, StepItem
 from fellm_b200.engine.step import StepBuffers
-from fellm_b200.parts import (FixedState, LayerSpec, Mixer, ModelSpec, ParamDecl, PartSpec, Run, build_part,
-                              register_part)
+from fellm_b200.models import normed, register_arrangement
+from fellm_b200.parts import (FeedForward, FixedState, LayerSpec, Mixer, ModelSpec, ParamDecl, PartSpec, PositionEncoding, Run,
+                              build_part, register_part)
 from fellm_b200.weights import write_model_folder
 
 pytestmark = pytest.mark.gpu
@@ -160,6 +161,76 @@ def test_attention_part_whole_and_cut(dtype, H, G, hd, pairing, window):
 
 
 # ----------------------------------------------------------------------------------------------
+# Another position encoding, defined here: rotary over the first `rot_dim` elements of a head only,
+# with every frequency divided by `factor` (the shape of a linear position scaling).  An attention
+# mixer asks a position part for inv_freq, pairing and rot_dim and for nothing else.
+
+@register_part("position", "toy_scaled_partial_rope")
+class ScaledPartialRope(PositionEncoding):
+    def __init__(self, *, dtype, rot_dim, theta, factor, pairing):
+        super().__init__()
+        self.rot_dim, self.pairing = rot_dim, pairing
+        self.inv_freq = P.rope_inv_freq(theta, rot_dim) / factor
+
+    def to(self, device):
+        self.inv_freq = self.inv_freq.to(device)
+        return self
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,rot,pairing,kind", [(32, 16, "adjacent", "rope"), (32, 16, "split_half", "rope"),
+                                                 (64, 32, "split_half", "rope"), (48, 20, "adjacent", "toy"),
+                                                 (64, 64, "split_half", "toy")])
+def test_attention_part_with_partial_rotary_and_another_position_encoding(dtype, hd, rot, pairing, kind):
+    """rot_dim < head_dim (FeLLM's rope_dim <= head_dim, crates/backend-cpu/src/kernels/rope.rs:37-44):
+    the elements behind rot_dim are normed and not rotated.  Page size 64 at head size 64 makes the
+    decode cuts take the kernel that rotates inside attention when rot_dim == head_dim, and the
+    separate rotation kernel otherwise."""
+    d, H, G, eps, theta = 72, 4, 2, 1e-5, 10000.0
+    if kind == "rope":
+        pos = PartSpec.make("rope", rot_dim=rot, theta=theta, pairing=pairing)
+        inv = P.rope_inv_freq(theta, rot)
+    else:
+        pos = PartSpec.make("toy_scaled_partial_rope", rot_dim=rot, theta=theta, factor=4.0, pairing=pairing)
+        inv = P.rope_inv_freq(theta, rot) / 4.0
+    spec = PartSpec.make("attention", size=d, heads=H, kv_heads=G, head_dim=hd, qk_norm=True, norm_eps=eps,
+                         position=pos, window=None)
+    part, raw = bound("mixer", spec, dtype, seed=hd + rot)
+    assert part.rot_dim == rot
+    T = 37
+    xn = torch.randn(T, d).bfloat16().float()
+    want = P.attention_mixer(xn, torch.arange(T), raw["q_proj.weight"], raw["k_proj.weight"], raw["v_proj.weight"],
+                             raw["out_proj.weight"], raw["q_norm.weight"], raw["k_norm.weight"], n_heads=H,
+                             n_kv_heads=G, hd=hd, eps=eps, inv_freq=inv, pairing=pairing)
+    # the rotation matters: without it the result is another one
+    flat = P.attention_mixer(xn, torch.arange(T), raw["q_proj.weight"], raw["k_proj.weight"], raw["v_proj.weight"],
+                             raw["out_proj.weight"], raw["q_norm.weight"], raw["k_norm.weight"], n_heads=H,
+                             n_kv_heads=G, hd=hd, eps=eps, inv_freq=inv * 0, pairing=pairing)
+    assert not near(flat, want, dtype)
+    h = Harness(part.cache_need(), dtype, page_tokens=64 if hd == 64 else 8)
+    for cuts in ([T], [20] + [1] * 17, [5, 2, 30]):
+        req = f"r{len(cuts)}"
+        out = torch.zeros(T, d, device=DEV)
+        at = 0
+        for n in cuts:
+            ctx, view = h.ctx([(req, n)])
+            part.forward(xn[at:at + n].to(DEV, tdtype(dtype)), ctx, view, out[at:at + n])
+            at += n
+        assert near(out.cpu(), want, dtype), cuts
+        h.cache.release(req)
+
+
+def test_a_position_part_that_does_not_fit_the_head_is_refused():
+    from fellm_b200.config import ConfigError
+    for rot in (80, 18 + 1):
+        spec = PartSpec.make("attention", size=72, heads=4, kv_heads=2, head_dim=64, qk_norm=True, norm_eps=1e-5,
+                             position=PartSpec.make("toy_scaled_partial_rope", rot_dim=rot, theta=1e4, factor=1.0,
+                                                    pairing="adjacent"), window=None)
+        with pytest.raises(ConfigError, match="rotary dimension"):
+            build_part("mixer", spec, "bfloat16")
+
+
+# ----------------------------------------------------------------------------------------------
 # A toy mixer with state of its own: y_t = W (sum of xn over the request's tokens 0..t).  Its
 # state is the running sum, one float32 vector per request.  Nothing of it is in the framework.
 
@@ -275,5 +346,136 @@ def test_toy_architecture_registers_builds_and_steps(dtype, tmp_path):
             at += n
         eng.release("t")
         ok, err, tolr = tiny.close(torch.cat(rows), want, dtype)
+        assert ok, (cuts, err, tolr)
+    eng.check_status()
+
+
+# ----------------------------------------------------------------------------------------------
+# A second toy architecture for the seams the first one leaves out, all of it defined here:
+#   * a mixer that keeps TWO states of different shapes (a running sum and the last token's
+#     input; FeLLM's GatedDeltaNet keeps a convolution history and a matrix the same way,
+#     crates/fellm-model/src/graph.rs:792-806): cache_need() returns a list, forward() gets a list;
+#   * a feed-forward with routing: a float32 router picks one of E experts per token;
+#   * a block arrangement of its own: one norm, mixer and feed-forward side by side
+#     (x += mixer(n(x)) + ffn(n(x))), registered by name;
+#   * a layer without a feed-forward.
+
+@register_part("mixer", "toy_sum_and_last")
+class SumAndLast(Mixer):
+    def __init__(self, *, dtype, size):
+        super().__init__()
+        self.size = size
+        self.decls = {"sum.weight": ParamDecl((size, size)), "last.weight": ParamDecl((size, size))}
+
+    def cache_need(self):
+        return [FixedState((self.size,)), FixedState((1, self.size))]
+
+    def forward(self, xn, ctx, cache, out, reads_only=False):
+        sums, last = cache
+        starts, slots = ctx.item_start.tolist(), sums.item_slot.tolist()
+        for i, slot in enumerate(slots):
+            x = xn[starts[i]:starts[i + 1]].float()
+            run = sums.states[slot] + torch.cumsum(x, dim=0)
+            prev = torch.cat([last.states[slot], x[:-1]], dim=0)          # the input of the token before
+            sums.states[slot] = run[-1]
+            last.states[slot] = x[-1:]
+            out[starts[i]:starts[i + 1]] += run @ self.w["sum.weight"].float().T + prev @ self.w["last.weight"].float().T
+        return out
+
+
+@register_part("feed_forward", "toy_routed")
+class Routed(FeedForward):
+    def __init__(self, *, dtype, size, ff, experts):
+        super().__init__()
+        self.decls = {"router.weight": ParamDecl((experts, size), role="vector")}      # kept float32
+        for e in range(experts):
+            self.decls[f"experts.{e}.up.weight"] = ParamDecl((ff, size))
+            self.decls[f"experts.{e}.down.weight"] = ParamDecl((size, ff))
+        self.experts = experts
+
+    def forward(self, hn, ctx, out):
+        h = hn.float()
+        pick = torch.argmax(h @ self.w["router.weight"].T, dim=-1)                      # router logits in float32
+        for e in range(self.experts):
+            rows = (pick == e).nonzero().flatten()
+            if rows.numel():
+                z = torch.relu(h[rows] @ self.w[f"experts.{e}.up.weight"].float().T)
+                out[rows] += z @ self.w[f"experts.{e}.down.weight"].float().T
+        return out
+
+
+@register_arrangement("toy_parallel")
+def _parallel(block, x, ctx, cache, act_dtype, reads_only):
+    xn = block.norm1.forward(x, act_dtype)               # both branches read the block's input
+    block.mixer.forward(xn, ctx, cache, x, reads_only=reads_only)
+    block.ffn.forward(xn, ctx, x)
+
+
+def toy2_spec(cfg):
+    d = cfg["hidden_size"]
+    norm = lambda p: PartSpec.make("rmsnorm", prefix=p, size=d, eps=1e-6)
+    layers = [
+        LayerSpec(norm("l0.n."), PartSpec.make("toy_sum_and_last", prefix="l0.mix.", size=d), None,
+                  PartSpec.make("toy_routed", prefix="l0.ff.", size=d, ff=cfg["ff"], experts=cfg["experts"]),
+                  arrangement="toy_parallel"),
+        LayerSpec(norm("l1.n."), PartSpec.make("toy_running_sum", prefix="l1.mix.", size=d)),     # no feed-forward
+        LayerSpec(norm("l2.n1."), PartSpec.make("toy_sum_and_last", prefix="l2.mix.", size=d), norm("l2.n2."),
+                  PartSpec.make("swiglu", prefix="l2.ff.", size=d, ff=cfg["ff"]))]
+    return ModelSpec("Toy2ForCausalLM", d, cfg["vocab_size"], cfg["max_position"],
+                     PartSpec.make("table", prefix="emb.", vocab=cfg["vocab_size"], size=d), layers,
+                     norm("norm."), PartSpec.make("linear", prefix="head.", vocab=cfg["vocab_size"], size=d, tied=False))
+
+
+register_architecture("Toy2ForCausalLM", lambda d: ToyConfig(d), toy2_spec)
+TOY2 = dict(architectures=["Toy2ForCausalLM"], vocab_size=61, hidden_size=40, ff=56, experts=3, max_position=128)
+
+
+def toy2_plain(w, tokens):
+    x = w["emb.weight"][torch.tensor(tokens)]
+
+    def sum_and_last(xn, p):
+        prev = torch.cat([torch.zeros(1, xn.shape[1]), xn[:-1]], dim=0)
+        return torch.cumsum(xn, 0) @ w[p + "sum.weight"].T + prev @ w[p + "last.weight"].T
+
+    xn = P.rmsnorm(x, w["l0.n.weight"], 1e-6)
+    pick = torch.argmax(xn @ w["l0.ff.router.weight"].T, dim=-1)
+    ff = torch.zeros_like(x)
+    for t in range(len(tokens)):
+        e = int(pick[t])
+        ff[t] = torch.relu(xn[t] @ w[f"l0.ff.experts.{e}.up.weight"].T) @ w[f"l0.ff.experts.{e}.down.weight"].T
+    x = x + sum_and_last(xn, "l0.mix.") + ff
+    x = x + torch.cumsum(P.rmsnorm(x, w["l1.n.weight"], 1e-6), 0) @ w["l1.mix.proj.weight"].T
+    x = x + sum_and_last(P.rmsnorm(x, w["l2.n1.weight"], 1e-6), "l2.mix.")
+    hn = P.rmsnorm(x, w["l2.n2.weight"], 1e-6)
+    x = x + P.swiglu(hn, w["l2.ff.gate.weight"], w["l2.ff.up.weight"], w["l2.ff.down.weight"])
+    return P.rmsnorm(x, w["norm.weight"], 1e-6) @ w["head.weight"].T
+
+
+def test_two_states_a_routed_feed_forward_and_an_arrangement_of_its_own(tmp_path):
+    """float32 only: the expert a token goes to must not flip on rounding."""
+    folder = write_model_folder(tmp_path / "toy2", TOY2, 5)
+    eng = Engine.open(folder, EngineOptions(dtype="float32", n_ctx=0, max_requests=4, max_tokens=256, page_tokens=16,
+                                            cuda_graphs=False))
+    needs = eng.model.cache_needs()
+    assert needs[0] == [FixedState((40,)), FixedState((1, 40))] and needs[1] == FixedState((40,))
+    # the running sums of all three layers share one group, the last-token vectors another
+    shapes = sorted(tuple(g.states.shape[1:]) for g in eng.cache.fixed)
+    assert shapes == [(2, 1, 40), (3, 40)] and not eng.cache.paged
+    assert eng.model.blocks[1].ffn is None and eng.model.blocks[0].norm2 is None
+    w = {k: v.float() for k, v in P.read_safetensors(folder / "model.safetensors").items()}
+    toks = [int(t) for t in torch.randint(0, 61, (33,), generator=torch.Generator().manual_seed(2))]
+    want = toy2_plain(w, toks)
+    other = [int(t) for t in torch.randint(0, 61, (9,), generator=torch.Generator().manual_seed(3))]
+    for cuts in ([33], [5, 1, 1, 2, 24], [1] * 33):
+        eng.add_request("t"), eng.add_request("o")          # a second request beside it, so that slots matter
+        rows, at = [], 0
+        for j, n in enumerate(cuts):
+            items = [StepItem("t", toks[at:at + n], list(range(n)))]
+            if j < len(other):
+                items.insert(0, StepItem("o", [other[j]], []))
+            rows.append(eng.step(items))
+            at += n
+        eng.release("t"), eng.release("o")
+        ok, err, tolr = tiny.close(torch.cat(rows), want, "float32")
         assert ok, (cuts, err, tolr)
     eng.check_status()

@@ -49,6 +49,41 @@ def check(tag, got, want, dtype):
     assert ok, f"{tag}: error {err:.3e} > {tol:.3e}"
 
 
+def mixed_phase(eng, rng, tag, toks, lens, want, dtype):
+    """Up to four live requests, portions of some beside decoded tokens of others, a request left out
+    of a step now and then; eight requests through a pool that holds far fewer, so that pages and
+    state slots are used again."""
+    from fellm_b200.engine import StepItem
+    queue, live, serial = list(range(5)) + [0, 1, 2], {}, 0   # mixed, pages and slots used again
+    while queue or live:
+        while queue and len(live) < 4:
+            idx = queue.pop(0)
+            name = f"m{serial}"
+            serial += 1
+            eng.add_request(name)
+            live[name] = [idx, 0]
+        items, refs = [], []
+        for name, (idx, at) in list(live.items()):
+            if rng.random() < 0.2 and len(live) > 1:
+                continue                                     # left out of this step
+            n = lens[idx]
+            s = 1 if at >= n - 32 else int(min(n - 32 - at, rng.choice([2, 3, 7, 16, 30, 64, 100])))
+            s = max(1, min(s, n - at))
+            items.append(StepItem(name, toks[idx][at:at + s], list(range(s))))
+            refs.append((idx, at, s))
+            live[name][1] = at + s
+        if not items:
+            continue
+        lg = eng.step(items)
+        row = 0
+        for idx, at, s in refs:
+            check(f"{tag}: mixed request {idx} at {at}+{s}", lg[row:row + s], want[idx][at:at + s], dtype)
+            row += s
+        for name in [k for k, v in live.items() if v[1] >= lens[v[0]]]:
+            eng.release(name)
+            del live[name]
+
+
 @pytest.mark.parametrize("trial", range(10))
 def test_a_random_configuration_under_every_cut(trial):
     from fellm_b200.config.options import EngineOptions
@@ -87,33 +122,18 @@ def test_a_random_configuration_under_every_cut(trial):
                   want[i][at:at + s], dtype)
             at += s
         eng.release("p")
-        queue, live, serial = list(range(5)) + [0, 1, 2], {}, 0   # mixed, pages and slots used again
-        while queue or live:
-            while queue and len(live) < 4:
-                idx = queue.pop(0)
-                name = f"m{serial}"
-                serial += 1
-                eng.add_request(name)
-                live[name] = [idx, 0]
-            items, refs = [], []
-            for name, (idx, at) in list(live.items()):
-                if rng.random() < 0.2 and len(live) > 1:
-                    continue                                     # left out of this step
-                n = lens[idx]
-                s = 1 if at >= n - 32 else int(min(n - 32 - at, rng.choice([2, 3, 7, 16, 30, 64, 100])))
-                s = max(1, min(s, n - at))
-                items.append(StepItem(name, toks[idx][at:at + s], list(range(s))))
-                refs.append((idx, at, s))
-                live[name][1] = at + s
-            if not items:
-                continue
-            lg = eng.step(items)
-            row = 0
-            for idx, at, s in refs:
-                check(f"{tag}: mixed request {idx} at {at}+{s}", lg[row:row + s], want[idx][at:at + s], dtype)
-                row += s
-            for name in [k for k, v in live.items() if v[1] >= lens[v[0]]]:
-                eng.release(name)
-                del live[name]
+        mixed_phase(eng, np.random.default_rng(trial), tag, toks, lens, want, dtype)
         eng.check_status()
         del eng
+        if dtype == "bfloat16" or trial % 2:
+            # the same mixed schedule three times with steps replayed from CUDA graphs where their counts
+            # come again: the first pass runs directly, the second captures, the third replays, each on
+            # the slots and pages that the pass before left free
+            eng = Engine.open(str(folder), EngineOptions(dtype=dtype, n_ctx=0, max_requests=8, cuda_graphs=True,
+                                                         max_tokens=pool, n_batch=4096))
+            for rep in range(3):
+                mixed_phase(eng, np.random.default_rng(trial), f"{tag} graphs pass {rep}", toks, lens, want, dtype)
+            assert any(k[0] == "rows" for k in eng.stepper.graphs)
+            eng.check_status()
+            eng.cache.audit()
+            del eng

@@ -259,3 +259,47 @@ def test_one_step_ahead_under_page_pressure_matches_the_plain_order():
     _, want_toks, want_done = _scenario(FakeBackend, False, **kw)
     s, toks, done = _scenario(AheadBackend, True, **kw)
     assert toks == want_toks and done == want_done
+
+
+def test_two_readers_each_get_their_own_events():
+    """Two requests read one after the other, each through poll_event(its id): the first reader
+    runs the iterations that also produce the second's tokens, and those must still be there when
+    the second reader comes (an engine with two live token streams reads them this way)."""
+    want_toks, want_done = run_all(_two(Scheduler(FakeBackend(), 64, 64))[0])
+    s, a, b = _two(Scheduler(FakeBackend(), 64, 64))
+    got = {a: [], b: []}
+    stats = {}
+    for rid in (a, b):
+        while True:
+            ev = s.poll_event(rid)
+            if ev is None:
+                break
+            assert ev.req == rid
+            if ev.kind == "token":
+                got[rid].append(ev.token)
+            else:
+                stats[rid] = ev.stats
+                break
+    assert got == want_toks and len(got[b]) == 9
+    assert {r: st.finish_reason for r, st in stats.items()} == {r: st.finish_reason for r, st in want_done.items()}
+    assert s.poll_event() is None and s.idle()
+    # a set of ids: events of both, in the order they were made; a third request's stay behind
+    s, a, b = _two(Scheduler(FakeBackend(), 64, 64))
+    c = s.enqueue_ids([9, 9], G(2))
+    seen = []
+    while True:
+        ev = s.poll_event({a, b})
+        if ev is None:
+            break
+        seen.append(ev.req)
+    assert set(seen) == {a, b} and c not in seen
+    rest = []
+    while (ev := s.poll_event()) is not None:
+        rest.append((ev.req, ev.kind))
+    assert rest == [(c, "token"), (c, "token"), (c, "done")]
+
+
+def _two(s):
+    a = s.enqueue_ids([1, 2, 3, 4, 5], G(6))
+    b = s.enqueue_ids([7, 8], G(9))
+    return s, a, b

@@ -1,0 +1,157 @@
+"""Logits of the schedules that the benchmark times, against the plain implementation: decode
+steps of 17 to 64 requests (other kernels than small steps: no fused norm, the convolution as a
+kernel of its own, the products of many rows, decode attention beyond one wave), the real layer
+sizes of the 350M / 700M / 1.2B shapes in two-layer cuts, and mixed steps replayed from CUDA graphs
+whose layout differs from the one they were captured with."""
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2
+import tiny
+from fellm_b200.config.options import EngineOptions
+from fellm_b200.engine import Engine, StepItem
+from fellm_b200.weights import write_model_folder
+
+pytestmark = pytest.mark.gpu
+_tmp = tempfile.TemporaryDirectory(prefix="fellm_b200_schedules_")
+
+
+def check(tag, got, want, dtype):
+    ok, err, tol = tiny.close(got, want, dtype)
+    assert ok, f"{tag}: error {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("n_req", [20, 40, 64])
+def test_many_requests_decode_together(n_req, graphs):
+    """Width 1024, heads of 64, pages of 64 tokens, bfloat16: 20, 40 and 64 requests with prompts of
+    different lengths decode 8 steps together (some cross a page's edge), directly and from a CUDA
+    graph; every row of every step against the plain implementation."""
+    n_dec = 8
+    rng = np.random.default_rng(n_req)
+    lens = [int(x) for x in rng.integers(1, 130, n_req)]
+    lens[0], lens[1], lens[2] = 60, 63, 64                   # a page's edge inside the decoded steps
+    toks = [tiny.tokens("C", n + n_dec, 300 + i) for i, n in enumerate(lens)]
+    eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs, max_requests=64, max_tokens=64 * 256)
+    for i, n in enumerate(lens):
+        eng.add_request(i)
+        eng.step([StepItem(i, toks[i][:n], [])])
+    rows = []
+    for t in range(n_dec):
+        rows.append(eng.step([StepItem(i, [toks[i][lens[i] + t]], [0]) for i in range(n_req)]).clone())
+    eng.check_status()
+    got = torch.stack(rows)                                  # [n_dec, requests, vocab]
+    if graphs:
+        assert len(eng.stepper.graphs) >= 1
+    for i, n in enumerate(lens):
+        want = tiny.plain_logits("C", n + n_dec, 300 + i)[n:]
+        check(f"request {i} of {n_req} (prompt {n})", got[:, i], want, "bfloat16")
+
+
+SHAPES = {   # the layer sizes of the benchmark shapes; two layers (one convolution, one attention) keep the plain side at seconds
+    "350m": dict(hidden_size=1024, num_attention_heads=16, block_ff_dim=6656),
+    "700m": dict(hidden_size=1536, num_attention_heads=24, block_ff_dim=10752),
+    "1.2b": dict(hidden_size=2048, num_attention_heads=32, block_ff_dim=12288),
+}
+
+
+def shape_config(name):
+    cfg = dict(architectures=["Lfm2ForCausalLM"], vocab_size=65536, num_hidden_layers=2, num_key_value_heads=8,
+               head_dim=64, layer_types=["conv", "full_attention"], block_auto_adjust_ff_dim=True,
+               block_ffn_dim_multiplier=1.0, block_multiple_of=256, rope_theta=1000000.0, rope_pairing="split_half",
+               conv_L_cache=3, conv_bias=False, norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=128000)
+    cfg.update(SHAPES[name])
+    return cfg
+
+
+@pytest.mark.parametrize("name", list(SHAPES))
+def test_the_benchmark_shapes_in_two_layer_cuts(name):
+    """Real widths, feed-forward sizes, head counts and the vocabulary of 65,536: a prompt of 70 tokens
+    whole, then in portions, then 6 decode steps (alone, and beside 8 and 39 other requests, which
+    moves the products to other kernels), in float32 and bfloat16."""
+    cfg = shape_config(name)
+    folder = write_model_folder(Path(_tmp.name) / name, cfg, 11)
+    pcfg, w = plain_lfm2.load_folder(str(folder))
+    assert plain_lfm2.ff_dim(pcfg) == {"350m": 4608, "700m": 7168, "1.2b": 8192}[name]
+    rng = np.random.default_rng(5)
+    n, n_dec = 70, 6
+    toks = [int(t) for t in rng.integers(0, 65536, n + n_dec)]
+    want = plain_lfm2.forward(pcfg, w, toks)
+    del w
+    others = [[int(t) for t in rng.integers(0, 65536, 3 + n_dec)] for _ in range(39)]
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.open(str(folder), EngineOptions(dtype=dtype, n_ctx=4096, max_requests=48, cuda_graphs=False,
+                                                     max_tokens=48 * 128, page_tokens=64, n_batch=4096))
+        eng.add_request("w")
+        check(f"{name} {dtype}: whole", eng.step([StepItem("w", toks[:n], list(range(n)))]), want[:n], dtype)
+        for t in range(n, n + n_dec):
+            check(f"{name} {dtype}: decode at {t}", eng.step([StepItem("w", [toks[t]], [0])]), want[t:t + 1], dtype)
+        eng.release("w")
+        eng.add_request("p")
+        at = 0
+        for s in (33, 2, 35):
+            check(f"{name} {dtype}: portion {at}+{s}", eng.step([StepItem("p", toks[at:at + s], list(range(s)))]),
+                  want[at:at + s], dtype)
+            at += s
+        if dtype == "bfloat16":
+            # the same decode steps beside 8, then 39 other requests: 9 and 40 rows a step
+            for k, o in enumerate(others):
+                eng.add_request(k)
+                eng.step([StepItem(k, o[:3], [])])
+            for j, t in enumerate(range(n, n + n_dec)):
+                beside = 8 if j < 3 else 39
+                items = [StepItem(k, [others[k][3 + j]], []) for k in range(beside)]
+                items.insert(4, StepItem("p", [toks[t]], [0]))
+                check(f"{name} {dtype}: decode at {t} beside {beside}", eng.step(items), want[t:t + 1], dtype)
+        eng.check_status()
+        del eng
+        torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("name,dtype,far", [("B", "float32", 900), ("B", "bfloat16", 900), ("C", "bfloat16", 400)])
+def test_a_replayed_graph_of_a_mixed_step_takes_another_layout(name, dtype, far):
+    """A step that is not pure decode is replayed from a graph keyed by its counts (rows, items, wanted
+    rows, the longest item): the same counts come again with the items in another order, with other
+    slots and pages, and at a cached prefix of hundreds of tokens instead of none."""
+    pt = 64 if name == "C" else 16
+    eng = tiny.make_engine(name, dtype, cuda_graphs=True, page_tokens=pt, max_tokens=4096, max_requests=12)
+    n1, n2 = 37, 12
+    serial = 0
+
+    def fresh(prefix):
+        nonlocal serial
+        serial += 1
+        rid = f"r{serial}"
+        eng.add_request(rid)
+        toks = tiny.tokens(name, prefix + n1, 500 + serial)
+        if prefix:
+            eng.step([StepItem(rid, toks[:prefix], [])])
+        return rid, toks, tiny.plain_logits(name, prefix + n1, 500 + serial), prefix
+
+    def mixed(first_long, prefixes):
+        """Two items, 37 and 12 tokens (in this or the other order), wanted: the last row of each."""
+        a, b = fresh(prefixes[0]), fresh(prefixes[1])
+        la, lb = (n1, n2) if first_long else (n2, n1)
+        items = [StepItem(a[0], a[1][a[3]:a[3] + la], [la - 1]), StepItem(b[0], b[1][b[3]:b[3] + lb], [lb - 1])]
+        got = eng.step(items)
+        check(f"{first_long} {prefixes}: first item", got[0:1], a[2][[a[3] + la - 1]], dtype)
+        check(f"{first_long} {prefixes}: second item", got[1:2], b[2][[b[3] + lb - 1]], dtype)
+        return a[0], b[0]
+
+    held = []
+    held += mixed(True, (0, 0))               # runs directly
+    held += mixed(True, (0, 0))               # captured
+    n_graphs = len([k for k in eng.stepper.graphs if k[0] == "rows"])
+    held += mixed(False, (0, 0))              # replayed: the short item first
+    eng.release(held.pop(0)), eng.release(held.pop(0))
+    held += mixed(True, (far, 3))             # replayed: a long cached prefix, other slots and pages
+    held += mixed(False, (5, far))
+    assert len([k for k in eng.stepper.graphs if k[0] == "rows"]) >= n_graphs >= 1
+    eng.check_status()
+    for r in held:
+        eng.release(r)
+    eng.cache.audit()

@@ -116,3 +116,22 @@ def test_random_mode_is_seeded_and_per_tensor(tmp_path):
     assert torch.equal(f.tensor(name), a[name])
     f.close()
     assert json.loads((folder / "config.json").read_text())["conv_L_cache"] == 3
+
+
+def test_a_tied_model_takes_a_file_that_also_stores_the_head(tmp_path):
+    """Files written from a state dict often carry lm_head.weight although the embeddings are
+    tied: a copy of the embedding matrix is accepted, anything else is refused by name (FeLLM reads
+    `output.weight` when it is there and ties otherwise, crates/fellm-model/src/graph.rs:29-34)."""
+    m = _model("A", "float32")
+    t = random_tensors(m, 0)
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    (tmp_path / "config.json").write_text(json.dumps(tiny.TINY_A))
+    write_safetensors(tmp_path / "model.safetensors", t)
+    load_into(m, tmp_path, "cpu")
+    assert m.head.w["weight"] is m.embedding.w["weight"]
+    t["lm_head.weight"] = t["lm_head.weight"] + 1.0
+    with pytest.raises(WeightError, match="ties lm_head.weight to model.embed_tokens.weight"):
+        bind_tensors(m, t, "cpu")
+    t["lm_head.weight"] = torch.zeros(3, 64)
+    with pytest.raises(WeightError, match="lm_head.weight: file has \\[3, 64\\], but it is tied"):
+        bind_tensors(m, t, "cpu")
