@@ -349,3 +349,221 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
     default: return FELLM_ERR_ARG;
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Few rows (a decode step of 17..64 requests): the product is bound by reading W once, and a
+// 128-row MMA fed with tokens would be three quarters empty.  So the operands change places:
+// D[n, t] = sum_k W[n, k] x[t, k], the 128 rows of the MMA are WEIGHT rows, its N the step's tokens
+// (16..64 columns of tensor memory).  A CTA owns one tile of 128 weight rows and one slice of K;
+// the slices of a tile are the ranks of a cluster (1, 2, 4 or 8), enough of them to spread the matrix
+// over the SMs.  The TMA thread asks for the tile's weights BEFORE it waits for the kernel in
+// front (they do not depend on it), for x after; the partial tiles go to shared memory
+// ([token][weight row] float32), and after a cluster barrier rank r sums tokens r, r+S, ... over
+// the ranks in rank order (distributed shared memory) and runs the epilogue: out[t, n] is written
+// with the 128 threads of a token on consecutive n.
+//
+// Roles (192 threads): warp 0 lane 0 = TMA, warp 1 = tensor memory + MMA (lane 0), warps 2-5 read
+// the accumulator (TMEM lane quarter = warp % 4).  All waits are bounded (status 111 TMA, 112 MMA,
+// 113 accumulator); a role that gives up still goes through both cluster barriers.
+#include <cooperative_groups.h>
+namespace cgx = cooperative_groups;
+
+#define SW_THREADS 192
+#define SW_W_BYTES (UM_BM * UM_BK * 2)          // 16 KB: 128 weight rows x 64 k
+#define SW_MAX_STAGES 12
+
+struct SwapArgs {
+  const float* bias; void* out; int* status;
+  int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..64)
+};
+
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
+  unsigned* r = reinterpret_cast<unsigned*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(SW_THREADS)
+gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, SwapArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * SW_MAX_STAGES + 1];     // full[], empty[], accumulator done
+  __shared__ unsigned tmem_base_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* tiles_ptr = smem_raw + (tiles - smem_u32(smem_raw));
+  const int stages = a.stages, stage_bytes = SW_W_BYTES + a.mt * UM_BK * 2;
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[SW_MAX_STAGES]), accfull = smem_u32(&bars[2 * SW_MAX_STAGES]);
+  const int split = a.splits > 1 ? (int)cgx::this_cluster().block_rank() : 0;
+  const int n0 = blockIdx.y * UM_BM;
+  const int kb_total = (a.K + UM_BK - 1) / UM_BK;
+  const int kb0 = (int)((long long)kb_total * split / a.splits), kb1 = (int)((long long)kb_total * (split + 1) / a.splits);
+  const int nkb = kb1 - kb0;
+  const unsigned tmem_cols = a.mt <= 32 ? 32u : 64u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(accfull, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+  pdl_launch_dependents();
+
+  if (warp == 0 && lane == 0) {
+    // weights first: they do not depend on the kernel in front
+    const int first = nkb < stages ? nkb : stages;
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(full0 + 8 * i, stage_bytes);
+      tma_load_2d(tiles + i * stage_bytes, &map_w, (kb0 + i) * UM_BK, n0, full0 + 8 * i);
+    }
+    pdl_wait(); FELLM_TRACE_WAITED();
+    for (int i = 0; i < first; ++i)
+      tma_load_2d(tiles + i * stage_bytes + SW_W_BYTES, &map_x, (kb0 + i) * UM_BK, 0, full0 + 8 * i);
+    for (int it = first; it < nkb; ++it) {
+      const int s = it % stages;
+      if (!mbar_wait(empty0 + 8 * s, (it / stages - 1) & 1, a.status, 111)) break;
+      mbar_expect_tx(full0 + 8 * s, stage_bytes);
+      tma_load_2d(tiles + s * stage_bytes, &map_w, (kb0 + it) * UM_BK, n0, full0 + 8 * s);
+      tma_load_2d(tiles + s * stage_bytes + SW_W_BYTES, &map_x, (kb0 + it) * UM_BK, 0, full0 + 8 * s);
+    }
+  } else {
+    pdl_wait();                      // every other thread reads (bias aside) what the kernel in front wrote, or nothing
+    if (warp == 1 && lane == 0) {
+      const unsigned idesc = umma_idesc(UM_BM, a.mt);
+      bool ok = true;
+      for (int it = 0; it < nkb; ++it) {
+        const int s = it % stages;
+        ok = mbar_wait(full0 + 8 * s, (it / stages) & 1, a.status, 112);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned sw = tiles + s * stage_bytes, sx = sw + SW_W_BYTES;
+        const unsigned long long dw = umma_desc(sw), dx = umma_desc(sx);
+#pragma unroll
+        for (int k = 0; k < UM_BK / 16; ++k)
+          umma_f16(tmem_base, dw + (unsigned long long)(k * 2), dx + (unsigned long long)(k * 2), idesc, (it | k) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      if (ok) umma_commit(accfull);
+    }
+  }
+  float* part = reinterpret_cast<float*>(tiles_ptr);       // [mt][128]: over the stages, once every MMA has read them
+  if (warp >= 2) {
+    const int q = warp & 3, row = q * 32 + lane;
+    if (mbar_wait(accfull, 0, a.status, 113)) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      for (int c0 = 0; c0 < a.mt; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(c0 + j) * UM_BM + row] = v[j];
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  if (a.splits > 1) cgx::this_cluster().sync(); else __syncthreads();
+
+  // rank r: tokens r, r + S, ...; a token's 128 outputs by 128 consecutive threads' turns
+  const int my_tokens = split < a.M ? (a.M - split + a.splits - 1) / a.splits : 0;
+  for (int e = threadIdx.x; e < my_tokens * UM_BM; e += SW_THREADS) {
+    const int row = e & (UM_BM - 1), t = split + (e >> 7) * a.splits, n = n0 + row;
+    float v = 0.f;
+    if (a.splits > 1) {
+      for (int j = 0; j < a.splits; ++j) v += cgx::this_cluster().map_shared_rank(part, j)[t * UM_BM + row];
+    } else {
+      v = part[t * UM_BM + row];
+    }
+    if (a.bias && n < a.N) v += a.bias[n];
+    if (EPI == EPI_SWIGLU) {
+      // rows in blocks of 16: 8 gate, then the 8 up rows of the same features; lanes 8..15 hand their up value down
+      const float up = __shfl_down_sync(0xffffffffu, v, 8);
+      if ((row & 15) < 8 && n < a.N)
+        ((bf16*)a.out)[(size_t)t * a.ldo + ((n0 + (row & ~15)) >> 1) + (row & 7)] = __float2bfloat16_rn((v / (1.0f + expf(-v))) * up);
+    } else if (n < a.N) {
+      const size_t o = (size_t)t * a.ldo + n;
+      if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v);
+      else if (EPI == EPI_ACC) ((float*)a.out)[o] += v;
+      else ((float*)a.out)[o] = v;
+    }
+  }
+  if (a.splits > 1) cgx::this_cluster().sync(); else __syncthreads();      // nobody leaves while its partial tile is being read
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+struct SwapPlan { int mt, splits, stages; size_t smem; };
+static bool plan_swap(int M, int N, int K, SwapPlan* p) {
+  if (M < 1 || M > 64 || K % 8) return false;
+  const int n_sm = fellm_sm_count();
+  const int n_tiles = ceil_div(N, UM_BM), kb_total = ceil_div(K, UM_BK);
+  p->mt = ceil_div(M, 16) * 16;
+  int splits = 1;
+  static int max_splits = 0;
+  if (!max_splits) { const char* e = getenv("FELLM_B200_SWAP_SPLITS"); max_splits = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 8; }
+  while (splits * 2 <= max_splits && splits * 2 <= kb_total && n_tiles * splits * 2 <= n_sm) splits *= 2;
+  p->splits = splits;
+  const int stage_bytes = SW_W_BYTES + p->mt * UM_BK * 2;
+  int stages = ceil_div(kb_total, splits);
+  const int fit = (200 * 1024) / stage_bytes;
+  if (stages > fit) stages = fit;
+  if (stages > SW_MAX_STAGES) stages = SW_MAX_STAGES;
+  p->stages = stages;
+  size_t bytes = (size_t)stages * stage_bytes, part = (size_t)p->mt * UM_BM * sizeof(float);
+  p->smem = (bytes > part ? bytes : part) + 1024;
+  return true;
+}
+
+template <int EPI>
+static int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, const SwapArgs& a, size_t smem, int n_tiles, cudaStream_t stream) {
+  auto kern = gemm_umma_swap_kernel<EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  return launch_k_class(1, kern, dim3(a.splits, n_tiles, 1), dim3(SW_THREADS, 1, 1), smem, stream, a.splits, mw, mx, a);
+}
+
+// Whether fellm_gemm_umma_swap takes the product (1) or not (0).
+FELLM_API int fellm_gemm_umma_swap_takes(int M, int N, int K) {
+  SwapPlan p;
+  return (M >= 1 && M <= 64 && N >= 1 && K >= 8 && plan_swap(M, N, K, &p)) ? 1 : 0;
+}
+
+// out[M, N] = x[M, K] W[N, K]^T for M <= 64 rows with the operands' places changed (see above).
+// Same epilogues and status word as fellm_gemm_umma (111..113 for this kernel's roles).
+FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
+                                   int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!x || !W || !out || K <= 0) return FELLM_ERR_ARG;
+  if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
+  if (epi == EPI_SWIGLU && (N % 16)) return FELLM_ERR_SIZE;
+  SwapPlan p;
+  if (!plan_swap(M, N, K, &p)) return FELLM_ERR_SIZE;
+  CUtensorMap mw, mx;
+  int e = make_map(&mw, W, N, K, ldw, UM_BM);
+  if (e) return e;
+  e = make_map(&mx, x, M, K, lda, p.mt);
+  if (e) return e;
+  SwapArgs a;
+  a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
+  a.mt = p.mt; a.splits = p.splits; a.stages = p.stages;
+  const int n_tiles = ceil_div(N, UM_BM);
+  switch (epi) {
+    case EPI_STORE: return launch_swap<EPI_STORE>(mw, mx, a, p.smem, n_tiles, stream);
+    case EPI_ACC: return launch_swap<EPI_ACC>(mw, mx, a, p.smem, n_tiles, stream);
+    case EPI_SWIGLU: return launch_swap<EPI_SWIGLU>(mw, mx, a, p.smem, n_tiles, stream);
+    case EPI_F32: return launch_swap<EPI_F32>(mw, mx, a, p.smem, n_tiles, stream);
+    default: return FELLM_ERR_ARG;
+  }
+}

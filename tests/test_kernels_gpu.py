@@ -627,7 +627,7 @@ def test_attention_decode_window_edge(hd, pt, window):
                 continue
             k2 = keys.clone(); k2[edge] = d * 30.0
             for trimmed in (False, True):
-                dead = max(0, pos + 1 - window + 1) // pt if trimmed else 0
+                dead = max(0, pos - window + 1) // pt if trimmed else 0      # what the manager gave back before this query
                 pool, table = build_cache_pages(k2[:pos + 1], values[:pos + 1], pt, torch.bfloat16, first_live_page=dead)
                 got = ops.attention_decode(q, pool, table, i32([pos]), i32([1]), 1, hd ** -0.5, window, C)
                 got = got.float().cpu().reshape(H, hd)
@@ -653,7 +653,7 @@ def test_attention_prefill_window_edge(hd, pt, window):
             k2 = keys.clone(); k2[edge] = d * 30.0
             q = torch.randn(n_new, H, hd) * 0.1
             q[row] = d * 30.0
-            dead = max(0, positions[0] + 1 - window + 1) // pt          # behind the FIRST row's window
+            dead = max(0, positions[0] - window + 1) // pt              # behind the FIRST row's window
             pool, table = build_cache_pages(k2, values, pt, torch.bfloat16, first_live_page=dead)
             got = ops.attention_prefill(q.to(DEV).bfloat16(), pool, table, i32(positions), i32([1] * n_new), i32([0, n_new]),
                                         1, n_new, 1, hd ** -0.5, window)
