@@ -357,18 +357,21 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
 // (16..64 columns of tensor memory).  A CTA owns one tile of 128 weight rows and one slice of K;
 // the slices of a tile are the ranks of a cluster (1, 2, 4 or 8), enough of them to spread the matrix
 // over the SMs.  The TMA thread asks for the tile's weights BEFORE it waits for the kernel in
-// front (they do not depend on it), for x after; the partial tiles go to shared memory
-// ([token][weight row] float32), and after a cluster barrier rank r sums tokens r, r+S, ... over
-// the ranks in rank order (distributed shared memory) and runs the epilogue: out[t, n] is written
-// with the 128 threads of a token on consecutive n.
+// front (they do not depend on it), for x after.  Token t of the tile belongs to rank t % S: every
+// rank stores its partial sums of that token into the owner's shared memory (distributed shared
+// memory stores: nobody waits for a remote load), and after ONE cluster barrier the owner adds the
+// S partial rows in rank order and runs the epilogue, a warp a token, a lane four consecutive
+// outputs.
 //
-// Roles (192 threads): warp 0 lane 0 = TMA, warp 1 = tensor memory + MMA (lane 0), warps 2-5 read
-// the accumulator (TMEM lane quarter = warp % 4).  All waits are bounded (status 111 TMA, 112 MMA,
-// 113 accumulator); a role that gives up still goes through both cluster barriers.
+// Roles (256 threads): warp 0 lane 0 = TMA, warp 1 = tensor memory + MMA (lane 0); once the
+// products are done all eight warps read the accumulator (TMEM lane quarter = warp % 4, 16-column
+// chunks by turns of warp / 4) and then share the owner's tokens.  All waits are bounded (status 111 TMA, 112 MMA,
+// 113 accumulator); a role that gives up still goes through the cluster barrier.
 #include <cooperative_groups.h>
 namespace cgx = cooperative_groups;
 
-#define SW_THREADS 192
+#define SW_THREADS 256
+#define SW_WARPS 8
 #define SW_W_BYTES (UM_BM * UM_BK * 2)          // 16 KB: 128 weight rows x 64 k
 #define SW_MAX_STAGES 12
 
@@ -377,17 +380,24 @@ struct SwapArgs {
   int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..64)
 };
 
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float* v) {
+__device__ __forceinline__ void tmem_ld16_nowait(unsigned taddr, float* v) {
   unsigned* r = reinterpret_cast<unsigned*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned mapa_rank(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(unsigned addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(addr), "f"(v) : "memory");
 }
 
-template <int EPI>
+template <int EPI, int S>
 __global__ void __launch_bounds__(SW_THREADS)
 gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, SwapArgs a) {
   FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
@@ -396,13 +406,14 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __shared__ unsigned tmem_base_s;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  unsigned char* tiles_ptr = smem_raw + (tiles - smem_u32(smem_raw));
   const int stages = a.stages, stage_bytes = SW_W_BYTES + a.mt * UM_BK * 2;
+  // behind the stages: what the ranks send this CTA, [token of mine][rank][128 weight rows] float32
+  float* recv = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + (size_t)stages * stage_bytes);
   const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[SW_MAX_STAGES]), accfull = smem_u32(&bars[2 * SW_MAX_STAGES]);
-  const int split = a.splits > 1 ? (int)cgx::this_cluster().block_rank() : 0;
+  const int split = S > 1 ? (int)cgx::this_cluster().block_rank() : 0;
   const int n0 = blockIdx.y * UM_BM;
   const int kb_total = (a.K + UM_BK - 1) / UM_BK;
-  const int kb0 = (int)((long long)kb_total * split / a.splits), kb1 = (int)((long long)kb_total * (split + 1) / a.splits);
+  const int kb0 = (int)((long long)kb_total * split / S), kb1 = (int)((long long)kb_total * (split + 1) / S);
   const int nkb = kb1 - kb0;
   const unsigned tmem_cols = a.mt <= 32 ? 32u : 64u;
 
@@ -420,6 +431,14 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem_base = tmem_base_s;
   pdl_launch_dependents();
+  // a rank's shared memory may be written only once the rank runs: everybody says so here and
+  // looks for the others' word before the first remote store (by then it has long been given)
+  if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
+
+  // the owner's part of the epilogue: warp w takes my tokens w, w + 8, ...; lane l the outputs 4l..4l+3
+  const int my_tokens = split < a.M ? (a.M - split + S - 1) / S : 0;
+  float4 res[2];                                    // += residual: fetched while the products run (up to 16 tokens a rank)
+  bool res_ok[2] = {false, false};
 
   if (warp == 0 && lane == 0) {
     // weights first: they do not depend on the kernel in front
@@ -438,8 +457,13 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       tma_load_2d(tiles + s * stage_bytes, &map_w, (kb0 + it) * UM_BK, n0, full0 + 8 * s);
       tma_load_2d(tiles + s * stage_bytes + SW_W_BYTES, &map_x, (kb0 + it) * UM_BK, 0, full0 + 8 * s);
     }
+#ifdef FELLM_TRACE
+    FELLM_TRACE_MARK(0);                                     // every load asked for
+    mbar_wait(accfull, 0, nullptr, 0);
+    FELLM_TRACE_MARK(1);                                     // the tile's products done
+#endif
   } else {
-    pdl_wait();                      // every other thread reads (bias aside) what the kernel in front wrote, or nothing
+    pdl_wait();                      // what the other threads read of global memory (out, for +=) the kernel in front wrote
     if (warp == 1 && lane == 0) {
       const unsigned idesc = umma_idesc(UM_BM, a.mt);
       bool ok = true;
@@ -458,46 +482,115 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       if (ok) umma_commit(accfull);
     }
   }
-  float* part = reinterpret_cast<float*>(tiles_ptr);       // [mt][128]: over the stages, once every MMA has read them
-  if (warp >= 2) {
-    const int q = warp & 3, row = q * 32 + lane;
-    if (mbar_wait(accfull, 0, a.status, 113)) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      for (int c0 = 0; c0 < a.mt; c0 += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+  __syncwarp();
+  if (S > 1) asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+  if (EPI == EPI_ACC && (a.ldo % 4) == 0) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) part[(c0 + j) * UM_BM + row] = v[j];
+    for (int i = 0; i < 2; ++i) {
+      const int tl = warp + SW_WARPS * i, n = n0 + 4 * lane;
+      if (tl < my_tokens && n + 4 <= a.N) {
+        res[i] = *(const float4*)((const float*)a.out + (size_t)(split + tl * S) * a.ldo + n);
+        res_ok[i] = true;
+      }
+    }
+  }
+  {
+    const int q = warp & 3, row = q * 32 + lane;
+    const bool done = mbar_wait(accfull, 0, a.status, 113);
+    __syncwarp();
+    if (done) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      // token t goes to rank t % S, slot [t / S][my rank][row] there
+      const unsigned recv0 = smem_u32(recv);
+      unsigned dst_rank[S];
+#pragma unroll
+      for (int j = 0; j < S; ++j) dst_rank[j] = S > 1 ? mapa_rank(recv0, (unsigned)j) : recv0;
+      for (int c0 = 16 * (warp >> 2); c0 < a.mt; c0 += 32) {
+        float v[16];
+        tmem_ld16_nowait(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = c0 + j;                    // c0 is a multiple of 16, S divides 16: the owner is j % S
+          if (t < a.M) st_cluster_f32(dst_rank[j % S] + (unsigned)((((t / S) * S + split) * UM_BM + row) * 4), v[j]);
+        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-  if (a.splits > 1) cgx::this_cluster().sync(); else __syncthreads();
+  if (S > 1) cgx::this_cluster().sync(); else __syncthreads();      // the remote stores are visible behind it
+  FELLM_TRACE_MARK(2);
 
-  // rank r: tokens r, r + S, ...; a token's 128 outputs by 128 consecutive threads' turns
-  const int my_tokens = split < a.M ? (a.M - split + a.splits - 1) / a.splits : 0;
-  for (int e = threadIdx.x; e < my_tokens * UM_BM; e += SW_THREADS) {
-    const int row = e & (UM_BM - 1), t = split + (e >> 7) * a.splits, n = n0 + row;
-    float v = 0.f;
-    if (a.splits > 1) {
-      for (int j = 0; j < a.splits; ++j) v += cgx::this_cluster().map_shared_rank(part, j)[t * UM_BM + row];
-    } else {
-      v = part[t * UM_BM + row];
+  auto finish = [&](int tl, float4 v, bool have_res, const float4& res_i) {
+    const int t = split + tl * S, n = n0 + 4 * lane;
+    if (a.bias) {
+      if (n < a.N) v.x += a.bias[n];
+      if (n + 1 < a.N) v.y += a.bias[n + 1];
+      if (n + 2 < a.N) v.z += a.bias[n + 2];
+      if (n + 3 < a.N) v.w += a.bias[n + 3];
     }
-    if (a.bias && n < a.N) v += a.bias[n];
     if (EPI == EPI_SWIGLU) {
-      // rows in blocks of 16: 8 gate, then the 8 up rows of the same features; lanes 8..15 hand their up value down
-      const float up = __shfl_down_sync(0xffffffffu, v, 8);
-      if ((row & 15) < 8 && n < a.N)
-        ((bf16*)a.out)[(size_t)t * a.ldo + ((n0 + (row & ~15)) >> 1) + (row & 7)] = __float2bfloat16_rn((v / (1.0f + expf(-v))) * up);
-    } else if (n < a.N) {
+      // rows in blocks of 16: 8 gate, then the 8 up rows of the same features: lanes 4b+2, 4b+3 hold the up values of lanes 4b, 4b+1
+      float4 up;
+      up.x = __shfl_down_sync(0xffffffffu, v.x, 2); up.y = __shfl_down_sync(0xffffffffu, v.y, 2);
+      up.z = __shfl_down_sync(0xffffffffu, v.z, 2); up.w = __shfl_down_sync(0xffffffffu, v.w, 2);
+      if ((lane & 3) < 2 && n < a.N) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn((v.x / (1.0f + expf(-v.x))) * up.x, (v.y / (1.0f + expf(-v.y))) * up.y);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn((v.z / (1.0f + expf(-v.z))) * up.z, (v.w / (1.0f + expf(-v.w))) * up.w);
+        bf16* dst = (bf16*)a.out + (size_t)t * a.ldo + ((n0 + 16 * (lane >> 2)) >> 1) + 4 * (lane & 1);
+        if ((a.ldo % 4) == 0) *(uint2*)dst = make_uint2(*(unsigned*)&p0, *(unsigned*)&p1);
+        else { dst[0] = p0.x; dst[1] = p0.y; dst[2] = p1.x; dst[3] = p1.y; }
+      }
+    } else if (n + 4 <= a.N && (a.ldo % 4) == 0) {
       const size_t o = (size_t)t * a.ldo + n;
-      if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v);
-      else if (EPI == EPI_ACC) ((float*)a.out)[o] += v;
-      else ((float*)a.out)[o] = v;
+      if (EPI == EPI_STORE) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(v.x, v.y), p1 = __floats2bfloat162_rn(v.z, v.w);
+        *(uint2*)((bf16*)a.out + o) = make_uint2(*(unsigned*)&p0, *(unsigned*)&p1);
+      } else {
+        if (EPI == EPI_ACC) {
+          const float4 r = have_res ? res_i : *(const float4*)((const float*)a.out + o);
+          v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+        }
+        *(float4*)((float*)a.out + o) = v;
+      }
+    } else {
+      const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        if (n + c >= a.N) break;
+        const size_t o = (size_t)t * a.ldo + n + c;
+        if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(e[c]);
+        else if (EPI == EPI_ACC) ((float*)a.out)[o] += e[c];
+        else ((float*)a.out)[o] = e[c];
+      }
+    }
+  };
+  // two tokens a turn: their 2 S partial rows are asked for together, summed in rank order
+#pragma unroll 1
+  for (int tl0 = warp; tl0 < my_tokens; tl0 += 2 * SW_WARPS) {
+    float4 p[2][S];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int tl = tl0 + SW_WARPS * u;
+      if (tl < my_tokens) {
+        const float4* rows = reinterpret_cast<const float4*>(recv + (size_t)tl * S * UM_BM) + lane;
+#pragma unroll
+        for (int j = 0; j < S; ++j) p[u][j] = rows[j * (UM_BM / 4)];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int tl = tl0 + SW_WARPS * u;
+      if (tl < my_tokens) {
+        float4 v = p[u][0];
+#pragma unroll
+        for (int j = 1; j < S; ++j) { v.x += p[u][j].x; v.y += p[u][j].y; v.z += p[u][j].z; v.w += p[u][j].w; }
+        finish(tl, v, tl0 == warp && res_ok[u], res[u]);
+      }
     }
   }
-  if (a.splits > 1) cgx::this_cluster().sync(); else __syncthreads();      // nobody leaves while its partial tile is being read
+  FELLM_TRACE_MARK(3);
+  __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
@@ -505,33 +598,56 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 }
 
 struct SwapPlan { int mt, splits, stages; size_t smem; };
+static int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e && e[0]) ? atoi(e) : dflt;
+}
+// One CTA to an SM with most of its shared memory as weight stages (measured on B200, a decode step of
+// 64 rows at width 1024: 0.93 ms with 128..200 KB a CTA against 1.02 ms with two CTAs of 100 KB to an SM);
+// as many K slices (1, 2, 4, 8) as keep the CTAs within one wave.
 static bool plan_swap(int M, int N, int K, SwapPlan* p) {
   if (M < 1 || M > 64 || K % 8) return false;
+  static int max_splits = 0, budget_kb = 0, cta_factor = 0;
+  if (!max_splits) {
+    max_splits = env_int("FELLM_B200_SWAP_SPLITS", 8);
+    budget_kb = env_int("FELLM_B200_SWAP_SMEM_KB", 160);
+    cta_factor = env_int("FELLM_B200_SWAP_CTAS_PER_SM", 2);
+  }
   const int n_sm = fellm_sm_count();
   const int n_tiles = ceil_div(N, UM_BM), kb_total = ceil_div(K, UM_BK);
   p->mt = ceil_div(M, 16) * 16;
+  const int per_sm = budget_kb <= 110 ? cta_factor : 1;
   int splits = 1;
-  static int max_splits = 0;
-  if (!max_splits) { const char* e = getenv("FELLM_B200_SWAP_SPLITS"); max_splits = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 8; }
-  while (splits * 2 <= max_splits && splits * 2 <= kb_total && n_tiles * splits * 2 <= n_sm) splits *= 2;
+  while (splits * 2 <= max_splits && splits * 2 <= 8 && splits * 2 <= kb_total && n_tiles * splits * 2 <= n_sm * per_sm) splits *= 2;
   p->splits = splits;
   const int stage_bytes = SW_W_BYTES + p->mt * UM_BK * 2;
+  const size_t recv = (size_t)ceil_div(p->mt, splits) * splits * UM_BM * sizeof(float);
   int stages = ceil_div(kb_total, splits);
-  const int fit = (200 * 1024) / stage_bytes;
+  int fit = (int)(((size_t)budget_kb * 1024 - 1024 - recv) / stage_bytes);
+  if (fit < 2) fit = 2;
   if (stages > fit) stages = fit;
   if (stages > SW_MAX_STAGES) stages = SW_MAX_STAGES;
   p->stages = stages;
-  size_t bytes = (size_t)stages * stage_bytes, part = (size_t)p->mt * UM_BM * sizeof(float);
-  p->smem = (bytes > part ? bytes : part) + 1024;
+  p->smem = (size_t)stages * stage_bytes + recv + 1024;
   return true;
 }
 
-template <int EPI>
-static int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, const SwapArgs& a, size_t smem, int n_tiles, cudaStream_t stream) {
-  auto kern = gemm_umma_swap_kernel<EPI>;
+template <int EPI, int S>
+static int launch_swap_s(const CUtensorMap& mw, const CUtensorMap& mx, const SwapArgs& a, size_t smem, int n_tiles, cudaStream_t stream) {
+  auto kern = gemm_umma_swap_kernel<EPI, S>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  return launch_k_class(1, kern, dim3(a.splits, n_tiles, 1), dim3(SW_THREADS, 1, 1), smem, stream, a.splits, mw, mx, a);
+  return launch_k_class(1, kern, dim3(S, n_tiles, 1), dim3(SW_THREADS, 1, 1), smem, stream, S, mw, mx, a);
+}
+template <int EPI>
+static int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, const SwapArgs& a, size_t smem, int n_tiles, cudaStream_t stream) {
+  switch (a.splits) {
+    case 1: return launch_swap_s<EPI, 1>(mw, mx, a, smem, n_tiles, stream);
+    case 2: return launch_swap_s<EPI, 2>(mw, mx, a, smem, n_tiles, stream);
+    case 4: return launch_swap_s<EPI, 4>(mw, mx, a, smem, n_tiles, stream);
+    case 8: return launch_swap_s<EPI, 8>(mw, mx, a, smem, n_tiles, stream);
+    default: return FELLM_ERR_SIZE;
+  }
 }
 
 // Whether fellm_gemm_umma_swap takes the product (1) or not (0).

@@ -326,6 +326,9 @@ def fast_gemm_modules():
 
 _umma_status = {}
 USE_UMMA = os.environ.get("FELLM_B200_UMMA", "1") != "0"
+USE_UMMA_SWAP = os.environ.get("FELLM_B200_UMMA_SWAP", "1") != "0"
+SWAP_MIN_ROWS = int(os.environ.get("FELLM_B200_SWAP_MIN_ROWS", 17))     # fewer rows: the weight-streaming kernel (norm and convolution fused)
+SWAP_MAX_N = 16384                                                       # wider (the vocabulary head): the persistent tcgen05 product
 
 
 def umma_status(device) -> torch.Tensor:
@@ -349,7 +352,8 @@ def check_umma_status(device):
             if code == 302:
                 raise KernelError("decode attention: a row's position has no cache page mapped")
             what = ("the TMA decode attention" if code == 301 else
-                    "the tcgen05 prefill attention" if 311 <= code <= 317 else "the tcgen05 product")
+                    "the tcgen05 prefill attention" if 311 <= code <= 317 else
+                    "the tcgen05 product of few rows" if 111 <= code <= 113 else "the tcgen05 product")
             raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
 
@@ -426,6 +430,9 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     # product (all of W requested at once by every SM), else up to 32 rows except for very wide products
     # (measured at 64 rows: 14 us against 26 us for [1024, 4608], 8 against 9-11 for K = 1024, but 13
     # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
+    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N:
+        # a decode step of 17..64 rows: tcgen05 with the weights as the MMA's 128 rows
+        return gemm_umma_swap(x, w, bias, out=out, epi=epi)
     skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
                           or (M <= SKINNY_MAX_ROWS and N < 8192))
     if skinny:
@@ -445,6 +452,16 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
         f = _fn("gemm_tiled", "fellm_gemm_tiled", _GEMM_ARGS)
         _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
                "gemm_tiled")
+    return out
+
+
+def gemm_umma_swap(x, w, bias=None, *, out, epi: int):
+    """The tcgen05 product for up to 64 rows (weights as the MMA's rows, K split over a cluster),
+    callable by itself.  epi: 0 store bfloat16, 1 add into float32, 2 SiLU(gate)*up, 3 store float32."""
+    M, K = x.shape
+    f = _fn("gemm_umma", "fellm_gemm_umma_swap", _GEMM_ARGS[:-1] + [_c_p, _c_p])
+    _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, w.shape[0], K, x.stride(0), w.stride(0), out.stride(0),
+             _p(umma_status(x.device)), _stream()), "gemm_umma_swap")
     return out
 
 

@@ -661,3 +661,38 @@ def test_attention_prefill_window_edge(hd, pt, window):
             assert not torch.isnan(got).any(), (row, edge)
             hit = torch.allclose(got[row, 0], values[edge, 0].bfloat16().float(), atol=3e-2)
             assert hit == inside, (window, row, edge, inside)
+
+
+@pytest.mark.parametrize("M", [1, 16, 17, 33, 40, 48, 63, 64])
+@pytest.mark.parametrize("N,K", [(1024, 1024), (1024, 4608), (3072, 1024), (9216, 1024), (2048, 2048), (200, 136), (515, 328),
+                                 (128, 64), (6144, 2048), (1536, 7168)])
+def test_gemm_umma_swap_few_rows(M, N, K):
+    """The tcgen05 product of a decode step of up to 64 rows (weights as the MMA's 128 rows, tokens as
+    its columns, K over a cluster): every epilogue against float64, the same bits on every run, and
+    its bounded waits must not have run out.  Sizes with ragged tiles in N and in K included."""
+    x, w, want = _gemm_case(M, N, K, seed=11)
+    xd, wd = x.to(DEV), w.to(DEV)
+    got = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_umma_swap(xd, wd, out=got, epi=3)
+    ops.check_umma_status(DEV)
+    assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4), (got.double().cpu() - want).abs().max()
+    again = torch.empty_like(got)
+    ops.gemm_umma_swap(xd, wd, out=again, epi=3)
+    assert torch.equal(again, got)                                    # ranks are summed in rank order
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    out = res.clone()
+    ops.gemm_umma_swap(xd, wd, bias, out=out, epi=1)
+    assert torch.allclose(out.double().cpu(), res.double().cpu() + want + bias.double().cpu(), rtol=1e-4, atol=1e-4)
+    outb = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_umma_swap(xd, wd, out=outb, epi=0)
+    assert torch.allclose(outb.double().cpu(), want, rtol=1e-2, atol=4e-3 * math.sqrt(K) * 0.2)
+    if N % 16 == 0:
+        F = N // 2
+        g = torch.Generator().manual_seed(F)
+        wg, wu = (torch.randn(F, K, generator=g) * 0.1).bfloat16(), (torch.randn(F, K, generator=g) * 0.1).bfloat16()
+        gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+        z = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_umma_swap(xd, ops.interleave_gate_up(wg.to(DEV), wu.to(DEV)), out=z, epi=2)
+        assert torch.allclose(z.double().cpu(), (gate / (1 + torch.exp(-gate))) * up, rtol=1.2e-2, atol=2e-3)
+    ops.check_umma_status(DEV)
