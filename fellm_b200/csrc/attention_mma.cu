@@ -503,41 +503,56 @@ struct DecodeFuse {
 };
 
 // One head of 64 elements by a warp, lane l holding elements 2l and 2l+1: RMSNorm (if w), rotation
-// by pos (if inv_freq) on pairs (2i, 2i+1) (pairing 0) or (i, i+32) (pairing 1).
-__device__ __forceinline__ float2 norm_rope_head64(const bf16* src, const float* w, float eps, const float* inv_freq,
-                                                   int pairing, int pos, int lane) {
+// by pos (if inv_freq) on pairs (2i, 2i+1) (pairing 0) or (i, i+32) (pairing 1).  What does not
+// depend on the kernel in front (the angles' sines and cosines, the norm weights) is worked out by
+// rope_coeffs()/norm_weights() before the wait for it.
+struct RopeCoeffs { float s0, c0, s1, c1; };
+__device__ __forceinline__ RopeCoeffs rope_coeffs(const float* inv_freq, int pairing, int pos, int lane) {
+  RopeCoeffs r = {0.f, 1.f, 0.f, 1.f};
+  if (inv_freq) {
+    if (pairing == 0) {
+      sincosf((float)pos * inv_freq[lane], &r.s0, &r.c0);
+    } else {
+      const int p0 = (2 * lane) & 31;
+      sincosf((float)pos * inv_freq[p0], &r.s0, &r.c0);
+      sincosf((float)pos * inv_freq[p0 + 1], &r.s1, &r.c1);
+    }
+  }
+  return r;
+}
+__device__ __forceinline__ float2 norm_weights(const float* w, int lane) {
+  return w ? make_float2(w[2 * lane], w[2 * lane + 1]) : make_float2(1.f, 1.f);
+}
+__device__ __forceinline__ float2 norm_rope_head64(const bf16* src, bool norm, float2 w, float eps, bool rotate,
+                                                   int pairing, const RopeCoeffs& rc, int lane) {
   float2 v = __bfloat1622float2(*(const __nv_bfloat162*)(src + 2 * lane));
-  if (w) {
+  if (norm) {
     float ss = fmaf(v.x, v.x, v.y * v.y);
     ss = warp_sum(ss);
     const float sc = 1.0f / sqrtf(ss / 64.0f + eps);
-    v.x = (v.x * sc) * w[2 * lane];
-    v.y = (v.y * sc) * w[2 * lane + 1];
+    v.x = (v.x * sc) * w.x;
+    v.y = (v.y * sc) * w.y;
   }
-  if (inv_freq) {
+  if (rotate) {
     if (pairing == 0) {
-      float sn, cs;
-      sincosf((float)pos * inv_freq[lane], &sn, &cs);
       const float x = v.x, y = v.y;
-      v.x = x * cs - y * sn; v.y = x * sn + y * cs;
+      v.x = x * rc.c0 - y * rc.s0; v.y = x * rc.s0 + y * rc.c0;
     } else {
       const float ox = __shfl_xor_sync(0xffffffffu, v.x, 16), oy = __shfl_xor_sync(0xffffffffu, v.y, 16);
-      const int p0 = (2 * lane) & 31;
-      float s0, c0, s1, c1;
-      sincosf((float)pos * inv_freq[p0], &s0, &c0);
-      sincosf((float)pos * inv_freq[p0 + 1], &s1, &c1);
-      if (lane < 16) { v.x = v.x * c0 - ox * s0; v.y = v.y * c1 - oy * s1; }      // first of the pair: a*c - b*s
-      else { v.x = ox * s0 + v.x * c0; v.y = oy * s1 + v.y * c1; }                // second: a*s + b*c
+      if (lane < 16) { v.x = v.x * rc.c0 - ox * rc.s0; v.y = v.y * rc.c1 - oy * rc.s1; }      // first of the pair: a*c - b*s
+      else { v.x = ox * rc.s0 + v.x * rc.c0; v.y = oy * rc.s1 + v.y * rc.c1; }                // second: a*s + b*c
     }
   }
   return v;
 }
 
+// NS: half-page stages a warp keeps in flight (2: 64 KB a CTA, three CTAs to an SM; 3: 96 KB, two; 4: 128 KB, one).
+template <int NS>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, DecodeFuse f, int* status) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long bars[DC_WARPS * 2];
+  __shared__ __align__(8) unsigned long long bars[DC_WARPS * NS];
   __shared__ int sm_pages[DC_MAX_PAGES];
   __shared__ int sm_last;
   __shared__ __align__(16) bf16 q_s[16 * HD];            // fused: the group's heads, normed and rotated
@@ -561,21 +576,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
   if (pages_in_smem)
     for (int i = threadIdx.x; i < n_pg; i += DC_WARPS * 32) sm_pages[i] = bt[pg0 + i];
-  if (threadIdx.x < DC_WARPS * 2) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
+  if (threadIdx.x < DC_WARPS * NS) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();
   const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
   float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
-  // a warp's two stages, each the K and the V tile of half a page (32 keys)
-  const unsigned stage0 = base + warp * 4 * DT_TILE_B;
-  const unsigned bar0 = (unsigned)__cvta_generic_to_shared(&bars[warp * 2]);
+  // a warp's NS stages, each the K and the V tile of half a page (32 keys)
+  const unsigned stage0 = base + warp * NS * 2 * DT_TILE_B;
+  const unsigned bar0 = (unsigned)__cvta_generic_to_shared(&bars[warp * NS]);
   const int my_pages = (n_pg - warp + DC_WARPS - 1) / DC_WARPS;                              // may be <= 0
   const int n_tiles = my_pages > 0 ? my_pages * 2 : 0;
   auto request = [&](int q) {                           // lane 0: K and V of the q-th half page of this warp
     const int lp = pg0 + warp + (q >> 1) * DC_WARPS;
     const int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
     const int row = (((page * a.layers_in_group + a.layer) * 2) * a.G + g) * DT_PT + (q & 1) * DT_HALF;   // < 2^31: the launcher checks
-    const unsigned st = stage0 + (q & 1) * 2 * DT_TILE_B, bar = bar0 + (q & 1) * 8;
+    const unsigned st = stage0 + (q % NS) * 2 * DT_TILE_B, bar = bar0 + (q % NS) * 8;
     at_mbar_expect_tx(bar, 2 * DT_TILE_B);
     at_tma_load_2d(st, &pool_map, 0, row, bar);
     at_tma_load_2d(st + DT_TILE_B, &pool_map, 0, row + a.G * DT_PT, bar);
@@ -584,23 +599,29 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   // are asked for before the wait, the row of the step's own position being replaced in the tile
   // later anyway.  Not fused, that kernel wrote the step's k and v: after the wait.
   const bool early = f.qkv != nullptr;
+  RopeCoeffs rc = {0.f, 1.f, 0.f, 1.f};
+  float2 qw = make_float2(1.f, 1.f), kw = qw;
+  if (early) {                                              // the angles and the norm weights do not wait either
+    rc = rope_coeffs(f.inv_freq, f.pairing, pos, lane);
+    qw = norm_weights(f.q_w, lane); kw = norm_weights(f.k_w, lane);
+  }
   if (early && lane == 0) {
-    if (n_tiles > 0) request(0);
-    if (n_tiles > 1) request(1);
+#pragma unroll
+    for (int q = 0; q < NS; ++q) if (q < n_tiles) request(q);
   }
   pdl_wait(); FELLM_TRACE_WAITED();
   const bf16* qkv_row = f.qkv ? f.qkv + (size_t)t * (a.H + 2 * a.G) * HD : nullptr;
   if (qkv_row) {
     for (int i = warp; i < 16; i += DC_WARPS) {
       float2 v = make_float2(0.f, 0.f);
-      if (i < R) v = norm_rope_head64(qkv_row + (size_t)(g * R + i) * HD, f.q_w, f.eps, f.inv_freq, f.pairing, pos, lane);
+      if (i < R) v = norm_rope_head64(qkv_row + (size_t)(g * R + i) * HD, f.q_w != nullptr, qw, f.eps, f.inv_freq != nullptr, f.pairing, rc, lane);
       *(__nv_bfloat162*)(q_s + i * HD + 2 * lane) = __floats2bfloat162_rn(v.x, v.y);
     }
   }
   __syncthreads();
   if (!early && lane == 0) {
-    if (n_tiles > 0) request(0);
-    if (n_tiles > 1) request(1);
+#pragma unroll
+    for (int q = 0; q < NS; ++q) if (q < n_tiles) request(q);
   }
   unsigned qf[KS][4];
   load_q(qf, [&](int i) -> const bf16* {
@@ -612,8 +633,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
   const int lo[2] = {k0, k0}, hi[2] = {k1 - 1, k1 - 1};
   for (int q = 0; q < n_tiles; ++q) {
-    const unsigned st = stage0 + (q & 1) * 2 * DT_TILE_B, bar = bar0 + (q & 1) * 8;
-    const bool arrived = __all_sync(0xffffffffu, at_mbar_wait(bar, (q >> 1) & 1));
+    const unsigned st = stage0 + (q % NS) * 2 * DT_TILE_B, bar = bar0 + (q % NS) * 8;
+    const bool arrived = __all_sync(0xffffffffu, at_mbar_wait(bar, (q / NS) & 1));
     if (q == 0) FELLM_TRACE_MARK(0);
     if (!arrived) {
       if (lane == 0 && status) atomicExch(status, 301);
@@ -625,7 +646,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
       // tile and into the cache page (no other CTA or warp reads this page's tile in this step)
       const int lp = pos / DT_PT;
       const int page = pages_in_smem ? sm_pages[lp - pg0] : bt[lp];
-      const float2 kv = norm_rope_head64(qkv_row + (size_t)(a.H + g) * HD, f.k_w, f.eps, f.inv_freq, f.pairing, pos, lane);
+      const float2 kv = norm_rope_head64(qkv_row + (size_t)(a.H + g) * HD, f.k_w != nullptr, kw, f.eps, f.inv_freq != nullptr, f.pairing, rc, lane);
       const __nv_bfloat162 kk = __floats2bfloat162_rn(kv.x, kv.y);
       const __nv_bfloat162 vv = *(const __nv_bfloat162*)(qkv_row + (size_t)(a.H + a.G + g) * HD + 2 * lane);
       const unsigned off = tile_off(pos - key0, (2 * lane) >> 3) + ((2 * lane) & 7) * 2;
@@ -652,9 +673,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
         attend_tile<DT_HALF / 8, false>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
     }
     __syncwarp();
-    if (q + 2 < n_tiles) {
+    if (q + NS < n_tiles) {
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // this warp's reads before the next copy's writes
-      if (lane == 0) request(q + 2);
+      if (lane == 0) request(q + NS);
     }
   }
   FELLM_TRACE_MARK(1);
@@ -890,12 +911,13 @@ FELLM_API int fellm_attn_decode_mma(const void* q, const void* pool, const int* 
 // qkv non-null: the QKV product's output [T, (H+2G)*64]; the kernel norms (q_w, k_w float32 [64] or null)
 // and rotates (inv_freq float32 [32] or null; pairing 0 adjacent / 1 split-half) q and k itself and
 // writes k and v into the cache; q is then not read.  status 302: a row's position has no page.
+// stages: half pages (32 keys) a warp keeps in flight, 2..4.
 FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n_pages, const int* block_table,
                                     int max_pages, const int* positions, const int* row_slot, void* out,
                                     float* scratch, int* counters, int T, int H, int G, int hd, int page_tokens,
                                     int layer, int layers_in_group, float scale, int window, int split_len,
                                     int max_splits, int* status, const void* qkv, const float* q_w, const float* k_w,
-                                    float eps, const float* inv_freq, int pairing, cudaStream_t stream) {
+                                    float eps, const float* inv_freq, int pairing, int stages, cudaStream_t stream) {
 #if HD == 64
   if (T <= 0) return 0;
   AttnArgs a;
@@ -911,9 +933,14 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   CUtensorMap map;
   e = pool_map_for(pool, rows, DT_HALF, &map);
   if (e) return e;
-  size_t tiles = (size_t)DC_WARPS * 4 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
+  // stages: half pages a warp keeps in flight, 2 (three CTAs to an SM), 3 or 4 (one CTA to an SM: the few CTAs of
+  // a step of one or two requests, which then have most of their keys on the way at once)
+  static int ns_env = -1;
+  if (ns_env < 0) { const char* ev = getenv("FELLM_B200_DECODE_STAGES"); ns_env = (ev && ev[0] >= '2' && ev[0] <= '4') ? ev[0] - '0' : 0; }
+  const int ns = ns_env ? ns_env : (stages >= 2 && stages <= 4 ? stages : 2);
+  size_t tiles = (size_t)DC_WARPS * ns * 2 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
   size_t smem = (tiles > mrg ? tiles : mrg) + 1024;
-  auto kern = attention_decode_tma_kernel;
+  auto kern = ns == 2 ? attention_decode_tma_kernel<2> : (ns == 3 ? attention_decode_tma_kernel<3> : attention_decode_tma_kernel<4>);
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
   DecodeFuse f;

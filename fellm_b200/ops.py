@@ -525,6 +525,7 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
 # SM).  Measured on B200, 16 layers of width 1024, context 2048 (4000): batch 8 379 (411) us a step
 # with 444, 387 (438) with 592, 399 (417) with 300; batch 32 764 with 444, 822 with 592.
 DECODE_TARGET_CTAS = int(os.environ.get("FELLM_B200_DECODE_TARGET", 0))     # 0: three CTAs for every SM of the device
+DECODE_STAGES = int(os.environ.get("FELLM_B200_DECODE_STAGES", 0))           # 0: by the step's size (decode_stages)
 _sm_count = {}
 
 
@@ -551,13 +552,24 @@ USE_UMMA_PREFILL = os.environ.get("FELLM_B200_UMMA_ATTN", "1") != "0"
 UMMA_PREFILL_MIN_ROWS = int(os.environ.get("FELLM_B200_UMMA_ATTN_MIN_ROWS", 1))    # (token, head) rows of the longest item
 
 
+def decode_stages(rows: int, kv_heads: int) -> int:
+    """Half pages a warp of the TMA decode kernel keeps in flight: 4 (a CTA to an SM) for the few CTAs of a
+    step of one or two requests, which then ask for most of their keys at once, else 2 (three CTAs to an SM).
+    Measured on B200 (16 layers of width 1024, context 2048): batch 1 0.332 ms a step with 4 against 0.356
+    with 2; batch 8 0.400 against 0.396; batch 64 1.22 against 0.92."""
+    if DECODE_STAGES:
+        return DECODE_STAGES
+    return 4 if rows * kv_heads <= 16 else 2
+
+
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     """(split_len, max_splits): key ranges of a multiple of 64 keys, enough of them to fill the
     machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
     while contexts grow."""
     bucket = -(-max(max_len, 1) // 1024) * 1024
     items = max(rows * kv_heads, 1)
-    target = target or decode_target_ctas()
+    if not target:
+        target = decode_target_ctas() // 3 if decode_stages(rows, kv_heads) == 4 else decode_target_ctas()
     want = max(1, target // items)
     if items > target:
         want = 2            # more than a wave even unsplit: halves, so that the last wave is a short one
@@ -611,7 +623,7 @@ def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, wi
         f = _fn("attention_mma", "fellm_attn_decode_tma",
                 [_c_p, _c_p, ctypes.c_longlong, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int,
                  _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_f, _c_p, _c_int,
-                 _c_p], defines={"HD": hd})
+                 _c_int, _c_p], defines={"HD": hd})
         if fuse is not None:
             qkv, q_w, k_w, eps, inv_freq, pairing = fuse
             extra = (_p(qkv), _p(q_w), _p(k_w), float(eps), _p(inv_freq), PAIRINGS[pairing])
@@ -619,8 +631,8 @@ def attention_decode(q, pool, block_table, positions, row_slot, layer, scale, wi
             extra = (None, None, None, 0.0, None, 0)
         _check(f(_p(q), _p(pool), pool.shape[0], _p(block_table), block_table.shape[1], _p(positions), _p(row_slot),
                  _p(out), _p(scratch), _p(counters), T, H, G, hd, page_tokens, layer, pool.shape[1], float(scale),
-                 int(window or 0), split_len, max_splits, _p(umma_status(pool.device)), *extra, _stream()),
-               "attention_decode (TMA)")
+                 int(window or 0), split_len, max_splits, _p(umma_status(pool.device)), *extra, decode_stages(T, G),
+                 _stream()), "attention_decode (TMA)")
         return out
     f = _fn("attention_mma", "fellm_attn_decode_mma",
             [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
