@@ -148,3 +148,34 @@ static inline int fellm_sm_count() {
   }
   return cached[dev];
 }
+
+
+// ---- the next product's weights into L2.  A decode step is a chain of short dependent products, each bound
+// by the latency of its own first bytes; which matrix the product AFTER this one reads is known on the
+// host, so a launch can be told (fellm_next_weights, consumed by the module's next launch) and its CTAs
+// then ask the L2 for that matrix, a share each, before they wait for the kernel in front: the DRAM
+// stream no longer stops between kernels, and the next product finds its weights a cache hit away.
+#ifdef FELLM_WEIGHT_PREFETCH
+struct NextWeights { const void* ptr; long long bytes; };
+static NextWeights g_next_weights = {nullptr, 0};
+FELLM_API int fellm_next_weights(const void* ptr, long long bytes) {
+  g_next_weights.ptr = (ptr && bytes >= 16 && !((uintptr_t)ptr & 15)) ? ptr : nullptr;
+  g_next_weights.bytes = g_next_weights.ptr ? bytes : 0;
+  return 0;
+}
+static inline NextWeights take_next_weights() {
+  NextWeights n = g_next_weights;
+  g_next_weights.ptr = nullptr; g_next_weights.bytes = 0;
+  return n;
+}
+// One thread of CTA `cta` of `n_ctas`: pieces cta, cta + n_ctas, ... of 16 KB.
+__device__ __forceinline__ void l2_prefetch_share(const void* ptr, long long bytes, int cta, int n_ctas) {
+  if (!ptr) return;
+  const long long piece = 16384, n = (bytes + piece - 1) / piece;
+  for (long long i = cta; i < n; i += n_ctas) {
+    const long long off = i * piece;
+    const unsigned size = (unsigned)((bytes - off < piece ? bytes - off : piece) & ~15ll);
+    if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"((const char*)ptr + off), "r"(size) : "memory");
+  }
+}
+#endif

@@ -26,6 +26,7 @@
 // to two MMAs as the k slots {2c,2c+1,2c+8,2c+9}; both operands use the same mapping.
 #include <cooperative_groups.h>
 
+#define FELLM_WEIGHT_PREFETCH 1
 #include "common.cuh"
 namespace cg = cooperative_groups;
 
@@ -70,6 +71,7 @@ struct SkinnyArgs {
   // EPI_CONV: the gated short convolution behind the input product of a ShortConv mixer
   const float* conv_w; const float* conv_bias; float* conv_state; const int* row_slot;
   long long conv_slot_stride; int conv_taps, red_offset;
+  const void* next_w; long long next_bytes;     // the next product's weights, asked into L2 (or null)
 };
 
 template <int MT, int EPI>
@@ -219,6 +221,8 @@ __global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1) gemm_skinny_kerne
   int ltl = 0, lrr = 0;
   if (total_rounds > 0) { load_round(ltl, lrr, wA0, wA1); advance(ltl, lrr); }
   if (total_rounds > 1) { load_round(ltl, lrr, wB0, wB1); advance(ltl, lrr); }
+  if (threadIdx.x == 0)
+    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   pdl_launch_dependents();
   if (a.pdl) {
     pdl_wait();
@@ -486,6 +490,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     const bf16* p0 = w_base + (size_t)tile * SK_ROWS * a.ldw;
     LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
   }
+  if (threadIdx.x == 0)
+    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   pdl_launch_dependents();
   if (a.pdl) {
     pdl_wait();
@@ -859,6 +865,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
     if (splits > 8) return FELLM_ERR_SIZE;
   }
   SkinnyArgs a;
+  { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = out;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo; a.splits = splits;
   a.warps_k = warps_k; a.k_per_cta = k_per_cta; a.xs_stride = x_stride(k_per_cta);
@@ -911,6 +918,7 @@ FELLM_API int fellm_gemm_skinny_conv(const void* x, const float* xf, const float
   if ((!x && !xf) || !W || !y || !conv_w || !state || !row_slot || (xf && !norm_w)) return FELLM_ERR_ARG;
   if (!conv_shape_ok(M, N, K, taps) || (ldw % 8) || (x && (lda % 8)) || (xf && (lda % 4)) || (xf && K > 4096)) return FELLM_ERR_SIZE;
   SkinnyArgs a;
+  { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = y;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo;
   a.splits = 1; a.warps_k = 4; a.log2_warps_k = 2; a.k_per_warp = K / 4; a.k_per_cta = K; a.xs_stride = x_stride(K);

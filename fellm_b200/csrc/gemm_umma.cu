@@ -15,6 +15,7 @@
 // (plugins/cuda_kernels/src/oxide_kernels.rs:3165).
 #include <cuda.h>
 
+#define FELLM_WEIGHT_PREFETCH 1
 #include "common.cuh"
 
 #define UM_BM 128
@@ -378,6 +379,7 @@ namespace cgx = cooperative_groups;
 struct SwapArgs {
   const float* bias; void* out; int* status;
   int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..64)
+  const void* next_w; long long next_bytes;     // the next product's weights, asked into L2 (or null)
 };
 
 __device__ __forceinline__ void tmem_ld16_nowait(unsigned taddr, float* v) {
@@ -447,6 +449,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       mbar_expect_tx(full0 + 8 * i, stage_bytes);
       tma_load_2d(tiles + i * stage_bytes, &map_w, (kb0 + i) * UM_BK, n0, full0 + 8 * i);
     }
+    l2_prefetch_share(a.next_w, a.next_bytes, blockIdx.y * S + blockIdx.x, gridDim.y * S);
     pdl_wait(); FELLM_TRACE_WAITED();
     for (int i = 0; i < first; ++i)
       tma_load_2d(tiles + i * stage_bytes + SW_W_BYTES, &map_x, (kb0 + i) * UM_BK, 0, full0 + 8 * i);
@@ -602,36 +605,6 @@ static int env_int(const char* name, int dflt) {
   const char* e = getenv(name);
   return (e && e[0]) ? atoi(e) : dflt;
 }
-// One CTA to an SM with most of its shared memory as weight stages (measured on B200, a decode step of
-// 64 rows at width 1024: 0.93 ms with 128..200 KB a CTA against 1.02 ms with two CTAs of 100 KB to an SM);
-// as many K slices (1, 2, 4, 8) as keep the CTAs within one wave.
-static bool plan_swap(int M, int N, int K, SwapPlan* p) {
-  if (M < 1 || M > 64 || K % 8) return false;
-  static int max_splits = 0, budget_kb = 0, cta_factor = 0;
-  if (!max_splits) {
-    max_splits = env_int("FELLM_B200_SWAP_SPLITS", 8);
-    budget_kb = env_int("FELLM_B200_SWAP_SMEM_KB", 160);
-    cta_factor = env_int("FELLM_B200_SWAP_CTAS_PER_SM", 2);
-  }
-  const int n_sm = fellm_sm_count();
-  const int n_tiles = ceil_div(N, UM_BM), kb_total = ceil_div(K, UM_BK);
-  p->mt = ceil_div(M, 16) * 16;
-  const int per_sm = budget_kb <= 110 ? cta_factor : 1;
-  int splits = 1;
-  while (splits * 2 <= max_splits && splits * 2 <= 8 && splits * 2 <= kb_total && n_tiles * splits * 2 <= n_sm * per_sm) splits *= 2;
-  p->splits = splits;
-  const int stage_bytes = SW_W_BYTES + p->mt * UM_BK * 2;
-  const size_t recv = (size_t)ceil_div(p->mt, splits) * splits * UM_BM * sizeof(float);
-  int stages = ceil_div(kb_total, splits);
-  int fit = (int)(((size_t)budget_kb * 1024 - 1024 - recv) / stage_bytes);
-  if (fit < 2) fit = 2;
-  if (stages > fit) stages = fit;
-  if (stages > SW_MAX_STAGES) stages = SW_MAX_STAGES;
-  p->stages = stages;
-  p->smem = (size_t)stages * stage_bytes + recv + 1024;
-  return true;
-}
-
 template <int EPI, int S>
 static int launch_swap_s(const CUtensorMap& mw, const CUtensorMap& mx, const SwapArgs& a, size_t smem, int n_tiles, cudaStream_t stream) {
   auto kern = gemm_umma_swap_kernel<EPI, S>;
@@ -648,6 +621,70 @@ static int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, const SwapA
     case 8: return launch_swap_s<EPI, 8>(mw, mx, a, smem, n_tiles, stream);
     default: return FELLM_ERR_SIZE;
   }
+}
+
+// Clusters of S CTAs with `smem` bytes each that the device holds at once (a cluster's CTAs sit in one GPC,
+// so this is less than SMs / S where a CTA fills an SM).  The += kernel stands for all epilogues (the same
+// resources).  Asked once per (device, S, KB of shared memory).
+template <int S>
+static int swap_max_clusters(size_t smem) {
+  static int cache[8][256];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 8) dev = 0;
+  const int kb = (int)(smem / 1024) < 255 ? (int)(smem / 1024) : 255;
+  if (!cache[dev][kb]) {
+    auto kern = gemm_umma_swap_kernel<EPI_ACC, S>;
+    int n = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(S, 4096, 1); cfg.blockDim = dim3(SW_THREADS, 1, 1); cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = S; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { n = 0; (void)cudaGetLastError(); }
+    }
+    cache[dev][kb] = n > 0 ? n : fellm_sm_count() / S / 2;      // no answer (no device here): a careful guess
+    if (cache[dev][kb] < 1) cache[dev][kb] = 1;
+  }
+  return cache[dev][kb];
+}
+
+// One CTA to an SM with most of its shared memory as weight stages (measured on B200, a decode step of
+// 64 rows at width 1024: 0.93 ms with 128..200 KB a CTA against 1.02 ms with two CTAs of 100 KB to an SM);
+// as many K slices (8, 4, 2, 1: the ranks of a cluster) as keep the tile's clusters in ONE wave: with
+// clusters of 8 CTAs that fill their SMs a B200 holds fewer than 148 / 8 of them, and a second wave
+// doubled the time of the [2048, 2048] product at 64 rows.
+static void plan_swap_s(int M, int N, int K, int splits, SwapPlan* p) {
+  static int budget_kb = 0;
+  if (!budget_kb) budget_kb = env_int("FELLM_B200_SWAP_SMEM_KB", 160);
+  const int kb_total = ceil_div(K, UM_BK);
+  p->mt = ceil_div(M, 16) * 16;
+  p->splits = splits;
+  const int stage_bytes = SW_W_BYTES + p->mt * UM_BK * 2;
+  const size_t recv = (size_t)ceil_div(p->mt, splits) * splits * UM_BM * sizeof(float);
+  int stages = ceil_div(kb_total, splits);
+  int fit = (int)(((size_t)budget_kb * 1024 - 1024 - recv) / stage_bytes);
+  if (fit < 2) fit = 2;
+  if (stages > fit) stages = fit;
+  if (stages > SW_MAX_STAGES) stages = SW_MAX_STAGES;
+  p->stages = stages;
+  p->smem = (size_t)stages * stage_bytes + recv + 1024;
+}
+static bool plan_swap(int M, int N, int K, SwapPlan* p) {
+  if (M < 1 || M > 64 || K % 8) return false;
+  static int max_splits = 0;
+  if (!max_splits) max_splits = env_int("FELLM_B200_SWAP_SPLITS", 8);
+  const int n_sm = fellm_sm_count();
+  const int n_tiles = ceil_div(N, UM_BM), kb_total = ceil_div(K, UM_BK);
+  for (int splits = 8; splits > 1; splits /= 2) {
+    if (splits > max_splits || splits > kb_total || n_tiles * splits > n_sm) continue;
+    plan_swap_s(M, N, K, splits, p);
+    const int room = splits == 8 ? swap_max_clusters<8>(p->smem) : (splits == 4 ? swap_max_clusters<4>(p->smem) : swap_max_clusters<2>(p->smem));
+    if (room >= n_tiles) return true;
+  }
+  plan_swap_s(M, N, K, 1, p);
+  return true;
 }
 
 // Whether fellm_gemm_umma_swap takes the product (1) or not (0).
@@ -674,6 +711,8 @@ FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bi
   SwapArgs a;
   a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
   a.mt = p.mt; a.splits = p.splits; a.stages = p.stages;
+  const NextWeights nw = take_next_weights();
+  a.next_w = nw.ptr; a.next_bytes = nw.bytes;
   const int n_tiles = ceil_div(N, UM_BM);
   switch (epi) {
     case EPI_STORE: return launch_swap<EPI_STORE>(mw, mx, a, p.smem, n_tiles, stream);

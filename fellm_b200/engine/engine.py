@@ -67,6 +67,8 @@ class Engine:
         max_rows = max(options.n_batch, options.n_ubatch) + options.max_requests
         for part in self.model.all_parts():
             part.reserve(self.device, options.max_requests, n_ctx)
+        from .. import ops
+        ops.register_weight_chain(self.model.weight_chain())
         self.stepper = Stepper(self.model, self.cache, max_rows=max_rows, max_items=options.max_requests,
                                device=self.device, cuda_graphs=options.cuda_graphs)
         self._sampler: Optional[Sampler] = None

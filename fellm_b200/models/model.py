@@ -130,6 +130,16 @@ class Model:
             mods += part.kernel_modules(self.dtype)
         return mods
 
+    def weight_chain(self):
+        """The matrices of one step in the order its products read them (the schedule's order)."""
+        chain = []
+        for run in self.schedule:
+            b = self.blocks[run.layer]
+            chain += b.mixer.weight_order()
+            if b.ffn is not None:
+                chain += b.ffn.weight_order()
+        return chain + self.head.weight_order()
+
     def cache_needs(self):
         """Per schedule entry: the mixer's cache need, or None when the entry reads another's."""
         return [None if run.cache_of is not None else self.blocks[run.layer].mixer.cache_need()

@@ -230,6 +230,7 @@ def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, no
     if out is None:
         out = torch.empty((M, d), dtype=torch.bfloat16, device=x.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    _announce_next("gemm_skinny", w_blocked, M)
     f = _fn("gemm_skinny", "fellm_gemm_skinny_conv",
             [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_int, _c_p])
@@ -374,6 +375,32 @@ def norm_fusable(x_f32, w, norm_w) -> bool:
 
 _single_shot_cache = {}
 
+# The matrix each bfloat16 product's successor reads, by the data pointer of the product's own matrix:
+# a product's launch tells its kernel, whose CTAs ask the L2 for it before they wait for the kernel in
+# front of them.  Filled by register_weight_chain(); empty: nobody prefetches.
+_next_weight = {}
+WEIGHT_PREFETCH = os.environ.get("FELLM_B200_WEIGHT_PREFETCH", "1") != "0"
+PREFETCH_MAX_BYTES = int(os.environ.get("FELLM_B200_WEIGHT_PREFETCH_MAX_MB", 48)) << 20     # well inside the L2's 126 MB
+
+
+def register_weight_chain(weights):
+    """weights: the bfloat16 matrices of a decode step in the order its products read them (the last
+    is followed by the first: the next step).  Replaces what was registered before for these matrices."""
+    ws = [w for w in weights if w is not None and w.dtype == torch.bfloat16 and w.is_cuda and w.is_contiguous()]
+    for w, nxt in zip(ws, ws[1:] + ws[:1]):
+        _next_weight[w.data_ptr()] = (nxt.data_ptr(), min(nxt.numel() * 2, PREFETCH_MAX_BYTES))
+
+
+PREFETCH_MAX_ROWS = 16     # measured on B200: 2% off a step of 1 or 8 rows, 1-6% ON a step of 64 (its products are short of bandwidth, not of latency)
+
+
+def _announce_next(module: str, w, rows: int):
+    """Tells the module's next launch which matrix comes after w."""
+    if WEIGHT_PREFETCH and _next_weight and rows <= PREFETCH_MAX_ROWS:
+        nxt = _next_weight.get(w.data_ptr())
+        if nxt is not None:
+            _fn(module, "fellm_next_weights", [_c_p, _c_ll])(nxt[0], nxt[1])
+
 
 def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
     key = (M, N, K, norm)
@@ -432,10 +459,12 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
     if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N:
         # a decode step of 17..64 rows: tcgen05 with the weights as the MMA's 128 rows
+        _announce_next("gemm_umma", w, M)
         return gemm_umma_swap(x, w, bias, out=out, epi=epi)
     skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
                           or (M <= SKINNY_MAX_ROWS and N < 8192))
     if skinny:
+        _announce_next("gemm_skinny", w, M)
         f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
         if norm is not None:
             code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0),

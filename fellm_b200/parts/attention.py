@@ -92,5 +92,8 @@ class Attention(Mixer):
         linear(a, self.w["out_proj.weight"], out=out, accumulate=True)
         return out
 
+    def weight_order(self):
+        return [self.w["qkv.weight"], self.w["out_proj.weight"]]
+
     def kernel_modules(self, dtype):
         return linear_modules(dtype) + [("qk_rope_write", None)] + ops.attention_modules(dtype, self.hd)

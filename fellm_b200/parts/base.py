@@ -74,6 +74,11 @@ class Part:
     def prepare(self):
         """Called once after bind(): repack or fuse weights for the kernels."""
 
+    def weight_order(self):
+        """The part's matrices in the order its forward() reads them (for the engine's chain of weights:
+        each product asks the L2 for the matrix of the product after it)."""
+        return []
+
     def reserve(self, device, max_rows: int, n_ctx: int):
         """Called once by the engine, after bind() and before the first step: allocate here what
         the part's kernels need besides inputs and outputs, sized for steps of up to max_rows rows

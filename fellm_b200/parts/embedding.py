@@ -39,5 +39,8 @@ class LinearHead(Head):
     def forward(self, xf):
         return linear(xf, self.w["weight"], out_dtype=torch.float32)
 
+    def weight_order(self):
+        return [self.w["weight"]]
+
     def kernel_modules(self, dtype):
         return linear_modules(dtype)

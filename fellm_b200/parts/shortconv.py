@@ -72,5 +72,8 @@ class ShortConv(Mixer):
         linear(y, self.w["out_proj.weight"], self.w.get("out_proj.bias"), out=out, accumulate=True)
         return out
 
+    def weight_order(self):
+        return [self.w["in_proj.weight"], self.w["out_proj.weight"]]
+
     def kernel_modules(self, dtype):
         return linear_modules(dtype) + [("shortconv", None)]

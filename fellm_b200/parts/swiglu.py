@@ -41,5 +41,8 @@ class SwiGLU(FeedForward):
         linear(z, self.w["down.weight"], out=out, accumulate=True)
         return out
 
+    def weight_order(self):
+        return [self.w["gate_up.weight"], self.w["down.weight"]]
+
     def kernel_modules(self, dtype):
         return linear_modules(dtype) + [("elementwise", None)]
