@@ -133,15 +133,22 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CON
     tokens = first.clone()
     items = [StepItem(r, [0], [0]) for r in reqs]
     step = engine.stepper.step                      # the step function itself: its logits are read by the sampler at once
+    sampler_launches = 0
     def one():
-        nonlocal tokens
-        logits = step(items, device_tokens=tokens)
-        tokens = engine.sampler.sample(logits, rows)
+        # greedy rows: the step may hand back the tokens themselves (the head picks them without storing
+        # the logits); else the sampler's two argmax kernels run on the logits
+        nonlocal tokens, sampler_launches
+        logits = step(items, device_tokens=tokens, greedy_tokens=engine.sampler.out_tokens)
+        if logits is None:
+            tokens = engine.sampler.out_tokens[:batch]
+        else:
+            tokens = engine.sampler.sample(logits, rows)
+            sampler_launches += 2
     for _ in range(max(warmup, context_end - prompt - steps)):
         one()
     torch.cuda.synchronize()
     l0 = engine.stepper.launches
-    s0 = engine.stepper.steps_run
+    sampler_launches = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ctx0 = engine.cache.length(reqs[0])
     e0.record()
@@ -151,7 +158,7 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CON
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     engine.check_status()
-    launches = engine.stepper.launches - l0 + 2 * (engine.stepper.steps_run - s0)   # + the two argmax kernels a step
+    launches = engine.stepper.launches - l0 + sampler_launches
     mean_ctx = ctx0 + (steps + 1) / 2                # a step at cache length c reads c + 1 positions
     for r in reqs:
         engine.release(r)

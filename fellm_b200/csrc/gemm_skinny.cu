@@ -38,7 +38,7 @@ namespace cg = cooperative_groups;
 #define SK_XF 2048                   // floats of a row that a warp's float32 buffer takes at a time
 #define SK_GAMMA_MAX 2048            // norm weights of up to this many columns are parked in shared memory
 
-enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3, EPI_CONV = 4 };
+enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3, EPI_CONV = 4, EPI_ARGMAX = 5 };
 #define SK_MAX_LC 8
 
 __device__ __forceinline__ void mma16816(float* d, const unsigned* a, unsigned b0, unsigned b1) {
@@ -72,7 +72,19 @@ struct SkinnyArgs {
   const float* conv_w; const float* conv_bias; float* conv_state; const int* row_slot;
   long long conv_slot_stride; int conv_taps, red_offset;
   const void* next_w; long long next_bytes;     // the next product's weights, asked into L2 (or null)
+  // EPI_ARGMAX: nothing of [M, N] is stored; every CTA leaves its best (value, index) of each row as a key
+  // in arg_keys[row * CTAs + CTA] (larger key = larger value, then lower index)
+  unsigned long long* arg_keys;
 };
+
+// float32 value and index as one number whose order is "the larger value, then the lower index":
+// greedy sampling's rule (crates/fellm-runtime/src/sampling.rs:588-604).
+__device__ __forceinline__ unsigned long long argmax_key(float v, int n) {
+  v += 0.0f;                                             // -0 counts as +0
+  unsigned u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return ((unsigned long long)u << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)n);
+}
 
 template <int MT, int EPI>
 __device__ __forceinline__ void epilogue_direct(const SkinnyArgs& a, float (*acc)[4], int n0, int g, int c) {
@@ -435,9 +447,11 @@ struct LeanLoad<N, N> {
 
 template <int MT, int EPI, bool NORM, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kernel(SkinnyArgs a) {
-  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * (EPI == EPI_CONV ? EPI_STORE : EPI));
+  FELLM_TRACE_SCOPE(TRACE_GEMM_SKINNY + 32 * (EPI == EPI_CONV ? EPI_STORE : (EPI == EPI_ARGMAX ? EPI_F32 : EPI)));
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr int MP = MT * 8;
+  __shared__ unsigned long long arg_best[EPI == EPI_ARGMAX ? MT * 8 : 1];     // the CTA's best key of each row
+  if (EPI == EPI_ARGMAX && threadIdx.x < MT * 8) arg_best[threadIdx.x] = 0ull;  // seen by all behind the barrier before the sums
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = a.splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
@@ -601,7 +615,11 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     const int n0 = tile_l * SK_ROWS;
     const float* mine = slots + (size_t)((wn << a.log2_warps_k) * tpw + tl) * SK_ROWS * MP;      // K warp 0 of this slab
     const int units = (EPI == EPI_SWIGLU ? 8 : SK_ROWS) * a.M;
-    for (int i = me * 32 + lane; i < units; i += workers * 32) {
+    for (int i0 = me * 32; i0 < units; i0 += workers * 32) {
+      // (the warp stays whole for EPI_ARGMAX's shuffles; units is a multiple of 16, so half warps are in or out together)
+      const bool live = i0 + lane < units;
+      if (EPI != EPI_ARGMAX && !live) continue;
+      const int i = live ? i0 + lane : 0;
       int m, j;
       if (EPI == EPI_SWIGLU) { m = i >> 3; j = i & 7; } else { m = i >> 4; j = i & 15; }
       const int n = n0 + j;
@@ -636,6 +654,16 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
         // B, C or X of (channel j, token m), rounded as the stored product would be
         if (a.bias) v0 += a.bias[n];
         ((float*)(smem + a.red_offset))[(wn * SK_ROWS + j) * MP + m] = __bfloat162float(__float2bfloat16_rn(v0));
+      } else if (EPI == EPI_ARGMAX) {
+        // the slab's 16 outputs of row m lie in one half warp: its best key, then one atomic a half warp
+        if (a.bias) v0 += a.bias[n];
+        unsigned long long key = live ? argmax_key(v0, n) : 0ull;
+#pragma unroll
+        for (int o2 = 8; o2 > 0; o2 >>= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o2);
+          key = other > key ? other : key;
+        }
+        if (live && (lane & 15) == 0) atomicMax(&arg_best[m], key);
       } else {
         if (a.bias) v0 += a.bias[n];
         if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
@@ -643,6 +671,11 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
         else ((float*)a.out)[o] = v0;
       }
     }
+  }
+  if (EPI == EPI_ARGMAX) {
+    __syncthreads();
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x, n_ctas = gridDim.x * gridDim.y;
+    if (threadIdx.x < a.M) a.arg_keys[(size_t)threadIdx.x * n_ctas + cta] = arg_best[threadIdx.x];
   }
   if (EPI == EPI_CONV) {
     // the CTA's three slabs are B, C and X of its 16 channels (the weight rows come in blocks of
@@ -688,7 +721,7 @@ static inline size_t smem_bytes(int mt, int k_per_cta, bool direct, int tiles_pe
 // own.  FELLM_B200_PDL_EPIS overrides the mask (bit = epilogue kind) for experiments.
 static int pdl_class_of(int epi) {
   static int mask = -1;
-  if (mask < 0) { const char* e = getenv("FELLM_B200_PDL_EPIS"); mask = e ? atoi(e) : 15; }
+  if (mask < 0) { const char* e = getenv("FELLM_B200_PDL_EPIS"); mask = e ? atoi(e) : 47; }
   return ((mask >> epi) & 1) ? 1 : 0;
 }
 
@@ -896,6 +929,55 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
     case EPI_F32: return dispatch_mt<EPI_F32>(a, ctas_y, stream);
     default: return FELLM_ERR_ARG;
   }
+}
+
+// Greedy tokens without the logits: argmax_n of x W^T (+ bias) for every row of a decode step of up to 16
+// rows (FeLLM: bf16_matmul_rows then argmax_token, plugins/cuda_kernels/src/oxide_kernels.rs:3165,116).
+// The single-shot product's CTAs each leave the best (value, index) of their part of a row as a key; a
+// second, tiny kernel takes the best key of each row.  Ties go to the lower index.
+__global__ void __launch_bounds__(32) argmax_keys_kernel(const unsigned long long* __restrict__ keys, int n_ctas, int* __restrict__ out_tokens) {
+  FELLM_TRACE_SCOPE(TRACE_ARGMAX_FINAL);
+  pdl_launch_dependents();
+  pdl_wait(); FELLM_TRACE_WAITED();
+  const int row = blockIdx.x, lane = threadIdx.x;
+  unsigned long long best = 0ull;
+  for (int c = lane; c < n_ctas; c += 32) { const unsigned long long k = keys[(size_t)row * n_ctas + c]; best = k > best ? k : best; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { const unsigned long long k = __shfl_xor_sync(0xffffffffu, best, o); best = k > best ? k : best; }
+  if (lane == 0) out_tokens[row] = best ? (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull)) : 0;
+}
+
+// Keys (8 bytes each) fellm_gemm_skinny_argmax needs for this product, or 0 if it does not take it.
+FELLM_API long long fellm_gemm_skinny_argmax_scratch(int M, int N, int K, int norm) {
+  LeanPlan lp;
+  if (M < 1 || M > 16 || (K % 8) || !plan_lean(M, N, K, norm != 0, &lp)) return 0;
+  return (long long)M * lp.splits * lp.ctas_y;
+}
+
+// x / xf / norm_w / eps as fellm_gemm_skinny; keys: fellm_gemm_skinny_argmax_scratch(...) entries;
+// out_tokens: int32 [M].  FELLM_ERR_SIZE where the single-shot product does not take the sizes.
+FELLM_API int fellm_gemm_skinny_argmax(const void* x, const float* xf, const float* norm_w, float eps, const void* W,
+                                       const float* bias, unsigned long long* keys, int* out_tokens, int M, int N, int K,
+                                       int lda, int ldw, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((!x && !xf) || !W || !keys || !out_tokens || K <= 0 || (xf && !norm_w)) return FELLM_ERR_ARG;
+  if (M > 16 || (K % 8) || (ldw % 8) || (x && (lda % 8)) || (xf && (lda % 4))) return FELLM_ERR_SIZE;
+  LeanPlan lp;
+  if (!plan_lean(M, N, K, xf != nullptr, &lp)) return FELLM_ERR_SIZE;
+  SkinnyArgs a;
+  { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
+  a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = nullptr;
+  a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = 0;
+  a.n_tiles = N / SK_ROWS;
+  a.splits = lp.splits; a.warps_k = lp.warps_k; a.log2_warps_k = 0;
+  while ((1 << a.log2_warps_k) < lp.warps_k) ++a.log2_warps_k;
+  a.k_per_warp = lp.k_per_warp; a.k_per_cta = lp.k_per_warp * lp.warps_k; a.xs_stride = x_stride(a.k_per_cta);
+  a.tiles_per_warp = lp.tiles_per_warp;
+  a.chunks_per_warp = a.k_per_warp / KCHUNK;
+  a.arg_keys = keys;
+  int e = dispatch_lean<EPI_ARGMAX>(a, lp.ctas_y, lp.warps, stream);
+  if (e) return e;
+  return launch_k(argmax_keys_kernel, dim3(M), dim3(32), 0, stream, 1, (const unsigned long long*)keys, lp.splits * lp.ctas_y, out_tokens);
 }
 
 // The input product of a ShortConv mixer with the gated convolution behind it, for a decode step:

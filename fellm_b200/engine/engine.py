@@ -150,13 +150,15 @@ class Engine:
         chain: the items (one token each, in the order of the last launch's sample rows) take the
         last launch's sampled tokens as they lie on the device.  The tokens and the kernels'
         status word are copied to one of a few pinned host buffers behind the launch."""
-        logits = self.stepper.step(items, device_tokens=self.sampler.out_tokens if chain else None)
         n = len(sample_rows)
+        # plain greedy rows: the head may pick the tokens itself and leave the logits unwritten
+        greedy = self.sampler.out_tokens if n and self.sampler.plain_greedy(sample_rows) else None
+        logits = self.stepper.step(items, device_tokens=self.sampler.out_tokens if chain else None, greedy_tokens=greedy)
         k = self._launch_no % len(self._tok_ring)
         self._launch_no += 1
         host, done = self._tok_ring[k]
         if n:
-            toks = self.sampler.sample(logits, sample_rows)
+            toks = self.sampler.out_tokens[:n] if logits is None else self.sampler.sample(logits, sample_rows)
             host[:n].copy_(toks, non_blocking=True)
         host[-1:].copy_(self.stepper.buffers.status, non_blocking=True)
         done.record()

@@ -157,6 +157,7 @@ def _fill_decode(self, plan, wants, toks, lens) -> StepContext:
 StepBuffers.fill_decode = _fill_decode
 
 
+_NOT_TAKEN = object()       # _step_decode's answer when the general path has to run the step (None is a result: tokens without logits)
 MAX_ROW_GRAPHS = 8          # captured graphs of steps that are not pure decode (each keeps its activations)
 MAX_DECODE_GRAPHS = 48      # captured decode steps (each keeps its logits [wanted, vocab]); the least recently used goes
 
@@ -189,7 +190,8 @@ class Stepper:
         self._decode_plans = {}
         self._plan_serial = 0
 
-    def step(self, items: List[StepItem], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, items: List[StepItem], device_tokens: Optional[torch.Tensor] = None,
+             greedy_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs exactly the given tokens as one batch and returns float32 logits
         [sum(len(want)), vocab] on the device, in the order of the items and of each `want`.
         Nothing is changed when the step cannot be placed (unknown request, no pages).
@@ -198,12 +200,15 @@ class Stepper:
         (Engine.step hands out a copy).
 
         device_tokens: int32 [rows] on the device to use instead of the items' token ids (which
-        are then placeholders): lets a decode loop feed sampled tokens back without the host."""
+        are then placeholders): lets a decode loop feed sampled tokens back without the host.
+        greedy_tokens: int32 [>= wanted rows] on the device: the caller only wants the greedy token of
+        every wanted row.  Where the model's head can pick them without storing the logits, they are
+        written there and None is returned; else the logits come back as usual."""
         if not items:
             raise FellmError("a step needs at least one item")
         if all(len(it.tokens) == 1 for it in items):
-            fast = self._step_decode(items, device_tokens)
-            if fast is not None:
+            fast = self._step_decode(items, device_tokens, greedy_tokens)
+            if fast is not _NOT_TAKEN:
                 return fast
         cache = self.cache
         seen = set()
@@ -253,17 +258,17 @@ class Stepper:
         if device_tokens is not None:
             ctx.tokens.copy_(device_tokens[:ctx.n_rows])
         cache.flush()
-        logits = self._run(ctx)
+        logits = self._run(ctx, greedy_tokens)
         for req, n in asks:
             cache.advance(req, n)
         self.steps_run += 1
         return logits
 
-    def _step_decode(self, items: List[StepItem], device_tokens) -> Optional[torch.Tensor]:
+    def _step_decode(self, items: List[StepItem], device_tokens, greedy_tokens=None):
         """Every item brings one token: the host work is a handful of numpy writes.  What does
         not change while the same requests decode together (slots, offsets, the wanted rows) is
         kept per composition; positions and lengths come from the cache's own counters.  Returns
-        None when the general path has to look at the step (unknown request, page or context
+        _NOT_TAKEN when the general path has to look at the step (unknown request, page or context
         limits, windows to trim)."""
         cache = self.cache
         reqs = tuple(it.req for it in items)
@@ -274,11 +279,11 @@ class Stepper:
             # a request's name may come again later in another slot: the slots are part of the key
             key = (reqs, tuple(slot_d[r] for r in reqs))
         except KeyError:
-            return None
+            return _NOT_TAKEN
         plan = self._decode_plans.get(key)
         if plan is None:
             if len(set(reqs)) != n:
-                return None
+                return _NOT_TAKEN
             if len(self._decode_plans) > 64:
                 self._decode_plans.clear()
             self._plan_serial += 1                         # never reused, unlike id(): names what a staging buffer holds
@@ -287,9 +292,9 @@ class Stepper:
             self._decode_plans[key] = plan
         wants = tuple(bool(it.want) for it in items)
         if int(lens.max()) + 1 > cache.n_ctx:
-            return None
+            return _NOT_TAKEN
         if cache.has_windows:
-            return None
+            return _NOT_TAKEN
         if device_tokens is None:
             toks = np.fromiter((it.tokens[0] for it in items), dtype=np.int64, count=n)
             if toks.min() < 0 or toks.max() >= self.vocab:
@@ -308,18 +313,19 @@ class Stepper:
         if device_tokens is not None:
             ctx.tokens.copy_(device_tokens[:n])
         cache.flush()
-        logits = self._run(ctx)
+        logits = self._run(ctx, greedy_tokens)
         for r in reqs:
             lens_d[r] += 1
         self.steps_run += 1
         return logits
 
-    def _run(self, ctx) -> torch.Tensor:
+    def _run(self, ctx, greedy_tokens=None) -> torch.Tensor:
         from .. import ops
         views = self.cache.views(ctx.item_slot)
+        greedy_key = None if greedy_tokens is None else greedy_tokens.data_ptr()
         if not self.cuda_graphs:
             before = ops.launch_count()
-            logits = self.model.forward(ctx, views)
+            logits = self.model.forward(ctx, views, greedy_tokens)
             self.launches += ops.launch_count() - before
             return logits
         # what the launches of a step depend on besides the device arrays: the counts that size the
@@ -327,9 +333,9 @@ class Stepper:
         # key-range split of decode attention).  Other steps (portions of prompts, mixed batches)
         # repeat their shape when prompts are cut into equal portions: a few of their graphs are kept.
         if ctx.all_single:
-            key = (ctx.n_items, ctx.n_logit_rows, -(-ctx.max_len // 1024))
+            key = (ctx.n_items, ctx.n_logit_rows, -(-ctx.max_len // 1024), greedy_key)
         else:
-            key = ("rows", ctx.n_rows, ctx.n_items, ctx.n_logit_rows, ctx.max_item_rows, ctx.logits_all)
+            key = ("rows", ctx.n_rows, ctx.n_items, ctx.n_logit_rows, ctx.max_item_rows, ctx.logits_all, greedy_key)
         entry = self.graphs.get(key)
         if entry is None:
             n_seen = self.graph_seen.get(key, 0)
@@ -338,13 +344,13 @@ class Stepper:
             self.graph_seen[key] = n_seen + 1
             if n_seen == 0:
                 before = ops.launch_count()
-                logits = self.model.forward(ctx, views)
+                logits = self.model.forward(ctx, views, greedy_tokens)
                 self.launches += ops.launch_count() - before
                 return logits
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(graph, pool=self.graph_pool):
-                logits = self.model.forward(ctx, views)
+                logits = self.model.forward(ctx, views, greedy_tokens)
             if self.graph_pool is None:
                 self.graph_pool = graph.pool()
             entry = (graph, logits, ops.launch_count() - before)

@@ -146,9 +146,11 @@ class Model:
                 for run in self.schedule]
 
     # ---- the step's body
-    def forward(self, ctx, caches) -> torch.Tensor:
+    def forward(self, ctx, caches, greedy_tokens=None) -> torch.Tensor:
         """ctx: StepContext; caches[n]: the cache view of schedule entry n.  Returns float32
-        logits [len(ctx.logit_rows), vocab] (an empty tensor when none are wanted)."""
+        logits [len(ctx.logit_rows), vocab] (an empty tensor when none are wanted).
+        greedy_tokens (int32, device): the caller only wants the greedy token of every wanted row; where the
+        head can give them without the logits it writes greedy_tokens[:wanted] and None is returned."""
         x = self.embedding.forward(ctx.tokens, ctx.status)
         for n, run in enumerate(self.schedule):
             src = n if run.cache_of is None else run.cache_of
@@ -157,8 +159,11 @@ class Model:
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         if ctx.logits_all and getattr(self.head, "takes_lazy_norm", False):
-            return self.head.forward(LazyNorm(x, self.final_norm, self.act_dtype))
-        xf = self.final_norm.forward(x, self.act_dtype, rows=ctx.logit_rows)
+            xf = LazyNorm(x, self.final_norm, self.act_dtype)
+        else:
+            xf = self.final_norm.forward(x, self.act_dtype, rows=ctx.logit_rows)
+        if greedy_tokens is not None and self.head.forward_greedy(xf, greedy_tokens):
+            return None
         return self.head.forward(xf)
 
 

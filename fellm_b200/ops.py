@@ -484,6 +484,51 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     return out
 
 
+_argmax_scratch_cache = {}
+FUSED_ARGMAX = os.environ.get("FELLM_B200_FUSED_ARGMAX", "1") != "0"
+
+
+def head_argmax_scratch(M: int, N: int, K: int, norm: bool) -> int:
+    """8-byte keys gemm_bf16_argmax needs for a product of these sizes; 0: it does not take it (more than
+    16 rows, or sizes the single-shot product leaves to the general kernel)."""
+    key = (M, N, K, norm)
+    hit = _argmax_scratch_cache.get(key)
+    if hit is None:
+        f = _fn("gemm_skinny", "fellm_gemm_skinny_argmax_scratch", [_c_int, _c_int, _c_int, _c_int])
+        f.restype = _c_ll
+        hit = _argmax_scratch_cache[key] = int(f(M, N, K, int(norm)))
+    return hit
+
+
+def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None):
+    """out_tokens[m] = argmax_n (x W^T + bias)[m, n], ties to the lower n, without storing the [M, N]
+    logits: the vocabulary head of a greedy decode step of up to 16 rows.  x bfloat16 [M, K], or with
+    norm=(weight, eps) the float32 residual rows; keys: int64 scratch of head_argmax_scratch() entries;
+    out_tokens int32 [>= M]."""
+    _dev(x, w, bias, keys, out_tokens)
+    M, K = x.shape
+    N = w.shape[0]
+    need = head_argmax_scratch(M, N, K, norm is not None)
+    if not need or w.dtype != torch.bfloat16 or w.stride(1) != 1 or x.stride(1) != 1:
+        raise KernelError(f"gemm_bf16_argmax does not take a product of {M} x {N} x {K}")
+    assert keys.dtype == torch.int64 and keys.numel() >= need and out_tokens.dtype == torch.int32 and out_tokens.numel() >= M
+    _announce_next("gemm_skinny", w, M)
+    f = _fn("gemm_skinny", "fellm_gemm_skinny_argmax",
+            [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
+    if norm is not None:
+        assert x.dtype == torch.float32 and norm[0].dtype == torch.float32
+        code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(keys), _p(out_tokens), M, N, K,
+                 x.stride(0), w.stride(0), _stream())
+    else:
+        assert x.dtype == torch.bfloat16
+        code = f(_p(x), None, None, 0.0, _p(w), _p(bias), _p(keys), _p(out_tokens), M, N, K, x.stride(0), w.stride(0),
+                 _stream())
+    _check(code, "gemm_skinny_argmax")
+    global _launches
+    _launches += 1                      # the product and the pick of the best key
+    return out_tokens
+
+
 def gemm_umma_swap(x, w, bias=None, *, out, epi: int):
     """The tcgen05 product for up to 64 rows (weights as the MMA's rows, K split over a cluster),
     callable by itself.  epi: 0 store bfloat16, 1 add into float32, 2 SiLU(gate)*up, 3 store float32."""

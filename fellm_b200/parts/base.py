@@ -135,6 +135,12 @@ class Head(Part):
         """xf [W, d] normed -> float32 logits [W, vocab]."""
         raise NotImplementedError
 
+    def forward_greedy(self, xf, out_tokens: torch.Tensor) -> bool:
+        """Greedy tokens of the rows without their logits: out_tokens[i] (int32, device) = argmax of row i's
+        logits, ties to the lower id.  Returns False where the head has no such path for these sizes (the
+        caller then takes forward() and the sampler)."""
+        return False
+
 
 # ----------------------------------------------------------------------------- registries
 

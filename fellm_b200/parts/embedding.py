@@ -7,7 +7,7 @@ import torch
 
 from .. import ops
 from .base import Embedding, Head, ParamDecl, register_part
-from .linear import linear, linear_modules
+from .linear import LazyNorm, linear, linear_modules
 
 
 @register_part("embedding", "table")
@@ -38,6 +38,29 @@ class LinearHead(Head):
 
     def forward(self, xf):
         return linear(xf, self.w["weight"], out_dtype=torch.float32)
+
+    def reserve(self, device, max_rows, n_ctx):
+        # best (value, index) of every CTA's part of a row, for greedy steps that skip the logits
+        self._argmax_keys = torch.zeros(16 * 1024, dtype=torch.int64, device=device)
+
+    def forward_greedy(self, xf, out_tokens):
+        w = self.w["weight"]
+        keys = getattr(self, "_argmax_keys", None)
+        if keys is None or w.dtype != torch.bfloat16 or not ops.FUSED_ARGMAX:
+            return False
+        fused = isinstance(xf, LazyNorm) and xf.fusable_with(w)
+        rows = xf.shape[0]
+        need = ops.head_argmax_scratch(rows, w.shape[0], w.shape[1], fused)
+        if not need or need > keys.numel():
+            return False
+        if fused:
+            ops.gemm_bf16_argmax(xf.x, w, None, keys, out_tokens, norm=(xf.norm.w["weight"], xf.norm.eps))
+        else:
+            x = xf.tensor() if isinstance(xf, LazyNorm) else xf
+            if not ops.fast_gemm_takes(x, w):
+                return False
+            ops.gemm_bf16_argmax(x, w, None, keys, out_tokens)
+        return True
 
     def weight_order(self):
         return [self.w["weight"]]

@@ -54,6 +54,12 @@ class Sampler:
             slots = torch.full_like(toks, slot)
             ops.count_tokens(self.counts, slots, toks)
 
+    @staticmethod
+    def plain_greedy(rows: List[tuple]) -> bool:
+        """Every row is argmax of its logits as they are (no penalties, no bias): such a step can ask the model
+        for the tokens themselves (Stepper.step(greedy_tokens=...)) and skip the logits."""
+        return all(p.is_greedy() and not p.uses_history() and not p.logit_bias for _, p, _ in rows)
+
     # ---- one launch per step
     def sample(self, logits: torch.Tensor, rows: List[tuple], return_probs: bool = False):
         """rows[i] = (slot, GenParams, draw_index) for logits[i].  Returns int32 tokens on the device
@@ -62,7 +68,7 @@ class Sampler:
         assert logits.shape[0] == n and logits.dtype == torch.float32 and logits.is_contiguous()
         if n > self.max_rows:
             raise KernelError(f"{n} rows to sample exceed the sampler's {self.max_rows}")
-        if not return_probs and all(p.is_greedy() and not p.uses_history() and not p.logit_bias for _, p, _ in rows):
+        if not return_probs and self.plain_greedy(rows):
             # plain argmax: no per-row parameters to ship, the row is reduced by 64 blocks at once
             ops.argmax_rows(logits, self.arg_val, self.arg_idx, self.out_tokens)
             return self.out_tokens[:n]

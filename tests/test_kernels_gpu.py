@@ -696,3 +696,40 @@ def test_gemm_umma_swap_few_rows(M, N, K):
         ops.gemm_umma_swap(xd, ops.interleave_gate_up(wg.to(DEV), wu.to(DEV)), out=z, epi=2)
         assert torch.allclose(z.double().cpu(), (gate / (1 + torch.exp(-gate))) * up, rtol=1.2e-2, atol=2e-3)
     ops.check_umma_status(DEV)
+
+
+@pytest.mark.parametrize("M,N,K,use_norm", [(1, 65536, 1024, True), (8, 65536, 1024, True), (16, 65536, 1024, False), (5, 4096, 1024, True),
+                                            (8, 65536, 2048, True), (3, 8192, 1536, False)])
+def test_head_argmax_without_logits(M, N, K, use_norm):
+    """The vocabulary head of a greedy decode step: the single-shot product leaves every CTA's best
+    (value, index) of each row, a second kernel picks the row's best; against argmax of the logits the
+    same product stores, with ties (equal largest logits far apart) going to the lower id."""
+    g = torch.Generator().manual_seed(N + M)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    w[N - 7] = w[11]                                               # two equal rows: whichever is largest ties with its twin
+    x = torch.randn(M, K, generator=g) * 2
+    x[0] = w[11].float() * 50.0                                    # row 0 points at the twins: the lower id must win
+    nw = torch.rand(K, generator=g) + 0.5 if use_norm else None
+    need = ops.head_argmax_scratch(M, N, K, use_norm)
+    assert ops.head_argmax_scratch(17, N, K, use_norm) == 0
+    if need == 0:                                                  # sizes the single-shot product leaves to the general kernel
+        with pytest.raises(KernelError, match="does not take"):
+            ops.gemm_bf16_argmax(x.bfloat16().to(DEV), w.to(DEV), None, torch.zeros(8, dtype=torch.int64, device=DEV),
+                                 torch.zeros(M, dtype=torch.int32, device=DEV))
+        assert K != 1024                                           # the 350M head is taken
+        return
+    keys = torch.zeros(need, dtype=torch.int64, device=DEV)
+    toks = torch.full((M + 2,), -5, dtype=torch.int32, device=DEV)
+    if use_norm:
+        if M == 1 and K == 1024:
+            x[0] = x[0] / nw                                       # the norm's weight must not turn row 0 away from the twins
+        logits = ops.gemm_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32, norm=(nw.to(DEV), 1e-5))
+        ops.gemm_bf16_argmax(x.to(DEV), w.to(DEV), None, keys, toks, norm=(nw.to(DEV), 1e-5))
+    else:
+        logits = ops.gemm_bf16(x.bfloat16().to(DEV), w.to(DEV), out_dtype=torch.float32)
+        ops.gemm_bf16_argmax(x.bfloat16().to(DEV), w.to(DEV), None, keys, toks)
+    want = torch.argmax(logits, dim=1).int()                       # the first maximum
+    assert torch.equal(toks[:M], want), (toks[:M], want)
+    assert int(toks[M]) == -5                                      # nothing written past the rows
+    if not use_norm or (M == 1 and K == 1024):
+        assert int(want[0]) == 11 and float(logits[0, 11]) == float(logits[0, N - 7])

@@ -155,3 +155,37 @@ def test_a_replayed_graph_of_a_mixed_step_takes_another_layout(name, dtype, far)
     for r in held:
         eng.release(r)
     eng.cache.audit()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_steps_that_skip_the_logits_give_the_plain_tokens(graphs):
+    """Width 1024 (the head's product then runs on the single-shot kernel): a greedy decode step asks for
+    the tokens themselves and the head picks them without storing the logits.  The tokens must be those
+    of the plain implementation (a near-tie may flip under bfloat16: then the two logits must be close),
+    and the same as the engine's own logits give."""
+    from fellm_b200 import ops
+    from fellm_b200.engine import GenParams
+    cfg, w = tiny.plain_model("C")
+    eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs)
+    assert ops.head_argmax_scratch(3, 384, 1024, True) > 0
+    prompts = [tiny.tokens("C", n, 700 + i) for i, n in enumerate((5, 40, 23))]
+    before = ops.launch_count()
+    got, stats = eng.generate_batch(prompts, GenParams.greedy(12))
+    assert all(s.predicted_tokens == 12 for s in stats)
+    for p, g in zip(prompts, got):
+        want = plain_lfm2.greedy(cfg, w, p, 12)
+        if g != want:
+            i = next(k for k in range(12) if g[k] != want[k])
+            lg = plain_lfm2.forward(cfg, w, p + want[:i])[-1]
+            assert abs(float(lg[g[i]] - lg[want[i]])) < 0.05 * float(lg.abs().max()), (g, want)
+    # the same requests through logits and the sampler's own argmax: the same tokens
+    eng2 = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False)
+    for i, p in enumerate(prompts):
+        eng2.add_request(i)
+        seq = list(p)
+        lg = eng2.step([StepItem(i, seq, [len(seq) - 1])])
+        for t in range(12):
+            tok = int(torch.argmax(lg[0]))
+            assert tok == got[i][t], (i, t)
+            lg = eng2.step([StepItem(i, [tok], [0])])
+    eng.check_status()
