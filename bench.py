@@ -3,10 +3,10 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-One JSON line on stdout.  `value`: decoded tokens a second at batch 8 over the LAST K decode steps
-before the contexts (2,048-token prompts, grown by decoding) reach 4,096: K = 2048 times the whole
-growth from 2,048 to 4,096, a smaller K the steps that end at 4,096, the steps before them running
-untimed; `metric` and `config` name the contexts the timed steps covered.  Timed on the device with
+One JSON line on stdout.  `value`: decoded tokens a second at batch 8 over K decode steps in the MIDDLE
+of the contexts' growth from the 2,048-token prompts to 4,096 (3,072 is the mean context of that
+growth): K = 2048 times the whole growth, a small K the steps that end at 3,072, the steps before
+them running untimed; `metric` and `config` name the contexts the timed steps covered.  Timed on the device with
 CUDA events around K decode steps that include greedy sampling and feed the sampled tokens back on
 the device.
 `e2e`: the same through the Python entry point's scheduler (host tokens in from pinned memory and
@@ -19,7 +19,8 @@ measured copy bandwidth.  `points`: decode at batch 1 and 64.  The engine works 
     python bench.py --shape 1.2b --workload concurrent   # 64 requests x 2,048-id prompts x 512 steps at temperature 0.8
 
 print one line each for the two other workloads of the benchmark (through the scheduler, host
-tokens in and out); `--workloads` adds both lines to the headline line under "workloads".
+tokens in and out); the default run adds both to the headline line under "workloads"
+(`--no-workloads` leaves them out).
 """
 import argparse
 import json
@@ -50,6 +51,14 @@ def shape_config(name):
     cfg = dict(LFM2_350M)
     cfg.update(hidden_size=hidden, num_attention_heads=heads, block_ff_dim=ff)
     return cfg, seed
+
+
+def untimed_steps(steps, warmup, prompt=PROMPT, context_end=CONTEXT_END):
+    """Decode steps to run before the timed ones: the timed window ends at the middle of the growth from
+    `prompt` to `context_end` (a window longer than half the growth is centred on it).  A window of a few
+    steps then lies inside one 1,024-bucket of contexts: no step of it is the first of a new CUDA graph."""
+    half = (context_end - prompt) // 2
+    return max(warmup, half - steps if steps <= half else (context_end - prompt - steps) // 2)
 
 
 def peaks():
@@ -113,8 +122,8 @@ def flops_per_token(cfg, n_layers_attn, context):
 
 
 def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CONTEXT_END):
-    """Prefills `batch` requests of `prompt` random ids, decodes untimed until `steps` steps are left
-    before the contexts reach `context_end` (at least `warmup` steps), then times those on the device.
+    """Prefills `batch` requests of `prompt` random ids, decodes untimed up to the `steps` steps in the
+    middle of the growth from `prompt` to `context_end` (at least `warmup` steps), then times those on the device.
     Returns (tokens/s, ms/step, launches in the timed region, mean context, first and last context)."""
     import torch
     from fellm_b200.engine import GenParams, StepItem
@@ -144,7 +153,7 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CON
         else:
             tokens = engine.sampler.sample(logits, rows)
             sampler_launches += 2
-    for _ in range(max(warmup, context_end - prompt - steps)):
+    for _ in range(untimed_steps(steps, warmup, prompt, context_end)):
         one()
     torch.cuda.synchronize()
     l0 = engine.stepper.launches
@@ -222,7 +231,7 @@ def run_e2e(engine, batch, steps, warmup, rng):
     from fellm_b200.engine import GenParams
     sched = engine.scheduler()
     vocab = engine.spec.vocab_size
-    ahead = max(warmup, CONTEXT_END - PROMPT - steps)            # untimed steps: the timed ones end at CONTEXT_END
+    ahead = max(untimed_steps(steps, warmup) - 2, warmup)        # the timed steps end just below the middle of the growth
     for _ in range(batch):
         sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(ahead + steps + 8))
     while any(r.prefilling for r in list(sched.running) + list(sched.waiting)) or sched.waiting:
@@ -399,8 +408,9 @@ def main():
     ap.add_argument("--shape", choices=sorted(SHAPES), default="350m")
     ap.add_argument("--workload", choices=["mixed", "concurrent"], default=None,
                     help="run one of the other workloads of the benchmark at --shape and print its line")
-    ap.add_argument("--workloads", action="store_true",
-                    help="after the headline measurement, run 700m/mixed and 1.2b/concurrent and add them under 'workloads'")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the two other workloads (700m/mixed, 1.2b/concurrent) that follow the headline measurement "
+                         "and are reported under 'workloads'")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling a small case; not a bench value)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
@@ -437,7 +447,7 @@ def main():
         cfg["num_hidden_layers"] = args.layers
         cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < args.layers]
     steps = args.steps
-    ctx_end = PROMPT + max(warmup, CONTEXT_END - PROMPT - steps) + steps + 16
+    ctx_end = PROMPT + untimed_steps(steps, warmup) + steps + 16
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
     opts = EngineOptions(dtype="bfloat16", n_ctx=max(ctx_end, CONTEXT_END + 64), n_batch=4096, n_ubatch=2048, page_tokens=64,
                          max_requests=max_batch, max_tokens=max_batch * (max(ctx_end, CONTEXT_END) + 64), cuda_graphs=True)
@@ -502,10 +512,15 @@ def main():
         "points": points,
         "clocks": clk,
     }
-    if args.workloads:
+    if not args.no_workloads and args.shape == "350m" and not args.layers:
         del engine
         torch.cuda.empty_cache()
-        out["workloads"] = {"700m_mixed": run_workload("700m", "mixed", hbm), "1.2b_concurrent": run_workload("1.2b", "concurrent", hbm)}
+        out["workloads"] = {}
+        for key, shape, workload in (("700m_mixed", "700m", "mixed"), ("1.2b_concurrent", "1.2b", "concurrent")):
+            try:
+                out["workloads"][key] = run_workload(shape, workload, hbm)
+            except Exception as e:                       # the headline line stands by itself
+                out["workloads"][key] = {"error": f"{type(e).__name__}: {e}"[:200]}
     print(json.dumps(out))
     return 0
 
