@@ -878,7 +878,7 @@ FELLM_API int fellm_attn_prefill_mma(const void* q, const void* pool, const int*
     cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
   }
-  return launch_k(kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, a);
+  return launch_k_class(launch_class_for_rows(T, 0), kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, a);
 }
 
 // One query row per item.  scratch: float32 [T*H*max_splits*(hd+2)]; counters: int32 [T*G], zero
@@ -982,7 +982,7 @@ FELLM_API int fellm_attn_prefill_tma(const void* q, const void* pool, long long 
   auto kern = attention_prefill_tma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
-  return launch_k(kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, map, a, status);
+  return launch_k_class(launch_class_for_rows(T, 0), kern, dim3((ceil_div(max_item_rows, tokb) + 1) / 2, G, n_items), dim3(PF_WARPS * 32), smem, stream, 1, map, a, status);
 #else
   return FELLM_ERR_SIZE;
 #endif

@@ -497,5 +497,5 @@ FELLM_API int fellm_attn_prefill_umma(const void* q, const void* pool, long long
   auto kern = attention_prefill_umma_kernel;
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
-  return launch_k(kern, dim3(ceil_div(max_item_rows, tokb) * G, 1, n_items), dim3(AU_THREADS), smem, stream, 1, map, a);
+  return launch_k_class(launch_class_for_rows(T, 0), kern, dim3(ceil_div(max_item_rows, tokb) * G, 1, n_items), dim3(AU_THREADS), smem, stream, 1, map, a);
 }

@@ -30,8 +30,8 @@ FELLM_API int fellm_embed_rows(const int* tokens, const void* table, int table_i
   if (!tokens || !table || !out) return FELLM_ERR_ARG;
   int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
   if (table_is_bf16)
-    return launch_k_class(2, embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
-  return launch_k_class(2, embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
+    return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const bf16*)table, out, d, vocab, status);
+  return launch_k_class(launch_class_for_rows(rows, 2), embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, 1, tokens, (const float*)table, out, d, vocab, status);
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -128,19 +128,19 @@ FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_i
     const int warps = 4;
     dim3 vgrid((n_out_rows + warps - 1) / warps);
     if (d <= 1024) {
-      if (out_is_bf16) return launch_k(rmsnorm_vec_kernel<bf16, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
-      return launch_k(rmsnorm_vec_kernel<float, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+      if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<bf16, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+      return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<float, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
     }
-    if (out_is_bf16) return launch_k(rmsnorm_vec_kernel<bf16, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
-    return launch_k(rmsnorm_vec_kernel<float, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+    if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<bf16, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+    return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<float, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
   }
   dim3 grid(n_out_rows);
   if (d >= 512) {
-    if (out_is_bf16) return launch_k(rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
-    return launch_k(rmsnorm_kernel<float, 256>, grid, dim3(256), 0, stream, 1, x, w, (float*)out, rows, d, eps);
+    if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+    return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<float, 256>, grid, dim3(256), 0, stream, 1, x, w, (float*)out, rows, d, eps);
   }
-  if (out_is_bf16) return launch_k(rmsnorm_kernel<bf16, 64>, grid, dim3(64), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
-  return launch_k(rmsnorm_kernel<float, 64>, grid, dim3(64), 0, stream, 1, x, w, (float*)out, rows, d, eps);
+  if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<bf16, 64>, grid, dim3(64), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+  return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<float, 64>, grid, dim3(64), 0, stream, 1, x, w, (float*)out, rows, d, eps);
 }
 
 // ---------------------------------------------------------------- SiLU gate
@@ -163,6 +163,6 @@ FELLM_API int fellm_silu_mul(const void* gu, void* out, int is_bf16, int rows, i
   if (rows <= 0) return 0;
   size_t n = (size_t)rows * F;
   int blocks = (int)((n + 255) / 256); if (blocks > fellm_sm_count() * 16) blocks = fellm_sm_count() * 16;
-  if (is_bf16) return launch_k(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, rows, F);
-  return launch_k(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (const float*)gu, (float*)out, rows, F);
+  if (is_bf16) return launch_k_class(launch_class_for_rows(rows, 0), silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1, (const bf16*)gu, (bf16*)out, rows, F);
+  return launch_k_class(launch_class_for_rows(rows, 0), silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, (const float*)gu, (float*)out, rows, F);
 }

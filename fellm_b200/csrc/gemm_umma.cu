@@ -14,6 +14,8 @@
 // FeLLM counterpart: bf16_matmul_rows, one thread per output
 // (plugins/cuda_kernels/src/oxide_kernels.rs:3165).
 #include <cuda.h>
+#include <cooperative_groups.h>
+namespace cgx = cooperative_groups;
 
 #define FELLM_WEIGHT_PREFETCH 1
 #include "common.cuh"
@@ -282,6 +284,177 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster, on the two SMs of a TPC, work on ONE tile
+// of 256 rows x BN columns.  Each CTA brings its own 128 rows of A and HALF of the tile's W rows
+// (BN / 2) by TMA into its own shared memory; the MMA, issued by one thread of the pair's first
+// CTA, reads both CTAs' shared memory and writes each CTA's 128 rows of the accumulator into that
+// CTA's tensor memory.  A 256 x 256 tile then costs a CTA 32 KB of operands a k-block where the
+// single-CTA 128 x 256 tile costs 48 KB and the 128 x 128 tile 32 KB for a quarter of the product:
+// the kernel above is bound by operand bytes from L2, this one moves half as many a FLOP.
+// No multicast load anywhere: both CTAs fetch their own halves.
+//
+// What the pair shares, as the PTX ISA gives it (cta_group::2 forms of tcgen05.alloc / mma / commit,
+// cp.async.bulk.tensor with .cta_group::2 completing bytes on the first CTA's mbarrier):
+//   * full[s] lives in the first CTA (rank 0): its producer expects the bytes of BOTH CTAs' copies;
+//     both producers name rank 0's barrier in their copies;
+//   * empty[s] and acc_full[b] live in both CTAs: the commit that follows the MMAs arrives on both
+//     (.multicast::cluster with mask 0b11); each producer / each CTA's epilogue waits on its own;
+//   * acc_empty[b] lives in rank 0 and counts the epilogue warps of both CTAs (the second CTA's
+//     arrive through the cluster's shared-memory window);
+//   * tensor memory is allocated and freed by warp 1 of BOTH CTAs with the cta_group::2 forms, the
+//     frees behind a cluster barrier.
+// Waits are bounded as in the kernel above (status 121 producer, 122 / 124 MMA, 123 epilogue).
+#define UP_THREADS 320
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned mapa_u32(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar_rank0) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+               ::"r"(dst), "l"(map), "r"(bar_rank0), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                              unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(unsigned bar) {          // arrives on `bar` of both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+
+template <int EPI, int BN>
+__global__ void __launch_bounds__(UP_THREADS)
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
+  constexpr int STAGE_BYTES = (UM_BM + BN / 2) * UM_BK * 2;                  // this CTA's part of a stage
+  constexpr int STAGES = BN == 256 ? 6 : 8;                                  // 192 KB either way
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];           // full[], empty[], acc_full[2], acc_empty[2]
+  __shared__ unsigned tmem_base_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank();                                   // 0: the pair's first CTA, which issues the MMAs
+  const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+  const unsigned accfull0 = smem_u32(&bars[2 * STAGES]), accempty0 = smem_u32(&bars[2 * STAGES + 2]);
+  const unsigned full0_rank0 = mapa_u32(full0, 0), accempty0_rank0 = mapa_u32(accempty0, 0);
+  const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
+  const int m_pairs = (a.M + 2 * UM_BM - 1) / (2 * UM_BM), n_tiles = (a.N + BN - 1) / BN, total = m_pairs * n_tiles;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(accfull0 + 8 * b, 1); mbar_init(accempty0 + 8 * b, 16); }   // 8 epilogue warps of each CTA
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {                   // two accumulators of 128 x BN float32 in this CTA's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  cgx::this_cluster().sync();        // both CTAs' barriers are initialised before either names the other's
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+  pdl_launch_dependents();
+  pdl_wait(); FELLM_TRACE_WAITED();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      unsigned it = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs) {
+        const int m0 = (t % m_pairs) * 2 * UM_BM + (int)rank * UM_BM, n0 = (t / m_pairs) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(empty0 + 8 * s, (it / STAGES - 1) & 1, a.status, 121)) { ok = false; break; }
+          const unsigned dst = tiles + s * STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);      // the bytes of both CTAs' copies
+          tma_load_2d_pair(dst, &map_a, kb * UM_BK, m0, full0_rank0 + 8 * s);
+          tma_load_2d_pair(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0_rank0 + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const unsigned idesc = umma_idesc(2 * UM_BM, BN);
+      unsigned it = 0, use = 0;
+      bool ok = true;
+      for (int t = pair; t < total && ok; t += n_pairs, ++use) {
+        const unsigned acc = use & 1, d_tmem = tmem_base + acc * BN;
+        if (use >= 2) {
+          ok = mbar_wait(accempty0 + 8 * acc, ((use >> 1) - 1) & 1, a.status, 124);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, a.status, 122);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const unsigned sa = tiles + s * STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
+          const unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+          for (int k = 0; k < UM_BK / 16; ++k)
+            umma_f16_pair(d_tmem, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          umma_commit_pair(empty0 + 8 * s);             // the stage is free, in both CTAs, once these MMAs have read it
+        }
+        if (ok) umma_commit_pair(accfull0 + 8 * acc);   // both CTAs' epilogues
+      }
+    }
+  } else {
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    unsigned use = 0;
+    for (int t = pair; t < total; t += n_pairs, ++use) {
+      const unsigned acc = use & 1;
+      const int m0 = (t % m_pairs) * 2 * UM_BM + (int)rank * UM_BM, n0 = (t / m_pairs) * BN;
+      const int m = m0 + q * 32 + lane;
+      constexpr int CHUNKS = BN / 2 / 32;
+      constexpr int PRE = CHUNKS < 2 ? CHUNKS : 2;
+      float4 res[EPI == EPI_ACC ? PRE : 1][8];
+      bool res_ok[CHUNKS];
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int n = n0 + half * (BN / 2) + ch * 32;
+        res_ok[ch] = EPI == EPI_ACC && ch < PRE && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
+        if (EPI == EPI_ACC && res_ok[ch]) {
+          const float4* src = (const float4*)((const float*)a.out + (size_t)m * a.ldo + n);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) res[ch][j] = src[j];
+        }
+      }
+      if (!mbar_wait(accfull0 + 8 * acc, (use >> 1) & 1, a.status, 123)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int c0 = half * (BN / 2) + ch * 32;
+        float v[32];
+        tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + acc * BN + (unsigned)c0, v);
+        if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch < PRE ? ch : 0] : nullptr);
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(accempty0_rank0 + 8 * acc);      // one of the sixteen arrivals that free the accumulator
+    }
+  }
+  // common exit: every role of both CTAs comes here, also after a wait that gave up
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  cgx::this_cluster().sync();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+}
+
 // ---- host side: tensor maps through the driver entry point (no link against libcuda)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -318,7 +491,19 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& 
   if (e != cudaSuccess) return (int)e;
   const int n_sm = fellm_sm_count();
   int total = ceil_div(a.N, BN) * ceil_div(a.M, UM_BM);
-  return launch_k(kern, dim3(total < n_sm ? total : n_sm, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
+  return launch_k_class(launch_class_for_rows(a.M, 0), kern, dim3(total < n_sm ? total : n_sm, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 1, ma, mw, a);
+}
+
+template <int EPI, int BN>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, cudaStream_t stream) {
+  size_t smem = (size_t)(BN == 256 ? 6 : 8) * (UM_BM + BN / 2) * UM_BK * 2 + 1024;
+  auto kern = gemm_umma_pair_kernel<EPI, BN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int pairs_dev = fellm_sm_count() / 2;
+  const int total = ceil_div(a.N, BN) * ceil_div(a.M, 2 * UM_BM);
+  const int pairs = total < pairs_dev ? total : pairs_dev;
+  return launch_k_class(launch_class_for_rows(a.M, 0), kern, dim3(2 * pairs, 1, 1), dim3(UP_THREADS, 1, 1), smem, stream, 2, ma, mw, a);
 }
 
 // status: device int32 that a role sets (101 producer, 102/104 MMA, 103 epilogue) if a wait ran out.
@@ -329,19 +514,52 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
   // TMA: 16-byte aligned bases and row strides
   if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
   if (epi == EPI_SWIGLU && ((N % 16) || (ldo % 8))) return FELLM_ERR_SIZE;
-  // 128 x 256 tiles (a quarter fewer operand bytes a FLOP) where they fill the SMs as well as 128 x 128 ones
-  const int m_tiles = ceil_div(M, UM_BM);
-  const int n_sm = fellm_sm_count();
-  const int waves128 = ceil_div(ceil_div(N, 128) * m_tiles, n_sm), waves256 = ceil_div(ceil_div(N, 256) * m_tiles, n_sm);
-  static int wide_ok = -1;
+  // The tile: 128 x 128 or 128 x 256 by one CTA, or 256 x 256 / 256 x 128 by a CTA pair.  Chosen by an
+  // estimate: waves x k-blocks x the time a CTA takes for a k-block of its tile (measured on B200 at
+  // 2,048 rows: 0.37 us for 128 x 128, 0.47 us for 128 x 256, 0.44 us and 0.39 us for a pair's CTA on
+  // 256 x 256 and 256 x 128) + 4.5 us of filling and draining; within 5% one CTA a tile stays.
+  // FELLM_B200_UMMA_PAIR=0: never pairs; =128 / =256: always that pair tile; FELLM_B200_UMMA_WIDE=0: no 128 x 256.
+  const int m_tiles = ceil_div(M, UM_BM), m_pairs = ceil_div(M, 2 * UM_BM), kb = ceil_div(K, UM_BK);
+  const int n_sm = fellm_sm_count(), pairs_dev = n_sm / 2;
+  static int wide_ok = -1, pair_mode = -1;
   if (wide_ok < 0) { const char* ev = getenv("FELLM_B200_UMMA_WIDE"); wide_ok = (ev && ev[0] == '0') ? 0 : 1; }
-  const bool wide = wide_ok && N >= 512 && 2 * waves256 <= waves128;
+  if (pair_mode < 0) { const char* ev = getenv("FELLM_B200_UMMA_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
+  auto estimate = [&](int tiles, int units, float t_kb) { return 4.5f + (float)ceil_div(tiles, units) * kb * t_kb; };
+  float best = estimate(ceil_div(N, 128) * m_tiles, n_sm, 0.37f);
+  int choice = 0;                                           // 0: 128 x 128, 1: 128 x 256, 2: pair 256 x 256, 3: pair 256 x 128
+  if (wide_ok && N >= 512) {
+    const float t = estimate(ceil_div(N, 256) * m_tiles, n_sm, 0.47f);
+    if (t < best) { best = t; choice = 1; }
+  }
+  if (pair_mode && M >= 512 && pairs_dev >= 1) {
+    if (N >= 256) {
+      const float t = estimate(ceil_div(N, 256) * m_pairs, pairs_dev, 0.44f);
+      if (t < 0.95f * best) { best = t; choice = 2; }
+    }
+    const float t = estimate(ceil_div(N, 128) * m_pairs, pairs_dev, 0.39f);
+    if (t < 0.95f * best) { best = t; choice = 3; }
+    if (pair_mode == 256 && N >= 256) choice = 2;
+    if (pair_mode == 128) choice = 3;
+  }
   CUtensorMap ma, mw;
   int e = make_map(&ma, A, M, K, lda, UM_BM);
   if (e) return e;
+  UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
+  if (choice >= 2) {
+    const bool bn256 = choice == 2;
+    e = make_map(&mw, W, N, K, ldw, bn256 ? 128 : 64);           // a CTA's half of the tile's W rows
+    if (e) return e;
+    switch (epi) {
+      case EPI_STORE: return bn256 ? launch_pair<EPI_STORE, 256>(ma, mw, a, stream) : launch_pair<EPI_STORE, 128>(ma, mw, a, stream);
+      case EPI_ACC: return bn256 ? launch_pair<EPI_ACC, 256>(ma, mw, a, stream) : launch_pair<EPI_ACC, 128>(ma, mw, a, stream);
+      case EPI_SWIGLU: return bn256 ? launch_pair<EPI_SWIGLU, 256>(ma, mw, a, stream) : launch_pair<EPI_SWIGLU, 128>(ma, mw, a, stream);
+      case EPI_F32: return bn256 ? launch_pair<EPI_F32, 256>(ma, mw, a, stream) : launch_pair<EPI_F32, 128>(ma, mw, a, stream);
+      default: return FELLM_ERR_ARG;
+    }
+  }
+  const bool wide = choice == 1;
   e = make_map(&mw, W, N, K, ldw, wide ? 256 : 128);
   if (e) return e;
-  UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
   switch (epi) {
     case EPI_STORE: return wide ? launch<EPI_STORE, 256>(ma, mw, a, stream) : launch<EPI_STORE, 128>(ma, mw, a, stream);
     case EPI_ACC: return wide ? launch<EPI_ACC, 256>(ma, mw, a, stream) : launch<EPI_ACC, 128>(ma, mw, a, stream);
@@ -368,9 +586,6 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
 // products are done all eight warps read the accumulator (TMEM lane quarter = warp % 4, 16-column
 // chunks by turns of warp / 4) and then share the owner's tokens.  All waits are bounded (status 111 TMA, 112 MMA,
 // 113 accumulator); a role that gives up still goes through the cluster barrier.
-#include <cooperative_groups.h>
-namespace cgx = cooperative_groups;
-
 #define SW_THREADS 256
 #define SW_WARPS 8
 #define SW_W_BYTES (UM_BM * UM_BK * 2)          // 16 KB: 128 weight rows x 64 k

@@ -216,7 +216,7 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
     while (gl < lanes) gl <<= 1;
     long long nthreads = warps * gl;
     dim3 vgrid((unsigned)((nthreads + threads - 1) / threads));
-#define RW_VEC(GL_) launch_k_class(2, qk_rope_write_vec_kernel<GL_>, vgrid, dim3(threads), 0, stream, 1, (const bf16*)qkv, q_w, k_w, \
+#define RW_VEC(GL_) launch_k_class(launch_class_for_rows(T, 2), qk_rope_write_vec_kernel<GL_>, vgrid, dim3(threads), 0, stream, 1, (const bf16*)qkv, q_w, k_w, \
                              eps, inv_freq, pairing, positions, row_slot, block_table, max_pages, (bf16*)pool, layer,     \
                              layers_in_group, page_tokens, (bf16*)q_out, T, H, G, hd, write_kv, status)
     switch (gl) {
@@ -229,10 +229,10 @@ FELLM_API int fellm_qk_rope_write(const void* qkv, int act_bf16, const float* q_
 #undef RW_VEC
   }
   if (act_bf16)
-    return launch_k_class(2, qk_rope_write_kernel<bf16, bf16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
+    return launch_k_class(launch_class_for_rows(T, 2), qk_rope_write_kernel<bf16, bf16>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
                     (const bf16*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
                     (bf16*)pool, layer, layers_in_group, page_tokens, (bf16*)q_out, T, H, G, hd, rot_dim, write_kv, status);
-  return launch_k_class(2, qk_rope_write_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
+  return launch_k_class(launch_class_for_rows(T, 2), qk_rope_write_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, stream, 1,
                   (const float*)qkv, q_w, k_w, eps, inv_freq, pairing, positions, row_slot, block_table, max_pages,
                   (float*)pool, layer, layers_in_group, page_tokens, (float*)q_out, T, H, G, hd, rot_dim, write_kv, status);
 }
