@@ -354,7 +354,8 @@ def check_umma_status(device):
                 raise KernelError("decode attention: a row's position has no cache page mapped")
             what = ("the TMA decode attention" if code == 301 else
                     "the tcgen05 prefill attention" if 311 <= code <= 317 else
-                    "the tcgen05 product of few rows" if 111 <= code <= 113 else "the tcgen05 product")
+                    "the tcgen05 product of few rows" if 111 <= code <= 113 else
+                    "the tcgen05 product on CTA pairs" if 121 <= code <= 124 else "the tcgen05 product")
             raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
 
