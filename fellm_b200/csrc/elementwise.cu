@@ -120,6 +120,14 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+// RMSNorm as a kernel of its own runs where the products do not take it in (17 rows and more): launched as a
+// programmatic dependent from FELLM_B200_NORM_PDL_ROWS rows on, its launch hides under the product in front.
+static int norm_class(int rows) {
+  static int from = -1;
+  if (from < 0) { const char* e = getenv("FELLM_B200_NORM_PDL_ROWS"); from = e ? atoi(e) : 17; }
+  return rows >= from ? 1 : 0;
+}
+
 FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_is_bf16,
                             const int* rows, int n_out_rows, int d, float eps, cudaStream_t stream) {
   if (n_out_rows <= 0) return 0;
@@ -128,19 +136,19 @@ FELLM_API int fellm_rmsnorm(const float* x, const float* w, void* out, int out_i
     const int warps = 4;
     dim3 vgrid((n_out_rows + warps - 1) / warps);
     if (d <= 1024) {
-      if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<bf16, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
-      return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<float, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+      if (out_is_bf16) return launch_k_class(norm_class(n_out_rows), rmsnorm_vec_kernel<bf16, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+      return launch_k_class(norm_class(n_out_rows), rmsnorm_vec_kernel<float, 8>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
     }
-    if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<bf16, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
-    return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_vec_kernel<float, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
+    if (out_is_bf16) return launch_k_class(norm_class(n_out_rows), rmsnorm_vec_kernel<bf16, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (bf16*)out, rows, n_out_rows, d, eps);
+    return launch_k_class(norm_class(n_out_rows), rmsnorm_vec_kernel<float, 16>, vgrid, dim3(warps * 32), 0, stream, 1, x, w, (float*)out, rows, n_out_rows, d, eps);
   }
   dim3 grid(n_out_rows);
   if (d >= 512) {
-    if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
-    return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<float, 256>, grid, dim3(256), 0, stream, 1, x, w, (float*)out, rows, d, eps);
+    if (out_is_bf16) return launch_k_class(norm_class(n_out_rows), rmsnorm_kernel<bf16, 256>, grid, dim3(256), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+    return launch_k_class(norm_class(n_out_rows), rmsnorm_kernel<float, 256>, grid, dim3(256), 0, stream, 1, x, w, (float*)out, rows, d, eps);
   }
-  if (out_is_bf16) return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<bf16, 64>, grid, dim3(64), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
-  return launch_k_class(launch_class_for_rows(n_out_rows, 0), rmsnorm_kernel<float, 64>, grid, dim3(64), 0, stream, 1, x, w, (float*)out, rows, d, eps);
+  if (out_is_bf16) return launch_k_class(norm_class(n_out_rows), rmsnorm_kernel<bf16, 64>, grid, dim3(64), 0, stream, 1, x, w, (bf16*)out, rows, d, eps);
+  return launch_k_class(norm_class(n_out_rows), rmsnorm_kernel<float, 64>, grid, dim3(64), 0, stream, 1, x, w, (float*)out, rows, d, eps);
 }
 
 // ---------------------------------------------------------------- SiLU gate

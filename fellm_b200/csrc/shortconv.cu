@@ -205,6 +205,12 @@ __global__ void shortconv_kernel(const TA* __restrict__ bcx, const float* __rest
 
 // bcx [T, 3d] (B | C | X thirds; or, blocked, [B16 | C16 | X16] per 16 channels), w [d, Lc] float32 (tap Lc-1 multiplies the current token),
 // conv_bias [d] or null, state: base of this layer's slots, slot_stride floats between slots.
+static int conv_class(int rows) {
+  static int from = -1;
+  if (from < 0) { const char* e = getenv("FELLM_B200_NORM_PDL_ROWS"); from = e ? atoi(e) : 17; }
+  return rows >= from ? 1 : 2;
+}
+
 FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, const float* conv_bias,
                               float* state, long long slot_stride, const int* item_slot,
                               const int* item_start, const int* row_item, void* y, int T, int n_items,
@@ -222,7 +228,7 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
     const int tiles_per_y = (gx * threads) / (d / 8);
     n_body = ceil_div(n_body, tiles_per_y);
     dim3 grid(gx, n_body + n_items);
-#define SC_VEC(LC_) launch_k_class(launch_class_for_rows(T, 2), shortconv_kernel<bf16, LC_>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state, \
+#define SC_VEC(LC_) launch_k_class(conv_class(T), shortconv_kernel<bf16, LC_>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state, \
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked)
     switch (Lc) {
       case 2: return SC_VEC(2);
@@ -234,8 +240,8 @@ FELLM_API int fellm_shortconv(const void* bcx, int is_bf16, const float* w, cons
   }
   dim3 grid(gx, n_body + n_items);
   if (is_bf16)
-    return launch_k_class(launch_class_for_rows(T, 2), shortconv_kernel<bf16, 0>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
+    return launch_k_class(conv_class(T), shortconv_kernel<bf16, 0>, grid, dim3(threads), 0, stream, 1, (const bf16*)bcx, w, conv_bias, state,
                     slot_stride, item_slot, item_start, row_item, (bf16*)y, T, n_items, d, Lc, n_body, blocked);
-  return launch_k_class(launch_class_for_rows(T, 2), shortconv_kernel<float, 0>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
+  return launch_k_class(conv_class(T), shortconv_kernel<float, 0>, grid, dim3(threads), 0, stream, 1, (const float*)bcx, w, conv_bias, state,
                   slot_stride, item_slot, item_start, row_item, (float*)y, T, n_items, d, Lc, n_body, blocked);
 }

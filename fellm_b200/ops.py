@@ -600,6 +600,7 @@ def reserve_decode_scratch(device, rows: int, heads: int, kv_heads: int, head_di
 # SM).  Measured on B200, 16 layers of width 1024, context 2048 (4000): batch 8 379 (411) us a step
 # with 444, 387 (438) with 592, 399 (417) with 300; batch 32 764 with 444, 822 with 592.
 DECODE_TARGET_CTAS = int(os.environ.get("FELLM_B200_DECODE_TARGET", 0))     # 0: three CTAs for every SM of the device
+BIG_BATCH_SPLITS = int(os.environ.get("FELLM_B200_DECODE_BIG_SPLITS", 2))
 DECODE_STAGES = int(os.environ.get("FELLM_B200_DECODE_STAGES", 0))           # 0: by the step's size (decode_stages)
 _sm_count = {}
 
@@ -647,7 +648,7 @@ def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
         target = decode_target_ctas() // 3 if decode_stages(rows, kv_heads) == 4 else decode_target_ctas()
     want = max(1, target // items)
     if items > target:
-        want = 2            # more than a wave even unsplit: halves, so that the last wave is a short one
+        want = BIG_BATCH_SPLITS      # more than a wave even unsplit: halves, so that the last wave is a short one
     split_len = max(64, -(-(-(-bucket // want)) // 64) * 64)
     if split_len > 256 and SPLIT_WHOLE_ROUNDS:
         split_len = -(-split_len // 256) * 256      # whole rounds of the kernel's four warps, a page each
