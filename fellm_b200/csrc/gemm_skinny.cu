@@ -75,7 +75,25 @@ struct SkinnyArgs {
   // EPI_ARGMAX: nothing of [M, N] is stored; every CTA leaves its best (value, index) of each row as a key
   // in arg_keys[row * CTAs + CTA] (larger key = larger value, then lower index)
   unsigned long long* arg_keys;
+  // EPI_ACC as the producer of the next RMSNorm's input (nn_x null: not asked for): beside out += ..., the
+  // single-shot kernel leaves nn_x[m, n] = bfloat16(out[m, n] * nn_w[n]) and, for every slab of 16 columns,
+  // nn_ssq[m * n_tiles + slab] = the sum of out[m, n]^2 over the slab
+  const float* nn_w; bf16* nn_x; float* nn_ssq; int nn_ldx;
+  // ... and its consumer (rs_ssq null: none): x is such an nn_x, and every finished sum of row m is
+  // multiplied by 1 / sqrt(sum_p rs_ssq[m * rs_parts + p] / K + rs_eps) before the bias is added:
+  // RMSNorm(x) W^T with the row's factor taken out of the product
+  const float* rs_ssq; int rs_parts; float rs_eps;
 };
+
+// What the next call of this module is to hand on or to take over (see SkinnyArgs); every entry point
+// takes it and clears it.
+struct NormHandoff { const float* nn_w; void* nn_x; float* nn_ssq; int nn_ldx; const float* rs_ssq; int rs_parts; float rs_eps; };
+static NormHandoff g_handoff = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0.f};
+static inline NormHandoff take_handoff() {
+  NormHandoff h = g_handoff;
+  g_handoff = NormHandoff{nullptr, nullptr, nullptr, 0, nullptr, 0, 0.f};
+  return h;
+}
 
 // float32 value and index as one number whose order is "the larger value, then the lower index":
 // greedy sampling's rule (crates/fellm-runtime/src/sampling.rs:588-604).
@@ -452,6 +470,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   constexpr int MP = MT * 8;
   __shared__ unsigned long long arg_best[EPI == EPI_ARGMAX ? MT * 8 : 1];     // the CTA's best key of each row
   if (EPI == EPI_ARGMAX && threadIdx.x < MT * 8) arg_best[threadIdx.x] = 0ull;  // seen by all behind the barrier before the sums
+  __shared__ float rs_scale[MT * 8];                   // the rows' norm factors when x comes pre-weighted (a.rs_ssq)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int split = a.splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
@@ -504,6 +523,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     const bf16* p0 = w_base + (size_t)tile * SK_ROWS * a.ldw;
     LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
   }
+  // EPI_ACC with a norm to hand on: the next norm's weight for the value this thread finishes first
+  const int first_unit = ((split << a.log2_warps_k) + wk) * 32 + lane;
+  float next_w_first = 0.f;
+  if (EPI == EPI_ACC && a.nn_x && first_unit < SK_ROWS * a.M && tile < a.n_tiles) next_w_first = a.nn_w[tile * SK_ROWS + (first_unit & 15)];
   if (threadIdx.x == 0)
     l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   pdl_launch_dependents();
@@ -512,6 +535,24 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     request_x();
   }
   FELLM_TRACE_WAITED();
+  // the rows' sums of squares come in parts (at most 128 a row): warp w asks for those of rows w and w + WARPS
+  // now and adds them up, always in the same order, behind the product, where nobody waits for them
+  float rs_part[2][4];
+  if (a.rs_ssq) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = warp + h * WARPS;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int p = lane + 32 * q;
+        rs_part[h][q] = (r < a.M && p < a.rs_parts) ? a.rs_ssq[(size_t)r * a.rs_parts + p] : 0.f;
+      }
+    }
+  }
+  // EPI_ACC: the value this thread adds to first is asked for now too
+  float old_first = 0.f;
+  if (EPI == EPI_ACC && first_unit < SK_ROWS * a.M && tile < a.n_tiles)
+    old_first = ((const float*)a.out)[(size_t)(first_unit >> 4) * a.ldo + tile * SK_ROWS + (first_unit & 15)];
 
   // EPI_CONV: thread (channel j of the CTA's 16, token m) asks for its taps and its state now; they
   // are used after the product
@@ -574,9 +615,14 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     float* p = slots + (size_t)(warp * tpw + tl) * SK_ROWS * MP;
 #pragma unroll
     for (int pass = 0; pass < MT / TP; ++pass) {
-      float acc[TP][4];
+      // up to 16 tokens: the two halves of a chunk add into sums of their own, so that an MMA waits for the one
+      // two before it, not for the one before it (the sums are added at the end; more tokens have MMAs enough)
+      constexpr int CH = TP <= 2 ? 2 : 1;
+      float acc[TP][CH][4];
 #pragma unroll
-      for (int t = 0; t < TP; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f; }
+      for (int t = 0; t < TP; ++t)
+#pragma unroll
+        for (int h = 0; h < CH; ++h) { acc[t][h][0] = acc[t][h][1] = acc[t][h][2] = acc[t][h][3] = 0.f; }
 #pragma unroll
       for (int u = 0; u < LEAN_CH; ++u) {
         if (u < 8 || u < n_chunks) {
@@ -585,20 +631,35 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
 #pragma unroll
           for (int t = 0; t < TP; ++t) {
             uint4 b = *(const uint4*)(xw + u * KCHUNK + (size_t)(pass * TP + t) * 8 * a.xs_stride);
-            mma16816(acc[t], fa, b.x, b.y);
-            mma16816(acc[t], fb, b.z, b.w);
+            mma16816(acc[t][0], fa, b.x, b.y);
+            mma16816(acc[t][CH - 1], fb, b.z, b.w);
           }
         }
       }
 #pragma unroll
       for (int t = 0; t < TP; ++t) {
-        *(float2*)(p + g * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][0], acc[t][1]);
-        *(float2*)(p + (g + 8) * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][2], acc[t][3]);
+        if (CH == 2) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[t][0][e] += acc[t][1][e];
+        }
+        *(float2*)(p + g * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][0][0], acc[t][0][1]);
+        *(float2*)(p + (g + 8) * MP + (pass * TP + t) * 8 + 2 * c) = make_float2(acc[t][0][2], acc[t][0][3]);
       }
     }
     if (tl + 1 < tpw && tile_l + tile_stride < a.n_tiles) {
       const bf16* p0 = w_base + (size_t)(tile_l + tile_stride) * SK_ROWS * a.ldw;
       LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
+    }
+  }
+  if (a.rs_ssq) {
+    // RMSNorm's factor of each row (crates/backend-cpu/src/kernels/norm.rs:6-39)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = warp + h * WARPS;
+      if (r < a.M) {                                   // (whole warps)
+        const float ss = warp_sum((rs_part[h][0] + rs_part[h][1]) + (rs_part[h][2] + rs_part[h][3]));
+        if (lane == 0) rs_scale[r] = 1.0f / sqrtf(ss / (float)a.K + a.rs_eps);
+      }
     }
   }
   FELLM_TRACE_MARK(1);
@@ -616,37 +677,62 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     const float* mine = slots + (size_t)((wn << a.log2_warps_k) * tpw + tl) * SK_ROWS * MP;      // K warp 0 of this slab
     const int units = (EPI == EPI_SWIGLU ? 8 : SK_ROWS) * a.M;
     for (int i0 = me * 32; i0 < units; i0 += workers * 32) {
-      // (the warp stays whole for EPI_ARGMAX's shuffles; units is a multiple of 16, so half warps are in or out together)
+      // (the warp stays whole for the shuffles of EPI_ARGMAX and EPI_ACC; units is a multiple of 16, so half
+      // warps are in or out together)
       const bool live = i0 + lane < units;
-      if (EPI != EPI_ARGMAX && !live) continue;
+      if (EPI != EPI_ARGMAX && EPI != EPI_ACC && !live) continue;
       const int i = live ? i0 + lane : 0;
       int m, j;
       if (EPI == EPI_SWIGLU) { m = i >> 3; j = i & 7; } else { m = i >> 4; j = i & 15; }
       const int n = n0 + j;
       const size_t o = (size_t)m * a.ldo + n;
-      float old = 0.f;
-      if (EPI == EPI_ACC) old = ((float*)a.out)[o];                  // asked for before the partial sums
+      float old = 0.f, next_w = 0.f;
+      if (EPI == EPI_ACC && live) {
+        if (tl == 0 && i0 == me * 32) { old = old_first; next_w = next_w_first; }      // asked for long ago
+        else {                                                       // asked for before the partial sums
+          old = ((float*)a.out)[o];
+          if (a.nn_x) next_w = a.nn_w[n];
+        }
+      }
       const float* mine_e = mine + j * MP + m;
       constexpr int RG = 8;
       float v0 = 0.f, v1 = 0.f;
-      for (int q0 = 0; q0 < workers; q0 += RG) {
-        float p0[RG], p1[RG];
+      if (a.splits == 1) {
+        // the CTA's own K warps, four at a time (their number is a power of two)
+        for (int w0 = 0; w0 < a.warps_k; w0 += 4) {
+          float p0[4], p1[4];
 #pragma unroll
-        for (int q = 0; q < RG; ++q) {
-          const int idx = q0 + q;
-          p0[q] = 0.f; p1[q] = 0.f;
-          if (idx < workers) {
-            const int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
-            const float* pp = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine_e, sr) : mine_e;
-            p0[q] = pp[w * warp_stride];
-            if (EPI == EPI_SWIGLU) p1[q] = pp[w * warp_stride + 8 * MP];
+          for (int q = 0; q < 4; ++q) {
+            const bool on = w0 + q < a.warps_k;
+            p0[q] = on ? mine_e[(w0 + q) * warp_stride] : 0.f;
+            p1[q] = (EPI == EPI_SWIGLU && on) ? mine_e[(w0 + q) * warp_stride + 8 * MP] : 0.f;
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (w0 + q < a.warps_k) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
           }
         }
+      } else {
+        for (int q0 = 0; q0 < workers; q0 += RG) {
+          float p0[RG], p1[RG];
 #pragma unroll
-        for (int q = 0; q < RG; ++q) {
-          if (q0 + q < workers) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
+          for (int q = 0; q < RG; ++q) {
+            const int idx = q0 + q;
+            p0[q] = 0.f; p1[q] = 0.f;
+            if (idx < workers) {
+              const int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
+              const float* pp = cg::this_cluster().map_shared_rank(mine_e, sr);
+              p0[q] = pp[w * warp_stride];
+              if (EPI == EPI_SWIGLU) p1[q] = pp[w * warp_stride + 8 * MP];
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < RG; ++q) {
+            if (q0 + q < workers) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
+          }
         }
       }
+      if (a.rs_ssq) { const float sc = rs_scale[m]; v0 *= sc; if (EPI == EPI_SWIGLU) v1 *= sc; }
       if (EPI == EPI_SWIGLU) {
         if (a.bias) { v0 += a.bias[n]; v1 += a.bias[n + 8]; }
         ((bf16*)a.out)[(size_t)m * a.ldo + (n0 >> 1) + j] = __float2bfloat16_rn((v0 / (1.0f + expf(-v0))) * v1);
@@ -667,8 +753,21 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
       } else {
         if (a.bias) v0 += a.bias[n];
         if (EPI == EPI_STORE) ((bf16*)a.out)[o] = __float2bfloat16_rn(v0);
-        else if (EPI == EPI_ACC) ((float*)a.out)[o] = old + v0;
-        else ((float*)a.out)[o] = v0;
+        else if (EPI == EPI_ACC) {
+          const float v = old + v0;
+          if (live) ((float*)a.out)[o] = v;
+          if (a.nn_x) {
+            // the slab's 16 new values of row m lie in one half warp: their squares' sum is one part of the
+            // row's; the value goes on weighted, the row's factor follows in the next product
+            float sq = live ? v * v : 0.f;
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o2);
+            if (live) {
+              a.nn_x[(size_t)m * a.nn_ldx + n] = __float2bfloat16_rn(v * next_w);
+              if ((lane & 15) == 0) a.nn_ssq[(size_t)m * a.n_tiles + tile_l] = sq;
+            }
+          }
+        } else ((float*)a.out)[o] = v0;
       }
     }
   }
@@ -832,6 +931,31 @@ FELLM_API int fellm_gemm_skinny_single_shot(int M, int N, int K, int norm) {
   return plan_lean(M, N, K, norm != 0, &p) ? 1 : 0;
 }
 
+// The norm handed on between two products (SkinnyArgs: nn_* and rs_*), announced for the module's next call.
+// nn_w float32 [N], nn_x bfloat16 [M, ldx], nn_ssq float32 [M, N / 16]: the next call is an accumulate
+// (epi 1) product of up to 16 rows that the single-shot kernel takes (fellm_gemm_skinny_single_shot).
+FELLM_API int fellm_gemm_skinny_next_norm(const float* nn_w, void* nn_x, int nn_ldx, float* nn_ssq) {
+  g_handoff.nn_w = nn_w; g_handoff.nn_x = nn_x; g_handoff.nn_ldx = nn_ldx; g_handoff.nn_ssq = nn_ssq;
+  return 0;
+}
+// ssq float32 [M, parts]: the next call's x is a pre-weighted input; its sums are multiplied by the rows'
+// factors 1 / sqrt(sum(ssq[m, :]) / K + eps).  Any epilogue, a product the single-shot kernel takes without norm.
+FELLM_API int fellm_gemm_skinny_row_scale(const float* ssq, int parts, float eps) {
+  g_handoff.rs_ssq = ssq; g_handoff.rs_parts = parts; g_handoff.rs_eps = eps;
+  return 0;
+}
+static int apply_handoff(SkinnyArgs& a, const NormHandoff& h, int M, int N, int K, int epi) {
+  if (!h.nn_x && !h.rs_ssq) return 0;
+  LeanPlan p;
+  if (M > 16 || (epi != EPI_CONV && !plan_lean(M, N, K, false, &p))) return FELLM_ERR_SIZE;
+  if (h.nn_x && epi != EPI_ACC) return FELLM_ERR_ARG;
+  if (h.nn_x && (!h.nn_w || !h.nn_ssq || h.nn_ldx < N)) return FELLM_ERR_ARG;
+  if (h.rs_ssq && (h.rs_parts < 1 || h.rs_parts > 128)) return FELLM_ERR_ARG;
+  a.nn_w = h.nn_w; a.nn_x = (bf16*)h.nn_x; a.nn_ssq = h.nn_ssq; a.nn_ldx = h.nn_ldx;
+  a.rs_ssq = h.rs_ssq; a.rs_parts = h.rs_parts; a.rs_eps = h.rs_eps;
+  return 0;
+}
+
 template <int EPI>
 static int dispatch_mt(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
   if (a.M <= 8) return launch<1, EPI>(a, ctas_y, s);
@@ -846,6 +970,7 @@ static int dispatch_mt(const SkinnyArgs& a, int ctas_y, cudaStream_t s) {
 FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* norm_w, float eps, const void* W,
                                 const float* bias, void* out, int epi, int M, int N, int K, int lda, int ldw,
                                 int ldo, cudaStream_t stream) {
+  const NormHandoff handoff = take_handoff();     // cleared whatever this call returns
   if (M <= 0 || N <= 0) return 0;
   if ((!x && !xf) || !W || !out || K <= 0) return FELLM_ERR_ARG;
   if (xf && !norm_w) return FELLM_ERR_ARG;
@@ -897,7 +1022,8 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
     if (!found) splits = 16;
     if (splits > 8) return FELLM_ERR_SIZE;
   }
-  SkinnyArgs a;
+  SkinnyArgs a = {};
+  if (int bad = apply_handoff(a, handoff, M, N, K, epi)) return bad;
   { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = out;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo; a.splits = splits;
@@ -922,6 +1048,7 @@ FELLM_API int fellm_gemm_skinny(const void* x, const float* xf, const float* nor
       default: return FELLM_ERR_ARG;
     }
   }
+  if (a.nn_x || a.rs_ssq) return FELLM_ERR_SIZE;           // only the single-shot kernel hands a norm on
   switch (epi) {
     case EPI_STORE: return dispatch_mt<EPI_STORE>(a, ctas_y, stream);
     case EPI_ACC: return dispatch_mt<EPI_ACC>(a, ctas_y, stream);
@@ -959,12 +1086,14 @@ FELLM_API long long fellm_gemm_skinny_argmax_scratch(int M, int N, int K, int no
 FELLM_API int fellm_gemm_skinny_argmax(const void* x, const float* xf, const float* norm_w, float eps, const void* W,
                                        const float* bias, unsigned long long* keys, int* out_tokens, int M, int N, int K,
                                        int lda, int ldw, cudaStream_t stream) {
+  const NormHandoff handoff = take_handoff();     // cleared whatever this call returns
   if (M <= 0 || N <= 0) return 0;
   if ((!x && !xf) || !W || !keys || !out_tokens || K <= 0 || (xf && !norm_w)) return FELLM_ERR_ARG;
   if (M > 16 || (K % 8) || (ldw % 8) || (x && (lda % 8)) || (xf && (lda % 4))) return FELLM_ERR_SIZE;
   LeanPlan lp;
   if (!plan_lean(M, N, K, xf != nullptr, &lp)) return FELLM_ERR_SIZE;
-  SkinnyArgs a;
+  SkinnyArgs a = {};
+  if (int bad = apply_handoff(a, handoff, M, N, K, EPI_ARGMAX)) return bad;
   { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = nullptr;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = 0;
@@ -996,10 +1125,12 @@ FELLM_API int fellm_gemm_skinny_conv(const void* x, const float* xf, const float
                                      const float* bias, const float* conv_w, const float* conv_bias, float* state,
                                      long long slot_stride, const int* row_slot, int taps, void* y, int M, int N, int K,
                                      int lda, int ldw, int ldo, cudaStream_t stream) {
+  const NormHandoff handoff = take_handoff();     // cleared whatever this call returns
   if (M <= 0) return 0;
   if ((!x && !xf) || !W || !y || !conv_w || !state || !row_slot || (xf && !norm_w)) return FELLM_ERR_ARG;
   if (!conv_shape_ok(M, N, K, taps) || (ldw % 8) || (x && (lda % 8)) || (xf && (lda % 4)) || (xf && K > 4096)) return FELLM_ERR_SIZE;
-  SkinnyArgs a;
+  SkinnyArgs a = {};
+  if (int bad = apply_handoff(a, handoff, M, N, K, EPI_CONV)) return bad;
   { const NextWeights nw = take_next_weights(); a.next_w = nw.ptr; a.next_bytes = nw.bytes; }
   a.x = (const bf16*)x; a.xf = xf; a.norm_w = norm_w; a.eps = eps; a.W = (const bf16*)W; a.bias = bias; a.out = y;
   a.M = M; a.N = N; a.K = K; a.lda = lda; a.ldw = ldw; a.ldo = ldo;

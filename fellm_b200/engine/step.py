@@ -13,6 +13,7 @@ copies it once; the logits come back for the wanted rows only.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -349,8 +350,17 @@ class Stepper:
                 return logits
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph, pool=self.graph_pool):
-                logits = self.model.forward(ctx, views, greedy_tokens)
+            # The garbage collector must not run inside a capture: if it finds an engine that was dropped
+            # earlier, that engine's graphs are destroyed then and there, which the capturing stream does not
+            # permit (the capture is invalidated and the next launch fails).  It waits until the capture is over.
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, pool=self.graph_pool):
+                    logits = self.model.forward(ctx, views, greedy_tokens)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             if self.graph_pool is None:
                 self.graph_pool = graph.pool()
             entry = (graph, logits, ops.launch_count() - before)

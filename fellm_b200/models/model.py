@@ -12,6 +12,7 @@ from typing import Dict, List
 
 import torch
 
+from .. import ops
 from ..config.errors import ConfigError
 from ..parts.base import ParamDecl, build_part
 from ..parts.linear import LazyNorm
@@ -32,7 +33,10 @@ def register_arrangement(name: str):
     """Decorator: `fn(block, x, ctx, cache, act_dtype, reads_only)` wires a block's parts for
     LayerSpec.arrangement == name.  x is the float32 residual stream [T, d] and is updated in
     place (mixers and feed-forwards ADD into the tensor they are given as `out`); `block` has
-    .norm1, .mixer, .norm2, .ffn (None where the spec names none)."""
+    .norm1, .mixer, .norm2, .ffn (None where the spec names none) and, during the call,
+    .norm_after: the norm that reads x after this block (the next block's first, or the final one;
+    None where that is not known).  An arrangement may tell a norm that it comes next
+    (`norm.expect(x)`) right before the part whose last act is to add into x."""
     def deco(fn):
         ARRANGEMENTS[name] = fn
         return fn
@@ -47,9 +51,16 @@ def normed(x, norm, consumer, act_dtype):
 @register_arrangement("prenorm")
 def _prenorm(block, x, ctx, cache, act_dtype, reads_only):
     """x += mixer(norm1(x)); x += ffn(norm2(x))   (crates/fellm-model/src/graph.rs:1650-1777)."""
-    block.mixer.forward(_normed(x, block.norm1, block.mixer, act_dtype), ctx, cache, x, reads_only=reads_only)
+    h = _normed(x, block.norm1, block.mixer, act_dtype)
+    after_mixer = block.norm2 if block.ffn is not None else block.norm_after
+    if after_mixer is not None:
+        after_mixer.expect(x)
+    block.mixer.forward(h, ctx, cache, x, reads_only=reads_only)
     if block.ffn is not None:
-        block.ffn.forward(_normed(x, block.norm2, block.ffn, act_dtype), ctx, x)
+        h = _normed(x, block.norm2, block.ffn, act_dtype)
+        if block.norm_after is not None:
+            block.norm_after.expect(x)
+        block.ffn.forward(h, ctx, x)
 
 
 class Block:
@@ -65,12 +76,14 @@ class Block:
         self.mixer = build_part("mixer", spec.mixer, dtype)
         self.norm2 = build_part("norm", spec.norm2, dtype) if spec.norm2 is not None else None
         self.ffn = build_part("feed_forward", spec.ffn, dtype) if spec.ffn is not None else None
+        self.norm_after = None
 
     def parts(self):
         return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
-    def forward(self, x, ctx, cache, act_dtype, reads_only=False):
+    def forward(self, x, ctx, cache, act_dtype, reads_only=False, norm_after=None):
         """x: float32 residual stream [T, d], updated in place."""
+        self.norm_after = norm_after
         self.arrange(self, x, ctx, cache, act_dtype, reads_only)
         return x
 
@@ -151,11 +164,16 @@ class Model:
         logits [len(ctx.logit_rows), vocab] (an empty tensor when none are wanted).
         greedy_tokens (int32, device): the caller only wants the greedy token of every wanted row; where the
         head can give them without the logits it writes greedy_tokens[:wanted] and None is returned."""
+        ops.forget_norm_handoff()
         x = self.embedding.forward(ctx.tokens, ctx.status)
         for n, run in enumerate(self.schedule):
             src = n if run.cache_of is None else run.cache_of
+            if n + 1 < len(self.schedule):
+                norm_after = self.blocks[self.schedule[n + 1].layer].norm1
+            else:
+                norm_after = self.final_norm if (ctx.logits_all and ctx.n_logit_rows) else None
             self.blocks[run.layer].forward(x, ctx, caches[src], self.act_dtype,
-                                           reads_only=run.cache_of is not None)
+                                           reads_only=run.cache_of is not None, norm_after=norm_after)
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         if ctx.logits_all and getattr(self.head, "takes_lazy_norm", False):

@@ -152,6 +152,8 @@ def gemm_simt(a, w, bias=None, out=None, out_dtype=None, accumulate=False):
         assert bias.dtype == torch.float32 and bias.numel() == N
     if _is_bf16(out) and not _is_bf16(a):
         raise KernelError("gemm_simt: float32 activations do not round down to a bfloat16 result")
+    if accumulate:
+        residual_written(out)
     f = _fn("gemm_simt", "fellm_gemm_simt",
             [_c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_p])
@@ -214,10 +216,11 @@ def conv_product_takes(M: int, N: int, K: int, taps: int) -> bool:
     return hit
 
 
-def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, norm=None, out=None):
+def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, norm=None, out=None, row_scale=None):
     """A decode step's ShortConv input product and gated convolution in one launch: every row of x
     is one token of its own request (row_slot[i] = its state slot).  x bfloat16 [M, K], or with
-    norm=(weight, eps) the float32 residual rows to be RMS-normed on the way in; w_blocked [3d, K]
+    norm=(weight, eps) the float32 residual rows to be RMS-normed on the way in, or with
+    row_scale=(ssq, parts, eps) the pre-weighted input of a handed-on norm; w_blocked [3d, K]
     and bias in block_bcx_rows order.  Returns y bfloat16 [M, d]; the states move on by one token."""
     _dev(x, w_blocked, bias, conv_w, conv_bias, state, row_slot)
     M, K = x.shape
@@ -231,6 +234,9 @@ def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, no
         out = torch.empty((M, d), dtype=torch.bfloat16, device=x.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     _announce_next("gemm_skinny", w_blocked, M)
+    if row_scale is not None:
+        assert norm is None
+        _announce_row_scale(row_scale, M, N, K, own_plan=True)
     f = _fn("gemm_skinny", "fellm_gemm_skinny_conv",
             [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_int, _c_p])
@@ -412,12 +418,118 @@ def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
     return hit
 
 
-def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False, norm=None):
+# ---- an RMSNorm handed on from the product that writes the residual stream to the product that reads it
+#
+# In a decode step of up to 16 rows every product is a few microseconds long, and a product that first has
+# to norm float32 rows (read them, sum the squares, scale, round) spends a third of that before its first
+# MMA.  So the product that ADDS into the residual stream can do the norm's work for its successor: beside
+# x += ..., it leaves xg = bfloat16(x * g) (g: the next norm's weights) and the sums of x^2 of every 16
+# columns.  The successor stages xg like any bfloat16 input and multiplies its finished sums by the rows'
+# factors 1 / sqrt(sum x^2 / K + eps): RMSNorm(x) W^T with the factor taken out of the product.
+#
+# Who writes and who reads is settled by the caller: expect_norm(x, g) says "the next product that adds
+# into x is followed by an RMSNorm with weights g"; norm_handoff(x, g) gives the reader what was left, if
+# it is still good (same tensor, same weights, nothing written to x since).
+NORM_HANDOFF = os.environ.get("FELLM_B200_NORM_HANDOFF", "1") != "0"
+HANDOFF_MAX_ROWS = 16
+_handoff_bufs = {}          # device -> (xg bfloat16 [16 * width], ssq float32 [16 * width / 16], width)
+_expected_norm = None       # (data_ptr of x, norm weights)
+_handoff = None             # NormHandoff: what the last such product left
+
+
+class NormHandoff:
+    __slots__ = ("x_ptr", "version", "rows", "norm_ptr", "xg", "ssq", "parts")
+
+
+def reserve_norm_handoff(device, width: int):
+    """Room for handed-on norms of rows up to `width` wide (called before the first step, so that nothing
+    is allocated under a captured graph).  Without it no norm is handed on."""
+    device = torch.device(device)
+    if device.type != "cuda" or width % 16 or width > 2048:        # the kernel takes up to 128 parts of 16 columns
+        return
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    have = _handoff_bufs.get(device)
+    if have is None or have[2] < width:
+        _handoff_bufs[device] = (torch.zeros(HANDOFF_MAX_ROWS * width, dtype=torch.bfloat16, device=device),
+                                 torch.zeros(HANDOFF_MAX_ROWS * width // 16, dtype=torch.float32, device=device), width)
+        forget_norm_handoff()
+
+
+def forget_norm_handoff():
+    global _expected_norm, _handoff
+    _expected_norm = _handoff = None
+
+
+def expect_norm(x, norm_w):
+    """The next product that adds into x (float32 [rows, d]) is followed by RMSNorm with norm_w [d]."""
+    global _expected_norm
+    _expected_norm = None
+    if (NORM_HANDOFF and x.is_cuda and x.dtype == torch.float32 and x.shape[0] <= HANDOFF_MAX_ROWS
+            and norm_w.dtype == torch.float32 and norm_w.numel() == x.shape[1] and norm_w.is_contiguous()):
+        bufs = _handoff_bufs.get(x.device)
+        if bufs is not None and bufs[2] >= x.shape[1]:
+            _expected_norm = (x.data_ptr(), norm_w)
+
+
+def residual_written(out):
+    """Every kernel call that adds into a float32 tensor says so: what was handed on for it is stale.
+    Returns the norm expected after this write (expect_norm), if one was announced for this tensor."""
+    global _handoff, _expected_norm
+    if _handoff is not None and _handoff.x_ptr == out.data_ptr():
+        _handoff = None
+    exp, _expected_norm = _expected_norm, None          # an expectation is for the very next write
+    return exp if (exp is not None and exp[0] == out.data_ptr()) else None
+
+
+def norm_handoff(x, norm_w):
+    """What the last product that added into x left for RMSNorm(x, norm_w), or None."""
+    h = _handoff
+    if (h is None or h.x_ptr != x.data_ptr() or h.version != x._version or h.rows != x.shape[0]
+            or h.norm_ptr != norm_w.data_ptr()):
+        return None
+    return h
+
+
+def row_scale_takes(M: int, N: int, K: int) -> bool:
+    """Whether a product of these sizes can take a handed-on norm's input (the single-shot kernel runs it)."""
+    return M <= HANDOFF_MAX_ROWS and K % 8 == 0 and _single_shot(M, N, K, False)
+
+
+def _announce_handoff(exp, out, M: int, N: int, K: int, norm_fused: bool):
+    """Before an accumulate product of the weight-streaming kernel: if its successor's norm is known (exp)
+    and the kernel can do it, tell the kernel and note what it leaves."""
+    global _handoff
+    if exp is None or M > HANDOFF_MAX_ROWS or N % 16 or not out.is_contiguous():
+        return
+    if norm_fused or not _single_shot(M, N, K, False):
+        return
+    xg, ssq, width = _handoff_bufs[out.device]
+    _handoff = None                      # the buffers are about to be rewritten
+    f = _fn("gemm_skinny", "fellm_gemm_skinny_next_norm", [_c_p, _c_p, _c_int, _c_p])
+    f(_p(exp[1]), _p(xg), N, _p(ssq))
+    h = NormHandoff()
+    h.x_ptr, h.version, h.rows, h.norm_ptr = out.data_ptr(), out._version, M, exp[1].data_ptr()
+    h.xg, h.ssq, h.parts = xg[:M * N].view(M, N), ssq, N // 16
+    return h
+
+
+def _announce_row_scale(row_scale, M: int, N: int, K: int, own_plan: bool = False):
+    ssq, parts, eps = row_scale
+    if not own_plan and not row_scale_takes(M, N, K):
+        raise KernelError(f"a product of {M} x {N} x {K} does not take a handed-on norm")
+    assert ssq.dtype == torch.float32 and ssq.numel() >= M * parts
+    _fn("gemm_skinny", "fellm_gemm_skinny_row_scale", [_c_p, _c_int, _c_f])(_p(ssq), int(parts), float(eps))
+
+
+def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False, norm=None, row_scale=None):
     """out = x[M,K] @ w[N,K]^T (+bias) on tensor cores, bfloat16 in, float32 sums.
     accumulate: out (float32 [M,N]) += ; swiglu: w's rows are interleaved in blocks of 8 gate / 8 up
     and out is bfloat16 [M, N/2] = silu(gate)*up; out_dtype float32: float32 store.
     norm=(weight float32 [K], eps): x is the float32 residual stream and is RMS-normed on its way
-    into the product (see norm_fusable)."""
+    into the product (see norm_fusable).
+    row_scale=(ssq, parts, eps): x is the pre-weighted input of a handed-on norm (norm_handoff)."""
+    global _handoff
     _dev(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0]
@@ -458,14 +570,20 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     # product (all of W requested at once by every SM), else up to 32 rows except for very wide products
     # (measured at 64 rows: 14 us against 26 us for [1024, 4608], 8 against 9-11 for K = 1024, but 13
     # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
-    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N:
+    expected = residual_written(out) if accumulate else None
+    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N and row_scale is None:
         # a decode step of 17..64 rows: tcgen05 with the weights as the MMA's 128 rows
         _announce_next("gemm_umma", w, M)
         return gemm_umma_swap(x, w, bias, out=out, epi=epi)
     skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
                           or (M <= SKINNY_MAX_ROWS and N < 8192))
+    if row_scale is not None and not skinny:
+        raise KernelError(f"a product of {M} x {N} x {K} does not take a handed-on norm")
     if skinny:
         _announce_next("gemm_skinny", w, M)
+        if row_scale is not None:
+            _announce_row_scale(row_scale, M, N, K)
+        left = _announce_handoff(expected, out, M, N, K, norm is not None)
         f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
         if norm is not None:
             code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0),
@@ -474,6 +592,8 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
             code = f(_p(x), None, None, 0.0, _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0),
                      out.stride(0), _stream())
         _check(code, "gemm_skinny")
+        if left is not None:
+            _handoff = left
     elif umma_ok:
         f = _fn("gemm_umma", "fellm_gemm_umma", _GEMM_ARGS[:-1] + [_c_p, _c_p])
         _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0), w.stride(0), out.stride(0),
@@ -501,11 +621,11 @@ def head_argmax_scratch(M: int, N: int, K: int, norm: bool) -> int:
     return hit
 
 
-def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None):
+def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None, row_scale=None):
     """out_tokens[m] = argmax_n (x W^T + bias)[m, n], ties to the lower n, without storing the [M, N]
     logits: the vocabulary head of a greedy decode step of up to 16 rows.  x bfloat16 [M, K], or with
-    norm=(weight, eps) the float32 residual rows; keys: int64 scratch of head_argmax_scratch() entries;
-    out_tokens int32 [>= M]."""
+    norm=(weight, eps) the float32 residual rows, or with row_scale=(ssq, parts, eps) the pre-weighted input
+    of a handed-on norm; keys: int64 scratch of head_argmax_scratch() entries; out_tokens int32 [>= M]."""
     _dev(x, w, bias, keys, out_tokens)
     M, K = x.shape
     N = w.shape[0]
@@ -514,6 +634,9 @@ def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None):
         raise KernelError(f"gemm_bf16_argmax does not take a product of {M} x {N} x {K}")
     assert keys.dtype == torch.int64 and keys.numel() >= need and out_tokens.dtype == torch.int32 and out_tokens.numel() >= M
     _announce_next("gemm_skinny", w, M)
+    if row_scale is not None:
+        assert norm is None
+        _announce_row_scale(row_scale, M, N, K)
     f = _fn("gemm_skinny", "fellm_gemm_skinny_argmax",
             [_c_p, _c_p, _c_p, _c_f, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p])
     if norm is not None:
@@ -534,6 +657,8 @@ def gemm_umma_swap(x, w, bias=None, *, out, epi: int):
     """The tcgen05 product for up to 64 rows (weights as the MMA's rows, K split over a cluster),
     callable by itself.  epi: 0 store bfloat16, 1 add into float32, 2 SiLU(gate)*up, 3 store float32."""
     M, K = x.shape
+    if epi == _EPI_ACC:
+        residual_written(out)
     f = _fn("gemm_umma", "fellm_gemm_umma_swap", _GEMM_ARGS[:-1] + [_c_p, _c_p])
     _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, w.shape[0], K, x.stride(0), w.stride(0), out.stride(0),
              _p(umma_status(x.device)), _stream()), "gemm_umma_swap")
@@ -543,6 +668,8 @@ def gemm_umma_swap(x, w, bias=None, *, out, epi: int):
 def gemm_tiled(x, w, bias=None, *, out, epi: int):
     """The mma.sync product, callable by itself (tests compare the tcgen05 product with it)."""
     M, K = x.shape
+    if epi == _EPI_ACC:
+        residual_written(out)
     f = _fn("gemm_tiled", "fellm_gemm_tiled", _GEMM_ARGS)
     _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, w.shape[0], K, x.stride(0), w.stride(0), out.stride(0), _stream()),
            "gemm_tiled")

@@ -96,6 +96,11 @@ class Norm(Part):
         out_dtype; `rows` (int32, device) picks rows of x."""
         raise NotImplementedError
 
+    def expect(self, x: torch.Tensor):
+        """A block says, before a part adds into the residual rows x: this norm reads x next.  A norm
+        whose work the adding product can do on the way (RMSNorm in a decode step) arranges that here;
+        nothing has to happen."""
+
 
 class PositionEncoding(Part):
     """What an attention mixer needs to place queries and keys: for rotary encodings the

@@ -48,8 +48,14 @@ class LinearHead(Head):
         keys = getattr(self, "_argmax_keys", None)
         if keys is None or w.dtype != torch.bfloat16 or not ops.FUSED_ARGMAX:
             return False
-        fused = isinstance(xf, LazyNorm) and xf.fusable_with(w)
         rows = xf.shape[0]
+        h = xf.handed_on() if isinstance(xf, LazyNorm) else None
+        if h is not None and ops.row_scale_takes(rows, w.shape[0], w.shape[1]):
+            need = ops.head_argmax_scratch(rows, w.shape[0], w.shape[1], False)
+            if need and need <= keys.numel():
+                ops.gemm_bf16_argmax(h.xg, w, None, keys, out_tokens, row_scale=(h.ssq, h.parts, xf.norm.eps))
+                return True
+        fused = isinstance(xf, LazyNorm) and xf.fusable_with(w)
         need = ops.head_argmax_scratch(rows, w.shape[0], w.shape[1], fused)
         if not need or need > keys.numel():
             return False

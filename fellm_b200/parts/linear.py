@@ -7,7 +7,9 @@ with the residual fused as a third input on the CPU side (crates/backend-cpu/src
 
 A block hands a part that says `takes_lazy_norm = True` its input as a LazyNorm: the float32
 residual rows and the norm that is to be applied.  linear() then runs the norm inside the product
-where the kernel can (decode-sized batches), and as a kernel of its own otherwise.
+where the kernel can (decode-sized batches), and as a kernel of its own otherwise.  Where the product
+that last added into those rows has already left them weighted for this norm (ops.expect_norm /
+ops.norm_handoff), the product reads that instead and only scales its sums.
 """
 from __future__ import annotations
 
@@ -32,6 +34,12 @@ class LazyNorm:
             self._done = self.norm.forward(self.x, self.act_dtype)
         return self._done
 
+    def handed_on(self):
+        """What the product that last added into the rows left for this norm (ops.norm_handoff), or None."""
+        if self._done is not None or getattr(self.norm, "kind", None) != "rmsnorm":
+            return None
+        return ops.norm_handoff(self.x, self.norm.w["weight"])
+
     def fusable_with(self, w) -> bool:
         rms = getattr(self.norm, "kind", None) == "rmsnorm"
         return rms and self._done is None and ops.norm_fusable(self.x, w, self.norm.w["weight"])
@@ -42,6 +50,10 @@ def linear(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swigl
     float32 `out` (the residual stream) instead of storing; swiglu=True: w is the interleaved
     gate/up matrix and the result is SiLU(gate)*up."""
     if isinstance(x, LazyNorm):
+        h = x.handed_on()
+        if h is not None and ops.fast_gemm_takes(h.xg, w) and ops.row_scale_takes(h.rows, w.shape[0], w.shape[1]):
+            return ops.gemm_bf16(h.xg, w, bias, out=out, out_dtype=out_dtype, accumulate=accumulate, swiglu=swiglu,
+                                 row_scale=(h.ssq, h.parts, x.norm.eps))
         if x.fusable_with(w):
             return ops.gemm_bf16(x.x, w, bias, out=out, out_dtype=out_dtype, accumulate=accumulate, swiglu=swiglu,
                                  norm=(x.norm.w["weight"], x.norm.eps))

@@ -59,12 +59,16 @@ class ShortConv(Mixer):
         w_in, b_in = self.w["in_proj.weight"], self.w.get("in_proj.bias")
         if self.blocked and FUSE_DECODE_CONV and ctx.all_single and ops.conv_product_takes(ctx.n_rows, 3 * self.size, self.size, self.taps):
             # a decode step: product and convolution in one launch
-            if isinstance(xn, LazyNorm) and xn.fusable_with(w_in):
+            h = xn.handed_on() if isinstance(xn, LazyNorm) else None
+            scale = None
+            if h is not None:
+                x, norm, scale = h.xg, None, (h.ssq, h.parts, xn.norm.eps)
+            elif isinstance(xn, LazyNorm) and xn.fusable_with(w_in):
                 x, norm = xn.x, (xn.norm.w["weight"], xn.norm.eps)
             else:
                 x, norm = (xn.tensor() if isinstance(xn, LazyNorm) else xn), None
             y = ops.gemm_bf16_conv(x, w_in, b_in, self.w["conv.weight"], self.w.get("conv.bias"), cache.states,
-                                   cache.item_slot, norm=norm)
+                                   cache.item_slot, norm=norm, row_scale=scale)
         else:
             bcx = linear(xn, w_in, b_in)
             y = ops.shortconv(bcx, self.w["conv.weight"], self.w.get("conv.bias"), cache.states, cache.item_slot,

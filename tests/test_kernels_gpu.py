@@ -733,3 +733,102 @@ def test_head_argmax_without_logits(M, N, K, use_norm):
     assert int(toks[M]) == -5                                      # nothing written past the rows
     if not use_norm or (M == 1 and K == 1024):
         assert int(want[0]) == 11 and float(logits[0, 11]) == float(logits[0, N - 7])
+
+
+@pytest.mark.parametrize("M,N,K,d_next", [(8, 1024, 1024, 3072), (1, 1024, 4608, 9216), (16, 2048, 2048, 6144), (5, 1024, 1024, 65536),
+                                           (13, 512, 1280, 512), (8, 2048, 8192, 2048)])
+def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
+    """The product that adds into the residual rows leaves them weighted for the next RMSNorm, with the sums of
+    squares in parts; the next product scales its sums by the rows' factors.  Against the plain norm and product."""
+    g = torch.Generator().manual_seed(M * N + K)
+    res = (torch.randn(M, N, generator=g) * 3).to(DEV)
+    res[M // 2, 7] = 90.0                                          # one value that dominates its row's sum of squares
+    y = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w_out = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    nw = (torch.rand(N, generator=g) + 0.5).to(DEV)
+    ops.forget_norm_handoff()
+    ops.reserve_norm_handoff(DEV, 2048)
+    plain_sum = res.clone()
+    ops.gemm_bf16(y, w_out, out=plain_sum, accumulate=True)        # nothing announced: nothing handed on
+    assert ops.norm_handoff(plain_sum, nw) is None
+    ops.expect_norm(res, nw)
+    ops.gemm_bf16(y, w_out, out=res, accumulate=True)
+    assert torch.equal(res, plain_sum)
+    h = ops.norm_handoff(res, nw)
+    assert h is not None and h.rows == M and h.parts == N // 16
+    assert ops.norm_handoff(res, nw.clone()) is None and ops.norm_handoff(res.clone(), nw) is None
+    assert torch.equal(h.xg, (res * nw).bfloat16())
+    ssq = h.ssq[:M * h.parts].view(M, h.parts)
+    assert torch.allclose(ssq, (res * res).view(M, h.parts, 16).sum(-1), rtol=1e-5)
+    # the consumers: every epilogue, against RMSNorm then product in float64
+    eps = 1e-5
+    xn = P.rmsnorm(res.cpu(), nw.cpu(), eps)
+    n2 = d_next
+    w = (torch.randn(n2, N, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(n2, generator=g)
+    want = xn.double() @ w.double().T + bias.double()
+    scale = (h.ssq, h.parts, eps)
+    atol = 2e-2 * 0.05 * math.sqrt(N) / 8 * 3
+    assert ops.row_scale_takes(M, n2, N)
+    got = ops.gemm_bf16(h.xg, w.to(DEV), bias.to(DEV), out_dtype=torch.float32, row_scale=scale)
+    assert torch.allclose(got.double().cpu(), want, rtol=4e-3, atol=atol)
+    # the norm inside the product rounds x*r*g, this way rounds x*g: each lies within the tolerance of the
+    # float64 result, so they lie within twice that of each other
+    fused = ops.gemm_bf16(res, w.to(DEV), bias.to(DEV), out_dtype=torch.float32, norm=(nw, eps))
+    assert torch.allclose(fused.double().cpu(), want, rtol=4e-3, atol=atol)
+    assert torch.allclose(got, fused, rtol=8e-3, atol=2 * atol)
+    got_b = ops.gemm_bf16(h.xg, w.to(DEV), bias.to(DEV), row_scale=scale)
+    assert torch.equal(got_b, got.bfloat16())
+    if n2 <= 16384:
+        wi = ops.interleave_gate_up(w[:n2 // 2].to(DEV), w[n2 // 2:].to(DEV))
+        got_s = ops.gemm_bf16(h.xg, wi, swiglu=True, row_scale=scale)
+        gu = want - bias.double()
+        gate, up = gu[:, :n2 // 2], gu[:, n2 // 2:]
+        ref_s = torch.nn.functional.silu(gate) * up
+        # gate and up are each within (atol + rtol |.|) of the float64 sums; SiLU's slope is at most 1.1; the
+        # product is rounded to bfloat16
+        bound = ((atol + 4e-3 * gate.abs()) * 1.1 * up.abs() + (atol + 4e-3 * up.abs()) * torch.nn.functional.silu(gate).abs()
+                 + ref_s.abs() * 2.0 ** -8 + 1e-6)
+        assert bool(((got_s.double().cpu() - ref_s).abs() <= bound).all())
+    need = ops.head_argmax_scratch(M, n2, N, False)
+    assert need
+    keys = torch.zeros(need, dtype=torch.int64, device=DEV)
+    toks = torch.full((M,), -1, dtype=torch.int32, device=DEV)
+    ops.gemm_bf16_argmax(h.xg, w.to(DEV), bias.to(DEV), keys, toks, row_scale=scale)
+    assert torch.equal(toks.long(), got.argmax(-1))
+    # a write into the rows ends what was handed on; so does a torch-side update
+    assert ops.norm_handoff(res, nw) is not None
+    res += 1
+    assert ops.norm_handoff(res, nw) is None
+    ops.expect_norm(res, nw)
+    ops.gemm_bf16(y, w_out, out=res, accumulate=True)
+    assert ops.norm_handoff(res, nw) is not None
+    ops.gemm_bf16(y, w_out, out=res, accumulate=True)              # a second product, nothing announced for it
+    assert ops.norm_handoff(res, nw) is None
+    ops.forget_norm_handoff()
+
+
+def test_handed_on_norm_into_the_convolution_product():
+    M, d, lc = 8, 1024, 3
+    g = torch.Generator().manual_seed(5)
+    res = (torch.randn(M, d, generator=g) * 2).to(DEV)
+    y = torch.randn(M, d, generator=g).bfloat16().to(DEV)
+    w_out = (torch.randn(d, d, generator=g) * 0.05).bfloat16().to(DEV)
+    nw = (torch.rand(d, generator=g) + 0.5).to(DEV)
+    w_in = ops.block_bcx_rows((torch.randn(3 * d, d, generator=g) * 0.05).bfloat16().to(DEV))
+    conv_w = torch.randn(d, lc, generator=g).to(DEV)
+    state = torch.randn(12, 1, lc - 1, d, generator=g).to(DEV)
+    slots = i32([3, 0, 11, 5, 6, 7, 1, 9])
+    ops.forget_norm_handoff()
+    ops.reserve_norm_handoff(DEV, 2048)
+    ops.expect_norm(res, nw)
+    ops.gemm_bf16(y, w_out, out=res, accumulate=True)
+    h = ops.norm_handoff(res, nw)
+    st_a, st_b = state.clone(), state.clone()
+    got = ops.gemm_bf16_conv(h.xg, w_in, None, conv_w, None, st_a[:, 0], slots, row_scale=(h.ssq, h.parts, 1e-5))
+    bcx = ops.gemm_bf16(h.xg, w_in, row_scale=(h.ssq, h.parts, 1e-5))
+    ref = ops.shortconv(bcx, conv_w, None, st_b[:, 0], slots, i32(list(range(M + 1))), i32(list(range(M))), M, True, blocked=True)
+    assert torch.equal(got, ref) and torch.equal(st_a, st_b)
+    fused = ops.gemm_bf16(res, w_in, norm=(nw, 1e-5))
+    assert torch.allclose(bcx.float(), fused.float(), rtol=2e-2, atol=2e-2)
+    ops.forget_norm_handoff()

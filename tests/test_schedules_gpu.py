@@ -189,3 +189,31 @@ def test_greedy_steps_that_skip_the_logits_give_the_plain_tokens(graphs):
             assert tok == got[i][t], (i, t)
             lg = eng2.step([StepItem(i, [tok], [0])])
     eng.check_status()
+
+
+def test_decode_steps_hand_the_norms_on(monkeypatch):
+    """Width 1024, decode steps of 3 rows: every product that adds into the residual rows leaves them weighted
+    for the norm that reads them next (all but the first norm of a step, which follows the embedding), and the
+    logits stay those of the plain implementation; with the hand-over switched off, too."""
+    from fellm_b200 import ops
+    taken = []
+    real = ops._announce_row_scale
+    monkeypatch.setattr(ops, "_announce_row_scale", lambda *a, **k: (taken.append(a[1:4]), real(*a, **k))[1])
+    prompts = [tiny.tokens("C", n + 6, 810 + i) for i, n in enumerate((7, 64, 30))]
+    lens = (7, 64, 30)
+    logits = {}
+    for on in (True, False):
+        monkeypatch.setattr(ops, "NORM_HANDOFF", on)
+        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False)
+        for i, n in enumerate(lens):
+            eng.add_request(i)
+            eng.step([StepItem(i, prompts[i][:n], [])])
+        taken.clear()
+        rows = [eng.step([StepItem(i, [prompts[i][lens[i] + t]], [0]) for i in range(3)]).clone() for t in range(6)]
+        eng.check_status()
+        logits[on] = torch.stack(rows)
+        n_layers = len(tiny.CONFIGS["C"][0]["layer_types"])
+        assert len(taken) == (6 * 2 * n_layers if on else 0), (on, len(taken))
+        for i, n in enumerate(lens):
+            want = tiny.plain_logits("C", n + 6, 810 + i)[n:]
+            check(f"hand-over {on}: request {i}", logits[on][:, i], want, "bfloat16")
