@@ -231,7 +231,9 @@ def run_e2e(engine, batch, steps, warmup, rng):
     from fellm_b200.engine import GenParams
     sched = engine.scheduler()
     vocab = engine.spec.vocab_size
-    ahead = max(untimed_steps(steps, warmup) - 2, warmup)        # the timed steps end just below the middle of the growth
+    # the timed steps end just below the middle of the growth: the first token comes with the prompt's last
+    # portion, the scheduler launches one step ahead, and a step's graph goes by the length AFTER the step
+    ahead = max(untimed_steps(steps, warmup) - 6, warmup)
     for _ in range(batch):
         sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(ahead + steps + 8))
     while any(r.prefilling for r in list(sched.running) + list(sched.waiting)) or sched.waiting:

@@ -595,7 +595,28 @@ struct SwapArgs {
   const float* bias; void* out; int* status;
   int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..64)
   const void* next_w; long long next_bytes;     // the next product's weights, asked into L2 (or null)
+  // EPI_ACC as the producer of the next RMSNorm's input (nn_x null: not asked for; N a multiple of 128): beside
+  // out += ..., nn_x[t, n] = bfloat16(out[t, n] * nn_w[n]) and nn_ssq[t * (N / 128) + tile] = the sum of
+  // out[t, n]^2 over the tile's 128 columns
+  const float* nn_w; bf16* nn_x; float* nn_ssq; int nn_ldx;
+  // ... and its consumer (rs_ssq null: none): x is such an nn_x; the finished sums of token t are multiplied by
+  // 1 / sqrt(sum_p rs_ssq[t * rs_parts + p] / K + rs_eps) before the bias: RMSNorm(x) W^T with the row's
+  // factor taken out of the product (crates/backend-cpu/src/kernels/norm.rs:6-39 has the norm)
+  const float* rs_ssq; int rs_parts; float rs_eps;
 };
+
+// What the next call of fellm_gemm_umma_swap is to hand on or to take over (see SwapArgs); taken and cleared
+// by every call.
+struct SwapHandoff { const float* nn_w; void* nn_x; float* nn_ssq; int nn_ldx; const float* rs_ssq; int rs_parts; float rs_eps; };
+static SwapHandoff g_swap_handoff = {nullptr, nullptr, nullptr, 0, nullptr, 0, 0.f};
+FELLM_API int fellm_gemm_umma_next_norm(const float* nn_w, void* nn_x, int nn_ldx, float* nn_ssq) {
+  g_swap_handoff.nn_w = nn_w; g_swap_handoff.nn_x = nn_x; g_swap_handoff.nn_ldx = nn_ldx; g_swap_handoff.nn_ssq = nn_ssq;
+  return 0;
+}
+FELLM_API int fellm_gemm_umma_row_scale(const float* ssq, int parts, float eps) {
+  g_swap_handoff.rs_ssq = ssq; g_swap_handoff.rs_parts = parts; g_swap_handoff.rs_eps = eps;
+  return 0;
+}
 
 __device__ __forceinline__ void tmem_ld16_nowait(unsigned taddr, float* v) {
   unsigned* r = reinterpret_cast<unsigned*>(v);
@@ -621,6 +642,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * SW_MAX_STAGES + 1];     // full[], empty[], accumulator done
   __shared__ unsigned tmem_base_s;
+  __shared__ float rs_scale[64];                       // the norm factors of this rank's tokens (a.rs_ssq)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = a.stages, stage_bytes = SW_W_BYTES + a.mt * UM_BK * 2;
@@ -656,6 +678,8 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int my_tokens = split < a.M ? (a.M - split + S - 1) / S : 0;
   float4 res[2];                                    // += residual: fetched while the products run (up to 16 tokens a rank)
   bool res_ok[2] = {false, false};
+  float4 nn_g = make_float4(0.f, 0.f, 0.f, 0.f);    // the next norm's weights of this lane's four columns
+  if (EPI == EPI_ACC && a.nn_x) nn_g = *(const float4*)(a.nn_w + n0 + 4 * lane);
 
   if (warp == 0 && lane == 0) {
     // weights first: they do not depend on the kernel in front
@@ -698,6 +722,16 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         umma_commit(empty0 + 8 * s);
       }
       if (ok) umma_commit(accfull);
+    } else if (warp >= 2 && a.rs_ssq) {
+      // the other warps have nothing to do until the products are done: the norm factors of this rank's
+      // tokens, the parts of a row always added in the same order
+      for (int tl = warp - 2; tl < my_tokens; tl += SW_WARPS - 2) {
+        const float* parts = a.rs_ssq + (size_t)(split + tl * S) * a.rs_parts;
+        float ss = 0.f;
+        for (int p = lane; p < a.rs_parts; p += 32) ss += parts[p];
+        ss = warp_sum(ss);
+        if (lane == 0) rs_scale[tl] = 1.0f / sqrtf(ss / (float)a.K + a.rs_eps);
+      }
     }
   }
   __syncwarp();
@@ -741,6 +775,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
   auto finish = [&](int tl, float4 v, bool have_res, const float4& res_i) {
     const int t = split + tl * S, n = n0 + 4 * lane;
+    if (a.rs_ssq) { const float sc = rs_scale[tl]; v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc; }
     if (a.bias) {
       if (n < a.N) v.x += a.bias[n];
       if (n + 1 < a.N) v.y += a.bias[n + 1];
@@ -768,6 +803,13 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (EPI == EPI_ACC) {
           const float4 r = have_res ? res_i : *(const float4*)((const float*)a.out + o);
           v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+          if (a.nn_x) {
+            // (N is a multiple of 128 here: the whole warp is in this branch)
+            const float sq = warp_sum(fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w))));
+            const __nv_bfloat162 g0 = __floats2bfloat162_rn(v.x * nn_g.x, v.y * nn_g.y), g1 = __floats2bfloat162_rn(v.z * nn_g.z, v.w * nn_g.w);
+            *(uint2*)(a.nn_x + (size_t)t * a.nn_ldx + n) = make_uint2(*(const unsigned*)&g0, *(const unsigned*)&g1);
+            if (lane == 0) a.nn_ssq[(size_t)t * gridDim.y + blockIdx.y] = sq;
+          }
         }
         *(float4*)((float*)a.out + o) = v;
       }
@@ -912,22 +954,29 @@ FELLM_API int fellm_gemm_umma_swap_takes(int M, int N, int K) {
 // Same epilogues and status word as fellm_gemm_umma (111..113 for this kernel's roles).
 FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
                                    int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
+  const SwapHandoff h = g_swap_handoff;                  // taken and cleared whatever this call returns
+  g_swap_handoff = SwapHandoff{nullptr, nullptr, nullptr, 0, nullptr, 0, 0.f};
+  const NextWeights nw = take_next_weights();
   if (M <= 0 || N <= 0) return 0;
   if (!x || !W || !out || K <= 0) return FELLM_ERR_ARG;
   if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return FELLM_ERR_SIZE;
   if (epi == EPI_SWIGLU && (N % 16)) return FELLM_ERR_SIZE;
   SwapPlan p;
   if (!plan_swap(M, N, K, &p)) return FELLM_ERR_SIZE;
+  if (h.nn_x && (epi != EPI_ACC || !h.nn_w || !h.nn_ssq || (N % UM_BM) || (ldo % 4) || (h.nn_ldx % 4) || h.nn_ldx < N ||
+                 ((uintptr_t)h.nn_x & 7) || ((uintptr_t)h.nn_w & 15))) return FELLM_ERR_ARG;
+  if (h.rs_ssq && h.rs_parts < 1) return FELLM_ERR_ARG;
   CUtensorMap mw, mx;
   int e = make_map(&mw, W, N, K, ldw, UM_BM);
   if (e) return e;
   e = make_map(&mx, x, M, K, lda, p.mt);
   if (e) return e;
-  SwapArgs a;
+  SwapArgs a = {};
   a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
   a.mt = p.mt; a.splits = p.splits; a.stages = p.stages;
-  const NextWeights nw = take_next_weights();
   a.next_w = nw.ptr; a.next_bytes = nw.bytes;
+  a.nn_w = h.nn_w; a.nn_x = (bf16*)h.nn_x; a.nn_ssq = h.nn_ssq; a.nn_ldx = h.nn_ldx;
+  a.rs_ssq = h.rs_ssq; a.rs_parts = h.rs_parts; a.rs_eps = h.rs_eps;
   const int n_tiles = ceil_div(N, UM_BM);
   switch (epi) {
     case EPI_STORE: return launch_swap<EPI_STORE>(mw, mx, a, p.smem, n_tiles, stream);

@@ -431,7 +431,7 @@ def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
 # into x is followed by an RMSNorm with weights g"; norm_handoff(x, g) gives the reader what was left, if
 # it is still good (same tensor, same weights, nothing written to x since).
 NORM_HANDOFF = os.environ.get("FELLM_B200_NORM_HANDOFF", "1") != "0"
-HANDOFF_MAX_ROWS = 16
+HANDOFF_MAX_ROWS = 64       # up to 16 rows: the weight-streaming kernel on both sides; 17..64: the tcgen05 product of few rows
 _handoff_bufs = {}          # device -> (xg bfloat16 [16 * width], ssq float32 [16 * width / 16], width)
 _expected_norm = None       # (data_ptr of x, norm weights)
 _handoff = None             # NormHandoff: what the last such product left
@@ -491,26 +491,42 @@ def norm_handoff(x, norm_w):
     return h
 
 
+def _swap_rows(M: int, N: int) -> bool:
+    """Whether gemm_bf16 gives a product of M rows and N columns to the tcgen05 product of few rows."""
+    return USE_UMMA and USE_UMMA_SWAP and max(SWAP_MIN_ROWS, 17) <= M <= 64 and N <= SWAP_MAX_N
+
+
 def row_scale_takes(M: int, N: int, K: int) -> bool:
-    """Whether a product of these sizes can take a handed-on norm's input (the single-shot kernel runs it)."""
-    return M <= HANDOFF_MAX_ROWS and K % 8 == 0 and _single_shot(M, N, K, False)
+    """Whether a product of these sizes can take a handed-on norm's input: up to 16 rows the single-shot
+    weight-streaming kernel, 17..64 rows the tcgen05 product of few rows."""
+    if K % 8:
+        return False
+    if M <= 16:
+        return _single_shot(M, N, K, False)
+    return _swap_rows(M, N)
 
 
 def _announce_handoff(exp, out, M: int, N: int, K: int, norm_fused: bool):
     """Before an accumulate product of the weight-streaming kernel: if its successor's norm is known (exp)
     and the kernel can do it, tell the kernel and note what it leaves."""
     global _handoff
-    if exp is None or M > HANDOFF_MAX_ROWS or N % 16 or not out.is_contiguous():
+    if exp is None or M > HANDOFF_MAX_ROWS or not out.is_contiguous() or norm_fused:
         return
-    if norm_fused or not _single_shot(M, N, K, False):
-        return
+    if M <= 16:
+        if N % 16 or not _single_shot(M, N, K, False):
+            return
+        module, per_part = "gemm_skinny", 16
+    else:
+        if N % 128 or not _swap_rows(M, N):
+            return
+        module, per_part = "gemm_umma", 128
     xg, ssq, width = _handoff_bufs[out.device]
     _handoff = None                      # the buffers are about to be rewritten
-    f = _fn("gemm_skinny", "fellm_gemm_skinny_next_norm", [_c_p, _c_p, _c_int, _c_p])
+    f = _fn(module, f"fellm_{module}_next_norm", [_c_p, _c_p, _c_int, _c_p])
     f(_p(exp[1]), _p(xg), N, _p(ssq))
     h = NormHandoff()
     h.x_ptr, h.version, h.rows, h.norm_ptr = out.data_ptr(), out._version, M, exp[1].data_ptr()
-    h.xg, h.ssq, h.parts = xg[:M * N].view(M, N), ssq, N // 16
+    h.xg, h.ssq, h.parts = xg[:M * N].view(M, N), ssq, N // per_part
     return h
 
 
@@ -519,7 +535,8 @@ def _announce_row_scale(row_scale, M: int, N: int, K: int, own_plan: bool = Fals
     if not own_plan and not row_scale_takes(M, N, K):
         raise KernelError(f"a product of {M} x {N} x {K} does not take a handed-on norm")
     assert ssq.dtype == torch.float32 and ssq.numel() >= M * parts
-    _fn("gemm_skinny", "fellm_gemm_skinny_row_scale", [_c_p, _c_int, _c_f])(_p(ssq), int(parts), float(eps))
+    module = "gemm_skinny" if M <= 16 else "gemm_umma"
+    _fn(module, f"fellm_{module}_row_scale", [_c_p, _c_int, _c_f])(_p(ssq), int(parts), float(eps))
 
 
 def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swiglu=False, norm=None, row_scale=None):
@@ -571,19 +588,25 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     # (measured at 64 rows: 14 us against 26 us for [1024, 4608], 8 against 9-11 for K = 1024, but 13
     # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
     expected = residual_written(out) if accumulate else None
-    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N and row_scale is None:
+    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N and (row_scale is None or M > 16):
         # a decode step of 17..64 rows: tcgen05 with the weights as the MMA's 128 rows
         _announce_next("gemm_umma", w, M)
-        return gemm_umma_swap(x, w, bias, out=out, epi=epi)
+        if row_scale is not None:
+            _announce_row_scale(row_scale, M, N, K)
+        left = _announce_handoff(expected, out, M, N, K, False) if M > 16 else None
+        gemm_umma_swap(x, w, bias, out=out, epi=epi, written=True)
+        if left is not None:
+            _handoff = left
+        return out
     skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
                           or (M <= SKINNY_MAX_ROWS and N < 8192))
-    if row_scale is not None and not skinny:
+    if row_scale is not None and (not skinny or M > 16):
         raise KernelError(f"a product of {M} x {N} x {K} does not take a handed-on norm")
     if skinny:
         _announce_next("gemm_skinny", w, M)
         if row_scale is not None:
             _announce_row_scale(row_scale, M, N, K)
-        left = _announce_handoff(expected, out, M, N, K, norm is not None)
+        left = _announce_handoff(expected, out, M, N, K, norm is not None) if M <= 16 else None
         f = _fn("gemm_skinny", "fellm_gemm_skinny", _SKINNY_ARGS)
         if norm is not None:
             code = f(None, _p(x), _p(norm[0]), float(norm[1]), _p(w), _p(bias), _p(out), epi, M, N, K, x.stride(0),
@@ -653,11 +676,11 @@ def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None, row_scale=None)
     return out_tokens
 
 
-def gemm_umma_swap(x, w, bias=None, *, out, epi: int):
+def gemm_umma_swap(x, w, bias=None, *, out, epi: int, written: bool = False):
     """The tcgen05 product for up to 64 rows (weights as the MMA's rows, K split over a cluster),
     callable by itself.  epi: 0 store bfloat16, 1 add into float32, 2 SiLU(gate)*up, 3 store float32."""
     M, K = x.shape
-    if epi == _EPI_ACC:
+    if epi == _EPI_ACC and not written:
         residual_written(out)
     f = _fn("gemm_umma", "fellm_gemm_umma_swap", _GEMM_ARGS[:-1] + [_c_p, _c_p])
     _check(f(_p(x), _p(w), _p(bias), _p(out), epi, M, w.shape[0], K, x.stride(0), w.stride(0), out.stride(0),

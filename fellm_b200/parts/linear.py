@@ -51,7 +51,9 @@ def linear(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, swigl
     gate/up matrix and the result is SiLU(gate)*up."""
     if isinstance(x, LazyNorm):
         h = x.handed_on()
-        if h is not None and ops.fast_gemm_takes(h.xg, w) and ops.row_scale_takes(h.rows, w.shape[0], w.shape[1]):
+        if (h is not None and ops.fast_gemm_takes(h.xg, w) and w.data_ptr() % 16 == 0
+                and ops.row_scale_takes(h.rows, w.shape[0], w.shape[1])
+                and not (swiglu and out is not None and out.stride(0) % 8)):
             return ops.gemm_bf16(h.xg, w, bias, out=out, out_dtype=out_dtype, accumulate=accumulate, swiglu=swiglu,
                                  row_scale=(h.ssq, h.parts, x.norm.eps))
         if x.fusable_with(w):
