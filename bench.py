@@ -260,23 +260,28 @@ def run_prefill(engine, tokens, reps, rng):
     import torch
     from fellm_b200.engine import StepItem
     vocab = engine.spec.vocab_size
-    times = []
-    for i in range(reps + 2):
-        r = f"pf{i}"
-        engine.add_request(r)
-        ids = rng.integers(0, vocab, tokens).tolist()
+    # `reps` prompts of `tokens` ids, each whole in one step, the steps queued one behind the other between two
+    # events (as the decode steps are): while the device runs a step the host prepares the next, as it does under
+    # the scheduler.  The time of one step alone, host preparation included, is ~0.25 ms longer.
+    def steps(n, tag):
+        names = [f"pf{tag}{i}" for i in range(n)]
+        ids = [rng.integers(0, vocab, tokens).tolist() for _ in names]
+        for r in names:
+            engine.add_request(r)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
-        engine.step([StepItem(r, ids, [tokens - 1])])
+        for r, t in zip(names, ids):
+            engine.step([StepItem(r, t, [tokens - 1])])
         e1.record()
         torch.cuda.synchronize()
-        if i >= 2:
-            times.append(e0.elapsed_time(e1))
-        engine.release(r)
+        for r in names:
+            engine.release(r)
+        return e0.elapsed_time(e1) / n
+    steps(2, "w")                                                 # the first runs directly, the second captures the graph
+    ms = steps(reps, "t")
     engine.check_status()
-    times.sort()
-    return times[len(times) // 2]
+    return ms
 
 
 def run_mixed_workload(engine, rng, n_requests, max_new):
