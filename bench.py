@@ -199,7 +199,7 @@ def run_timeline(engine, batch, context, out_path):
         graph.replay()
     tl.reset()
     graph.replay()
-    launches = tl.launches()
+    launches = tl.launches(detail=True)
     tl.close()
     total = launches[-1].end_us - launches[0].begin_us
     agg, prev_end = {}, None
@@ -216,6 +216,7 @@ def run_timeline(engine, batch, context, out_path):
              "|---|---|---|---|---|---|---|"]
     for (name, blocks), a in sorted(agg.items(), key=lambda kv: -(kv[1][1] + kv[1][2] + kv[1][3])):
         lines.append(f"| {name} | {blocks} | {a[0]} | {a[1] / a[0]:.2f} | {a[2] / a[0]:.2f} | {a[3] / a[0]:.2f} | {a[1] + a[2] + a[3]:.1f} |")
+    lines += ["", "Per CTA, between its own wait and its exit, cut at the kernel's marks:", "", Timeline.phases(launches)]
     lines += ["", Timeline.table(launches), ""]
     with open(out_path, "w") as f:
         f.write("\n".join(lines))

@@ -115,6 +115,33 @@ class Timeline:
         return group_records(self.records[:n].cpu().tolist(), detail)
 
     @staticmethod
+    def phases(launches: List[Launch]) -> str:
+        """For launches made with detail=True: what a CTA spends between its own wait and its exit, cut at the
+        kernel's marks (medians over the CTAs of all launches of a kernel and grid; marks a CTA did not pass
+        are left out).  Which place of a kernel a mark is, the kernel's source says (FELLM_TRACE_MARK)."""
+        groups = {}
+        for l in launches:
+            for c in l.ctas:
+                begin, waited, end, marks = c[0], c[1], c[2], c[3:]
+                if not any(marks):
+                    continue
+                g = groups.setdefault((l.name, l.blocks), {})
+                prev, label = waited, "wait"
+                for k, m in enumerate(marks):
+                    if m:
+                        g.setdefault(f"{label} -> mark {k}", []).append(m - prev)
+                        prev, label = m, f"mark {k}"
+                g.setdefault(f"{label} -> exit", []).append(end - prev)
+                g.setdefault("wait -> exit", []).append(end - waited)
+                g.setdefault("entry -> wait", []).append(waited - begin)
+        lines = ["| kernel | CTAs | phase | median us | 90% us | max us |", "|---|---|---|---|---|---|"]
+        for (name, blocks), g in groups.items():
+            for phase, v in g.items():
+                v = sorted(v)
+                lines.append(f"| {name} | {blocks} | {phase} | {v[len(v) // 2]:.2f} | {v[int(len(v) * 0.9)]:.2f} | {v[-1]:.2f} |")
+        return "\n".join(lines)
+
+    @staticmethod
     def table(launches: List[Launch]) -> str:
         lines = ["| # | kernel | CTAs | begin us | wait us | run us | gap to the one before us |", "|---|---|---|---|---|---|---|"]
         prev_end = None
