@@ -234,9 +234,11 @@ def run_e2e(engine, batch, steps, warmup, rng):
     vocab = engine.spec.vocab_size
     # the timed steps end just below the middle of the growth: the first token comes with the prompt's last
     # portion, the scheduler launches one step ahead, and a step's graph goes by the length AFTER the step
-    ahead = max(untimed_steps(steps, warmup) - 6, warmup)
+    # (and the requests whose prompts were run first are as many tokens ahead as the prompts took steps)
+    skew = -(-batch * PROMPT // 4096)
+    ahead = max(untimed_steps(steps, warmup) - 6 - skew, warmup)
     for _ in range(batch):
-        sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(ahead + steps + 8))
+        sched.enqueue_ids(rng.integers(0, vocab, PROMPT).tolist(), GenParams.greedy(ahead + steps + 8 + skew))   # none ends inside the window
     while any(r.prefilling for r in list(sched.running) + list(sched.waiting)) or sched.waiting:
         sched.step()
     for _ in range(ahead):

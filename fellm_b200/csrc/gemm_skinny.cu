@@ -832,7 +832,7 @@ static int launch(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   a.xf_offset = (int)smem;                                 // a float32 row piece per warp
   if (a.xf) smem += (size_t)SK_WARPS * (a.K < SK_XF ? a.K : SK_XF) * sizeof(float);
   auto kern = gemm_skinny_kernel<MT, EPI>;
-  if (smem > 48 * 1024) {
+  if (smem + 1024 > 48 * 1024) {                            // (the kernel's static shared memory counts toward the 48 KB too)
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -852,7 +852,7 @@ static int launch_lean(SkinnyArgs a, int ctas_y, cudaStream_t stream) {
   a.red_offset = (int)smem;
   if (EPI == EPI_CONV) smem += (size_t)3 * SK_ROWS * MT * 8 * sizeof(float);
   auto kern = gemm_lean_kernel<MT, EPI, NORM, WARPS>;
-  if (smem > 48 * 1024) {
+  if (smem + 1024 > 48 * 1024) {                            // (the kernel's static shared memory counts toward the 48 KB too)
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

@@ -48,7 +48,7 @@ class Event:
     message: str = ""
 
 
-@dataclass
+@dataclass(eq=False)                  # a request is itself: `r in running` must not compare prompts
 class Request:
     id: int
     prompt: List[int]                 # what has to be in the cache before the next sample

@@ -433,6 +433,7 @@ def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
 NORM_HANDOFF = os.environ.get("FELLM_B200_NORM_HANDOFF", "1") != "0"
 HANDOFF_MAX_ROWS = 64       # up to 16 rows: the weight-streaming kernel on both sides; 17..64: the tcgen05 product of few rows
 _handoff_bufs = {}          # device -> (xg bfloat16 [16 * width], ssq float32 [16 * width / 16], width)
+_handoff_retired = []
 _expected_norm = None       # (data_ptr of x, norm weights)
 _handoff = None             # NormHandoff: what the last such product left
 
@@ -451,6 +452,8 @@ def reserve_norm_handoff(device, width: int):
         device = torch.device("cuda", torch.cuda.current_device())
     have = _handoff_bufs.get(device)
     if have is None or have[2] < width:
+        if have is not None:
+            _handoff_retired.append(have)      # graphs captured with the old buffers may still be replayed
         _handoff_bufs[device] = (torch.zeros(HANDOFF_MAX_ROWS * width, dtype=torch.bfloat16, device=device),
                                  torch.zeros(HANDOFF_MAX_ROWS * width // 16, dtype=torch.float32, device=device), width)
         forget_norm_handoff()

@@ -815,8 +815,11 @@ def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
     ops.forget_norm_handoff()
 
 
-def test_handed_on_norm_into_the_convolution_product():
-    M, d, lc = 8, 1024, 3
+@pytest.mark.parametrize("M", [1, 8, 9, 15, 16])
+def test_handed_on_norm_into_the_convolution_product(M):
+    """(At 9 to 16 rows and width 1024 the kernel's dynamic shared memory is exactly 48 KB: with its static part
+    it needs the opt-in.)"""
+    d, lc = 1024, 3
     g = torch.Generator().manual_seed(5)
     res = (torch.randn(M, d, generator=g) * 2).to(DEV)
     y = torch.randn(M, d, generator=g).bfloat16().to(DEV)
@@ -825,7 +828,8 @@ def test_handed_on_norm_into_the_convolution_product():
     w_in = ops.block_bcx_rows((torch.randn(3 * d, d, generator=g) * 0.05).bfloat16().to(DEV))
     conv_w = torch.randn(d, lc, generator=g).to(DEV)
     state = torch.randn(12, 1, lc - 1, d, generator=g).to(DEV)
-    slots = i32([3, 0, 11, 5, 6, 7, 1, 9])
+    state = torch.randn(20, 1, lc - 1, d, generator=g).to(DEV)
+    slots = i32(torch.randperm(20, generator=g)[:M].tolist())
     ops.forget_norm_handoff()
     ops.reserve_norm_handoff(DEV, 2048)
     ops.expect_norm(res, nw)

@@ -191,25 +191,26 @@ def test_greedy_steps_that_skip_the_logits_give_the_plain_tokens(graphs):
     eng.check_status()
 
 
-def test_decode_steps_hand_the_norms_on(monkeypatch):
-    """Width 1024, decode steps of 3 rows: every product that adds into the residual rows leaves them weighted
+@pytest.mark.parametrize("n_req", [3, 12])
+def test_decode_steps_hand_the_norms_on(n_req, monkeypatch):
+    """Width 1024, decode steps of 3 and of 12 rows (one and two token tiles of the products): every product that adds into the residual rows leaves them weighted
     for the norm that reads them next (all but the first norm of a step, which follows the embedding), and the
     logits stay those of the plain implementation; with the hand-over switched off, too."""
     from fellm_b200 import ops
     taken = []
     real = ops._announce_row_scale
     monkeypatch.setattr(ops, "_announce_row_scale", lambda *a, **k: (taken.append(a[1:4]), real(*a, **k))[1])
-    prompts = [tiny.tokens("C", n + 6, 810 + i) for i, n in enumerate((7, 64, 30))]
-    lens = (7, 64, 30)
+    lens = (7, 64, 30, 1, 63, 12, 100, 5, 33, 65, 2, 90)[:n_req]
+    prompts = [tiny.tokens("C", n + 6, 810 + i) for i, n in enumerate(lens)]
     logits = {}
     for on in (True, False):
         monkeypatch.setattr(ops, "NORM_HANDOFF", on)
-        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False)
+        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False, max_requests=16, max_tokens=16 * 256)
         for i, n in enumerate(lens):
             eng.add_request(i)
             eng.step([StepItem(i, prompts[i][:n], [])])
         taken.clear()
-        rows = [eng.step([StepItem(i, [prompts[i][lens[i] + t]], [0]) for i in range(3)]).clone() for t in range(6)]
+        rows = [eng.step([StepItem(i, [prompts[i][lens[i] + t]], [0]) for i in range(n_req)]).clone() for t in range(6)]
         eng.check_status()
         logits[on] = torch.stack(rows)
         n_layers = len(tiny.CONFIGS["C"][0]["layer_types"])
