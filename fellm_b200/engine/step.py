@@ -343,7 +343,9 @@ class Stepper:
             if len(self.graph_seen) > 4096:                  # shapes seen once and never again
                 self.graph_seen = {k: v for k, v in self.graph_seen.items() if k in self.graphs}
             self.graph_seen[key] = n_seen + 1
-            if n_seen == 0:
+            # a shape of prompt portions is captured when it comes a second time (most never do); a decode step's
+            # count of requests comes again almost surely, and a direct run costs as much as a capture
+            if n_seen == 0 and not ctx.all_single:
                 before = ops.launch_count()
                 logits = self.model.forward(ctx, views, greedy_tokens)
                 self.launches += ops.launch_count() - before

@@ -218,3 +218,42 @@ def test_decode_steps_hand_the_norms_on(n_req, monkeypatch):
         for i, n in enumerate(lens):
             want = tiny.plain_logits("C", n + 6, 810 + i)[n:]
             check(f"hand-over {on}: request {i}", logits[on][:, i], want, "bfloat16")
+
+
+def test_every_row_count_from_1_to_40_with_and_without_the_handed_on_norm(monkeypatch):
+    """Width 1024: decode steps of 1, 2, ... 40 requests (each count picks its own kernels, tile counts and shared
+    memory sizes), run by an engine that hands the norms on and by one that does not, on the same tokens: the
+    logits agree within twice the tolerance each has against the plain implementation, and the last step of
+    some requests is compared with that directly."""
+    from fellm_b200 import ops
+    n_max, n_dec = 40, 41
+    lens = [1 + (7 * i) % 23 for i in range(n_max)]
+    toks = [tiny.tokens("C", lens[i] + n_dec, 900 + i) for i in range(n_max)]
+    engines = {}
+    for on in (True, False):
+        monkeypatch.setattr(ops, "NORM_HANDOFF", on)
+        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False, max_requests=n_max, max_tokens=n_max * 128)
+        for i in range(n_max):
+            eng.add_request(i)
+            eng.step([StepItem(i, toks[i][:lens[i]], [])])
+        engines[on] = eng
+    done = [0] * n_max
+    last = {}
+    for n in range(1, n_max + 1):
+        items = [StepItem(i, [toks[i][lens[i] + done[i]]], [0]) for i in range(n)]
+        out = {}
+        for on in (True, False):
+            monkeypatch.setattr(ops, "NORM_HANDOFF", on)
+            out[on] = engines[on].step(items).clone()
+        for i in range(n):
+            done[i] += 1
+        scale = float(out[False].abs().max())
+        err = float((out[True] - out[False]).abs().max())
+        assert err <= 2 * 2.5e-2 * scale, (n, err, scale)
+        last[n] = out[True]
+    for on in (True, False):
+        engines[on].check_status()
+    # request i took part in the steps n = i + 1 .. 40: its row of the last step against the plain implementation
+    for i in (0, 7, 15, 16, 31, 39):
+        want = tiny.plain_logits("C", lens[i] + done[i], 900 + i)[-1:]
+        check(f"request {i} after {done[i]} steps", last[n_max][i:i + 1], want, "bfloat16")
