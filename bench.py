@@ -340,6 +340,7 @@ def run_concurrent_workload(engine, rng, n_requests, prompt, steps, temperature,
     for _ in range(n_requests):
         sched.enqueue_ids(rng.integers(0, vocab, prompt).tolist(), params)
     n_tok, t_decode, tok_at_decode, ctx_sum, dec_steps = 0, None, 0, 0.0, 0
+    t_decode_end, tok_at_end = None, 0
     distinct = set()
     while not sched.idle():
         all_decode = (not sched.waiting and len(sched.running) == n_requests
@@ -347,6 +348,11 @@ def run_concurrent_workload(engine, rng, n_requests, prompt, steps, temperature,
         if all_decode and t_decode is None:
             torch.cuda.synchronize()
             t_decode, tok_at_decode = time.perf_counter(), n_tok
+        if not all_decode and t_decode is not None and t_decode_end is None:
+            # the first request is through: what follows (fewer and fewer rows a step, the requests whose prompts
+            # ran first being that many tokens ahead) is not part of the decode figures
+            torch.cuda.synchronize()
+            t_decode_end, tok_at_end = time.perf_counter(), n_tok
         if all_decode:
             ctx_sum += sum(engine.cache.length(r.id) for r in sched.running) / n_requests + 1
             dec_steps += 1
@@ -358,7 +364,9 @@ def run_concurrent_workload(engine, rng, n_requests, prompt, steps, temperature,
                 raise RuntimeError(ev.message)
     torch.cuda.synchronize()
     t1 = time.perf_counter()
-    prefill_s, decode_s = t_decode - t0, t1 - t_decode
+    if t_decode_end is None:
+        t_decode_end, tok_at_end = t1, n_tok
+    prefill_s, decode_s = t_decode - t0, t_decode_end - t_decode
     mean_ctx = ctx_sum / max(dec_steps, 1)
     wbytes = model_bytes(engine)
     state_bytes = sum(g.bytes_per_request() for g in engine.cache.fixed)
@@ -366,7 +374,8 @@ def run_concurrent_workload(engine, rng, n_requests, prompt, steps, temperature,
     ms_step = decode_s / max(dec_steps, 1) * 1e3
     return {"requests": n_requests, "prompt_len": prompt, "decode_steps": dec_steps, "temperature": temperature,
             "prompt_eval_tok_s": round(n_requests * prompt / prefill_s, 1),
-            "decode_tok_s": round((n_tok - tok_at_decode) / decode_s, 1), "ms_per_step": round(ms_step, 4),
+            "decode_tok_s": round((tok_at_end - tok_at_decode) / decode_s, 1), "ms_per_step": round(ms_step, 4),
+            "wall_s": round(t1 - t0, 3),
             "context_mean": round(mean_ctx, 1), "distinct_tokens": len(distinct),
             "roofline_frac": round(step_bytes / (ms_step / 1e3) / 1e9 / hbm, 4), "weights_mb": wbytes // 1000000}
 

@@ -95,12 +95,16 @@ class _PagedGroup:
         self.need, self.entries = need, list(entries)
         self.page_tokens, self.width = page_tokens, width
         self.alloc = PageAllocator(n_pages)
-        self.pool = torch.zeros((max(n_pages, 1), len(self.entries), 2, need.kv_heads, page_tokens,
+        # one page and one block-table row beyond what the allocators hand out: the padding rows of a decode
+        # step (CacheManager.pad_slot) keep their single position there
+        self.pool = torch.zeros((n_pages + 1, len(self.entries), 2, need.kv_heads, page_tokens,
                                  need.head_dim), dtype=dtype, device=device)
         # pageable on purpose: a copy from pageable memory is staged by the driver before the call
         # returns, so later edits of the mirror cannot reach a copy that is still queued
-        self.table_host = torch.full((n_slots, width), -1, dtype=torch.int32)
-        self.table_dev = torch.full((n_slots, width), -1, dtype=torch.int32, device=device)
+        self.table_host = torch.full((n_slots + 1, width), -1, dtype=torch.int32)
+        self.table_dev = torch.full((n_slots + 1, width), -1, dtype=torch.int32, device=device)
+        self.table_host[n_slots, 0] = n_pages
+        self.table_dev[n_slots, 0] = n_pages
         self.dirty: Dict[int, List[int]] = {}            # slot -> [lo, hi) of changed entries
         self.first_page: Dict[int, int] = {}             # slot -> first logical page still held
         self.n_logical: Dict[int, int] = {}              # slot -> logical pages ever mapped
@@ -168,8 +172,8 @@ class _PagedGroup:
 class _StateGroup:
     def __init__(self, need: FixedState, entries, n_slots, device):
         self.need, self.entries = need, list(entries)
-        self.states = torch.zeros((n_slots, len(self.entries), *need.shape), dtype=torch.float32,
-                                  device=device)
+        self.states = torch.zeros((n_slots + 1, len(self.entries), *need.shape), dtype=torch.float32,
+                                  device=device)               # (the last row: CacheManager.pad_slot)
 
     def bytes_per_request(self) -> int:
         return self.states[0].numel() * 4
@@ -185,6 +189,10 @@ class CacheManager:
         max_tokens: positions the page pool of each group holds (rounded up to whole pages)."""
         self.page_tokens, self.n_slots, self.n_ctx = int(page_tokens), int(max_requests), int(n_ctx)
         self.device = device
+        # A slot no request ever gets, with one position of cache (a page of its own in every paged group) and
+        # a state row: a step may carry rows that belong to nobody (a decode step filled up to a row count whose
+        # CUDA graph exists); they read and write there and their results are dropped.
+        self.pad_slot = self.n_slots
         self.slots = SlotAllocator(self.n_slots)
         self.paged: List[_PagedGroup] = []
         self.fixed: List[_StateGroup] = []

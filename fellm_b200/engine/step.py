@@ -160,6 +160,7 @@ StepBuffers.fill_decode = _fill_decode
 
 _NOT_TAKEN = object()       # _step_decode's answer when the general path has to run the step (None is a result: tokens without logits)
 MAX_ROW_GRAPHS = 8          # captured graphs of steps that are not pure decode (each keeps its activations)
+DECODE_ROWS_STEP = 8        # decode steps of more than 16 rows run with a multiple of this many rows (the last ones padding)
 MAX_DECODE_GRAPHS = 48      # captured decode steps (each keeps its logits [wanted, vocab]); the least recently used goes
 
 
@@ -281,6 +282,17 @@ class Stepper:
             key = (reqs, tuple(slot_d[r] for r in reqs))
         except KeyError:
             return _NOT_TAKEN
+        wants = tuple(bool(it.want) for it in items)
+        # A graph is captured for every count of rows a decode step has; from 17 rows on the count is filled up
+        # to a multiple of 8 with rows that belong to nobody (the cache's pad slot: position 0 of a page of its
+        # own, a state row of its own), so that a batch that grows or drains by one request at a time meets a
+        # new graph every eighth count, not at every one.  Up to 16 rows each count has kernels of its own cost.
+        n_pad = n
+        if self.cuda_graphs and n > 16 and all(wants):
+            n_pad = -(-n // DECODE_ROWS_STEP) * DECODE_ROWS_STEP
+            if n_pad > self.buffers.max_items:
+                n_pad = n
+        key = key + (n_pad,)
         plan = self._decode_plans.get(key)
         if plan is None:
             if len(set(reqs)) != n:
@@ -288,10 +300,9 @@ class Stepper:
             if len(self._decode_plans) > 64:
                 self._decode_plans.clear()
             self._plan_serial += 1                         # never reused, unlike id(): names what a staging buffer holds
-            plan = {"slots": np.array(key[1], dtype=np.int64), "arange": np.arange(n + 1),
+            plan = {"slots": np.array(key[1] + (cache.pad_slot,) * (n_pad - n), dtype=np.int64), "arange": np.arange(n_pad + 1),
                     "ring": [None] * len(self.buffers.ring), "serial": self._plan_serial}
             self._decode_plans[key] = plan
-        wants = tuple(bool(it.want) for it in items)
         if int(lens.max()) + 1 > cache.n_ctx:
             return _NOT_TAKEN
         if cache.has_windows:
@@ -310,15 +321,21 @@ class Stepper:
             for r, l in zip(reqs, lens):
                 if l % pt == 0:
                     cache.reserve(r, 1)
+        if n_pad > n:
+            wants = wants + (True,) * (n_pad - n)
+            fill = np.zeros(n_pad - n, dtype=np.int64)
+            lens = np.concatenate([lens, fill])
+            # (token 0 for the padding rows, also where the real rows' tokens come from the device)
+            toks = np.zeros(n_pad, dtype=np.int64) if toks is None else np.concatenate([toks, fill])
         ctx = self.buffers.fill_decode(plan, wants, toks, lens)
         if device_tokens is not None:
-            ctx.tokens.copy_(device_tokens[:n])
+            ctx.tokens[:n].copy_(device_tokens[:n])
         cache.flush()
         logits = self._run(ctx, greedy_tokens)
         for r in reqs:
             lens_d[r] += 1
         self.steps_run += 1
-        return logits
+        return logits if (logits is None or n_pad == n) else logits[:n]
 
     def _run(self, ctx, greedy_tokens=None) -> torch.Tensor:
         from .. import ops

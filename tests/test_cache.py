@@ -36,12 +36,16 @@ def test_allocator_discipline():
 def test_groups_by_need():
     c = make((CONV, FULL, CONV, FULL, WIN, None))
     assert len(c.paged) == 2 and len(c.fixed) == 1
-    assert c.paged[0].pool.shape == (8, 2, 2, 2, 8, 16)          # pages, layers, k/v, G, tokens, hd
-    assert c.paged[1].pool.shape == (8, 1, 2, 1, 8, 32)
-    assert c.fixed[0].states.shape == (4, 2, 2, 8)
+    # 8 pages and 4 slots to hand out, and one page and one slot more that nobody gets: the padding rows' own
+    assert c.paged[0].pool.shape == (9, 2, 2, 2, 8, 16)          # pages, layers, k/v, G, tokens, hd
+    assert c.paged[1].pool.shape == (9, 1, 2, 1, 8, 32)
+    assert c.fixed[0].states.shape == (5, 2, 2, 8)
+    assert c.n_pages == 8 and c.free_pages() == 8 and c.pad_slot == 4
+    for g in c.paged:
+        assert int(g.table_host[c.pad_slot, 0]) == 8 and int(g.table_host[c.pad_slot, 1]) == -1
     v = c.views(None)
     assert v[1].layer == 0 and v[3].layer == 1 and v[4].window == 24 and v[5] is None
-    assert v[0].states.shape == (4, 2, 8) and v[2].states.data_ptr() != v[0].states.data_ptr()
+    assert v[0].states.shape == (5, 2, 8) and v[2].states.data_ptr() != v[0].states.data_ptr()
 
 
 def test_reserve_advance_release_and_reuse():
@@ -134,7 +138,7 @@ def test_block_table_mirror_and_flush():
     c.flush()
     assert torch.equal(g.table_dev, g.table_host) and not g.dirty
     c.advance("a", 17); c.release("a"); c.flush()
-    assert int(g.table_dev.max()) == -1
+    assert int(g.table_dev[:c.pad_slot].max()) == -1        # (the row behind the slots is the padding rows' own)
 
 
 @pytest.mark.parametrize("seed", range(6))

@@ -26,9 +26,9 @@ def check(tag, got, want, dtype):
 
 
 @pytest.mark.parametrize("graphs", [False, True])
-@pytest.mark.parametrize("n_req", [20, 40, 64])
+@pytest.mark.parametrize("n_req", [20, 33, 64])
 def test_many_requests_decode_together(n_req, graphs):
-    """Width 1024, heads of 64, pages of 64 tokens, bfloat16: 20, 40 and 64 requests with prompts of
+    """Width 1024, heads of 64, pages of 64 tokens, bfloat16: 20, 33 (under graphs: filled up to 24 and 40 rows) and 64 requests with prompts of
     different lengths decode 8 steps together (some cross a page's edge), directly and from a CUDA
     graph; every row of every step against the plain implementation."""
     n_dec = 8
@@ -220,11 +220,14 @@ def test_decode_steps_hand_the_norms_on(n_req, monkeypatch):
             check(f"hand-over {on}: request {i}", logits[on][:, i], want, "bfloat16")
 
 
-def test_every_row_count_from_1_to_40_with_and_without_the_handed_on_norm(monkeypatch):
+@pytest.mark.parametrize("graphs", [False, True])
+def test_every_row_count_from_1_to_40_with_and_without_the_handed_on_norm(graphs, monkeypatch):
     """Width 1024: decode steps of 1, 2, ... 40 requests (each count picks its own kernels, tile counts and shared
     memory sizes), run by an engine that hands the norms on and by one that does not, on the same tokens: the
     logits agree within twice the tolerance each has against the plain implementation, and the last step of
-    some requests is compared with that directly."""
+    some requests is compared with that directly.  Under CUDA graphs the counts above 16 are filled up to 24, 32
+    and 40 rows with rows of nobody: three graphs for 24 counts, the same logits for the real rows, and the
+    cache's books in order."""
     from fellm_b200 import ops
     n_max, n_dec = 40, 41
     lens = [1 + (7 * i) % 23 for i in range(n_max)]
@@ -232,7 +235,7 @@ def test_every_row_count_from_1_to_40_with_and_without_the_handed_on_norm(monkey
     engines = {}
     for on in (True, False):
         monkeypatch.setattr(ops, "NORM_HANDOFF", on)
-        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=False, max_requests=n_max, max_tokens=n_max * 128)
+        eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs, max_requests=n_max, max_tokens=n_max * 128)
         for i in range(n_max):
             eng.add_request(i)
             eng.step([StepItem(i, toks[i][:lens[i]], [])])
@@ -253,6 +256,10 @@ def test_every_row_count_from_1_to_40_with_and_without_the_handed_on_norm(monkey
         last[n] = out[True]
     for on in (True, False):
         engines[on].check_status()
+        engines[on].cache.audit()
+        if graphs:
+            decode_keys = [k for k in engines[on].stepper.graphs if k[0] != "rows" and k[1] > 0]      # (a prompt of one token is such a step too, with no row wanted)
+            assert sorted(k[0] for k in decode_keys) == list(range(1, 17)) + [24, 32, 40], decode_keys
     # request i took part in the steps n = i + 1 .. 40: its row of the last step against the plain implementation
     for i in (0, 7, 15, 16, 31, 39):
         want = tiny.plain_logits("C", lens[i] + done[i], 900 + i)[-1:]
