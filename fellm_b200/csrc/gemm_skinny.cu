@@ -524,7 +524,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     LeanLoad<0, LEAN_CH>::run(p0, p0 + (size_t)8 * a.ldw, w0, w1, n_chunks);
   }
   // EPI_ACC with a norm to hand on: the next norm's weight for the value this thread finishes first
-  const int first_unit = ((split << a.log2_warps_k) + wk) * 32 + lane;
+  // which share of a slab's outputs this warp finishes: K warp w of rank r is number w * ranks + r of them, so that
+  // the first shares of a slab go to different ranks (a slab of 8 tokens has four shares of 32 outputs)
+  const int me = wk * a.splits + split;
+  const int first_unit = me * 32 + lane;
   float next_w_first = 0.f;
   if (EPI == EPI_ACC && a.nn_x && first_unit < SK_ROWS * a.M && tile < a.n_tiles) next_w_first = a.nn_w[tile * SK_ROWS + (first_unit & 15)];
   if (threadIdx.x == 0)
@@ -663,13 +666,27 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
     }
   }
   FELLM_TRACE_MARK(1);
+  const int warp_stride = tpw * SK_ROWS * MP;
+  // K over a cluster: every CTA first adds up its own K warps (into the slot of K warp 0 of each slab, all threads
+  // sharing the elements), so that what is read from the other ranks afterwards is one value a rank, not one a warp
+  const bool own_first = a.splits > 1 && a.warps_k > 1;
+  if (own_first) {
+    __syncthreads();
+    const int slab_elems = SK_ROWS * MP, slabs = (WARPS >> a.log2_warps_k) * tpw;
+    for (int e = threadIdx.x; e < slabs * slab_elems; e += WARPS * 32) {
+      const int sl = e / slab_elems, off = e - sl * slab_elems, wn_ = sl / tpw, tl_ = sl - wn_ * tpw;
+      float* first = slots + (size_t)((wn_ << a.log2_warps_k) * tpw + tl_) * slab_elems + off;
+      float v = first[0];
+      for (int w = 1; w < a.warps_k; ++w) v += first[(size_t)w * warp_stride];
+      first[0] = v;
+    }
+  }
   if (a.splits > 1) cg::this_cluster().sync(); else __syncthreads();
   FELLM_TRACE_MARK(2);
 
   // ---- sum the partial slabs over the cluster's ranks and the CTA's K warps, in that order; every
   // (rank, K warp) finishes a share of each slab's outputs
-  const int workers = a.splits << a.log2_warps_k, me = (split << a.log2_warps_k) + wk;
-  const int warp_stride = tpw * SK_ROWS * MP;
+  const int workers = a.splits << a.log2_warps_k;
   for (int tl = 0; tl < tpw; ++tl) {
     const int tile_l = tile + tl * tile_stride;
     if (tile_l >= a.n_tiles) break;
@@ -713,14 +730,15 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
           }
         }
       } else {
-        for (int q0 = 0; q0 < workers; q0 += RG) {
+        const int parts = own_first ? a.splits : workers;             // a value a rank, or a value a (rank, K warp)
+        for (int q0 = 0; q0 < parts; q0 += RG) {
           float p0[RG], p1[RG];
 #pragma unroll
           for (int q = 0; q < RG; ++q) {
             const int idx = q0 + q;
             p0[q] = 0.f; p1[q] = 0.f;
-            if (idx < workers) {
-              const int sr = idx >> a.log2_warps_k, w = idx & (a.warps_k - 1);
+            if (idx < parts) {
+              const int sr = own_first ? idx : idx >> a.log2_warps_k, w = own_first ? 0 : idx & (a.warps_k - 1);
               const float* pp = cg::this_cluster().map_shared_rank(mine_e, sr);
               p0[q] = pp[w * warp_stride];
               if (EPI == EPI_SWIGLU) p1[q] = pp[w * warp_stride + 8 * MP];
@@ -728,7 +746,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
           }
 #pragma unroll
           for (int q = 0; q < RG; ++q) {
-            if (q0 + q < workers) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
+            if (q0 + q < parts) { v0 += p0[q]; if (EPI == EPI_SWIGLU) v1 += p1[q]; }
           }
         }
       }
@@ -890,18 +908,19 @@ struct LeanPlan { int warps, warps_k, splits, ctas_y, k_per_warp, tiles_per_warp
 static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
   if (M > 64 || (norm && M > 16) || N % SK_ROWS) return false;
   const int n_sm = fellm_sm_count();
-  const int in_flight = 2 * SK_U * KCHUNK;
-  int slices = 1;
-  while (slices < 64 && ceil_div(K, slices) > in_flight) slices *= 2;
-  if (slices < 2 || K % slices || (K / slices) % KCHUNK) return false;
-  const int kpw = K / slices;
-  if (kpw < 8 * KCHUNK || kpw > LEAN_CH * KCHUNK) return false;
   const int mt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)), n_tiles = N / SK_ROWS;
   bool found = false;
   LeanPlan best = {};
   long long best_key = 0;
+  // K slices of 8..LEAN_CH whole chunks: any number of them that is (a power of two of warps) x (up to 8 ranks of
+  // a cluster), e.g. 1536 = 6 x 256 (2 warps x 3 ranks), 7168 = 28 x 256 (4 x 7), 3072 = 12 x 256 (4 x 3)
+  for (int slices = 2; slices <= 128; ++slices) {
+  if (K % slices || (K / slices) % KCHUNK) continue;
+  const int kpw = K / slices;
+  if (kpw < 8 * KCHUNK || kpw > LEAN_CH * KCHUNK) continue;
   for (int warps = 8; warps <= 16; warps *= 2) {
-    int wk = slices < warps ? slices : warps;
+    int wk = 1;
+    while (wk * 2 <= warps && slices % (wk * 2) == 0) wk *= 2;
     while (wk > 1 && lean_smem(mt, warps, kpw * wk, norm, K) > 200 * 1024) wk /= 2;
     const int sp = slices / wk, warps_n = warps / wk;
     if (sp > 8 || (norm && (sp > 1 || K > 4096))) continue;
@@ -920,6 +939,7 @@ static bool plan_lean(int M, int N, int K, bool norm, LeanPlan* out) {
       if (!found || key < best_key) { best = LeanPlan{warps, wk, sp, ct, kpw, tpw}; best_key = key; found = true; }
       break;
     }
+  }
   }
   if (found) *out = best;
   return found;

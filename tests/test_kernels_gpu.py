@@ -309,7 +309,9 @@ def _gemm_case(M, N, K, seed=0):
 # (the decode-sized ones up to 16 rows take its single-shot form: a slab per warp, 8..10 chunks of K per warp)
 # (wide products of a larger model: several slabs a warp, K = 8192 over a cluster of two; many rows and a wide N:
 # the tcgen05 product in 128 x 256 tiles, also with a ragged last tile)
+# (K slices over clusters of 3, 5 and 7 ranks: widths of 1536, 7168, 3072 and 6400 = 20 x 320 = 4 warps x 5 ranks)
 GEMM_SHAPES = [(1, 3072, 1024), (8, 1024, 4608), (13, 1024, 1024), (16, 2048, 2048), (9, 1536, 4608), (8, 6144, 2048),
+               (8, 4608, 1536), (16, 1536, 7168), (3, 1536, 1536), (12, 9216, 3072), (5, 1024, 6400),
                (16, 2048, 8192), (40, 6144, 2048), (3, 515, 144), (2048, 2048, 1024), (2048, 2000, 136), (17, 96, 72), (33, 200, 328), (64, 1024, 1024),
                (64, 2048, 200), (5, 65536, 64), (65, 144, 144), (128, 515, 320), (300, 1000, 1000), (2048, 256, 136)]
 
@@ -332,7 +334,7 @@ def test_gemm_bf16_store_acc_f32(M, N, K):
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (2048, 4608, 1024), (1900, 1000, 200), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (8, 7168, 1536), (14, 1024, 3072), (2048, 4608, 1024), (1900, 1000, 200), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
 def test_gemm_bf16_swiglu_epilogue(M, F, K):
     g = torch.Generator().manual_seed(F)
     x = torch.randn(M, K, generator=g).bfloat16()
@@ -736,7 +738,7 @@ def test_head_argmax_without_logits(M, N, K, use_norm):
 
 
 @pytest.mark.parametrize("M,N,K,d_next", [(8, 1024, 1024, 3072), (1, 1024, 4608, 9216), (16, 2048, 2048, 6144), (5, 1024, 1024, 65536),
-                                           (13, 512, 1280, 512), (8, 2048, 8192, 2048),
+                                           (13, 512, 1280, 512), (8, 2048, 8192, 2048), (8, 1536, 1536, 4608), (16, 1536, 7168, 14336),
                                            (17, 1024, 4608, 9216), (40, 1024, 1024, 3072), (64, 2048, 2048, 6144), (33, 1536, 1536, 4608),
                                            (24, 128, 64, 200)])
 def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
