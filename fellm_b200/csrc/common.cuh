@@ -177,11 +177,12 @@ static inline NextWeights take_next_weights() {
   g_next_weights.ptr = nullptr; g_next_weights.bytes = 0;
   return n;
 }
-// One thread of CTA `cta` of `n_ctas`: pieces cta, cta + n_ctas, ... of 16 KB.
-__device__ __forceinline__ void l2_prefetch_share(const void* ptr, long long bytes, int cta, int n_ctas) {
+// CTA `cta` of `n_ctas` asks for the pieces cta, cta + n_ctas, ... of 16 KB; `lane` of `lanes` of its threads take
+// them in turns (one thread: lane 0 of 1).
+__device__ __forceinline__ void l2_prefetch_share(const void* ptr, long long bytes, int cta, int n_ctas, int lane = 0, int lanes = 1) {
   if (!ptr) return;
   const long long piece = 16384, n = (bytes + piece - 1) / piece;
-  for (long long i = cta; i < n; i += n_ctas) {
+  for (long long i = cta + (long long)lane * n_ctas; i < n; i += (long long)lanes * n_ctas) {
     const long long off = i * piece;
     const unsigned size = (unsigned)((bytes - off < piece ? bytes - off : piece) & ~15ll);
     if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"((const char*)ptr + off), "r"(size) : "memory");

@@ -251,8 +251,8 @@ __global__ void __launch_bounds__(SK_THREADS, MT <= 2 ? 2 : 1) gemm_skinny_kerne
   int ltl = 0, lrr = 0;
   if (total_rounds > 0) { load_round(ltl, lrr, wA0, wA1); advance(ltl, lrr); }
   if (total_rounds > 1) { load_round(ltl, lrr, wB0, wB1); advance(ltl, lrr); }
-  if (threadIdx.x == 0)
-    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
+  if (threadIdx.x < 32)                                   // (a lane a piece: one thread's loop was 40 turns long for a wide matrix)
+    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z, lane, 32);
   pdl_launch_dependents();
   if (a.pdl) {
     pdl_wait();
@@ -530,20 +530,23 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   const int first_unit = me * 32 + lane;
   float next_w_first = 0.f;
   if (EPI == EPI_ACC && a.nn_x && first_unit < SK_ROWS * a.M && tile < a.n_tiles) next_w_first = a.nn_w[tile * SK_ROWS + (first_unit & 15)];
-  if (threadIdx.x == 0)
-    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
+  if (threadIdx.x < 32)                                   // (a lane a piece: one thread's loop was 40 turns long for a wide matrix)
+    l2_prefetch_share(a.next_w, a.next_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z, lane, 32);
   pdl_launch_dependents();
   if (a.pdl) {
     pdl_wait();
     request_x();
   }
   FELLM_TRACE_WAITED();
-  // the rows' sums of squares come in parts (at most 128 a row): warp w asks for those of rows w and w + WARPS
-  // now and adds them up, always in the same order, behind the product, where nobody waits for them
-  float rs_part[2][4];
+  // the rows' sums of squares come in parts (at most 128 a row): warp w asks for those of rows w and (with more rows
+  // than warps) w + WARPS now, beside x; a lane adds its parts up once x is there (one register a row is then held
+  // through the product: held as they came, eight of them cost the kernel its weights in flight), and the lanes'
+  // sums are added behind the product, where nobody waits for them.  Always in the same order.
+  constexpr int RS_H = (MT * 8 > WARPS) ? 2 : 1;
+  float rs_part[RS_H][4], rs_sum[RS_H];
   if (a.rs_ssq) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < RS_H; ++h) {
       const int r = warp + h * WARPS;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
@@ -573,6 +576,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   }
 
   sk_cp_async_wait_all();
+  if (a.rs_ssq) {
+#pragma unroll
+    for (int h = 0; h < RS_H; ++h) rs_sum[h] = (rs_part[h][0] + rs_part[h][1]) + (rs_part[h][2] + rs_part[h][3]);
+  }
   if (NORM) {
     // RMSNorm (crates/backend-cpu/src/kernels/norm.rs:6-39): a warp per row, whole rows
     const float4* gamma_s = (const float4*)(smem + a.gamma_offset);
@@ -657,10 +664,10 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
   if (a.rs_ssq) {
     // RMSNorm's factor of each row (crates/backend-cpu/src/kernels/norm.rs:6-39)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < RS_H; ++h) {
       const int r = warp + h * WARPS;
       if (r < a.M) {                                   // (whole warps)
-        const float ss = warp_sum((rs_part[h][0] + rs_part[h][1]) + (rs_part[h][2] + rs_part[h][3]));
+        const float ss = warp_sum(rs_sum[h]);
         if (lane == 0) rs_scale[r] = 1.0f / sqrtf(ss / (float)a.K + a.rs_eps);
       }
     }
@@ -739,7 +746,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemm_lean_kern
             p0[q] = 0.f; p1[q] = 0.f;
             if (idx < parts) {
               const int sr = own_first ? idx : idx >> a.log2_warps_k, w = own_first ? 0 : idx & (a.warps_k - 1);
-              const float* pp = cg::this_cluster().map_shared_rank(mine_e, sr);
+              const float* pp = a.splits > 1 ? cg::this_cluster().map_shared_rank(mine_e, sr) : mine_e;
               p0[q] = pp[w * warp_stride];
               if (EPI == EPI_SWIGLU) p1[q] = pp[w * warp_stride + 8 * MP];
             }
