@@ -27,7 +27,7 @@ namespace cgx = cooperative_groups;
 #define UM_SPIN_LIMIT (1u << 26)
 #define UM_WAIT_NS 1000000000ull       // one second: far beyond any healthy wait, short enough to stay responsive
 
-enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3 };
+enum { EPI_STORE = 0, EPI_ACC = 1, EPI_SWIGLU = 2, EPI_F32 = 3, EPI_CONV = 4 };      // 4: only the product of few rows
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -603,7 +603,14 @@ struct SwapArgs {
   // 1 / sqrt(sum_p rs_ssq[t * rs_parts + p] / K + rs_eps) before the bias: RMSNorm(x) W^T with the row's
   // factor taken out of the product (crates/backend-cpu/src/kernels/norm.rs:6-39 has the norm)
   const float* rs_ssq; int rs_parts; float rs_eps;
+  // EPI_CONV: the gated short convolution behind a ShortConv mixer's input product in a decode step (every token a
+  // request of its own).  W's rows come in blocks of 16 B / 16 C / 16 X rows of 16 channels; a tile is two such blocks
+  // (96 rows); out is y bfloat16 [M, N / 3]; the state of token t is conv_state + row_slot[t] * conv_slot_stride,
+  // [taps - 1][N / 3] float32, and moves on by one token.
+  const float* conv_w; const float* conv_bias; float* conv_state; const int* row_slot; long long conv_slot_stride; int conv_taps;
 };
+#define SW_CONV_ROWS 96
+#define SW_CONV_MAX_TAPS 4
 
 // What the next call of fellm_gemm_umma_swap is to hand on or to take over (see SwapArgs); taken and cleared
 // by every call.
@@ -650,7 +657,11 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   float* recv = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + (size_t)stages * stage_bytes);
   const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[SW_MAX_STAGES]), accfull = smem_u32(&bars[2 * SW_MAX_STAGES]);
   const int split = S > 1 ? (int)cgx::this_cluster().block_rank() : 0;
-  const int n0 = blockIdx.y * UM_BM;
+  // EPI_CONV: a tile is 96 weight rows (two blocks of 16 channels' B, C and X rows); the MMA still spans 128 rows,
+  // the last 32 of which read whatever the stage holds there and are never looked at
+  constexpr int TILE_ROWS = EPI == EPI_CONV ? SW_CONV_ROWS : UM_BM;
+  const int n0 = blockIdx.y * TILE_ROWS;
+  const int tx_bytes = TILE_ROWS * UM_BK * 2 + a.mt * UM_BK * 2;       // what the two copies of a stage bring
   const int kb_total = (a.K + UM_BK - 1) / UM_BK;
   const int kb0 = (int)((long long)kb_total * split / S), kb1 = (int)((long long)kb_total * (split + 1) / S);
   const int nkb = kb1 - kb0;
@@ -680,12 +691,25 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   bool res_ok[2] = {false, false};
   float4 nn_g = make_float4(0.f, 0.f, 0.f, 0.f);    // the next norm's weights of this lane's four columns
   if (EPI == EPI_ACC && a.nn_x) nn_g = *(const float4*)(a.nn_w + n0 + 4 * lane);
+  // EPI_CONV: lanes 0..3 and 12..15 hold the B rows of four channels each (C: four lanes on, X: eight lanes on); they
+  // run the convolution of those channels and ask for the taps now
+  const bool conv_lane = EPI == EPI_CONV && lane < 24 && (lane % 12) < 4;
+  const int conv_ch = n0 / 3 + 16 * (lane / 12) + 4 * (lane % 12);         // first of the lane's four channels
+  float cw[EPI == EPI_CONV ? 4 : 1][SW_CONV_MAX_TAPS], cb[4] = {0.f, 0.f, 0.f, 0.f};
+  if (EPI == EPI_CONV && conv_lane) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int tt = 0; tt < SW_CONV_MAX_TAPS; ++tt) cw[c][tt] = tt < a.conv_taps ? a.conv_w[(size_t)(conv_ch + c) * a.conv_taps + tt] : 0.f;
+      if (a.conv_bias) cb[c] = a.conv_bias[conv_ch + c];
+    }
+  }
 
   if (warp == 0 && lane == 0) {
     // weights first: they do not depend on the kernel in front
     const int first = nkb < stages ? nkb : stages;
     for (int i = 0; i < first; ++i) {
-      mbar_expect_tx(full0 + 8 * i, stage_bytes);
+      mbar_expect_tx(full0 + 8 * i, tx_bytes);
       tma_load_2d(tiles + i * stage_bytes, &map_w, (kb0 + i) * UM_BK, n0, full0 + 8 * i);
     }
     l2_prefetch_share(a.next_w, a.next_bytes, blockIdx.y * S + blockIdx.x, gridDim.y * S);
@@ -695,7 +719,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     for (int it = first; it < nkb; ++it) {
       const int s = it % stages;
       if (!mbar_wait(empty0 + 8 * s, (it / stages - 1) & 1, a.status, 111)) break;
-      mbar_expect_tx(full0 + 8 * s, stage_bytes);
+      mbar_expect_tx(full0 + 8 * s, tx_bytes);
       tma_load_2d(tiles + s * stage_bytes, &map_w, (kb0 + it) * UM_BK, n0, full0 + 8 * s);
       tma_load_2d(tiles + s * stage_bytes + SW_W_BYTES, &map_x, (kb0 + it) * UM_BK, 0, full0 + 8 * s);
     }
@@ -750,7 +774,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int q = warp & 3, row = q * 32 + lane;
     const bool done = mbar_wait(accfull, 0, a.status, 113);
     __syncwarp();
-    if (done) {
+    if (done && (EPI != EPI_CONV || q < 3)) {                  // (EPI_CONV: rows 96..127 are nobody's)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       // token t goes to rank t % S, slot [t / S][my rank][row] there
       const unsigned recv0 = smem_u32(recv);
@@ -782,7 +806,46 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       if (n + 2 < a.N) v.z += a.bias[n + 2];
       if (n + 3 < a.N) v.w += a.bias[n + 3];
     }
-    if (EPI == EPI_SWIGLU) {
+    if (EPI == EPI_CONV) {
+      // B, C and X as the stored product would round them; bx = B*X; conv = bx*w[Lc-1] + sum_t state[t]*w[t]
+      // (oldest first); y = C*(conv + bias); the state moves on by one (crates/backend-cpu/src/kernels/shortconv.rs:61-106)
+      v.x = __bfloat162float(__float2bfloat16_rn(v.x)); v.y = __bfloat162float(__float2bfloat16_rn(v.y));
+      v.z = __bfloat162float(__float2bfloat16_rn(v.z)); v.w = __bfloat162float(__float2bfloat16_rn(v.w));
+      float cv[4], xv[4];
+      cv[0] = __shfl_down_sync(0xffffffffu, v.x, 4); cv[1] = __shfl_down_sync(0xffffffffu, v.y, 4);
+      cv[2] = __shfl_down_sync(0xffffffffu, v.z, 4); cv[3] = __shfl_down_sync(0xffffffffu, v.w, 4);
+      xv[0] = __shfl_down_sync(0xffffffffu, v.x, 8); xv[1] = __shfl_down_sync(0xffffffffu, v.y, 8);
+      xv[2] = __shfl_down_sync(0xffffffffu, v.z, 8); xv[3] = __shfl_down_sync(0xffffffffu, v.w, 8);
+      if (conv_lane) {
+        const int H = a.conv_taps - 1, d = a.N / 3;
+        float* st = a.conv_state + (size_t)a.row_slot[t] * a.conv_slot_stride + conv_ch;
+        float4 hist[SW_CONV_MAX_TAPS - 1];
+#pragma unroll
+        for (int tt = 0; tt < SW_CONV_MAX_TAPS - 1; ++tt) hist[tt] = tt < H ? *(const float4*)(st + (size_t)tt * d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float bv[4] = {v.x, v.y, v.z, v.w};
+        float bx[4], y[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          bx[c] = bv[c] * xv[c];
+          float wlast = 0.f;
+#pragma unroll
+          for (int tt = 0; tt < SW_CONV_MAX_TAPS; ++tt) if (tt == H) wlast = cw[c][tt];
+          float conv = bx[c] * wlast;
+#pragma unroll
+          for (int tt = 0; tt < SW_CONV_MAX_TAPS - 1; ++tt) {
+            const float hc = c == 0 ? hist[tt].x : (c == 1 ? hist[tt].y : (c == 2 ? hist[tt].z : hist[tt].w));
+            if (tt < H) conv = fmaf(hc, cw[c][tt], conv);
+          }
+          y[c] = cv[c] * (conv + cb[c]);
+        }
+        const __nv_bfloat162 y0 = __floats2bfloat162_rn(y[0], y[1]), y1 = __floats2bfloat162_rn(y[2], y[3]);
+        *(uint2*)((bf16*)a.out + (size_t)t * a.ldo + conv_ch) = make_uint2(*(const unsigned*)&y0, *(const unsigned*)&y1);
+#pragma unroll
+        for (int tt = 0; tt < SW_CONV_MAX_TAPS - 1; ++tt) {
+          if (tt < H) *(float4*)(st + (size_t)tt * d) = (tt + 1 < H) ? hist[tt + 1 < SW_CONV_MAX_TAPS - 1 ? tt + 1 : tt] : make_float4(bx[0], bx[1], bx[2], bx[3]);
+        }
+      }
+    } else if (EPI == EPI_SWIGLU) {
       // rows in blocks of 16: 8 gate, then the 8 up rows of the same features: lanes 4b+2, 4b+3 hold the up values of lanes 4b, 4b+1
       float4 up;
       up.x = __shfl_down_sync(0xffffffffu, v.x, 2); up.y = __shfl_down_sync(0xffffffffu, v.y, 2);
@@ -928,12 +991,12 @@ static void plan_swap_s(int M, int N, int K, int splits, SwapPlan* p) {
   p->stages = stages;
   p->smem = (size_t)stages * stage_bytes + recv + 1024;
 }
-static bool plan_swap(int M, int N, int K, SwapPlan* p) {
+static bool plan_swap(int M, int N, int K, SwapPlan* p, int tile_rows = UM_BM) {
   if (M < 1 || M > 64 || K % 8) return false;
   static int max_splits = 0;
   if (!max_splits) max_splits = env_int("FELLM_B200_SWAP_SPLITS", 8);
   const int n_sm = fellm_sm_count();
-  const int n_tiles = ceil_div(N, UM_BM), kb_total = ceil_div(K, UM_BK);
+  const int n_tiles = ceil_div(N, tile_rows), kb_total = ceil_div(K, UM_BK);
   for (int splits = 8; splits > 1; splits /= 2) {
     if (splits > max_splits || splits > kb_total || n_tiles * splits > n_sm) continue;
     plan_swap_s(M, N, K, splits, p);
@@ -985,4 +1048,45 @@ FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bi
     case EPI_F32: return launch_swap<EPI_F32>(mw, mx, a, p.smem, n_tiles, stream);
     default: return FELLM_ERR_ARG;
   }
+}
+
+// A decode step's ShortConv input product and gated convolution in one launch, for 17..64 tokens (every token a
+// request of its own; fellm_gemm_skinny_conv is the same for up to 16): W [3d, K] with its rows in blocks of 16 B /
+// 16 C / 16 X rows of 16 channels, d a multiple of 32, 2..4 taps; y bfloat16 [M, d]; state float32, slot_stride floats
+// between slots, row_slot[t] the slot of token t.  x may be the weighted rows of a handed-on norm
+// (fellm_gemm_umma_row_scale before the call).  FELLM_ERR_SIZE for what it does not take (fellm_gemm_umma_swap_conv_takes).
+static bool swap_conv_ok(int M, int N, int K, int taps) {
+  return M >= 1 && M <= 64 && N > 0 && N % SW_CONV_ROWS == 0 && K >= 8 && K % 8 == 0 && taps >= 2 && taps <= SW_CONV_MAX_TAPS;
+}
+FELLM_API int fellm_gemm_umma_swap_conv_takes(int M, int N, int K, int taps) {
+  SwapPlan p;
+  return (swap_conv_ok(M, N, K, taps) && plan_swap(M, N, K, &p, SW_CONV_ROWS)) ? 1 : 0;
+}
+FELLM_API int fellm_gemm_umma_swap_conv(const void* x, const void* W, const float* bias, const float* conv_w, const float* conv_bias,
+                                        float* state, long long slot_stride, const int* row_slot, int taps, void* y,
+                                        int M, int N, int K, int lda, int ldw, int ldy, int* status, cudaStream_t stream) {
+  const SwapHandoff h = g_swap_handoff;                  // taken and cleared whatever this call returns
+  g_swap_handoff = SwapHandoff{nullptr, nullptr, nullptr, 0, nullptr, 0, 0.f};
+  const NextWeights nw = take_next_weights();
+  if (M <= 0 || N <= 0) return 0;
+  if (!x || !W || !y || !conv_w || !state || !row_slot || K <= 0) return FELLM_ERR_ARG;
+  if (!swap_conv_ok(M, N, K, taps) || (lda % 8) || (ldw % 8) || (ldy % 4) || (slot_stride % 4) || ((uintptr_t)x & 15) || ((uintptr_t)W & 15) ||
+      ((uintptr_t)state & 15) || ((uintptr_t)y & 7)) return FELLM_ERR_SIZE;
+  if (h.nn_x) return FELLM_ERR_ARG;
+  if (h.rs_ssq && h.rs_parts < 1) return FELLM_ERR_ARG;
+  SwapPlan p;
+  if (!plan_swap(M, N, K, &p, SW_CONV_ROWS)) return FELLM_ERR_SIZE;
+  CUtensorMap mw, mx;
+  int e = make_map(&mw, W, N, K, ldw, SW_CONV_ROWS);
+  if (e) return e;
+  e = make_map(&mx, x, M, K, lda, p.mt);
+  if (e) return e;
+  SwapArgs a = {};
+  a.bias = bias; a.out = y; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldy;
+  a.mt = p.mt; a.splits = p.splits; a.stages = p.stages;
+  a.next_w = nw.ptr; a.next_bytes = nw.bytes;
+  a.rs_ssq = h.rs_ssq; a.rs_parts = h.rs_parts; a.rs_eps = h.rs_eps;
+  a.conv_w = conv_w; a.conv_bias = conv_bias; a.conv_state = state; a.row_slot = row_slot; a.conv_slot_stride = slot_stride;
+  a.conv_taps = taps;
+  return launch_swap<EPI_CONV>(mw, mx, a, p.smem, N / SW_CONV_ROWS, stream);
 }

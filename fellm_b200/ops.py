@@ -206,13 +206,21 @@ _conv_takes_cache = {}
 
 
 def conv_product_takes(M: int, N: int, K: int, taps: int) -> bool:
-    """Whether gemm_bf16_conv runs a product of these sizes (decode steps of up to 16 requests,
-    K of 1024..1280 in whole chunks)."""
+    """Whether gemm_bf16_conv runs a product of these sizes: decode steps of up to 16 requests on the weight-streaming
+    kernel (K of 1024..1280 in whole chunks), of 17..64 requests on the tcgen05 product of few rows (channels a multiple
+    of 32, up to 4 taps)."""
     key = (M, N, K, taps)
     hit = _conv_takes_cache.get(key)
     if hit is None:
-        f = _fn("gemm_skinny", "fellm_gemm_skinny_conv_takes", [_c_int, _c_int, _c_int, _c_int])
-        hit = _conv_takes_cache[key] = bool(f(M, N, K, taps))
+        if M <= 16:
+            f = _fn("gemm_skinny", "fellm_gemm_skinny_conv_takes", [_c_int, _c_int, _c_int, _c_int])
+            hit = bool(f(M, N, K, taps))
+        else:
+            f = _fn("gemm_umma", "fellm_gemm_umma_swap_conv_takes", [_c_int, _c_int, _c_int, _c_int])
+            # measured on B200: a step of 32 rows at width 1024 0.629 -> 0.604 ms, of 64 rows 0.849 -> 0.842 ms, but at
+            # width 2048 (64 rows) 1.298 -> 1.318 ms: tiles of 96 rows cost the wider product more than the launch saves
+            hit = bool(_swap_rows(M, N) and FUSE_SWAP_CONV and K <= SWAP_CONV_MAX_K and f(M, N, K, taps))
+        _conv_takes_cache[key] = hit
     return hit
 
 
@@ -233,6 +241,20 @@ def gemm_bf16_conv(x, w_blocked, bias, conv_w, conv_bias, state, row_slot, *, no
     if out is None:
         out = torch.empty((M, d), dtype=torch.bfloat16, device=x.device)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    if M > 16:
+        # 17..64 requests: the tcgen05 product of few rows, the convolution in its owners' epilogue
+        if norm is not None or x.dtype != torch.bfloat16:
+            raise KernelError("gemm_bf16_conv: more than 16 rows take bfloat16 rows (normed before, or a handed-on norm's)")
+        if not conv_product_takes(M, N, K, taps):
+            raise KernelError(f"gemm_bf16_conv does not take a product of {M} x {N} x {K} with {taps} taps")
+        if row_scale is not None:
+            _announce_row_scale(row_scale, M, N, K, own_plan=True)
+        f = _fn("gemm_umma", "fellm_gemm_umma_swap_conv",
+                [_c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p])
+        _check(f(_p(x), _p(w_blocked), _p(bias), _p(conv_w), _p(conv_bias), _p(state), state.stride(0), _p(row_slot), taps,
+                 _p(out), M, N, K, x.stride(0), w_blocked.stride(0), out.stride(0), _p(umma_status(x.device)), _stream()),
+               "gemm_umma_swap_conv")
+        return out
     _announce_next("gemm_skinny", w_blocked, M)
     if row_scale is not None:
         assert norm is None
@@ -334,6 +356,8 @@ def fast_gemm_modules():
 _umma_status = {}
 USE_UMMA = os.environ.get("FELLM_B200_UMMA", "1") != "0"
 USE_UMMA_SWAP = os.environ.get("FELLM_B200_UMMA_SWAP", "1") != "0"
+FUSE_SWAP_CONV = os.environ.get("FELLM_B200_FUSE_SWAP_CONV", "1") != "0"     # the convolution in that product's epilogue (17..64 rows)
+SWAP_CONV_MAX_K = int(os.environ.get("FELLM_B200_SWAP_CONV_MAX_K", 1536))
 SWAP_MIN_ROWS = int(os.environ.get("FELLM_B200_SWAP_MIN_ROWS", 17))     # fewer rows: the weight-streaming kernel (norm and convolution fused)
 SWAP_MAX_N = 16384                                                       # wider (the vocabulary head): the persistent tcgen05 product
 

@@ -63,7 +63,7 @@ class ShortConv(Mixer):
             scale = None
             if h is not None:
                 x, norm, scale = h.xg, None, (h.ssq, h.parts, xn.norm.eps)
-            elif isinstance(xn, LazyNorm) and xn.fusable_with(w_in):
+            elif ctx.n_rows <= 16 and isinstance(xn, LazyNorm) and xn.fusable_with(w_in):
                 x, norm = xn.x, (xn.norm.w["weight"], xn.norm.eps)
             else:
                 x, norm = (xn.tensor() if isinstance(xn, LazyNorm) else xn), None

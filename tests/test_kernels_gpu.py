@@ -149,8 +149,8 @@ def test_decode_conv_product_equals_product_then_convolution(M, d, K, lc, use_bi
     """A decode step's ShortConv input product with the convolution in its epilogue: the same y and
     the same states, to the bit, as the product and the convolution kernel one after the other."""
     torch.manual_seed(M + d)
-    assert ops.conv_product_takes(M, 3 * d, K, lc) and not ops.conv_product_takes(17, 3 * d, K, lc)
-    assert not ops.conv_product_takes(M, 3 * d, 2048, lc)
+    assert ops.conv_product_takes(M, 3 * d, K, lc) and not ops.conv_product_takes(65, 3 * d, K, lc)
+    assert not ops.conv_product_takes(M, 3 * d, 2048, lc)            # (17..64 rows are another kernel's: the next test)
     w_in = ops.block_bcx_rows((torch.randn(3 * d, K, device=DEV) * 0.05).bfloat16())
     b_in = ops.block_bcx_rows(torch.randn(3 * d, device=DEV)) if use_bias else None
     conv_w = torch.randn(d, lc, device=DEV)
@@ -844,4 +844,52 @@ def test_handed_on_norm_into_the_convolution_product(M):
     assert torch.equal(got, ref) and torch.equal(st_a, st_b)
     fused = ops.gemm_bf16(res, w_in, norm=(nw, 1e-5))
     assert torch.allclose(bcx.float(), fused.float(), rtol=2e-2, atol=2e-2)
+    ops.forget_norm_handoff()
+
+
+@pytest.mark.parametrize("M,d,K,lc,use_bias,handed_on", [(17, 1024, 1024, 3, False, True), (64, 1024, 1024, 3, False, True), (40, 2048, 2048, 4, True, False),
+                                                          (33, 1536, 1536, 2, True, True), (24, 96, 72, 3, False, False), (50, 1024, 4608, 3, False, False)])
+def test_decode_conv_product_of_17_to_64_rows_equals_product_then_convolution(M, d, K, lc, use_bias, handed_on, monkeypatch):
+    """A decode step's ShortConv input product of 17..64 requests with the convolution in the epilogue of the tcgen05
+    product of few rows (tiles of 96 weight rows = two blocks of 16 channels): the same y and the same states, to the
+    bit, as that product and the convolution kernel one after the other; also behind a handed-on norm."""
+    g = torch.Generator().manual_seed(M + d + lc)
+    monkeypatch.setattr(ops, "SWAP_CONV_MAX_K", 8192)        # (the engine takes it up to K = 1536; the kernel any K)
+    monkeypatch.setattr(ops, "_conv_takes_cache", {})
+    assert ops.conv_product_takes(M, 3 * d, K, lc)
+    assert not ops.conv_product_takes(65, 3 * d, K, lc) and not ops.conv_product_takes(M, 3 * d, K, 5)
+    w_in = ops.block_bcx_rows((torch.randn(3 * d, K, generator=g) * 0.05).bfloat16().to(DEV))
+    b_in = ops.block_bcx_rows(torch.randn(3 * d, generator=g).to(DEV)) if use_bias else None
+    conv_w = torch.randn(d, lc, generator=g).to(DEV)
+    conv_b = torch.randn(d, generator=g).to(DEV) if use_bias else None
+    state = torch.randn(70, 2, lc - 1, d, generator=g).to(DEV)
+    slots = torch.randperm(70, generator=g)[:M].tolist()
+    scale = None
+    if handed_on:
+        assert K == d
+        res = (torch.randn(M, K, generator=g) * 2).to(DEV)
+        y0 = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+        w0 = (torch.randn(K, K, generator=g) * 0.05).bfloat16().to(DEV)
+        nw = (torch.rand(K, generator=g) + 0.5).to(DEV)
+        ops.forget_norm_handoff()
+        ops.reserve_norm_handoff(DEV, 2048)
+        ops.expect_norm(res, nw)
+        ops.gemm_bf16(y0, w0, out=res, accumulate=True)
+        h = ops.norm_handoff(res, nw)
+        assert h is not None
+        x, scale = h.xg, (h.ssq, h.parts, 1e-5)
+    else:
+        x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    st_a, st_b = state.clone(), state.clone()
+    for step in range(3):                                   # the state is carried from launch to launch
+        y = ops.gemm_bf16_conv(x, w_in, b_in, conv_w, conv_b, st_a[:, 1], i32(slots), row_scale=scale)
+        bcx = ops.gemm_bf16(x, w_in, b_in, row_scale=scale)
+        ref = ops.shortconv(bcx, conv_w, conv_b, st_b[:, 1], i32(slots), i32(list(range(M + 1))), i32(list(range(M))),
+                            M, True, blocked=True)
+        assert torch.equal(y, ref), (step, (y.float() - ref.float()).abs().max())
+        assert torch.equal(st_a, st_b), step
+        if not handed_on:
+            x = (x.float() * 0.9 + 0.1).bfloat16()
+    untouched = [s for s in range(70) if s not in slots]
+    assert torch.equal(st_a[untouched], state[untouched]) and torch.equal(st_a[:, 0], state[:, 0])
     ops.forget_norm_handoff()
