@@ -163,7 +163,13 @@ class Scheduler:
             if not self.cache.can_admit():
                 self.counters["admission_waits"] += 1
                 return
-            need = 1 if self.cache.paged else 0         # room for one token (scheduler.rs:728-786)
+            # FeLLM admits on room for one token (scheduler.rs:728-786) and fails the batch when pages run out
+            # mid-run; here a request that does not fit is preempted and recomputed, so one is admitted beside
+            # running requests only when its whole prompt (which for a preempted request includes what it had
+            # generated) and one token more fit the free pages: admitted on less it is cut page by page, dropped
+            # and preempted again, each time with its prompt to run anew (measured on a pool of 45 pages under 40
+            # slots: 1,624 preemptions and 31% of all tokens run twice with the one-token rule)
+            need = -(-(len(r.prompt) + 1) // self.cache.page_tokens) if self.cache.paged else 0
             if need > self.cache.free_pages() and self.running:
                 self.counters["admission_waits"] += 1
                 return                                  # waits; the head of the queue blocks the rest

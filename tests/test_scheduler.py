@@ -146,17 +146,40 @@ def test_shrinks_portions_then_preempts_newest_and_tokens_do_not_change():
     assert b.cache.free_pages() == b.cache.n_pages
 
 
-def test_prefill_portion_shrinks_to_the_pages_left():
+def test_a_prompt_that_does_not_fit_the_free_pages_waits():
+    """Beside running requests one is admitted only when its whole prompt and one token more fit the free pages."""
     b = FakeBackend(page_tokens=4, max_tokens=24, max_requests=4)   # 6 pages
     s = Scheduler(b, 64, 64)
     r0 = s.enqueue_ids(list(range(1, 15)), G(2))            # 14 tokens -> 4 pages
     evs = s.step()
-    r1 = s.enqueue_ids(list(range(1, 13)), G(2))            # wants 3 pages, 2 are free
+    r1 = s.enqueue_ids(list(range(1, 13)), G(2))            # 12 tokens + 1 want 4 pages, 2 are free
     evs += s.step()
-    assert (r1, 8, False) in b.batches[-1] and s.counters["shrunk"] == 1
+    assert b.batches[-1] == [(r0, 1, True)] and s.counters["admission_waits"] >= 1 and s.counters["shrunk"] == 0
+    assert [r.id for r in s.waiting] == [r1]
     toks, done = run_all(s)
     done.update({e.req: e.stats for e in evs if e.kind == "done"})
-    assert set(done) == {r0, r1}
+    assert set(done) == {r0, r1} and done[r1].predicted_tokens == 2 and s.counters["preempted"] == 0
+    assert b.cache.free_pages() == b.cache.n_pages
+
+
+def test_prefill_portion_shrinks_to_the_pages_left():
+    """A request is admitted when its prompt fits, but its prompt runs in portions, and meanwhile a decoding request
+    may take a page: the portion that no longer fits is cut to the pages left (or left out of the step)."""
+    alone = {}
+    prompts = [[5, 1, 4, 2, 6, 3, 9], list(range(1, 12))]
+    for i, p in enumerate(prompts):
+        s = Scheduler(FakeBackend(max_tokens=64), 64, 64)
+        rid = s.enqueue_ids(p, G(6 if i else 12))
+        alone[i] = run_all(s)[0][rid]
+    b = FakeBackend(page_tokens=4, max_tokens=20, max_requests=4)   # 5 pages
+    s = Scheduler(b, 64, 4)                                 # portions of up to 4 tokens
+    r0 = s.enqueue_ids(prompts[0], G(12))                   # 7 tokens: 2 pages, growing to 5
+    s.step(); s.step()
+    r1 = s.enqueue_ids(prompts[1], G(6))                    # 11 tokens + 1: 3 pages, 3 are free: admitted
+    toks, done = run_all(s)
+    assert s.counters["shrunk"] >= 1
+    assert toks[r0][-len(alone[0]):] == alone[0][-len(toks[r0]):] and toks[r1] == alone[1]
+    assert set(done) >= {r1} and b.cache.free_pages() == b.cache.n_pages
 
 
 def test_cancel():
