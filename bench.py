@@ -403,7 +403,7 @@ def run_workload(shape, workload, hbm, layers=None):
     rng = np.random.default_rng(SHAPES[shape][3])
     c = engine.config
     if workload == "mixed":
-        run_mixed_workload(engine, np.random.default_rng(0), 4, 8)          # kernels loaded, graphs of the common shapes captured
+        run_mixed_workload(engine, np.random.default_rng(0), 32, 8)         # every kernel of such a run loaded, graphs of the common shapes captured
         out = run_mixed_workload(engine, rng, 32, 128)
     else:
         run_concurrent_workload(engine, np.random.default_rng(0), 64, 128, 8, 0.8, hbm)
