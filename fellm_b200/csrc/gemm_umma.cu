@@ -285,6 +285,166 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------------
+// K over a cluster of two: a product of a few hundred rows (prompt portions beside decode tokens) with a narrow N
+// has few 128 x 128 tiles for 148 SMs and a long K for each of them.  Here every tile is the work of TWO CTAs, each
+// with half of the k-blocks (own TMA, own MMAs, own tensor memory, as in the kernel above); the second CTA's epilogue
+// warps send their float32 partial tile to the first CTA's shared memory (st.shared::cluster, rows 528 bytes apart),
+// arrive on a barrier there, and the first CTA's epilogue adds the two parts (own first, then the other's: a fixed
+// order) and runs the epilogue.  One tile a cluster, no tile loop.  Waits bounded: status 131 producer, 132 MMA,
+// 133 accumulator, 134 the other CTA's part.
+#define UK_STAGES 4
+#define UK_RECV_LD (UM_BM + 4)        // floats between rows of the received tile
+__device__ __forceinline__ unsigned cluster_ctarank();
+__device__ __forceinline__ unsigned mapa_u32(unsigned smem_addr, unsigned rank);
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr);
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity, int* status, int code) {
+  // (the phase was completed by arrivals of another CTA: acquire at cluster scope, so that what it stored before is seen)
+  const unsigned long long t0 = global_ns();
+  for (unsigned i = 0; i < UM_SPIN_LIMIT; ++i) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63) == 63 && global_ns() - t0 > UM_WAIT_NS) break;
+  }
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void st_cluster_v4(unsigned addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(UM_THREADS)
+gemm_umma_ksplit_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, UmmaArgs a) {
+  FELLM_TRACE_SCOPE(TRACE_GEMM_UMMA);
+  constexpr int BN = 128, STAGE_BYTES = (UM_BM + BN) * UM_BK * 2;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  __shared__ __align__(8) unsigned long long bars[2 * UK_STAGES + 2];    // full[], empty[], accumulator done, the other's part here
+  __shared__ unsigned tmem_base_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  float* recv = reinterpret_cast<float*>(smem_raw + (tiles - smem_u32(smem_raw)) + (size_t)UK_STAGES * STAGE_BYTES);
+  const unsigned full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[UK_STAGES]);
+  const unsigned accfull = smem_u32(&bars[2 * UK_STAGES]), recvfull = smem_u32(&bars[2 * UK_STAGES + 1]);
+  const unsigned rank = cluster_ctarank();
+  const int k_blocks = (a.K + UM_BK - 1) / UM_BK;
+  const int kb_lo = rank == 0 ? 0 : k_blocks / 2, kb_hi = rank == 0 ? k_blocks / 2 : k_blocks;     // (k_blocks >= 2: the launcher checks)
+  const int m_tiles = (a.M + UM_BM - 1) / UM_BM;
+  const int t = blockIdx.x >> 1;
+  const int m0 = (t % m_tiles) * UM_BM, n0 = (t / m_tiles) * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UK_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(accfull, 1);
+    mbar_init(recvfull, 8);                                  // the other CTA's eight epilogue warps
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_s)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  cgx::this_cluster().sync();                                // both CTAs run and their barriers are set up
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const unsigned tmem_base = tmem_base_s;
+  pdl_launch_dependents();
+  pdl_wait(); FELLM_TRACE_WAITED();                        // A is the output of the kernel before this one
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = kb_lo, it = 0; kb < kb_hi; ++kb, ++it) {
+        const int s = it % UK_STAGES;
+        if (it >= UK_STAGES && !mbar_wait(empty0 + 8 * s, (it / UK_STAGES - 1) & 1, a.status, 131)) break;
+        const unsigned dst = tiles + s * STAGE_BYTES;
+        mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+        tma_load_2d(dst, &map_a, kb * UM_BK, m0, full0 + 8 * s);
+        tma_load_2d(dst + UM_BM * UM_BK * 2, &map_w, kb * UM_BK, n0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const unsigned idesc = umma_idesc(UM_BM, BN);
+      bool ok = true;
+      for (int kb = kb_lo, it = 0; kb < kb_hi; ++kb, ++it) {
+        const int s = it % UK_STAGES;
+        ok = mbar_wait(full0 + 8 * s, (it / UK_STAGES) & 1, a.status, 132);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const unsigned sa = tiles + s * STAGE_BYTES, sb = sa + UM_BM * UM_BK * 2;
+        const unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+        for (int k = 0; k < UM_BK / 16; ++k)
+          umma_f16(tmem_base, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (it | k) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      if (ok) umma_commit(accfull);
+    }
+  } else {
+    // epilogue warps: TMEM lanes 32*(warp%4) .. +32 = output rows; two warps share a quarter, a column half each
+    const int q = warp & 3, half = (warp - 2) >> 2, row = q * 32 + lane;
+    const int m = m0 + row;
+    constexpr int CHUNKS = BN / 2 / 32;                       // 2
+    float4 res[EPI == EPI_ACC ? CHUNKS : 1][8];
+    bool res_ok[CHUNKS];
+#pragma unroll
+    for (int ch = 0; ch < CHUNKS; ++ch) {
+      const int n = n0 + half * (BN / 2) + ch * 32;
+      res_ok[ch] = EPI == EPI_ACC && rank == 0 && m < a.M && n + 32 <= a.N && (a.ldo % 4) == 0;
+      if (EPI == EPI_ACC && res_ok[ch]) {
+        const float4* src = (const float4*)((const float*)a.out + (size_t)m * a.ldo + n);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) res[ch][j] = src[j];
+      }
+    }
+    const bool done = mbar_wait(accfull, 0, a.status, 133);
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    if (rank == 1) {
+      // this CTA's part goes to the first CTA, row by row as the tensor memory gives it
+      const unsigned there = mapa_u32(smem_u32(recv), 0);
+      if (done) {
+#pragma unroll
+        for (int ch = 0; ch < CHUNKS; ++ch) {
+          const int c0 = half * (BN / 2) + ch * 32;
+          float v[32];
+          tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_cluster_v4(there + (unsigned)((row * UK_RECV_LD + c0 + 4 * j) * 4), make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(recvfull, 0));       // (release at cluster scope: the stores above come first)
+    } else {
+      const bool got = mbar_wait_cluster(recvfull, 0, a.status, 134);
+      if (done && got) {
+#pragma unroll
+        for (int ch = 0; ch < CHUNKS; ++ch) {
+          const int c0 = half * (BN / 2) + ch * 32;
+          float v[32];
+          tmem_ld32(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+          const float4* other = reinterpret_cast<const float4*>(recv + row * UK_RECV_LD + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 o = other[j];
+            v[4 * j] += o.x; v[4 * j + 1] += o.y; v[4 * j + 2] += o.z; v[4 * j + 3] += o.w;
+          }
+          if (m < a.M && n0 + c0 < a.N) store_chunk<EPI>(a, v, m, n0 + c0, (EPI == EPI_ACC && res_ok[ch]) ? res[ch] : nullptr);
+        }
+      }
+    }
+  }
+  // common exit: every role comes here, also after a wait that gave up.  The second CTA may leave before the first
+  // (nobody reads its shared memory); the first leaves after it has taken the other's part, or given up on it.
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(BN) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster, on the two SMs of a TPC, work on ONE tile
 // of 256 rows x BN columns.  Each CTA brings its own 128 rows of A and HALF of the tile's W rows
 // (BN / 2) by TMA into its own shared memory; the MMA, issued by one thread of the pair's first
@@ -506,6 +666,16 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaA
   return launch_k_class(launch_class_for_rows(a.M, 0), kern, dim3(2 * pairs, 1, 1), dim3(UP_THREADS, 1, 1), smem, stream, 2, ma, mw, a);
 }
 
+template <int EPI>
+static int launch_ksplit(const CUtensorMap& ma, const CUtensorMap& mw, const UmmaArgs& a, cudaStream_t stream) {
+  const size_t smem = (size_t)UK_STAGES * (UM_BM + 128) * UM_BK * 2 + (size_t)UM_BM * UK_RECV_LD * sizeof(float) + 1024;
+  auto kern = gemm_umma_ksplit_kernel<EPI>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int total = ceil_div(a.N, 128) * ceil_div(a.M, UM_BM);
+  return launch_k_class(launch_class_for_rows(a.M, 0), kern, dim3(2 * total, 1, 1), dim3(UM_THREADS, 1, 1), smem, stream, 2, ma, mw, a);
+}
+
 // status: device int32 that a role sets (101 producer, 102/104 MMA, 103 epilogue) if a wait ran out.
 FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
                               int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
@@ -545,6 +715,20 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
   int e = make_map(&ma, A, M, K, lda, UM_BM);
   if (e) return e;
   UmmaArgs a; a.bias = bias; a.out = out; a.status = status; a.M = M; a.N = N; a.K = K; a.ldo = ldo;
+  // few tiles and a long K (a few hundred rows, a narrow N): two CTAs a 128 x 128 tile, half of K each
+  static int ksplit = -1;
+  if (ksplit < 0) { const char* ev = getenv("FELLM_B200_UMMA_KSPLIT"); ksplit = (ev && ev[0] == '0') ? 0 : 1; }
+  if (ksplit && 2 * ceil_div(N, 128) * m_tiles <= n_sm && kb >= 8) {
+    e = make_map(&mw, W, N, K, ldw, 128);
+    if (e) return e;
+    switch (epi) {
+      case EPI_STORE: return launch_ksplit<EPI_STORE>(ma, mw, a, stream);
+      case EPI_ACC: return launch_ksplit<EPI_ACC>(ma, mw, a, stream);
+      case EPI_SWIGLU: return launch_ksplit<EPI_SWIGLU>(ma, mw, a, stream);
+      case EPI_F32: return launch_ksplit<EPI_F32>(ma, mw, a, stream);
+      default: return FELLM_ERR_ARG;
+    }
+  }
   if (choice >= 2) {
     const bool bn256 = choice == 2;
     e = make_map(&mw, W, N, K, ldw, bn256 ? 128 : 64);           // a CTA's half of the tile's W rows

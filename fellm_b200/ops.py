@@ -385,7 +385,8 @@ def check_umma_status(device):
             what = ("the TMA decode attention" if code == 301 else
                     "the tcgen05 prefill attention" if 311 <= code <= 317 else
                     "the tcgen05 product of few rows" if 111 <= code <= 113 else
-                    "the tcgen05 product on CTA pairs" if 121 <= code <= 124 else "the tcgen05 product")
+                    "the tcgen05 product on CTA pairs" if 121 <= code <= 124 else
+                    "the tcgen05 product with K over two CTAs" if 131 <= code <= 134 else "the tcgen05 product")
             raise KernelError(f"{what} gave up waiting on a barrier (role {code})")
 
 

@@ -334,7 +334,8 @@ def test_gemm_bf16_store_acc_f32(M, N, K):
     assert torch.allclose(out.double().cpu(), res.double().cpu() + want, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (8, 7168, 1536), (14, 1024, 3072), (2048, 4608, 1024), (1900, 1000, 200), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 4608, 1024), (8, 4608, 1024), (11, 2048, 2048), (8, 8192, 2048), (8, 7168, 1536), (14, 1024, 3072),
+                                   (200, 512, 1024), (520, 1024, 1536), (130, 96, 600), (2048, 4608, 1024), (1900, 1000, 200), (64, 4608, 1024), (50, 1024, 2048), (8, 320, 144), (40, 64, 72), (64, 200, 136), (100, 328, 200), (513, 192, 64)])
 def test_gemm_bf16_swiglu_epilogue(M, F, K):
     g = torch.Generator().manual_seed(F)
     x = torch.randn(M, K, generator=g).bfloat16()
@@ -558,7 +559,8 @@ def test_attention_prefill_finds_one_far_key(far, qpos, tcgen05, monkeypatch):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 144, 144), (300, 1000, 1000), (2048, 1024, 4608),
                                    (513, 3072, 1024), (1000, 200, 72), (64, 1024, 4608), (64, 1024, 1024), (48, 3072, 1024),
-                                   (128, 2048, 1000), (33, 1000, 4608)])
+                                   (128, 2048, 1000), (33, 1000, 4608),
+                                   (520, 1536, 7168), (130, 200, 4096), (600, 1024, 1024), (65, 9000, 512), (200, 1000, 520)])
 def test_gemm_umma_tcgen05(M, N, K):
     """The tcgen05 / TMEM / TMA product by itself: against float64, against the mma.sync product,
     and its bounded waits must not have run out.  (Products of up to 64 rows that the weight-streaming
