@@ -754,10 +754,10 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
 }
 
 // ------------------------------------------------------------------------------------------------
-// Few rows (a decode step of 17..64 requests): the product is bound by reading W once, and a
-// 128-row MMA fed with tokens would be three quarters empty.  So the operands change places:
+// Few rows (a decode step of 17..128 requests): the product is bound by reading W once, and a
+// 128-row MMA fed with a few tokens would be mostly empty.  So the operands change places:
 // D[n, t] = sum_k W[n, k] x[t, k], the 128 rows of the MMA are WEIGHT rows, its N the step's tokens
-// (16..64 columns of tensor memory).  A CTA owns one tile of 128 weight rows and one slice of K;
+// (16..128 columns of tensor memory).  A CTA owns one tile of 128 weight rows and one slice of K;
 // the slices of a tile are the ranks of a cluster (1, 2, 4 or 8), enough of them to spread the matrix
 // over the SMs.  The TMA thread asks for the tile's weights BEFORE it waits for the kernel in
 // front (they do not depend on it), for x after.  Token t of the tile belongs to rank t % S: every
@@ -774,10 +774,11 @@ FELLM_API int fellm_gemm_umma(const void* A, const void* W, const float* bias, v
 #define SW_WARPS 8
 #define SW_W_BYTES (UM_BM * UM_BK * 2)          // 16 KB: 128 weight rows x 64 k
 #define SW_MAX_STAGES 12
+#define SW_MAX_ROWS 128                         // tokens of a step this kernel takes
 
 struct SwapArgs {
   const float* bias; void* out; int* status;
-  int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..64)
+  int M, N, K, ldo, mt, splits, stages;         // mt: token columns of the MMA (a multiple of 16, 16..128)
   const void* next_w; long long next_bytes;     // the next product's weights, asked into L2 (or null)
   // EPI_ACC as the producer of the next RMSNorm's input (nn_x null: not asked for; N a multiple of 128): beside
   // out += ..., nn_x[t, n] = bfloat16(out[t, n] * nn_w[n]) and nn_ssq[t * (N / 128) + tile] = the sum of
@@ -833,7 +834,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * SW_MAX_STAGES + 1];     // full[], empty[], accumulator done
   __shared__ unsigned tmem_base_s;
-  __shared__ float rs_scale[64];                       // the norm factors of this rank's tokens (a.rs_ssq)
+  __shared__ float rs_scale[SW_MAX_ROWS];              // the norm factors of this rank's tokens (a.rs_ssq)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = a.stages, stage_bytes = SW_W_BYTES + a.mt * UM_BK * 2;
@@ -849,7 +850,7 @@ gemm_umma_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int kb_total = (a.K + UM_BK - 1) / UM_BK;
   const int kb0 = (int)((long long)kb_total * split / S), kb1 = (int)((long long)kb_total * (split + 1) / S);
   const int nkb = kb1 - kb0;
-  const unsigned tmem_cols = a.mt <= 32 ? 32u : 64u;
+  const unsigned tmem_cols = a.mt <= 32 ? 32u : (a.mt <= 64 ? 64u : 128u);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -1168,7 +1169,8 @@ static void plan_swap_s(int M, int N, int K, int splits, SwapPlan* p) {
   const int stage_bytes = SW_W_BYTES + p->mt * UM_BK * 2;
   const size_t recv = (size_t)ceil_div(p->mt, splits) * splits * UM_BM * sizeof(float);
   int stages = ceil_div(kb_total, splits);
-  int fit = (int)(((size_t)budget_kb * 1024 - 1024 - recv) / stage_bytes);
+  const int budget = p->mt > 64 ? 220 : budget_kb;            // (more than 64 tokens: their partial rows alone take up to 64 KB)
+  int fit = (int)(((size_t)budget * 1024 - 1024 - recv) / stage_bytes);
   if (fit < 2) fit = 2;
   if (stages > fit) stages = fit;
   if (stages > SW_MAX_STAGES) stages = SW_MAX_STAGES;
@@ -1176,7 +1178,7 @@ static void plan_swap_s(int M, int N, int K, int splits, SwapPlan* p) {
   p->smem = (size_t)stages * stage_bytes + recv + 1024;
 }
 static bool plan_swap(int M, int N, int K, SwapPlan* p, int tile_rows = UM_BM) {
-  if (M < 1 || M > 64 || K % 8) return false;
+  if (M < 1 || M > SW_MAX_ROWS || K % 8) return false;
   static int max_splits = 0;
   if (!max_splits) max_splits = env_int("FELLM_B200_SWAP_SPLITS", 8);
   const int n_sm = fellm_sm_count();
@@ -1194,10 +1196,10 @@ static bool plan_swap(int M, int N, int K, SwapPlan* p, int tile_rows = UM_BM) {
 // Whether fellm_gemm_umma_swap takes the product (1) or not (0).
 FELLM_API int fellm_gemm_umma_swap_takes(int M, int N, int K) {
   SwapPlan p;
-  return (M >= 1 && M <= 64 && N >= 1 && K >= 8 && plan_swap(M, N, K, &p)) ? 1 : 0;
+  return (M >= 1 && M <= SW_MAX_ROWS && N >= 1 && K >= 8 && plan_swap(M, N, K, &p)) ? 1 : 0;
 }
 
-// out[M, N] = x[M, K] W[N, K]^T for M <= 64 rows with the operands' places changed (see above).
+// out[M, N] = x[M, K] W[N, K]^T for M <= 128 rows with the operands' places changed (see above).
 // Same epilogues and status word as fellm_gemm_umma (111..113 for this kernel's roles).
 FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bias, void* out, int epi, int M, int N, int K,
                                    int lda, int ldw, int ldo, int* status, cudaStream_t stream) {
@@ -1234,13 +1236,13 @@ FELLM_API int fellm_gemm_umma_swap(const void* x, const void* W, const float* bi
   }
 }
 
-// A decode step's ShortConv input product and gated convolution in one launch, for 17..64 tokens (every token a
+// A decode step's ShortConv input product and gated convolution in one launch, for 17..128 tokens (every token a
 // request of its own; fellm_gemm_skinny_conv is the same for up to 16): W [3d, K] with its rows in blocks of 16 B /
 // 16 C / 16 X rows of 16 channels, d a multiple of 32, 2..4 taps; y bfloat16 [M, d]; state float32, slot_stride floats
 // between slots, row_slot[t] the slot of token t.  x may be the weighted rows of a handed-on norm
 // (fellm_gemm_umma_row_scale before the call).  FELLM_ERR_SIZE for what it does not take (fellm_gemm_umma_swap_conv_takes).
 static bool swap_conv_ok(int M, int N, int K, int taps) {
-  return M >= 1 && M <= 64 && N > 0 && N % SW_CONV_ROWS == 0 && K >= 8 && K % 8 == 0 && taps >= 2 && taps <= SW_CONV_MAX_TAPS;
+  return M >= 1 && M <= SW_MAX_ROWS && N > 0 && N % SW_CONV_ROWS == 0 && K >= 8 && K % 8 == 0 && taps >= 2 && taps <= SW_CONV_MAX_TAPS;
 }
 FELLM_API int fellm_gemm_umma_swap_conv_takes(int M, int N, int K, int taps) {
   SwapPlan p;

@@ -208,7 +208,7 @@ _conv_takes_cache = {}
 def conv_product_takes(M: int, N: int, K: int, taps: int) -> bool:
     """Whether gemm_bf16_conv runs a product of these sizes: decode steps of up to 16 requests on the weight-streaming
     kernel (K of 1024..1280 in whole chunks), of 17..64 requests on the tcgen05 product of few rows (channels a multiple
-    of 32, up to 4 taps)."""
+    of 32, up to 4 taps; the kernel itself takes up to 128 rows)."""
     key = (M, N, K, taps)
     hit = _conv_takes_cache.get(key)
     if hit is None:
@@ -218,8 +218,10 @@ def conv_product_takes(M: int, N: int, K: int, taps: int) -> bool:
         else:
             f = _fn("gemm_umma", "fellm_gemm_umma_swap_conv_takes", [_c_int, _c_int, _c_int, _c_int])
             # measured on B200: a step of 32 rows at width 1024 0.629 -> 0.604 ms, of 64 rows 0.849 -> 0.842 ms, but at
-            # width 2048 (64 rows) 1.298 -> 1.318 ms: tiles of 96 rows cost the wider product more than the launch saves
-            hit = bool(_swap_rows(M, N) and FUSE_SWAP_CONV and K <= SWAP_CONV_MAX_K and f(M, N, K, taps))
+            # width 2048 (64 rows) 1.298 -> 1.318 ms: tiles of 96 rows cost the wider product more than the launch saves;
+            # at 96 and 128 rows the two ways lie within 2% of each other (width 1024: 1.061 / 1.065 and 1.283 / 1.271
+            # ms; width 1536: 1.289 / 1.264 and 1.580 / 1.543 ms), so the kernel of its own stays there
+            hit = bool(_swap_rows(M, N) and FUSE_SWAP_CONV and M <= SWAP_CONV_MAX_ROWS and K <= SWAP_CONV_MAX_K and f(M, N, K, taps))
         _conv_takes_cache[key] = hit
     return hit
 
@@ -358,7 +360,9 @@ USE_UMMA = os.environ.get("FELLM_B200_UMMA", "1") != "0"
 USE_UMMA_SWAP = os.environ.get("FELLM_B200_UMMA_SWAP", "1") != "0"
 FUSE_SWAP_CONV = os.environ.get("FELLM_B200_FUSE_SWAP_CONV", "1") != "0"     # the convolution in that product's epilogue (17..64 rows)
 SWAP_CONV_MAX_K = int(os.environ.get("FELLM_B200_SWAP_CONV_MAX_K", 1536))
+SWAP_CONV_MAX_ROWS = int(os.environ.get("FELLM_B200_SWAP_CONV_MAX_ROWS", 64))
 SWAP_MIN_ROWS = int(os.environ.get("FELLM_B200_SWAP_MIN_ROWS", 17))     # fewer rows: the weight-streaming kernel (norm and convolution fused)
+SWAP_MAX_ROWS = int(os.environ.get("FELLM_B200_SWAP_MAX_ROWS", 128))     # more rows: the persistent tcgen05 product (width 1024, 128 rows: 1.68 ms a step there, 1.28 here)
 SWAP_MAX_N = 16384                                                       # wider (the vocabulary head): the persistent tcgen05 product
 
 
@@ -456,7 +460,7 @@ def _single_shot(M: int, N: int, K: int, norm: bool) -> bool:
 # into x is followed by an RMSNorm with weights g"; norm_handoff(x, g) gives the reader what was left, if
 # it is still good (same tensor, same weights, nothing written to x since).
 NORM_HANDOFF = os.environ.get("FELLM_B200_NORM_HANDOFF", "1") != "0"
-HANDOFF_MAX_ROWS = 64       # up to 16 rows: the weight-streaming kernel on both sides; 17..64: the tcgen05 product of few rows
+HANDOFF_MAX_ROWS = 128       # up to 16 rows: the weight-streaming kernel on both sides; 17..128: the tcgen05 product of few rows
 _handoff_bufs = {}          # device -> (xg bfloat16 [16 * width], ssq float32 [16 * width / 16], width)
 _handoff_retired = []
 _expected_norm = None       # (data_ptr of x, norm weights)
@@ -521,12 +525,12 @@ def norm_handoff(x, norm_w):
 
 def _swap_rows(M: int, N: int) -> bool:
     """Whether gemm_bf16 gives a product of M rows and N columns to the tcgen05 product of few rows."""
-    return USE_UMMA and USE_UMMA_SWAP and max(SWAP_MIN_ROWS, 17) <= M <= 64 and N <= SWAP_MAX_N
+    return USE_UMMA and USE_UMMA_SWAP and max(SWAP_MIN_ROWS, 17) <= M <= SWAP_MAX_ROWS and N <= SWAP_MAX_N
 
 
 def row_scale_takes(M: int, N: int, K: int) -> bool:
     """Whether a product of these sizes can take a handed-on norm's input: up to 16 rows the single-shot
-    weight-streaming kernel, 17..64 rows the tcgen05 product of few rows."""
+    weight-streaming kernel, 17..128 rows the tcgen05 product of few rows."""
     if K % 8:
         return False
     if M <= 16:
@@ -616,8 +620,8 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
     # (measured at 64 rows: 14 us against 26 us for [1024, 4608], 8 against 9-11 for K = 1024, but 13
     # against 11 for the 9216 rows of gate/up, which stays with tcgen05 beyond 32 rows)
     expected = residual_written(out) if accumulate else None
-    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= 64 and N <= SWAP_MAX_N and (row_scale is None or M > 16):
-        # a decode step of 17..64 rows: tcgen05 with the weights as the MMA's 128 rows
+    if umma_ok and USE_UMMA_SWAP and SWAP_MIN_ROWS <= M <= SWAP_MAX_ROWS and N <= SWAP_MAX_N and (row_scale is None or M > 16):
+        # a decode step of 17..128 rows: tcgen05 with the weights as the MMA's 128 rows
         _announce_next("gemm_umma", w, M)
         if row_scale is not None:
             _announce_row_scale(row_scale, M, N, K)
@@ -705,7 +709,7 @@ def gemm_bf16_argmax(x, w, bias, keys, out_tokens, *, norm=None, row_scale=None)
 
 
 def gemm_umma_swap(x, w, bias=None, *, out, epi: int, written: bool = False):
-    """The tcgen05 product for up to 64 rows (weights as the MMA's rows, K split over a cluster),
+    """The tcgen05 product for up to 128 rows (weights as the MMA's rows, K split over a cluster),
     callable by itself.  epi: 0 store bfloat16, 1 add into float32, 2 SiLU(gate)*up, 3 store float32."""
     M, K = x.shape
     if epi == _EPI_ACC and not written:

@@ -149,8 +149,8 @@ def test_decode_conv_product_equals_product_then_convolution(M, d, K, lc, use_bi
     """A decode step's ShortConv input product with the convolution in its epilogue: the same y and
     the same states, to the bit, as the product and the convolution kernel one after the other."""
     torch.manual_seed(M + d)
-    assert ops.conv_product_takes(M, 3 * d, K, lc) and not ops.conv_product_takes(65, 3 * d, K, lc)
-    assert not ops.conv_product_takes(M, 3 * d, 2048, lc)            # (17..64 rows are another kernel's: the next test)
+    assert ops.conv_product_takes(M, 3 * d, K, lc) and not ops.conv_product_takes(129, 3 * d, K, lc)
+    assert not ops.conv_product_takes(M, 3 * d, 2048, lc)            # (17..128 rows are another kernel's: the next test)
     w_in = ops.block_bcx_rows((torch.randn(3 * d, K, device=DEV) * 0.05).bfloat16())
     b_in = ops.block_bcx_rows(torch.randn(3 * d, device=DEV)) if use_bias else None
     conv_w = torch.randn(d, lc, device=DEV)
@@ -667,11 +667,11 @@ def test_attention_prefill_window_edge(hd, pt, window):
             assert hit == inside, (window, row, edge, inside)
 
 
-@pytest.mark.parametrize("M", [1, 16, 17, 33, 40, 48, 63, 64])
+@pytest.mark.parametrize("M", [1, 16, 17, 33, 40, 48, 63, 64, 65, 96, 100, 128])
 @pytest.mark.parametrize("N,K", [(1024, 1024), (1024, 4608), (3072, 1024), (9216, 1024), (2048, 2048), (200, 136), (515, 328),
                                  (128, 64), (6144, 2048), (1536, 7168)])
 def test_gemm_umma_swap_few_rows(M, N, K):
-    """The tcgen05 product of a decode step of up to 64 rows (weights as the MMA's 128 rows, tokens as
+    """The tcgen05 product of a decode step of up to 128 rows (weights as the MMA's 128 rows, tokens as
     its columns, K over a cluster): every epilogue against float64, the same bits on every run, and
     its bounded waits must not have run out.  Sizes with ragged tiles in N and in K included."""
     x, w, want = _gemm_case(M, N, K, seed=11)
@@ -742,7 +742,7 @@ def test_head_argmax_without_logits(M, N, K, use_norm):
 @pytest.mark.parametrize("M,N,K,d_next", [(8, 1024, 1024, 3072), (1, 1024, 4608, 9216), (16, 2048, 2048, 6144), (5, 1024, 1024, 65536),
                                            (13, 512, 1280, 512), (8, 2048, 8192, 2048), (8, 1536, 1536, 4608), (16, 1536, 7168, 14336),
                                            (17, 1024, 4608, 9216), (40, 1024, 1024, 3072), (64, 2048, 2048, 6144), (33, 1536, 1536, 4608),
-                                           (24, 128, 64, 200)])
+                                           (24, 128, 64, 200), (65, 1024, 1024, 3072), (128, 1024, 4608, 9216), (100, 2048, 2048, 6144)])
 def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
     """The product that adds into the residual rows leaves them weighted for the next RMSNorm, with the sums of
     squares in parts; the next product scales its sums by the rows' factors.  Against the plain norm and product."""
@@ -762,7 +762,7 @@ def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
     assert torch.equal(res, plain_sum)
     h = ops.norm_handoff(res, nw)
     # up to 16 rows the weight-streaming kernel does it (a part = 16 columns), beyond that the tcgen05 product (128)
-    assert h is not None and h.rows == M and h.parts == N // (16 if M <= 16 else 128)
+    assert h is not None and h.rows == M and h.parts == N // (16 if M <= 16 else 128)      # (17..128 rows)
     assert ops.norm_handoff(res, nw.clone()) is None and ops.norm_handoff(res.clone(), nw) is None
     assert torch.equal(h.xg, (res * nw).bfloat16())
     ssq = h.ssq[:M * h.parts].view(M, h.parts)
@@ -775,29 +775,41 @@ def test_rmsnorm_handed_on_from_the_adding_product(M, N, K, d_next):
     bias = torch.randn(n2, generator=g)
     want = xn.double() @ w.double().T + bias.double()
     scale = (h.ssq, h.parts, eps)
-    atol = 2e-2 * 0.05 * math.sqrt(N) / 8 * 3
+    # Two references.  (1) Float64 sums of the very bfloat16 operands a kernel read: only the float32 accumulation
+    # (2^-24 a term, far fewer in practice) and the row factor's float32 lie between.  (2) The unrounded norm: the
+    # rounding of a normed value to bfloat16 is at most 2^-8 of it and, over a row, adds like independent errors
+    # of standard deviation <= 2^-8 / sqrt(3); seven of those for every element, on top of (1).
+    wd = w.double()
+    r = 1.0 / torch.sqrt((res.double().cpu() ** 2).mean(-1, keepdim=True) + eps)
+    xg = h.xg.double().cpu()
+    exact_handed = (xg @ wd.T) * r + bias.double()
+    acc = 2e-6 * ((xg.abs() @ wd.abs().T) * r + bias.abs().double()) + 1e-6
+    rounding = 7 * 2.0 ** -8 / math.sqrt(3) * torch.sqrt((xn.double() ** 2) @ (wd ** 2).T) + acc
     assert ops.row_scale_takes(M, n2, N)
     got = ops.gemm_bf16(h.xg, w.to(DEV), bias.to(DEV), out_dtype=torch.float32, row_scale=scale)
-    assert torch.allclose(got.double().cpu(), want, rtol=4e-3, atol=atol)
-    # the norm inside the product rounds x*r*g, this way rounds x*g: each lies within the tolerance of the
-    # float64 result, so they lie within twice that of each other
+    assert bool(((got.double().cpu() - exact_handed).abs() <= acc).all())
+    assert bool(((got.double().cpu() - want).abs() <= rounding).all())
+    # the norm inside the product (up to 16 rows) or in front of it rounds x*r*g, the handed-on rows are x*g rounded
     if M <= 16:
         fused = ops.gemm_bf16(res, w.to(DEV), bias.to(DEV), out_dtype=torch.float32, norm=(nw, eps))
     else:
-        fused = ops.gemm_bf16(ops.rmsnorm(res, nw, eps, torch.bfloat16), w.to(DEV), bias.to(DEV), out_dtype=torch.float32)
-    assert torch.allclose(fused.double().cpu(), want, rtol=4e-3, atol=atol)
-    assert torch.allclose(got, fused, rtol=8e-3, atol=2 * atol)
+        xb = ops.rmsnorm(res, nw, eps, torch.bfloat16)
+        fused = ops.gemm_bf16(xb, w.to(DEV), bias.to(DEV), out_dtype=torch.float32)
+        exact_normed = xb.double().cpu() @ wd.T + bias.double()
+        assert bool(((fused.double().cpu() - exact_normed).abs() <= acc).all())
+    assert bool(((fused.double().cpu() - want).abs() <= rounding).all())
     got_b = ops.gemm_bf16(h.xg, w.to(DEV), bias.to(DEV), row_scale=scale)
     assert torch.equal(got_b, got.bfloat16())
     if n2 <= 16384 and n2 % 16 == 0:
         wi = ops.interleave_gate_up(w[:n2 // 2].to(DEV), w[n2 // 2:].to(DEV))
         got_s = ops.gemm_bf16(h.xg, wi, swiglu=True, row_scale=scale)
-        gu = want - bias.double()
+        gu = exact_handed - bias.double()
         gate, up = gu[:, :n2 // 2], gu[:, n2 // 2:]
         ref_s = torch.nn.functional.silu(gate) * up
-        # gate and up are each within (atol + rtol |.|) of the float64 sums; SiLU's slope is at most 1.1; the
-        # product is rounded to bfloat16
-        bound = ((atol + 4e-3 * gate.abs()) * 1.1 * up.abs() + (atol + 4e-3 * up.abs()) * torch.nn.functional.silu(gate).abs()
+        # gate and up are each within `acc` of these sums; SiLU's slope is at most 1.1; the product is rounded to
+        # bfloat16
+        ag, au = acc[:, :n2 // 2], acc[:, n2 // 2:]
+        bound = (ag * 1.1 * up.abs() + au * torch.nn.functional.silu(gate).abs() + ag * au
                  + ref_s.abs() * 2.0 ** -8 + 1e-6)
         assert bool(((got_s.double().cpu() - ref_s).abs() <= bound).all())
     if M <= 16:
@@ -850,22 +862,24 @@ def test_handed_on_norm_into_the_convolution_product(M):
 
 
 @pytest.mark.parametrize("M,d,K,lc,use_bias,handed_on", [(17, 1024, 1024, 3, False, True), (64, 1024, 1024, 3, False, True), (40, 2048, 2048, 4, True, False),
-                                                          (33, 1536, 1536, 2, True, True), (24, 96, 72, 3, False, False), (50, 1024, 4608, 3, False, False)])
-def test_decode_conv_product_of_17_to_64_rows_equals_product_then_convolution(M, d, K, lc, use_bias, handed_on, monkeypatch):
-    """A decode step's ShortConv input product of 17..64 requests with the convolution in the epilogue of the tcgen05
+                                                          (33, 1536, 1536, 2, True, True), (24, 96, 72, 3, False, False), (50, 1024, 4608, 3, False, False),
+                                                          (128, 1024, 1024, 3, False, True), (97, 1024, 1024, 3, True, False)])
+def test_decode_conv_product_of_17_to_128_rows_equals_product_then_convolution(M, d, K, lc, use_bias, handed_on, monkeypatch):
+    """A decode step's ShortConv input product of 17..128 requests with the convolution in the epilogue of the tcgen05
     product of few rows (tiles of 96 weight rows = two blocks of 16 channels): the same y and the same states, to the
     bit, as that product and the convolution kernel one after the other; also behind a handed-on norm."""
     g = torch.Generator().manual_seed(M + d + lc)
-    monkeypatch.setattr(ops, "SWAP_CONV_MAX_K", 8192)        # (the engine takes it up to K = 1536; the kernel any K)
+    monkeypatch.setattr(ops, "SWAP_CONV_MAX_K", 8192)        # (the engine takes it up to K = 1536 and 64 rows; the
+    monkeypatch.setattr(ops, "SWAP_CONV_MAX_ROWS", 128)      # kernel any K and up to 128 rows)
     monkeypatch.setattr(ops, "_conv_takes_cache", {})
     assert ops.conv_product_takes(M, 3 * d, K, lc)
-    assert not ops.conv_product_takes(65, 3 * d, K, lc) and not ops.conv_product_takes(M, 3 * d, K, 5)
+    assert not ops.conv_product_takes(129, 3 * d, K, lc) and not ops.conv_product_takes(M, 3 * d, K, 5)
     w_in = ops.block_bcx_rows((torch.randn(3 * d, K, generator=g) * 0.05).bfloat16().to(DEV))
     b_in = ops.block_bcx_rows(torch.randn(3 * d, generator=g).to(DEV)) if use_bias else None
     conv_w = torch.randn(d, lc, generator=g).to(DEV)
     conv_b = torch.randn(d, generator=g).to(DEV) if use_bias else None
-    state = torch.randn(70, 2, lc - 1, d, generator=g).to(DEV)
-    slots = torch.randperm(70, generator=g)[:M].tolist()
+    state = torch.randn(140, 2, lc - 1, d, generator=g).to(DEV)
+    slots = torch.randperm(140, generator=g)[:M].tolist()
     scale = None
     if handed_on:
         assert K == d
@@ -892,6 +906,6 @@ def test_decode_conv_product_of_17_to_64_rows_equals_product_then_convolution(M,
         assert torch.equal(st_a, st_b), step
         if not handed_on:
             x = (x.float() * 0.9 + 0.1).bfloat16()
-    untouched = [s for s in range(70) if s not in slots]
+    untouched = [s for s in range(140) if s not in slots]
     assert torch.equal(st_a[untouched], state[untouched]) and torch.equal(st_a[:, 0], state[:, 0])
     ops.forget_norm_handoff()

@@ -26,17 +26,18 @@ def check(tag, got, want, dtype):
 
 
 @pytest.mark.parametrize("graphs", [False, True])
-@pytest.mark.parametrize("n_req", [20, 33, 64])
+@pytest.mark.parametrize("n_req", [20, 33, 64, 97])
 def test_many_requests_decode_together(n_req, graphs):
     """Width 1024, heads of 64, pages of 64 tokens, bfloat16: 20, 33 (under graphs: filled up to 24 and 40 rows) and 64 requests with prompts of
-    different lengths decode 8 steps together (some cross a page's edge), directly and from a CUDA
+    different lengths decode 8 steps together, and 97 (104 rows: beyond 64 the few-rows tcgen05 product has TMEM and
+    partial tiles of 128 columns) (some cross a page's edge), directly and from a CUDA
     graph; every row of every step against the plain implementation."""
     n_dec = 8
     rng = np.random.default_rng(n_req)
     lens = [int(x) for x in rng.integers(1, 130, n_req)]
     lens[0], lens[1], lens[2] = 60, 63, 64                   # a page's edge inside the decoded steps
     toks = [tiny.tokens("C", n + n_dec, 300 + i) for i, n in enumerate(lens)]
-    eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs, max_requests=64, max_tokens=64 * 256)
+    eng = tiny.make_engine("C", "bfloat16", page_tokens=64, cuda_graphs=graphs, max_requests=max(64, n_req), max_tokens=64 * 256)
     for i, n in enumerate(lens):
         eng.add_request(i)
         eng.step([StepItem(i, toks[i][:n], [])])
