@@ -160,6 +160,103 @@ __device__ __forceinline__ void load_q(unsigned (&qf)[KS][4], F row_ptr, int lan
   }
 }
 
+// ---- keys as the MMA's rows (decode, up to 8 heads a kv head) ----
+// With one query row a head, S = Q K^T fills 2 of the MMA's 16 rows.  Turned round, S^T = K Q^T has 16 KEYS as the
+// rows and the (up to 8) heads as the 8 columns: half the MMAs, half the scores and exponentials a lane, half the
+// output registers (O^T[dim][head] = V^T P^T).  Thread (g = lane/4, c = lane%4) owns keys g and g+8 of a block of
+// 16 and heads 2c and 2c+1; P^T becomes the B operand by movmatrix (an 8x8 transpose across the warp).
+__device__ __forceinline__ unsigned movmatrix_trans(unsigned x) {
+  unsigned y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+  return y;
+}
+// Query fragments as the B operand: lane (g, c) holds head g's dims ks*16 + 2c, +1 and ks*16 + 8 + 2c, +1.
+template <typename F>
+__device__ __forceinline__ void load_q_as_b(unsigned (&qb)[KS][2], F row_ptr, int lane) {
+  const int g = lane >> 2, c = lane & 3;
+  const bf16* r = row_ptr(g);
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    qb[ks][0] = r ? *(const unsigned*)(r + ks * 16 + 2 * c) : 0u;
+    qb[ks][1] = r ? *(const unsigned*)(r + ks * 16 + 8 + 2 * c) : 0u;
+  }
+}
+// NKT*8 keys at k_s / v_s against the heads in qb; a key counts iff lo <= key0 + i <= hi.  ot[dm] = O^T of dims
+// dm*16 + g (elements 0, 1: heads 2c, 2c+1) and dm*16 + g + 8 (elements 2, 3); m, l per head 2c, 2c+1 (l: this
+// thread's keys only).
+template <int NKT, bool MASKED>
+__device__ __forceinline__ void attend_tile_keys_as_rows(const unsigned (&qb)[KS][2], unsigned k_s, unsigned v_s, int key0,
+                                                         int lo, int hi, float scale_log2, float (&ot)[HD / 16][4],
+                                                         float (&m)[2], float (&l)[2], int lane) {
+  constexpr int KB = NKT / 2;                            // blocks of 16 keys
+  const int g = lane >> 2;
+  float s[KB][4];
+#pragma unroll
+  for (int b = 0; b < KB; ++b) { s[b][0] = s[b][1] = s[b][2] = s[b][3] = 0.f; }
+  // S^T = K Q^T: one ldmatrix.x4 = (keys 0-7, k lo) (keys 8-15, k lo) (keys 0-7, k hi) (keys 8-15, k hi)
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+    for (int b = 0; b < KB; ++b) {
+      const int row = b * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int chunk = ks * 2 + (lane >> 4);
+      unsigned r[4];
+      ldsm_x4(r, k_s + tile_off(row, chunk));
+      mma16816(s[b], r, qb[ks][0], qb[ks][1]);
+    }
+  }
+  float mx[2] = {m[0], m[1]};
+#pragma unroll
+  for (int b = 0; b < KB; ++b) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int key = key0 + b * 16 + g + ((e >> 1) << 3);
+      const float v = (!MASKED || (key >= lo && key <= hi)) ? s[b][e] * scale_log2 : -INFINITY;
+      s[b][e] = v;
+      mx[e & 1] = fmaxf(mx[e & 1], v);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+  }
+  float corr[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    corr[h] = (mx[h] == -INFINITY) ? 1.f : exp2f(m[h] - mx[h]);       // nothing seen yet: keep the zeros
+    m[h] = mx[h];
+    l[h] *= corr[h];
+  }
+#pragma unroll
+  for (int dm = 0; dm < HD / 16; ++dm) { ot[dm][0] *= corr[0]; ot[dm][1] *= corr[1]; ot[dm][2] *= corr[0]; ot[dm][3] *= corr[1]; }
+#pragma unroll
+  for (int b = 0; b < KB; ++b) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = (mx[e & 1] == -INFINITY) ? 0.f : exp2f(s[b][e] - mx[e & 1]);
+      s[b][e] = p;
+      l[e & 1] += p;
+    }
+  }
+  // O^T += V^T P^T: V^T's A fragments by ldmatrix.trans = (keys 0-7, dims lo) (keys 0-7, dims hi) (keys 8-15, dims lo)
+  // (keys 8-15, dims hi)
+#pragma unroll
+  for (int b = 0; b < KB; ++b) {
+    const unsigned p0 = movmatrix_trans(pack_bf16(s[b][0], s[b][1]));       // keys 2c, 2c+1 of head g
+    const unsigned p1 = movmatrix_trans(pack_bf16(s[b][2], s[b][3]));       // keys 2c+8, 2c+9
+#pragma unroll
+    for (int dm = 0; dm < HD / 16; ++dm) {
+      const int row = b * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int chunk = dm * 2 + ((lane >> 3) & 1);
+      unsigned r[4];
+      ldsm_x4_trans(r, v_s + tile_off(row, chunk));
+      mma16816(ot[dm], r, p0, p1);
+    }
+  }
+}
+
 struct AttnArgs {
   const bf16* q; const bf16* pool; const int* block_table; const int* positions; const int* row_slot;
   const int* item_start;          // prefill: rows of item i are item_start[i] .. item_start[i+1]
@@ -293,9 +390,11 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(AttnAr
 // different keys: they are combined through `merge` ([warp][16][HD + 2] floats of shared memory that
 // no warp reads as a key tile any more) into the CTA's result, which goes to `out` when the CTA is the
 // only one of its (row, kv head), else into the CTA's record of the scratch buffer.
+__device__ __forceinline__ void decode_merge_records(const AttnArgs& a, const float* merge, int t, int g, int r0, int R,
+                                                     int split_index, int n_active, float* cta_rec = nullptr);
 __device__ __forceinline__ void decode_warps_to_cta(const AttnArgs& a, float (&o)[DN][4], float (&m)[2], float (&l)[2],
                                                     float* merge, int warp, int lane, int t, int g, int r0, int R,
-                                                    int split_index, int n_active) {
+                                                    int split_index, int n_active, float* cta_rec = nullptr) {
   const int gq = lane >> 2, c = lane & 3;
   const int SW = HD + 2;
 #pragma unroll
@@ -307,6 +406,33 @@ __device__ __forceinline__ void decode_warps_to_cta(const AttnArgs& a, float (&o
     for (int d = 0; d < DN; ++d) { rec[d * 8 + 2 * c] = o[d][2 * r]; rec[d * 8 + 2 * c + 1] = o[d][2 * r + 1]; }
     if (c == 0) { rec[HD] = m[r]; rec[HD + 1] = l[r]; }
   }
+  decode_merge_records(a, merge, t, g, r0, R, split_index, n_active, cta_rec);
+}
+// The same from the keys-as-rows layout (heads 0..7 only: rows 8..15 of the records are not written and, with R <= 8,
+// not read).
+__device__ __forceinline__ void decode_warps_to_cta_keys_as_rows(const AttnArgs& a, float (&ot)[HD / 16][4], float (&m)[2],
+                                                                 float (&l)[2], float* merge, int warp, int lane, int t,
+                                                                 int g, int R, int split_index, int n_active,
+                                                                 float* cta_rec = nullptr) {
+  const int gq = lane >> 2, c = lane & 3;
+  const int SW = HD + 2;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    l[e] += __shfl_xor_sync(0xffffffffu, l[e], 4);
+    l[e] += __shfl_xor_sync(0xffffffffu, l[e], 8);
+    l[e] += __shfl_xor_sync(0xffffffffu, l[e], 16);
+    float* rec = merge + ((size_t)warp * 16 + 2 * c + e) * SW;
+#pragma unroll
+    for (int dm = 0; dm < HD / 16; ++dm) { rec[dm * 16 + gq] = ot[dm][e]; rec[dm * 16 + gq + 8] = ot[dm][2 + e]; }
+    if (gq == 0) { rec[HD] = m[e]; rec[HD + 1] = l[e]; }
+  }
+  decode_merge_records(a, merge, t, g, 0, R, split_index, n_active, cta_rec);
+}
+// cta_rec: the CTA's record stays in its shared memory ([row][HD + 2] floats) for the cluster's first active CTA to
+// read, instead of going to the scratch buffer.
+__device__ __forceinline__ void decode_merge_records(const AttnArgs& a, const float* merge, int t, int g, int r0, int R,
+                                                     int split_index, int n_active, float* cta_rec) {
+  const int SW = HD + 2;
   __syncthreads();
   const int rows_here = min(16, R - r0);
   for (int i = threadIdx.x; i < rows_here * HD; i += DC_WARPS * 32) {
@@ -326,7 +452,8 @@ __device__ __forceinline__ void decode_warps_to_cta(const AttnArgs& a, float (&o
     if (n_active == 1) {
       a.out[((size_t)t * a.H + h) * HD + d] = __float2bfloat16_rn(at / lt);
     } else {
-      float* rec = a.scratch + (((size_t)t * a.H + h) * a.max_splits + split_index) * SW;
+      float* rec = cta_rec ? cta_rec + (size_t)(r0 + row) * SW
+                           : a.scratch + (((size_t)t * a.H + h) * a.max_splits + split_index) * SW;
       rec[d] = at;
       if (d == 0) { rec[HD] = mx; rec[HD + 1] = lt; }
     }
@@ -547,7 +674,26 @@ __device__ __forceinline__ float2 norm_rope_head64(const bf16* src, bool norm, f
 }
 
 // NS: half-page stages a warp keeps in flight (2: 64 KB a CTA, three CTAs to an SM; 3: 96 KB, two; 4: 128 KB, one).
-template <int NS>
+__device__ __forceinline__ float ld_cluster_f32(unsigned addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned mapa_cta(unsigned smem_addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_barrier() {       // every thread of every CTA of the cluster, the same number of times
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+// KR: keys as the MMA's rows (up to 8 heads a kv head).  CL: the key ranges of a (row, kv head) are the CTAs of
+// one cluster (up to 8): their records stay in shared memory and the first active one adds them up in range order
+// through distributed shared memory, instead of records in a scratch buffer, a fence, a counter and the last CTA
+// reading them back from L2.  Every CTA of the cluster, active or not, passes the same two cluster barriers.
+template <int NS, bool KR, bool CL>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnArgs a, DecodeFuse f, int* status) {
   FELLM_TRACE_SCOPE(TRACE_ATTENTION_DECODE);
@@ -567,10 +713,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   const int s_end = (int)gridDim.x - 1;
   const int s_lo = min(kb / a.split_len, s_end), s_hi = min(pos / a.split_len, s_end);
   pdl_launch_dependents();
-  if (s < s_lo || s > s_hi) return;
+  const bool active = s >= s_lo && s <= s_hi;
+  if (!CL && !active) return;
   const int n_active = s_hi - s_lo + 1;
-  const int k0 = max(kb, s * a.split_len), k1 = s == s_end ? pos + 1 : min(pos + 1, (s + 1) * a.split_len);
   const int R = a.H / a.G;                              // <= 16 (the launcher checks)
+  const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
+  float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
+  float* cta_rec = CL ? merge + DC_WARPS * 16 * (HD + 2) : nullptr;
+  if (active) {
+  const int k0 = max(kb, s * a.split_len), k1 = s == s_end ? pos + 1 : min(pos + 1, (s + 1) * a.split_len);
   const int* bt = a.block_table + (size_t)a.row_slot[t] * a.max_pages;
   const int pg0 = k0 / DT_PT, n_pg = (k1 - 1) / DT_PT - pg0 + 1;
   const bool pages_in_smem = n_pg <= DC_MAX_PAGES;
@@ -579,8 +730,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   if (threadIdx.x < DC_WARPS * NS) at_mbar_init((unsigned)__cvta_generic_to_shared(&bars[threadIdx.x]), 1);
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   __syncthreads();
-  const unsigned base = ((unsigned)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;      // the swizzle is by address
-  float* merge = (float*)(smem_raw + (base - (unsigned)__cvta_generic_to_shared(smem_raw)));  // over the tiles, once the warps are done
   // a warp's NS stages, each the K and the V tile of half a page (32 keys)
   const unsigned stage0 = base + warp * NS * 2 * DT_TILE_B;
   const unsigned bar0 = (unsigned)__cvta_generic_to_shared(&bars[warp * NS]);
@@ -623,14 +772,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
 #pragma unroll
     for (int q = 0; q < NS; ++q) if (q < n_tiles) request(q);
   }
-  unsigned qf[KS][4];
-  load_q(qf, [&](int i) -> const bf16* {
+  auto q_row = [&](int i) -> const bf16* {
     if (i >= R) return nullptr;
     return qkv_row ? q_s + i * HD : a.q + ((size_t)t * a.H + g * R + i) * HD;
-  }, lane);
-  float o[DN][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  };
+  unsigned qf[KR ? 1 : KS][4], qb[KR ? KS : 1][2];
+  float o[KR ? 1 : DN][4], ot[KR ? HD / 16 : 1][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  if constexpr (KR) {
+    load_q_as_b(qb, q_row, lane);
 #pragma unroll
-  for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    for (int d = 0; d < HD / 16; ++d) { ot[d][0] = ot[d][1] = ot[d][2] = ot[d][3] = 0.f; }
+  } else {
+    load_q(qf, q_row, lane);
+#pragma unroll
+    for (int d = 0; d < DN; ++d) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+  }
   const int lo[2] = {k0, k0}, hi[2] = {k1 - 1, k1 - 1};
   for (int q = 0; q < n_tiles; ++q) {
     const unsigned st = stage0 + (q % NS) * 2 * DT_TILE_B, bar = bar0 + (q % NS) * 8;
@@ -667,10 +823,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
         for (int i = (k1 - key0) * CPR + lane; i < DT_HALF * CPR; i += 32) st_shared_zero16(st + DT_TILE_B + tile_off(i / CPR, i % CPR));
         __syncwarp();
       }
-      if (key0 < k0 || key0 + DT_HALF > k1)
-        attend_tile<DT_HALF / 8, true>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
-      else
-        attend_tile<DT_HALF / 8, false>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      const bool edge = key0 < k0 || key0 + DT_HALF > k1;
+      if constexpr (KR) {
+        if (edge) attend_tile_keys_as_rows<DT_HALF / 8, true>(qb, st, st + DT_TILE_B, key0, k0, k1 - 1, a.scale_log2, ot, m, l, lane);
+        else attend_tile_keys_as_rows<DT_HALF / 8, false>(qb, st, st + DT_TILE_B, key0, k0, k1 - 1, a.scale_log2, ot, m, l, lane);
+      } else {
+        if (edge) attend_tile<DT_HALF / 8, true>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+        else attend_tile<DT_HALF / 8, false>(qf, st, st + DT_TILE_B, key0, lo, hi, a.scale_log2, o, m, l, lane);
+      }
     }
     __syncwarp();
     if (q + NS < n_tiles) {
@@ -680,9 +840,45 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, AttnAr
   }
   FELLM_TRACE_MARK(1);
   __syncthreads();                                         // every warp has left its tiles
-  decode_warps_to_cta(a, o, m, l, merge, warp, lane, t, g, 0, R, s - s_lo, n_active);
+  if constexpr (KR) decode_warps_to_cta_keys_as_rows(a, ot, m, l, merge, warp, lane, t, g, R, s - s_lo, n_active, cta_rec);
+  else decode_warps_to_cta(a, o, m, l, merge, warp, lane, t, g, 0, R, s - s_lo, n_active, cta_rec);
   FELLM_TRACE_MARK(2);
-  decode_last_cta_merges(a, &sm_last, t, g, R, n_active);
+  if constexpr (!CL) decode_last_cta_merges(a, &sm_last, t, g, R, n_active);
+  }                                                        // active
+  if constexpr (CL) {
+    cluster_barrier();                                     // the records of all ranges are written
+    if (active && n_active > 1 && s == s_lo) {
+      const int SW = HD + 2;
+      const unsigned mine = (unsigned)__cvta_generic_to_shared(cta_rec);
+      for (int i = threadIdx.x; i < R * HD; i += DC_WARPS * 32) {
+        const int r = i / HD, d = i - r * HD;
+        float mj[8], lj[8], aj[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j < n_active) {
+            const unsigned rec = mapa_cta(mine + (unsigned)(r * SW) * 4u, (unsigned)(s_lo + j));
+            aj[j] = ld_cluster_f32(rec + d * 4);
+            mj[j] = ld_cluster_f32(rec + HD * 4);
+            lj[j] = ld_cluster_f32(rec + (HD + 1) * 4);
+          } else {
+            aj[j] = 0.f; mj[j] = -INFINITY; lj[j] = 0.f;
+          }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, mj[j]);
+        float lt = 0.f, at = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float cj = j < n_active ? exp2f(mj[j] - mx) : 0.f;
+          lt += lj[j] * cj;
+          at += aj[j] * cj;
+        }
+        a.out[((size_t)t * a.H + g * R + r) * HD + d] = __float2bfloat16_rn(at / lt);
+      }
+    }
+    cluster_barrier();                                     // nobody leaves while its record may be read
+  }
 }
 
 // ------------------------------------------------------------------------------------ prefill, TMA
@@ -938,9 +1134,33 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   static int ns_env = -1;
   if (ns_env < 0) { const char* ev = getenv("FELLM_B200_DECODE_STAGES"); ns_env = (ev && ev[0] >= '2' && ev[0] <= '4') ? ev[0] - '0' : 0; }
   const int ns = ns_env ? ns_env : (stages >= 2 && stages <= 4 ? stages : 2);
-  size_t tiles = (size_t)DC_WARPS * ns * 2 * DT_TILE_B, mrg = (size_t)DC_WARPS * 16 * (HD + 2) * sizeof(float);
+  size_t tiles = (size_t)DC_WARPS * ns * 2 * DT_TILE_B, mrg = (size_t)(DC_WARPS + 1) * 16 * (HD + 2) * sizeof(float);
   size_t smem = (tiles > mrg ? tiles : mrg) + 1024;
-  auto kern = ns == 2 ? attention_decode_tma_kernel<2> : (ns == 3 ? attention_decode_tma_kernel<3> : attention_decode_tma_kernel<4>);
+  // up to 8 heads a kv head: the keys as the MMA's rows (FELLM_B200_DECODE_KEYS_AS_ROWS=0: the heads, as with more)
+  static int kr_env = -1;
+  if (kr_env < 0) { const char* ev = getenv("FELLM_B200_DECODE_KEYS_AS_ROWS"); kr_env = (ev && ev[0] == '0') ? 0 : 1; }
+  const bool kr = kr_env && H / G <= 8;
+  // up to 8 key ranges: they are one cluster and merge through its shared memory (FELLM_B200_DECODE_CLUSTER=0: the
+  // scratch buffer and the last CTA, as with more ranges)
+  static int cl_env = -1;
+  if (cl_env < 0) { const char* ev = getenv("FELLM_B200_DECODE_CLUSTER"); cl_env = (ev && ev[0] == '0') ? 0 : 1; }
+  static int n_sm = 0;
+  if (!n_sm) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+  }
+  // ... where all CTAs are resident at once (measured on B200, 16 layers of width 1024, context 2,050..2,250: batch 8,
+  // 6 ranges, 0.374 -> 0.369 ms a step; batch 1, 8 ranges, 0.316 -> 0.310 ms; but batch 64, 1,024 CTAs in pairs over
+  // 2.3 waves, 0.826 -> 0.860 ms: a pair waits for a place for both and for the slower of the two)
+  const int ctas_per_sm = ns == 2 ? 3 : (ns == 3 ? 2 : 1);
+  const bool cl = cl_env && max_splits >= 2 && max_splits <= 8 && (long long)max_splits * G * T <= (long long)n_sm * ctas_per_sm;
+  void (*kern)(const CUtensorMap, AttnArgs, DecodeFuse, int*) = nullptr;
+#define FELLM_PICK(NS_) \
+  kern = kr ? (cl ? attention_decode_tma_kernel<NS_, true, true> : attention_decode_tma_kernel<NS_, true, false>) \
+            : (cl ? attention_decode_tma_kernel<NS_, false, true> : attention_decode_tma_kernel<NS_, false, false>)
+  if (ns == 2) { FELLM_PICK(2); } else if (ns == 3) { FELLM_PICK(3); } else { FELLM_PICK(4); }
+#undef FELLM_PICK
   cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return (int)ce;
   DecodeFuse f;
@@ -950,7 +1170,7 @@ FELLM_API int fellm_attn_decode_tma(const void* q, const void* pool, long long n
   // FELLM_B200_ATTN_PDL=0 launches it the ordinary way)
   static int attn_class = -1;
   if (attn_class < 0) { const char* e = getenv("FELLM_B200_ATTN_PDL"); attn_class = (e && e[0] == '0') ? 0 : 1; }
-  return launch_k_class(qkv ? attn_class : 0, kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, 1, map, a, f, status);
+  return launch_k_class(qkv ? attn_class : 0, kern, dim3(max_splits, G, T), dim3(DC_WARPS * 32), smem, stream, cl ? max_splits : 1, map, a, f, status);
 #else
   return FELLM_ERR_SIZE;
 #endif
