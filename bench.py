@@ -135,7 +135,9 @@ def run_decode(engine, batch, steps, warmup, rng, prompt=PROMPT, context_end=CON
     for i, r in enumerate(reqs):
         slot = engine.add_request(r)
         ids = rng.integers(0, vocab, prompt).tolist()
-        logits = engine.step([StepItem(r, ids, [prompt - 1])])
+        for lo in range(0, prompt, PROMPT):                     # portions of at most PROMPT tokens (--context: longer prompts)
+            part = ids[lo:lo + PROMPT]
+            logits = engine.step([StepItem(r, part, [len(part) - 1] if lo + PROMPT >= prompt else [])])
         rows.append((slot, params, 0))
         first[i:i + 1] = engine.sampler.sample(logits, [rows[-1]])
     engine.check_status()
@@ -466,7 +468,7 @@ def main():
         cfg["num_hidden_layers"] = args.layers
         cfg["full_attn_idxs"] = [i for i in cfg["full_attn_idxs"] if i < args.layers]
     steps = args.steps
-    ctx_end = PROMPT + untimed_steps(steps, warmup) + steps + 16
+    ctx_end = max(PROMPT, args.context) + untimed_steps(steps, warmup) + steps + 16
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
     opts = EngineOptions(dtype="bfloat16", n_ctx=max(ctx_end, CONTEXT_END + 64), n_batch=4096, n_ubatch=2048, page_tokens=64,
                          max_requests=max_batch, max_tokens=max_batch * (max(ctx_end, CONTEXT_END) + 64), cuda_graphs=True)
@@ -482,7 +484,8 @@ def main():
         return 0
     if args.only:
         if args.only == "decode":
-            v, ms, _, _, c0, c1 = run_decode(engine, args.batch, steps, warmup, rng, context_end=args.context + warmup + steps)
+            v, ms, _, _, c0, c1 = run_decode(engine, args.batch, steps, warmup, rng, prompt=args.context,
+                                             context_end=args.context + warmup + steps)
             print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg["num_hidden_layers"], "tokens_per_s": round(v, 1),
                               "ms_per_step": round(ms, 4), "contexts": [c0, c1]}))
         else:
