@@ -823,8 +823,8 @@ def decode_stages(rows: int, kv_heads: int) -> int:
 
 def decode_split(max_len: int, rows: int, kv_heads: int, target: int = 0):
     """(split_len, max_splits): key ranges of a multiple of 64 keys, enough of them to fill the
-    machine.  max_len is rounded up to 1024 so that the choice (and a captured graph) holds
-    while contexts grow."""
+    machine (at most 8, one cluster, while a range then stays within 512 keys).  max_len is
+    rounded up to 1024 so that the choice (and a captured graph) holds while contexts grow."""
     bucket = -(-max(max_len, 1) // 1024) * 1024
     items = max(rows * kv_heads, 1)
     if not target:
