@@ -406,7 +406,20 @@ def norm_fusable(x_f32, w, norm_w) -> bool:
     M, K = x_f32.shape
     return (M <= NORM_FUSE_MAX_ROWS and w.dtype == torch.bfloat16 and x_f32.dtype == torch.float32
             and norm_w.dtype == torch.float32 and K % 8 == 0 and K <= 8192 and w.stride(0) % 8 == 0
-            and x_f32.stride(1) == 1 and x_f32.stride(0) % 4 == 0 and w.stride(1) == 1)
+            and x_f32.stride(1) == 1 and x_f32.stride(0) % 4 == 0 and w.stride(1) == 1
+            and not _wide_on_umma(M, w.shape[0], K))
+
+
+WIDE_GENERAL_N = int(os.environ.get("FELLM_B200_WIDE_GENERAL_N", 32768))
+
+
+def _wide_on_umma(M: int, N: int, K: int) -> bool:
+    """A very wide product (a vocabulary head) of 9..16 rows that the single-shot weight-streaming kernel does not
+    take (K = 1536: six slices, no power of two of K warps) runs on the persistent tcgen05 product behind an
+    RMSNorm kernel of its own: the general weight-streaming kernel with two row tiles is bound by its instructions
+    there (measured on B200, [65536 x 1536]: 83 us at 16 rows, 32 us at 8, 31 us of bytes)."""
+    return (USE_UMMA and 8 < M <= 16 and N >= WIDE_GENERAL_N and K % 8 == 0
+            and not _single_shot(M, N, K, False) and not _single_shot(M, N, K, True))
 
 
 _single_shot_cache = {}
@@ -630,7 +643,8 @@ def gemm_bf16(x, w, bias=None, *, out=None, out_dtype=None, accumulate=False, sw
         if left is not None:
             _handoff = left
         return out
-    skinny = M <= 64 and (M <= 16 or not umma_ok or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
+    skinny = M <= 64 and ((M <= 16 and not (umma_ok and _wide_on_umma(M, N, K))) or not umma_ok
+                          or (_single_shot(M, N, K, norm is not None) and (M <= 32 or N < 8192))
                           or (M <= SKINNY_MAX_ROWS and N < 8192))
     if row_scale is not None and (not skinny or M > 16):
         raise KernelError(f"a product of {M} x {N} x {K} does not take a handed-on norm")

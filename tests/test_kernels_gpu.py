@@ -582,6 +582,31 @@ def test_gemm_umma_tcgen05(M, N, K):
     assert torch.equal(ops.gemm_bf16(xd, wd, out_dtype=torch.float32), got)       # the same bits every run
 
 
+@pytest.mark.parametrize("M", [9, 12, 16])
+def test_a_vocabulary_head_of_9_to_16_rows_off_the_single_shot_kernel(M):
+    """A very wide product whose K the single-shot weight-streaming kernel does not take (1536 = six slices), at 9..16
+    rows: the persistent tcgen05 product behind an RMSNorm kernel, not the general weight-streaming kernel with the
+    norm inside.  Through linear(), as the head calls it; against the plain norm and a float64 product."""
+    from fellm_b200.parts.linear import LazyNorm, linear
+    from fellm_b200.parts.rmsnorm import RMSNorm
+    N, K, eps = 65536, 1536, 1e-5
+    assert ops._wide_on_umma(M, N, K) and not ops._wide_on_umma(8, N, K) and not ops._wide_on_umma(M, N, 1024)
+    g = torch.Generator().manual_seed(M)
+    x = (torch.randn(M, K, generator=g) * 2).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    norm = RMSNorm(dtype="bfloat16", size=K, eps=eps)
+    norm.w = {"weight": (torch.rand(K, generator=g) + 0.5).to(DEV)}
+    assert not ops.norm_fusable(x, w, norm.w["weight"]) and ops.norm_fusable(x[:8], w, norm.w["weight"])
+    got = linear(LazyNorm(x, norm, torch.bfloat16), w, out_dtype=torch.float32)
+    ops.check_umma_status(DEV)
+    xb = ops.rmsnorm(x, norm.w["weight"], eps, torch.bfloat16)
+    assert torch.allclose(xb.float().cpu(), P.rmsnorm(x.cpu(), norm.w["weight"].cpu(), eps), rtol=2 ** -7, atol=1e-6)
+    want = xb.double().cpu() @ w.double().cpu().T               # the rounded rows: what the product read
+    assert torch.allclose(got.double().cpu(), want, rtol=1e-4, atol=1e-4)
+    few = linear(LazyNorm(x[:8], norm, torch.bfloat16), w, out_dtype=torch.float32)        # 8 rows: the norm inside
+    assert torch.allclose(few, got[:8], rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("M,N,K", [(33, 200, 328), (48, 1024, 1024), (64, 2048, 200), (64, 515, 144)])
 def test_gemm_skinny_up_to_64_rows(M, N, K, monkeypatch):
     """The weight-streaming kernel takes up to 64 rows (it is the fallback where the tcgen05 product cannot run)."""
