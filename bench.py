@@ -203,6 +203,38 @@ def run_timeline(engine, batch, context, out_path):
     graph.replay()
     launches = tl.launches(detail=True)
     tl.close()
+    total = write_timeline(out_path, f"batch {batch}, context {context}", launches)
+    for r in reqs:
+        engine.release(r)
+    return len(launches), total
+
+
+def run_prefill_timeline(engine, tokens, out_path, rng):
+    """The kernel timeline of one prefill step of `tokens` ids of one request (FELLM_B200_TRACE=1): three steps
+    first (the shape's CUDA graph exists from the second), then one traced step."""
+    import torch
+    from fellm_b200.engine import StepItem
+    from fellm_b200.engine.timeline import Timeline
+    vocab = engine.spec.vocab_size
+
+    def one(tag):
+        engine.add_request(tag)
+        engine.step([StepItem(tag, rng.integers(0, vocab, tokens).tolist(), [tokens - 1])])
+        torch.cuda.synchronize()
+        engine.release(tag)
+    for i in range(3):
+        one(f"pw{i}")
+    tl = Timeline()
+    one("px")
+    tl.reset()
+    one("pt")
+    launches = tl.launches(detail=True)
+    tl.close()
+    return len(launches), write_timeline(out_path, f"prefill of {tokens} tokens", launches)
+
+
+def write_timeline(out_path, title, launches):
+    from fellm_b200.engine.timeline import Timeline
     total = launches[-1].end_us - launches[0].begin_us
     agg, prev_end = {}, None
     for l in launches:
@@ -213,7 +245,7 @@ def run_timeline(engine, batch, context, out_path):
         if prev_end is not None:
             a[3] += l.begin_us - prev_end
         prev_end = l.end_us
-    lines = [f"batch {batch}, context {context}: {len(launches)} launches, {total:.1f} us from the first entry to the last exit",
+    lines = [f"{title}: {len(launches)} launches, {total:.1f} us from the first entry to the last exit",
              "", "| kernel | CTAs | launches | run us (mean) | before its wait us (mean) | gap to the kernel before us (mean) | sum us |",
              "|---|---|---|---|---|---|---|"]
     for (name, blocks), a in sorted(agg.items(), key=lambda kv: -(kv[1][1] + kv[1][2] + kv[1][3])):
@@ -222,9 +254,7 @@ def run_timeline(engine, batch, context, out_path):
     lines += ["", Timeline.table(launches), ""]
     with open(out_path, "w") as f:
         f.write("\n".join(lines))
-    for r in reqs:
-        engine.release(r)
-    return len(launches), total
+    return total
 
 
 def run_e2e(engine, batch, steps, warmup, rng):
@@ -435,7 +465,7 @@ def main():
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling a small case; not a bench value)")
     ap.add_argument("--timeline", default=None, metavar="FILE",
-                    help="with FELLM_B200_TRACE=1: write the kernel timeline of one decode step (--batch requests, "
+                    help="with FELLM_B200_TRACE=1: write the kernel timeline of one decode step (--batch requests, or with --only prefill of one prefill step; "
                          "--context tokens each) to FILE and stop; not a bench value")
     ap.add_argument("--context", type=int, default=PROMPT)
     args = ap.parse_args()
@@ -477,6 +507,11 @@ def main():
     clocks = ClockSampler()
     clocks.start()
 
+    if args.timeline and args.only == "prefill":
+        n, us = run_prefill_timeline(engine, PREFILL_TOKENS, args.timeline, rng)
+        print(json.dumps({"timeline": args.timeline, "prefill_tokens": PREFILL_TOKENS, "launches": n, "us": round(us, 1)}))
+        clocks.stop()
+        return 0
     if args.timeline:
         n, us = run_timeline(engine, args.batch, args.context, args.timeline)
         print(json.dumps({"timeline": args.timeline, "batch": args.batch, "context": args.context, "launches": n, "us": round(us, 1)}))
