@@ -1,6 +1,6 @@
 """Logits of the schedules that the benchmark times, against the plain implementation: decode
-steps of 17 to 64 requests (other kernels than small steps: no fused norm, the convolution as a
-kernel of its own, the products of many rows, decode attention beyond one wave), the real layer
+steps of 17 to 97 requests (other kernels than small steps: the tcgen05 product of few rows with the
+norm handed on and, up to 64 rows, the convolution in its epilogue; decode attention beyond one wave), the real layer
 sizes of the 350M / 700M / 1.2B shapes in two-layer cuts, and mixed steps replayed from CUDA graphs
 whose layout differs from the one they were captured with."""
 import tempfile
